@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-weight linear layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--workload NAME] [--impl reference]
+
+Default workload (N = 1): the Q4_0 decode GEMV pair at Llama-7B FFN shapes, batch 1 — one step
+is y1 = W_up . x (K=4096 -> N=11008) followed by y2 = W_down . y1 (K=11008 -> N=4096), weights as
+raw GGUF Q4_0 blocks, f32 activations, f32 outputs.  Metric: HBM GB/s = algorithmic bytes
+(packed W + x + y of both launches, each counted once) / time.
+
+Timing: CUDA events on the launching stream, W >= 3 warm-up steps, a barrier and a device
+synchronise on both sides, max over ranks.  Successive steps use different weight copies (the
+rotation set is larger than twice the 126 MB L2), so every step streams its weights from HBM.
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+WORKLOADS = {
+    # name: (scheme name, [(k, n), ...] chained projections, activation dtype)
+    "q4_0_llama7b_ffn_gemv": ("q4_0", [(4096, 11008), (11008, 4096)], "f32"),
+    "q8_0_4096_gemv": ("q8_0", [(4096, 4096)], "f32"),
+    "q4_k_8b_up_gemv": ("q4_k", [(4096, 14336)], "bf16"),
+    "q6_k_8b_down_gemv": ("q6_k", [(14336, 4096)], "bf16"),
+}
+SCHEME_IDS = {"q4_k": 0, "q6_k": 2, "q4_0": 6, "q8_0": 7}
+GEOM = {"q4_k": (256, 144), "q6_k": (256, 210), "q4_0": (32, 18), "q8_0": (32, 34)}
+
+
+def packed_bytes(sch: str, k: int, n: int) -> int:
+    be, bb = GEOM[sch]
+    return k * n // be * bb
+
+
+def algorithmic_bytes(sch: str, layers, m: int, act_bytes: int) -> list[int]:
+    """Per launch: packed W + x + y (f32 y), each once."""
+    return [packed_bytes(sch, k, n) + m * k * act_bytes + m * n * 4 for k, n in layers]
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()          # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU baseline (the oracle = a port of the reference's CPU path; see oracle/rlxq_oracle.h)
+# --------------------------------------------------------------------------------------------
+def cpu_step(O, sch_id, layers, weights, x, threads):
+    cur = x
+    m = x.shape[0]
+    for (k, n), w in zip(layers, weights):
+        cur = O.matmul_bt_mt(cur, w, m, k, n, sch_id, threads=threads)
+    return cur
+
+
+def cpu_baseline(sch: str, layers, m: int, act: str, budget_s: float = 12.0) -> dict:
+    from oracle import oracle as O
+    sid = O.SCHEMES[sch]
+    weights = [O.fill_weights(sid, 1000 + i, k, n) for i, (k, n) in enumerate(layers)]
+    x = O.fill_normal(77, m * layers[0][0]).reshape(m, layers[0][0])
+    cores = os.cpu_count() or 1
+    total_bytes = sum(algorithmic_bytes(sch, layers, m, 4 if act == "f32" else 2))
+    out = {}
+    for label, threads in (("all_cores", cores), ("one_thread", 1)):
+        cpu_step(O, sid, layers, weights, x, threads)            # warm
+        t0 = time.perf_counter(); reps = 0
+        while True:
+            cpu_step(O, sid, layers, weights, x, threads); reps += 1
+            if time.perf_counter() - t0 > budget_s / 2 or reps >= 20:
+                break
+        dt = (time.perf_counter() - t0) / reps
+        out[label] = {"gbs": total_bytes / dt / 1e9, "ms_per_step": dt * 1e3, "threads": threads, "reps": reps}
+    return {"value": out["all_cores"]["gbs"], "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{out['all_cores']['reps']} full steps of the same workload (all {cores} host threads, rows split "
+                      f"across threads); single thread (what the reference runs): {out['one_thread']['gbs']:.3f} GB/s, "
+                      f"{out['one_thread']['ms_per_step']:.1f} ms/step",
+            "one_thread_value": out["one_thread"]["gbs"], "ms_per_step": out["all_cores"]["ms_per_step"]}
+
+
+def run_reference_arm(args, rank: int, world: int) -> None:
+    """The reference's CPU implementation of the path, timed on the host cores.  The reference is
+    Rust and cannot be built in this image, so this is the oracle port of it."""
+    if rank != 0:
+        return
+    sch, layers, act = WORKLOADS[args.workload]
+    from oracle import oracle as O
+    sid = O.SCHEMES[sch]
+    m = args.batch
+    weights = [O.fill_weights(sid, 1000 + i, k, n) for i, (k, n) in enumerate(layers)]
+    x = O.fill_normal(77, m * layers[0][0]).reshape(m, layers[0][0])
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_step(O, sid, layers, weights, x, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(O, sid, layers, weights, x, cores)
+    dt = (time.perf_counter() - t0) / args.steps
+    total_bytes = sum(algorithmic_bytes(sch, layers, m, 4 if act == "f32" else 2))
+    val = total_bytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, sch, layers, act, rotation=1),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} full steps, all {cores} host threads (rows split across threads)"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, sch, layers, act, rotation):
+    return {"workload": args.workload, "scheme": sch, "batch": args.batch,
+            "layers_k_to_n": [[k, n] for k, n in layers], "activations": act, "output": "f32",
+            "l2": f"rotating {rotation} distinct weight copies per rank "
+                  f"({rotation * sum(packed_bytes(sch, k, n) for k, n in layers) / 1e6:.0f} MB) > 2 x 126 MB L2"}
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--workload", default="q4_0_llama7b_ffn_gemv", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rlxq kernels have no CPU path")
+    import rlx_b200 as R
+    from oracle import oracle as O      # input generation and the cpu_baseline leg only
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    sch, layers, act = WORKLOADS[args.workload]
+    sid = SCHEME_IDS[sch]
+    m = args.batch
+    act_t = torch.float32 if act == "f32" else torch.bfloat16
+    act_bytes = 4 if act == "f32" else 2
+    per_launch = algorithmic_bytes(sch, layers, m, act_bytes)
+    step_bytes = sum(per_launch)
+    w_step = sum(packed_bytes(sch, k, n) for k, n in layers)
+    rotation = max(2, -(-2 * L2_BYTES // w_step) + 1)
+
+    # ---- inputs resident in HBM: `rotation` independent weight sets, one activation per rank
+    dev = torch.device("cuda", local_rank)
+    wsets = []
+    for r in range(rotation):
+        wsets.append([torch.from_numpy(O.fill_weights(sid, 1000 + 100 * rank + 10 * r + i, k, n)).to(dev)
+                      for i, (k, n) in enumerate(layers)])
+    x_host = O.fill_normal(77 + rank, m * layers[0][0]).reshape(m, layers[0][0])
+    x_dev = torch.from_numpy(x_host).to(dev).to(act_t)
+    outs = [torch.empty((m, n), dtype=torch.float32, device=dev) for _, n in layers]
+    ws_need = max(R.workspace_bytes(sid, m, k, n, 0 if act == "f32" or i else 1, 0) for i, (k, n) in enumerate(layers))
+    ws = torch.empty(max(ws_need, 16), dtype=torch.uint8, device=dev)
+
+    def step(i: int) -> None:
+        cur = x_dev
+        for li, (k, n) in enumerate(layers):
+            R.matmul(cur, wsets[i % rotation][li], sid, n, out=outs[li], workspace=ws)
+            cur = outs[li]
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    sync_all()
+    # The K timed steps are captured once into a CUDA graph (the reference's ExecMode::Graph does the
+    # same with its step loop) so that the device, not the Python launch path, sets the pace.
+    launches0 = R.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(args.warmup + i)
+    launches = R.launch_count() - launches0     # kernels per replay
+    graph.replay()                              # one untimed replay on top of the W warm-up steps
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    ev0.record()
+    graph.replay()
+    ev1.record()
+    sync_all()
+    R.device_status()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        lt = torch.tensor([launches], dtype=torch.int64, device=dev)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt.item())
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the Graph / Session API with pinned host buffers
+    g = R.Graph("bench")
+    xi = g.input("x", [m, layers[0][0]], R.DType.F32 if act == "f32" else R.DType.BF16)
+    cur, names = xi, []
+    for li, (k, n) in enumerate(layers):
+        p = g.param(f"w{li}", [packed_bytes(sch, k, n)])
+        names.append(f"w{li}")
+        cur = g.dequant_matmul_packed(cur, p, R.QuantScheme(sid), n)
+    g.set_outputs([cur])
+    compiled = []
+    sess = R.Session(R.Device.Cuda, index=local_rank, exec_mode="graph")
+    for r in range(rotation):
+        c = sess.compile(g)
+        for li, nm in enumerate(names):
+            c.set_param_typed(nm, wsets[r][li].cpu().numpy(), R.DType.U8)
+        compiled.append(c)
+    x_pin = torch.from_numpy(x_host).to(act_t).pin_memory()
+    y_pin = torch.empty((m, layers[-1][1]), dtype=torch.float32).pin_memory()
+    h2d, d2h = x_pin.numel() * x_pin.element_size(), y_pin.numel() * 4
+    dt_in = 0 if act == "f32" else 1
+
+    def e2e_step(i: int) -> None:
+        compiled[i % rotation].run_raw(["x"], [x_pin.data_ptr()], [h2d], [dt_in], y_pin.data_ptr(), d2h, 0)
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = world * step_bytes / (e2e_s / args.steps) / 1e9
+    # the e2e output must be the same numbers the resident path produced
+    step(args.warmup + args.steps - 1)
+    torch.cuda.synchronize()
+    e2e_matches = bool(torch.equal(outs[-1].cpu(), y_pin))
+
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        n_launch = len(layers) * args.steps
+        avg_launch_s = ms * 1e-3 / n_launch
+        bytes_per_launch = step_bytes / len(layers)
+        achieved = bytes_per_launch / avg_launch_s / 1e9
+        line = {
+            "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, sch, layers, act, rotation),
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s / args.steps * 1e3, "matches_resident_path": e2e_matches,
+                    "api": "Session(Device.Cuda).compile(graph).run, pinned host buffers, ExecMode::Graph"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "kernel": "gemv_staged_kernel", "bytes_per_launch": bytes_per_launch,
+                         "avg_launch_us": avg_launch_s * 1e6,
+                         "timing": "CUDA events over the timed region / launches (includes inter-launch gaps)",
+                         "traffic": None},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

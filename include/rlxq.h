@@ -1,0 +1,133 @@
+/*
+ * rlxq — B200 (sm_100a) kernels for RLX's GGUF quantized-weight linear layer, behind a C ABI.
+ *
+ * This is the boundary RLX's Rust `rlx-cuda` backend binds in place of its
+ * dequant-to-f32-scratch + cublasSgemm lowering of `Op::DequantMatMul` (GGUF schemes).
+ * Every entry point takes plain pointers and sizes; device pointers are "arena base +
+ * byte offset" exactly as the reference computes them (rlx-cuda/src/gguf_gpu.rs:105-111).
+ *
+ * Conventions
+ *  - Return value: 0 on success, a negative rlxq_status otherwise.  Nothing aborts.  The
+ *    reference panics on failure (`.expect(...)`, rlx-cuda/src/gguf_gpu.rs:99-103,132); a
+ *    Rust shim keeps that behaviour by `expect`-ing a zero status.
+ *  - Work is enqueued on the caller's stream; no entry point that takes a stream
+ *    synchronises, allocates, or reads device memory from the host, so they may be called
+ *    on a capturing stream (the reference captures its step loop in ExecMode::Graph,
+ *    rlx-cuda/src/backend.rs:4015-4037).
+ *  - `w_blocks` is the raw GGUF block stream of a weight W[n,k], row-major by blocks,
+ *    `n*k/block_elems*block_bytes` bytes, as uploaded by set_param_bytes
+ *    (rlx-cuda/src/backend.rs:3937-3945).  k must be a multiple of block_elems.
+ *  - Matrices: x is [m,k] row-major, y is [m,n] row-major: y = x . W^T
+ *    (rlx-cpu/src/gguf_matmul.rs:40-95).
+ */
+#ifndef RLXQ_H
+#define RLXQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define RLXQ_API __attribute__((visibility("default")))
+#else
+#define RLXQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* rlxq_stream_t; /* a cudaStream_t / CUstream */
+
+enum rlxq_status {
+    RLXQ_OK = 0,
+    RLXQ_E_SCHEME = -1,    /* unknown scheme id */
+    RLXQ_E_SHAPE = -2,     /* k not a multiple of the block size, zero-sized where not allowed, overflow */
+    RLXQ_E_NULL = -3,      /* null pointer for a non-empty buffer */
+    RLXQ_E_DTYPE = -4,     /* unknown activation / output dtype */
+    RLXQ_E_WORKSPACE = -5, /* workspace smaller than rlxq_workspace_bytes reports */
+    RLXQ_E_CUDA = -6,      /* a CUDA call failed; rlxq_last_error() has the text */
+    RLXQ_E_NCCL = -7,      /* an NCCL call failed */
+    RLXQ_E_TIMEOUT = -8,   /* a bounded device- or host-side wait ran out */
+    RLXQ_E_ALIGN = -9,     /* pointer alignment below what the entry point states */
+    RLXQ_E_ARG = -10,      /* other invalid argument (unknown option, bad rank, name not found) */
+    RLXQ_E_LIMIT = -11     /* size beyond a stated fixed maximum */
+};
+
+/* Scheme ids.  0 and 2 keep the values of gguf_scheme_id (rlx-cuda/src/gguf_host.rs:24-34);
+ * Q4_0 and Q8_0 have no id there (that function panics on them) and get 6 and 7. */
+enum rlxq_scheme { RLXQ_Q4_K = 0, RLXQ_Q6_K = 2, RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7 };
+
+/* Activation / output element types: the two the reference's typed I/O carries on this
+ * path (run_typed, rlx-runtime/src/backend.rs:2181-2206). */
+enum rlxq_dtype { RLXQ_F32 = 0, RLXQ_BF16 = 1 };
+
+/* Library version (major*10000 + minor*100 + patch). */
+RLXQ_API int rlxq_version(void);
+
+/* Static text for a status code. */
+RLXQ_API const char* rlxq_status_string(int status);
+
+/* Thread-local text of the most recent failure in this thread ("" if none). */
+RLXQ_API const char* rlxq_last_error(void);
+
+/* Replaces QuantScheme::gguf_block_size / gguf_block_bytes (rlx-ir/src/quant.rs:138-164). */
+RLXQ_API int rlxq_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32_t* block_bytes);
+
+/* Replaces slab_bytes_for (rlx-cuda/src/gguf_gpu.rs:29-33): bytes of a packed W[n,k]. */
+RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t* bytes);
+
+/* Replaces dequant_gguf_scratch_bytes (rlx-cuda/src/gguf_gpu.rs:35-59) at plan time: the
+ * scratch rlxq_matmul needs for this shape (0 for every GEMV shape; the reference reserves
+ * k*n*4 bytes). */
+RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
+                         uint32_t x_dtype, uint32_t y_dtype, size_t* bytes);
+
+/* Replaces the `dequant_gguf` kernel launch (rlx-cuda/src/gguf_gpu.rs:81-103;
+ * rlx-gpu-kernels/kernels/dequant_gguf.cu:46-244): decode n_elems weights to f32, bit-identical
+ * to rlx_gguf::dequant_{q8_0,q4_0,q4_k,q6_k} (rlx-gguf/src/lib.rs:600-633,974-1013,1070-1114).
+ * `out` must be 16-byte aligned; w_blocks 2-byte aligned. */
+RLXQ_API int rlxq_dequant_f32(rlxq_stream_t stream, uint32_t scheme, const void* w_blocks,
+                     uint64_t n_elems, float* out);
+
+/* Replaces run_dequant_matmul_gguf_gpu (rlx-cuda/src/gguf_gpu.rs:62-134) and the host fallback
+ * run_dequant_matmul_gguf (rlx-cuda/src/gguf_host.rs:90-128): y = x . W^T with the blocks
+ * decoded inside the kernel.  m <= 8 runs the streaming GEMV; larger m runs the tensor-core
+ * GEMM when the shape allows it (rlxq_workspace_bytes tells what it needs), else a tiled kernel.
+ * x: f32 or bf16 [m,k]; y: f32 or bf16 [m,n]; accumulation is f32.  x must be 16-byte aligned, y
+ * aligned to its element size, w_blocks to 2 bytes (16 bytes enables the bulk-copy fast paths).
+ * workspace: rlxq_workspace_bytes(...) bytes, 16-byte aligned, contents irrelevant on entry; it is
+ * private to the call while the kernels run (two calls in flight must not share it). */
+RLXQ_API int rlxq_matmul(rlxq_stream_t stream, uint32_t scheme,
+                const void* x, uint32_t x_dtype, const void* w_blocks,
+                void* y, uint32_t y_dtype, uint32_t m, uint32_t k, uint32_t n,
+                void* workspace, size_t workspace_bytes);
+
+/* Once per device, with that device current and outside any stream capture: allocates the
+ * library's per-device error word (4 bytes).  The reference creates its per-process device state
+ * in cuda_context() (rlx-cuda/src/device.rs:44-60).  rlxq_matmul calls it lazily if it was not. */
+RLXQ_API int rlxq_init_device(void);
+
+/* Synchronises the current device and reports whether any kernel of this library gave up on a
+ * bounded wait since the last call (RLXQ_E_TIMEOUT, *device_error = which wait).  Every spin in
+ * the kernels has an iteration limit, so a lost copy or a missing signal ends as this error, not
+ * as a hung GPU.  Not capture-safe (it synchronises); the reference's equivalent is the
+ * stream.synchronize() + panic in CudaExecutable::run (rlx-cuda/src/backend.rs:6675-6693). */
+RLXQ_API int rlxq_device_status(int* device_error);
+
+/* Number of kernels this library has launched in this process (all threads). */
+RLXQ_API uint64_t rlxq_launch_count(void);
+
+/* Tuning / dispatch override, the counterpart of the reference's RLX_KERNEL_DISPATCH and
+ * RLX_CUDA_* environment keys (rlx-ir/src/env.rs:57-104).  Keys:
+ *   "gemv_kernel": 0 = automatic, 1 = force the generic warp-per-row kernel,
+ *                  2 = force the staged tensor-core GEMV (error if the shape does not allow it)
+ *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
+ *   "gemv_kslices": 0 = automatic, n > 0 = split k over n CTAs per row tile in the staged GEMV
+ * Returns RLXQ_E_ARG for an unknown key. */
+RLXQ_API int rlxq_set_option(const char* key, int64_t value);
+RLXQ_API int rlxq_get_option(const char* key, int64_t* value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLXQ_H */

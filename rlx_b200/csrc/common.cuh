@@ -1,0 +1,62 @@
+// Shared host-side plumbing for the rlxq library: status codes, error text, launch counting.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/rlxq.h"
+
+namespace rlxq {
+
+// Per-thread failure text returned by rlxq_last_error().
+char* last_error_buf();
+int fail(int status, const char* fmt, ...);
+
+// Every kernel launch made by the library goes through this counter.
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(uint64_t n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Options set through rlxq_set_option.
+struct Options {
+    std::atomic<int64_t> gemv_kernel{0};
+    std::atomic<int64_t> gemm_kernel{0};
+    std::atomic<int64_t> gemv_kslices{0};
+};
+Options& options();
+
+struct Geometry { uint32_t elems, bytes; };
+inline bool geometry(uint32_t scheme, Geometry* g) {
+    switch (scheme) {
+        case RLXQ_Q4_K: *g = {256, 144}; return true;
+        case RLXQ_Q6_K: *g = {256, 210}; return true;
+        case RLXQ_Q4_0: *g = {32, 18}; return true;
+        case RLXQ_Q8_0: *g = {32, 34}; return true;
+        default: return false;
+    }
+}
+
+// Checks the launch itself (not the execution): never synchronises.
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(RLXQ_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return RLXQ_OK;
+}
+
+#define RLXQ_CUDA_TRY(expr)                                                              \
+    do {                                                                                 \
+        cudaError_t e__ = (expr);                                                        \
+        if (e__ != cudaSuccess)                                                          \
+            return ::rlxq::fail(RLXQ_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+// Cached per-device properties (SM count), looked up without synchronising.
+int sm_count();
+
+}  // namespace rlxq

@@ -1,0 +1,40 @@
+// Kernel selection for rlxq_matmul: the counterpart of the reference's
+// `use_gpu = dequant_scratch_off > 0 && blas.is_some()` branch and host fallback
+// (rlx-cuda/src/backend.rs:5366-5405).  There is no host fallback here: every shape runs on
+// the GPU, through the fastest kernel that supports it.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace rlxq {
+
+size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t x_dtype,
+                              uint32_t y_dtype) {
+    (void)x_dtype; (void)y_dtype;
+    if (m == 0 || n == 0 || k == 0) return 0;
+    if (m <= 8) return staged_workspace_bytes(scheme, m, k, n);
+    return 0;
+}
+
+int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    if (k == 0) {
+        // empty reduction: the reference zero-fills the output (rlx-cpu/src/gguf_matmul.rs:52)
+        RLXQ_CUDA_TRY(cudaMemsetAsync(y, 0, (size_t)m * n * (ybf ? 2 : 4), stream));
+        return RLXQ_OK;
+    }
+    if (!x || !w) return fail(RLXQ_E_NULL, "null input buffer");
+    if ((uintptr_t)w & 1u) return fail(RLXQ_E_ALIGN, "w_blocks must be 2-byte aligned");
+    if ((uintptr_t)x & 15u) return fail(RLXQ_E_ALIGN, "x must be 16-byte aligned");
+    if ((uintptr_t)y & (ybf ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
+    if (m <= 8) {
+        const int64_t force = options().gemv_kernel.load();
+        const bool can = staged_supported(scheme, m, k, n, w, x, xbf);
+        if (force == 2 && !can)
+            return fail(RLXQ_E_SHAPE, "staged GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
+        if (can && force != 1) return launch_gemv_staged(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
+    }
+    return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
+}
+
+}  // namespace rlxq

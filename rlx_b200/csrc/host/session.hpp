@@ -1,0 +1,90 @@
+// Host-side mirror of the reference's Graph / Session / CompiledGraph for the quantized-matmul
+// path (C++; the reference's are Rust: rlx-ir/src/graph.rs, rlx-runtime/src/session.rs:42-87,
+// rlx-runtime/src/compiled.rs:55-63,192-205, rlx-cuda/src/backend.rs:2327-2358,3923-3994).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+namespace rlxq {
+
+enum class OpKind { Input, Param, DequantMatMul, SwigluMul };
+
+struct Node {
+    OpKind op;
+    std::string name;      // inputs and params only
+    uint32_t rows = 0;     // m
+    uint32_t cols = 0;     // k for inputs, n for compute nodes
+    uint32_t dtype = 0;    // RLXQ_F32 / RLXQ_BF16 (element type of the node's value)
+    uint32_t scheme = 0;   // DequantMatMul
+    uint64_t bytes = 0;    // size of the node's device slot
+    int in0 = -1, in1 = -1;
+};
+
+class Graph {
+public:
+    explicit Graph(std::string name) : name_(std::move(name)) {}
+    int input(const std::string& name, uint32_t m, uint32_t k, uint32_t dtype);
+    int param(const std::string& name, uint64_t bytes);                    // Shape([bytes], U8)
+    int dequant_matmul(int x, int w, uint32_t scheme, uint32_t n, uint32_t out_dtype);
+    int swiglu_mul(int gate, int up);
+    int set_output(int node);
+    const std::vector<Node>& nodes() const { return nodes_; }
+    int output() const { return output_; }
+    const std::string& name() const { return name_; }
+
+private:
+    std::string name_;
+    std::vector<Node> nodes_;
+    int output_ = -1;
+};
+
+enum class ExecMode { Stream = 0, Graph = 1 };
+
+class CompiledGraph {
+public:
+    ~CompiledGraph();
+    CompiledGraph(const CompiledGraph&) = delete;
+    CompiledGraph& operator=(const CompiledGraph&) = delete;
+
+    int set_param_typed(const std::string& name, const void* data, uint64_t len);
+    // inputs: host pointers to each named input in its declared dtype; out: host pointer
+    int run_typed(uint32_t n_inputs, const char* const* names, const void* const* data,
+                  const uint64_t* bytes, const uint32_t* dtypes, void* out, uint64_t out_bytes,
+                  uint32_t out_dtype);
+    uint64_t arena_bytes() const { return arena_bytes_; }
+
+private:
+    friend class Session;
+    CompiledGraph() = default;
+    int enqueue_steps(cudaStream_t s);
+
+    int device_ = 0;
+    ExecMode mode_ = ExecMode::Stream;
+    std::vector<Node> nodes_;
+    std::vector<uint64_t> offsets_;   // arena byte offset of every node's slot
+    int output_ = -1;
+    uint8_t* arena_ = nullptr;
+    uint64_t arena_bytes_ = 0;
+    uint64_t ws_off_ = 0, ws_bytes_ = 0;
+    cudaStream_t stream_ = nullptr;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    void* pinned_ = nullptr;          // staging for pageable host buffers
+    uint64_t pinned_bytes_ = 0;
+};
+
+class Session {
+public:
+    explicit Session(int device) : device_(device) {}   // Session::new(Device::Cuda)
+    int compile(const Graph& g, ExecMode mode, CompiledGraph** out);
+
+private:
+    int device_;
+};
+
+int launch_swiglu_mul(cudaStream_t stream, const float* gate, const float* up, float* out, uint64_t n);
+
+}  // namespace rlxq

@@ -1,0 +1,28 @@
+// Internal launch entry points shared between the translation units of the library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace rlxq {
+
+int launch_dequant_f32(cudaStream_t stream, uint32_t scheme, const uint8_t* w, uint64_t n_elems, float* out);
+
+int launch_matmul_generic(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
+                          void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n);
+
+// Staged tensor-core GEMV (m <= 8).
+bool staged_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf);
+size_t staged_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
+int launch_gemv_staged(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
+                       void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+int staged_device_error(int* value);   // synchronises the device
+int staged_prepare_device();           // allocates the per-device error word (call outside capture)
+
+// Shape-based selection used by rlxq_matmul / rlxq_workspace_bytes.
+size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t x_dtype, uint32_t y_dtype);
+int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+
+}  // namespace rlxq

@@ -1,0 +1,215 @@
+"""GPU parity of rlxq_matmul (through the C ABI) against the CPU oracle.
+
+Tolerance (stated by the path's specification): |y - y_ref| <= 1e-3 * ||x_row|| * ||w_row|| per
+element with f32 accumulation.  The kernels are far inside it; the tests also pin the much
+tighter bounds the two kernels are designed to: 2e-5 for the f32 generic kernel and 3e-4 for the
+staged GEMV (whose only extra rounding is x -> fp16, relative 2^-12).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import rlx_b200 as R
+from oracle import oracle as O
+from tests.helpers import assert_within_tolerance, bound, make_case, reference
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(autouse=True)
+def _reset_options():
+    yield
+    R.set_option("gemv_kernel", 0)
+    R.set_option("gemm_kernel", 0)
+    R.set_option("gemv_kslices", 0)
+
+
+def _run(scheme, w, x, n, x_bf16=False, y_bf16=False):
+    import torch
+    wd = torch.from_numpy(w).cuda()
+    xd = torch.from_numpy(x).cuda()
+    if x_bf16:
+        xd = xd.to(torch.bfloat16)
+    y = R.matmul(xd, wd, scheme, n, out_dtype=torch.bfloat16 if y_bf16 else torch.float32)
+    R.device_status()
+    return y.float().cpu().numpy()
+
+
+GENERIC_SHAPES = [("q8_0", 1, 32, 1), ("q8_0", 3, 96, 7), ("q4_0", 1, 32, 5), ("q4_0", 8, 512, 17),
+                  ("q4_k", 1, 256, 1), ("q4_k", 5, 256, 33), ("q6_k", 2, 512, 9), ("q6_k", 1, 256, 3),
+                  ("q4_0", 20, 160, 11), ("q8_0", 9, 64, 4)]
+
+
+@pytest.mark.parametrize("sch,m,k,n", GENERIC_SHAPES)
+def test_generic_kernel_matches_oracle(sch, m, k, n):
+    s = O.SCHEMES[sch]
+    R.set_option("gemv_kernel", 1)
+    w, x = make_case(s, m, k, n, seed=50 + m + n)
+    y = _run(s, w, x, n)
+    ref = reference(s, w, x, n, serial=True)
+    assert_within_tolerance(y, ref, bound(s, w, x, n), tol=2e-5, what=f"generic {sch} {m}x{k}x{n}")
+
+
+def test_committed_fixtures_both_kernels():
+    z = np.load(os.path.join(GOLDEN, "seeded_small.npz"))
+    for nm in sorted({k.split(".")[0] for k in z.files}):
+        s, m, k, n, _ = (int(v) for v in z[f"{nm}.meta"])
+        w, x, ref = z[f"{nm}.w"], z[f"{nm}.x"], z[f"{nm}.y"]
+        for kern in (1, 0):
+            R.set_option("gemv_kernel", kern)
+            y = _run(s, w, x, n)
+            assert_within_tolerance(y, ref, bound(s, w, x, n), tol=3e-4, what=f"{nm} kernel={kern}")
+
+
+def test_reference_known_answer_matmuls():
+    with open(os.path.join(GOLDEN, "known_answers.json")) as f:
+        cases = [c for c in json.load(f) if "matmul" in c]
+    assert len(cases) == 2
+    for case in cases:
+        s = O.SCHEMES[case["scheme"]]
+        mm = case["matmul"]
+        w = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8).copy()
+        x = np.ones((mm["m"], mm["k"]), np.float32)
+        for kern in (1, 0):
+            R.set_option("gemv_kernel", kern)
+            y = _run(s, w, x, mm["n"]).ravel()
+            exp = np.array(mm["expected"], np.float32)
+            if "rel_tol" in mm:
+                assert np.all(np.abs(y - exp) / np.maximum(np.abs(exp), 1.0) < mm["rel_tol"]), case["name"]
+            else:
+                assert np.all(np.abs(y - exp) < mm["abs_tol"]), case["name"]
+
+
+def test_layout_regression_shape_distinct_rows():
+    """The n=4, m=2, k=256 shape of rlx-runtime/tests/dequant_matmul_gguf.rs:176-241: rows of W
+    differ, so an [n,k] / [k,n] mix-up (the reference's CUDA path has one) cannot pass."""
+    for sch in ("q8_0", "q4_k"):
+        s = O.SCHEMES[sch]
+        w = O.fill_weights(s, 77, 256, 4)
+        x = (0.01 * (np.arange(512, dtype=np.float32) + 1.0)).reshape(2, 256)
+        ref = reference(s, w, x, 4, serial=True)
+        for kern in (1, 0):
+            R.set_option("gemv_kernel", kern)
+            y = _run(s, w, x, 4)
+            rel = np.abs(y - ref) / np.maximum(np.abs(ref), 1.0)
+            assert rel.max() < 1e-4, (sch, kern, rel.max())
+
+
+STAGED_SHAPES = [
+    ("q4_0", 1, 256, 16), ("q4_0", 1, 256, 24), ("q4_0", 2, 1024, 17), ("q4_0", 8, 2304, 50), ("q4_0", 5, 4096, 130),
+    ("q8_0", 1, 256, 16), ("q8_0", 3, 768, 33), ("q8_0", 8, 1280, 64), ("q8_0", 1, 4096, 100),
+    ("q4_k", 1, 256, 1), ("q4_k", 1, 512, 19), ("q4_k", 4, 1280, 40), ("q4_k", 8, 2048, 48), ("q4_k", 7, 4096, 31),
+    ("q6_k", 1, 2048, 9), ("q6_k", 2, 2048, 16), ("q6_k", 8, 4096, 37), ("q6_k", 3, 6144, 20),
+]
+
+
+@pytest.mark.parametrize("sch,m,k,n", STAGED_SHAPES)
+@pytest.mark.parametrize("x_bf16", [False, True])
+def test_staged_gemv_matches_oracle(sch, m, k, n, x_bf16):
+    s = O.SCHEMES[sch]
+    R.set_option("gemv_kernel", 2)
+    w, x = make_case(s, m, k, n, seed=300 + m + n, x_bf16=x_bf16)
+    y = _run(s, w, x, n, x_bf16=x_bf16)
+    ref = reference(s, w, x, n)
+    assert_within_tolerance(y, ref, bound(s, w, x, n), tol=3e-4, what=f"staged {sch} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("sch,k", [("q4_0", 2048), ("q8_0", 1536), ("q4_k", 2560), ("q6_k", 8192)])
+@pytest.mark.parametrize("ksl", [1, 2, 3])
+def test_staged_gemv_split_k_is_deterministic_and_correct(sch, k, ksl):
+    s = O.SCHEMES[sch]
+    R.set_option("gemv_kernel", 2)
+    R.set_option("gemv_kslices", ksl)
+    m, n = 3, 77
+    w, x = make_case(s, m, k, n, seed=900 + ksl)
+    y1 = _run(s, w, x, n)
+    y2 = _run(s, w, x, n)
+    assert np.array_equal(y1, y2)   # fixed reduction order
+    assert_within_tolerance(y1, reference(s, w, x, n), bound(s, w, x, n), tol=3e-4, what=f"{sch} ksl={ksl}")
+
+
+def test_bf16_output_is_rne_of_f32_output():
+    import torch
+    s = O.Q4_0
+    w, x = make_case(s, 4, 1024, 64, seed=5)
+    yf = _run(s, w, x, 64)
+    yb = _run(s, w, x, 64, y_bf16=True)
+    exp = torch.from_numpy(yf).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(yb, exp)
+
+
+def test_activation_range_is_rescaled():
+    """Rows far outside fp16's range (1e-30 .. 1e30) must come out as accurately as O(1) rows."""
+    s = O.Q8_0
+    w, x = make_case(s, 4, 1024, 48, seed=6)
+    x = (x * np.array([[1e-30], [1.0], [1e20], [3e4]], np.float32)).astype(np.float32)
+    R.set_option("gemv_kernel", 2)
+    y = _run(s, w, x, 48)
+    assert_within_tolerance(y, reference(s, w, x, 48), bound(s, w, x, 48), tol=3e-4, what="range")
+
+
+def test_one_hot_activation_reproduces_the_weight_column():
+    """Size-independent property: x = e_p gives y[j] = W[j,p], checked against the bit-exact
+    decoder at a full benchmark size (Q4_0 11008 -> 4096)."""
+    import torch
+    s, k, n = O.Q4_0, 11008, 4096
+    w = O.fill_weights(s, 31, k, n)
+    wd = torch.from_numpy(w).cuda()
+    deq = R.dequant_f32(wd, s, k * n).view(n, k)
+    for p in (0, 17, 5000, 11007):
+        x = torch.zeros((1, k), dtype=torch.float32, device="cuda")
+        x[0, p] = 1.0
+        y = R.matmul(x, wd, s, n)
+        assert torch.equal(y[0], deq[:, p]), p
+
+
+def test_zero_activation_gives_zero():
+    import torch
+    for s, k in ((O.Q4_K, 4096), (O.Q6_K, 4096)):
+        wd = torch.from_numpy(O.fill_weights(s, 3, k, 256)).cuda()
+        y = R.matmul(torch.zeros((2, k), device="cuda"), wd, s, 256)
+        assert torch.count_nonzero(y).item() == 0
+
+
+FULL = [("q8_0", 1, 4096, 4096, False), ("q4_0", 1, 4096, 11008, False), ("q4_0", 4, 4096, 11008, False),
+        ("q4_0", 8, 4096, 11008, False), ("q4_0", 1, 11008, 4096, False), ("q4_0", 4, 11008, 4096, False),
+        ("q4_0", 8, 11008, 4096, False), ("q4_k", 1, 4096, 14336, True), ("q6_k", 1, 14336, 4096, True)]
+
+
+@pytest.mark.parametrize("sch,m,k,n,x_bf16", FULL)
+def test_benchmark_configurations_full_size(sch, m, k, n, x_bf16):
+    """Configurations 0, 1 and the decode half of 2 at their real sizes, every output checked."""
+    s = O.SCHEMES[sch]
+    w, x = make_case(s, m, k, n, seed=1, x_bf16=x_bf16)
+    y = _run(s, w, x, n, x_bf16=x_bf16)
+    worst = assert_within_tolerance(y, reference(s, w, x, n), bound(s, w, x, n), what=f"cfg {sch} m={m}")
+    assert worst < 3e-4
+
+
+def test_matmul_edge_cases():
+    import torch
+    s = O.Q4_0
+    wd = torch.from_numpy(O.fill_weights(s, 1, 64, 8)).cuda()
+    # m = 0 and n = 0 are empty outputs, not errors
+    assert R.matmul(torch.zeros((0, 64), device="cuda"), wd, s, 8).shape == (0, 8)
+    # k not a multiple of the block
+    with pytest.raises(R.RlxqError) as e:
+        R.matmul(torch.zeros((1, 48), device="cuda"), wd, s, 8)
+    assert e.value.status == -2
+    # forcing the staged kernel on a shape it cannot take is an error, not a silent fallback
+    R.set_option("gemv_kernel", 2)
+    with pytest.raises(R.RlxqError):
+        R.matmul(torch.zeros((1, 64), device="cuda"), wd, s, 8)
+
+
+def test_launch_counter_counts_kernels():
+    import torch
+    s = O.Q8_0
+    wd = torch.from_numpy(O.fill_weights(s, 1, 256, 16)).cuda()
+    x = torch.zeros((1, 256), device="cuda")
+    before = R.launch_count()
+    R.matmul(x, wd, s, 16)
+    assert R.launch_count() == before + 1
