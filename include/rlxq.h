@@ -77,8 +77,8 @@ RLXQ_API int rlxq_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32
 RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t* bytes);
 
 /* Replaces dequant_gguf_scratch_bytes (rlx-cuda/src/gguf_gpu.rs:35-59) at plan time: the
- * scratch rlxq_matmul needs for this shape (0 for every GEMV shape; the reference reserves
- * k*n*4 bytes). */
+ * scratch rlxq_matmul needs for this shape: 0 unless the GEMV splits k over several CTAs, and
+ * then a few partial output rows (ksl*m*n*4 bytes); the reference reserves k*n*4 bytes. */
 RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
                          uint32_t x_dtype, uint32_t y_dtype, size_t* bytes);
 
@@ -119,10 +119,15 @@ RLXQ_API uint64_t rlxq_launch_count(void);
 
 /* Tuning / dispatch override, the counterpart of the reference's RLX_KERNEL_DISPATCH and
  * RLX_CUDA_* environment keys (rlx-ir/src/env.rs:57-104).  Keys:
- *   "gemv_kernel": 0 = automatic, 1 = force the generic warp-per-row kernel,
- *                  2 = force the staged tensor-core GEMV (error if the shape does not allow it)
+ *   "gemv_kernel": 0 = automatic (integer kernel for m <= 2, tensor-mode kernel for m <= 8),
+ *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
+ *                  GEMV, 3 = force the staged integer GEMV (2, 3: error if the shape does not allow it)
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
  *   "gemv_kslices": 0 = automatic, n > 0 = split k over n CTAs per row tile in the staged GEMV
+ *   "pdl": 1 (default) = launch the GEMV kernels with programmatic stream serialization so a
+ *          kernel's weight prefetch overlaps the tail of its predecessor, 0 = plain launches
+ *   "gemv_debug": profiling aid, 0 in production; bit 0 skips the arithmetic of the staged GEMVs,
+ *                 bit 1 the activation staging (outputs are then meaningless)
  * Returns RLXQ_E_ARG for an unknown key. */
 RLXQ_API int rlxq_set_option(const char* key, int64_t value);
 RLXQ_API int rlxq_get_option(const char* key, int64_t* value);

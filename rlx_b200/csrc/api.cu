@@ -144,6 +144,8 @@ int rlxq_set_option(const char* key, int64_t value) {
     if (!strcmp(key, "gemv_kernel")) { options().gemv_kernel = value; return RLXQ_OK; }
     if (!strcmp(key, "gemm_kernel")) { options().gemm_kernel = value; return RLXQ_OK; }
     if (!strcmp(key, "gemv_kslices")) { options().gemv_kslices = value; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_debug")) { options().gemv_debug = value; return RLXQ_OK; }
+    if (!strcmp(key, "pdl")) { options().pdl = value; return RLXQ_OK; }
     return fail(RLXQ_E_ARG, "unknown option '%s'", key);
 }
 
@@ -152,6 +154,8 @@ int rlxq_get_option(const char* key, int64_t* value) {
     if (!strcmp(key, "gemv_kernel")) { *value = options().gemv_kernel; return RLXQ_OK; }
     if (!strcmp(key, "gemm_kernel")) { *value = options().gemm_kernel; return RLXQ_OK; }
     if (!strcmp(key, "gemv_kslices")) { *value = options().gemv_kslices; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_debug")) { *value = options().gemv_debug; return RLXQ_OK; }
+    if (!strcmp(key, "pdl")) { *value = options().pdl; return RLXQ_OK; }
     return fail(RLXQ_E_ARG, "unknown option '%s'", key);
 }
 

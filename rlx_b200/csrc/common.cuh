@@ -25,6 +25,8 @@ struct Options {
     std::atomic<int64_t> gemv_kernel{0};
     std::atomic<int64_t> gemm_kernel{0};
     std::atomic<int64_t> gemv_kslices{0};
+    std::atomic<int64_t> gemv_debug{0};
+    std::atomic<int64_t> pdl{1};
 };
 Options& options();
 

@@ -1,0 +1,761 @@
+// Streaming decode GEMV for batch 1-2: integer dot products (dp4a) on raw block quants.
+//
+// Two kernels per call.
+//
+// 1. quantise_x_kernel (tiny): the activations are quantised once to two int8 limbs per value,
+//    X = round(x / s_b) in [-16256, 16256] = 128*h + l, one f32 scale s_b per 32 values, with the
+//    integer block sums the formats' offsets need, into the call's workspace.  It also clears
+//    the tile counters of the main kernel.
+//
+// 2. gemv_int_kernel (the streaming kernel).  Persistent CTAs, two per SM.  All CTAs together
+//    walk one global list of work items, (16-row weight tile, 2048-weight chunk), split into
+//    equal contiguous ranges ("stream-K"), so every SM streams the same number of bytes whatever
+//    n and k are.  Per CTA a producer warp keeps a ring of shared-memory stages full with 1-D
+//    bulk async copies (cp.async.bulk + mbarrier complete_tx; one copy = one row's 16-byte-
+//    aligned run of whole blocks; the ring takes all the shared memory the CTA has, about 90 KB
+//    in flight per CTA) and eight consumer warps take one 256-weight unit of the stage each.
+//    The quantised activations arrive by bulk copy too.  Weights are never converted: four 4-bit
+//    (or 8-, 6-bit) quants are masked into one register and multiplied against four activations
+//    by one dp4a, exact in int32; one int->float conversion and one FMA per 32-weight block apply
+//    d_block * s_block (f32 from there on).  A thread owns (tile row, half of a unit): the two
+//    halves of a warp read the same activation words (broadcast) and contiguous, 8-byte-aligned
+//    weight words.  A tile whose chunks fall into more than one CTA's range is finished by the
+//    CTA that arrives last at the tile's counter: it adds the partial tiles in chunk order, so the
+//    result does not depend on timing and no CTA waits for another.
+//
+// Both kernels use programmatic dependent launch: the streaming kernel is made resident while
+// its predecessor drains and prefetches its first weight stages (weights are immutable) before
+// griddepcontrol.wait, so back-to-back launches do not pay the pipeline fill each time.
+//
+// Error: the activation quantisation only; |y - y_exact| <= 2^-15 * sqrt(32) * |x| * |w_row|
+// = 1.7e-4 * |x| * |w_row| in the worst case, about 1e-6 typically, plus f32 accumulation over
+// blocks.  (The legacy HMMA pipe of this GPU sustains one m16n8k16 per 32 cycles per sub-core,
+// which alone would cap a tensor-mode Q4_0 GEMV below the HBM roofline; dp4a does not.)
+//
+// Replaces, for m <= 2, the reference's dequantise-everything + cublasSgemm
+// (rlx-cuda/src/gguf_gpu.rs:62-134).
+#include "common.cuh"
+#include "decode.cuh"
+#include "kernels.h"
+#include "staged_common.cuh"
+#include "tensormap.cuh"
+
+namespace rlxq {
+
+constexpr uint32_t kIntWarps = 8;                      // consumer warps
+constexpr uint32_t kIntThreads = (kIntWarps + 2) * 32; // + one producer warp + one finisher warp
+constexpr uint32_t kIntRB = 4;                         // ring of reduction buffers between consumers and finisher
+constexpr uint32_t kIntCU = 8;                         // 256-weight units per stage = one per warp
+
+// A stage is NB boxes of 16 rows x UB units, each box fetched by ONE 2-D TMA request (a request
+// per row costs about 250 cycles of issue time each and caps the stream near 3 TB/s; one box per
+// request does not).  A box row is UB units plus 16 bytes (read from the next units, or zero past
+// the row end) so that rows do not all start on the same shared-memory bank; Q6_K's 1680-byte
+// rows already do not.  TMA boxes are at most 256 eight-byte elements wide, hence two for Q8_0.
+template <uint32_t SCHEME> struct IntBox {
+    static constexpr uint32_t NB = (SCHEME == RLXQ_Q8_0) ? 2u : 1u;
+    static constexpr uint32_t UB = kIntCU / NB;                               // units per box
+    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : 16u);
+    static constexpr uint32_t BOX_BYTES = 16 * ROW;
+    static constexpr uint32_t STAGE_BYTES = NB * BOX_BYTES;
+};
+
+struct IntParams {
+    CUtensorMap wmap;      // W as [n rows][row_bytes / 8] eight-byte elements, box = 16 rows x IntBox::ROW
+    const uint8_t* w;
+    void* y;
+    const uint8_t* xq;     // workspace: per row [h: k][l: k][s_b: k/32 f32][sums: k/SUB i32]
+    float* partial;        // [ntiles][slots][MM][16]
+    uint32_t* counters;    // [ntiles] chunks finished per tile
+    int* err;
+    uint32_t k, n, y_bf16;
+    uint32_t use_red;      // shared tiles have exactly two contributors: add them into zeroed f32 y
+    uint32_t row_bytes, ntiles, nchunks, total_chunks, slots;
+    uint32_t nstages;
+    uint32_t xq_row_bytes; // bytes of one row of xq
+    uint32_t off_stage, off_red, off_bar;
+    uint32_t debug;
+};
+
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Per-thread view for the integer kernel.
+struct QLane {
+    const uint8_t* row;    // this thread's tile row inside the current stage
+    const int8_t* xh;      // high limbs of activation row 0
+    const int8_t* xl;      // low limbs of activation row 0
+    const float* sb;       // [k/32]  scale of each 32-value activation block
+    const int* sx;         // [k/SUB] offset-premultiplied integer block sums (format specific)
+    uint32_t xstride;      // bytes between activation rows (all four arrays of a row move together)
+    uint32_t xstride4;     // the same in 4-byte words
+    uint32_t half;         // which half of a 256-weight unit this thread handles
+};
+
+__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint2 lds64(const void* p) { return *reinterpret_cast<const uint2*>(p); }
+
+// Sum over 32 weights of q * X for one activation row: q words against the two limb planes.
+template <int NW>
+__device__ __forceinline__ int dot_limbs(const uint32_t (&q)[NW], const int8_t* xh, const int8_t* xl,
+                                         uint32_t k, int init_low) {
+    int ah = 0, al = init_low;
+#pragma unroll
+    for (int i = 0; i < NW; i += 4) {
+        const uint4 h = lds128(xh + k + 4 * i), l = lds128(xl + k + 4 * i);
+        ah = __dp4a((int)q[i], (int)h.x, ah);         al = __dp4a((int)q[i], (int)l.x, al);
+        ah = __dp4a((int)q[i + 1], (int)h.y, ah);     al = __dp4a((int)q[i + 1], (int)l.y, al);
+        ah = __dp4a((int)q[i + 2], (int)h.z, ah);     al = __dp4a((int)q[i + 2], (int)l.z, al);
+        ah = __dp4a((int)q[i + 3], (int)h.w, ah);     al = __dp4a((int)q[i + 3], (int)l.w, al);
+    }
+    return ah * 128 + al;
+}
+
+template <uint32_t SCHEME, int MM> struct QUnit;
+
+// ---- Q4_0: unit = 8 blocks of 18 bytes; a thread takes 4 consecutive blocks (72 bytes) ----
+template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
+        const uint8_t* p = L.row + u * 144 + 72 * L.half;
+        uint32_t w[18];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) { const uint2 v = lds64(p + 8 * i); w[2 * i] = v.x; w[2 * i + 1] = v.y; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int base = (j >> 1) * 9;            // two blocks = 36 bytes = 9 words
+            uint32_t qs[4], dbits;
+            if ((j & 1) == 0) {                       // block starts on a word: d | qs shifted by 2 bytes
+                dbits = w[base] & 0xFFFFu;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qs[i] = __funnelshift_r(w[base + i], w[base + i + 1], 16);
+            } else {                                  // block starts 2 bytes into word base+4
+                dbits = w[base + 4] >> 16;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qs[i] = w[base + 5 + i];
+            }
+            // low nibbles are weights 0..15 of the block, high nibbles 16..31
+            uint32_t q[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { q[i] = qs[i] & 0x0F0F0F0Fu; q[4 + i] = (qs[i] >> 4) & 0x0F0F0F0Fu; }
+            const float d = f16_bits_to_f32(dbits);
+            const uint32_t blk = (kb >> 5) + 4 * L.half + j;
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+                // sx holds -8 * sum(X): the format's offset
+                const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, L.sx[m * L.xstride4 + blk]);
+                tot[m] = fmaf(d * L.sb[m * L.xstride4 + blk], (float)c, tot[m]);
+            }
+        }
+    }
+};
+
+// ---- Q8_0: unit = 8 blocks of 34 bytes; a thread takes 4 consecutive blocks (136 bytes) ----
+template <int MM> struct QUnit<RLXQ_Q8_0, MM> {
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
+        const uint8_t* p = L.row + u * 272 + 136 * L.half;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {              // two blocks = 68 bytes = 17 words at a time
+            uint32_t w[18];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) { const uint2 v = lds64(p + 68 * jj - 4 * jj + 8 * i); w[2 * i] = v.x; w[2 * i + 1] = v.y; }
+            // jj = 0 reads bytes [0, 72): words 0..17 hold blocks 0 and 1 (17 words) plus one spare.
+            // jj = 1 reads bytes [64, 136): block 2 starts at byte 68, i.e. at word 1 of this window.
+            const int o = jj;                          // word offset of the block pair inside w[]
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint32_t q[8], dbits;
+                if (j == 0) {
+                    dbits = w[o] & 0xFFFFu;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[o + i], w[o + i + 1], 16);
+                } else {
+                    dbits = w[o + 8] >> 16;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) q[i] = w[o + 9 + i];
+                }
+                const float d = f16_bits_to_f32(dbits);
+                const uint32_t blk = (kb >> 5) + 4 * L.half + 2 * jj + j;
+#pragma unroll
+                for (int m = 0; m < MM; ++m) {
+                    const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, 0);
+                    tot[m] = fmaf(d * L.sb[m * L.xstride4 + blk], (float)c, tot[m]);
+                }
+            }
+        }
+    }
+};
+
+// ---- Q4_K: unit = one 144-byte super-block; a thread takes sub-blocks 4*half .. 4*half+3 ----
+template <int MM> struct QUnit<RLXQ_Q4_K, MM> {
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
+        const uint8_t* p = L.row + u * 144;
+        const uint4 hd = lds128(p);                   // d, dmin, 12 scale bytes
+        const float d = f16_bits_to_f32(hd.x & 0xFFFFu), dmin = f16_bits_to_f32(hd.x >> 16);
+        uint32_t scb, mnb;                            // four 6-bit scales / mins, one per byte
+        if (L.half == 0) {
+            scb = hd.y & 0x3F3F3F3Fu;
+            mnb = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scb = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mnb = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+        }
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {              // a pair of sub-blocks shares 32 bytes
+            const uint8_t* qp = p + 16 + 64 * L.half + 32 * pp;
+            const uint4 a = lds128(qp), b = lds128(qp + 16);
+            const uint32_t raw[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int nib = 0; nib < 2; ++nib) {
+                uint32_t q[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q[i] = (raw[i] >> (4 * nib)) & 0x0F0F0F0Fu;
+                const int js = 2 * pp + nib;          // sub-block index within this half
+                const float dsc = d * (float)((scb >> (8 * js)) & 0xFFu);
+                const float dmn = dmin * (float)((mnb >> (8 * js)) & 0xFFu);
+                const uint32_t blk = (kb >> 5) + 4 * L.half + js;
+#pragma unroll
+                for (int m = 0; m < MM; ++m) {
+                    const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, 0);
+                    const float sbv = L.sb[m * L.xstride4 + blk];
+                    // sx holds sum(X) of the block: the min term is dmin * m * s_b * sum(X)
+                    const float sxf = sbv * (float)L.sx[m * L.xstride4 + blk];
+                    tot[m] = fmaf(dsc * sbv, (float)c, fmaf(-dmn, sxf, tot[m]));
+                }
+            }
+        }
+    }
+};
+
+// ---- Q6_K: unit = one 210-byte super-block (only 2-byte aligned); a thread takes one half ----
+template <int MM> struct QUnit<RLXQ_Q6_K, MM> {
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
+        // 210*u is 2 mod 4 for odd u: read aligned words from 2 bytes earlier and funnel-shift.
+        const uint32_t odd = u & 1u, sh = odd * 16u;
+        const uint8_t* pa = L.row + u * 210 - 2 * odd;
+        const uint32_t h = L.half;
+        uint32_t ql[16], qh[8], scw[2];
+        {
+            uint32_t a[17];
+#pragma unroll
+            for (int i = 0; i < 17; ++i) a[i] = *reinterpret_cast<const uint32_t*>(pa + 64 * h + 4 * i);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ql[i] = __funnelshift_r(a[i], a[i + 1], sh);
+            uint32_t b[9];
+#pragma unroll
+            for (int i = 0; i < 9; ++i) b[i] = *reinterpret_cast<const uint32_t*>(pa + 128 + 32 * h + 4 * i);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) qh[i] = __funnelshift_r(b[i], b[i + 1], sh);
+            uint32_t c3[3];
+#pragma unroll
+            for (int i = 0; i < 3; ++i) c3[i] = *reinterpret_cast<const uint32_t*>(pa + 192 + 8 * h + 4 * i);
+            scw[0] = __funnelshift_r(c3[0], c3[1], sh);
+            scw[1] = __funnelshift_r(c3[1], c3[2], sh);
+        }
+        const uint32_t dw = *reinterpret_cast<const uint32_t*>(pa + 208);
+        const float d = f16_bits_to_f32((dw >> sh) & 0xFFFFu);
+#pragma unroll
+        for (int g4 = 0; g4 < 4; ++g4) {              // four interleaved 32-weight groups per half
+            const int nib = g4 >> 1, ps = g4 & 1;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {             // 16-weight sub-blocks, each with its own scale
+                uint32_t q[4];
+#pragma unroll
+                for (int wv = 0; wv < 4; ++wv) {
+                    const uint32_t lo = (ql[8 * ps + 4 * i + wv] >> (4 * nib)) & 0x0F0F0F0Fu;
+                    const uint32_t hv = qh[4 * i + wv];
+                    const uint32_t hi = (g4 < 2 ? (hv << (4 - 2 * g4)) : (hv >> (2 * g4 - 4))) & 0x30303030u;
+                    q[wv] = lo | hi;
+                }
+                const int si = 2 * g4 + i;            // scale index inside the half
+                const float ds = d * (float)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFFu);
+                const uint32_t ke = kb + 128 * h + 32 * g4 + 16 * i;
+#pragma unroll
+                for (int m = 0; m < MM; ++m) {
+                    // sx holds -32 * sum(X) per 16 values
+                    const int c = dot_limbs<4>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, ke, L.sx[m * L.xstride4 + (ke >> 4)]);
+                    tot[m] = fmaf(ds * L.sb[m * L.xstride4 + (ke >> 5)], (float)c, tot[m]);
+                }
+            }
+        }
+    }
+};
+
+// What the per-block integer sums are multiplied by before they are stored.
+template <uint32_t SCHEME> struct SumBias;
+template <> struct SumBias<RLXQ_Q4_0> { static constexpr int value = -8; };
+template <> struct SumBias<RLXQ_Q8_0> { static constexpr int value = 0; };
+template <> struct SumBias<RLXQ_Q4_K> { static constexpr int value = 1; };
+template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 1: activations -> two int8 limbs + per-32 scale + per-SUB integer sums (workspace).
+// One thread per 8 values; the scale is local to a 32-value block (four lanes).
+// ---------------------------------------------------------------------------------------------
+template <uint32_t SUB>
+__global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
+                                                         uint32_t k, int bias, uint8_t* __restrict__ xq,
+                                                         uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
+                                                         uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count) {
+    griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
+    griddep_wait();                // x (and the counters) may still be in use by the previous kernel
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
+    for (uint32_t i = gtid; i < ntiles; i += gridDim.x * blockDim.x) counters[i] = 0u;
+    for (uint32_t i = gtid; i < y_count; i += gridDim.x * blockDim.x) y_zero[i] = 0.f;   // two-contributor add mode
+    const uint32_t groups_per_row = k / 8;
+    const uint32_t total = groups_per_row * m;          // a multiple of 32
+    if (gtid >= total) return;                          // whole warps leave together
+    const uint32_t r = gtid / groups_per_row, c = (gtid - r * groups_per_row) * 8;
+    float f[8];
+    if (x_bf16) {
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)r * k + c);
+        const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            f[2 * q] = __uint_as_float(wv[q] << 16);
+            f[2 * q + 1] = __uint_as_float(wv[q] & 0xFFFF0000u);
+        }
+    } else {
+        const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)r * k + c);
+        const float4 a = p[0], b = p[1];
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const bool ok = amax > 0.f && amax < 3.0e38f;
+    const float inv = ok ? 16256.0f / amax : 0.f;
+    const float s = ok ? amax * (1.0f / 16256.0f) : 0.f;
+    int sum = 0;
+    uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const int X = max(-16256, min(16256, __float2int_rn(f[q] * inv)));
+        sum += X;
+        const int hq = (X + 64) >> 7;             // in [-127, 127]
+        const int lq = X - (hq << 7);             // in [-64, 63]
+        hw[q >> 2] |= ((uint32_t)hq & 0xFFu) << (8 * (q & 3));
+        lw[q >> 2] |= ((uint32_t)lq & 0xFFu) << (8 * (q & 3));
+    }
+    uint8_t* row = xq + (size_t)r * xq_row_bytes;
+    *reinterpret_cast<uint2*>(row + c) = make_uint2(hw[0], hw[1]);
+    *reinterpret_cast<uint2*>(row + k + c) = make_uint2(lw[0], lw[1]);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    if (SUB == 32) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    float* sb = reinterpret_cast<float*>(row + 2 * (size_t)k);
+    int* sx = reinterpret_cast<int*>(row + 2 * (size_t)k + (size_t)(k / 32) * 4);
+    if ((lane & 3u) == 0) sb[c / 32] = s;
+    if ((lane & (SUB / 8 - 1)) == 0) sx[c / SUB] = bias * sum;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Work list ("stream-K").  All (tile, chunk) items form one list, chunk-major inside a tile; CTA i
+// takes the contiguous range [i*T/G, (i+1)*T/G), so every CTA streams the same number of bytes
+// (+-1 chunk) whatever n and k are.  A range cuts at most two tiles: its head and its tail.  Those
+// two shared segments are processed FIRST, the whole tiles between them afterwards, so that the
+// latency of finishing a shared tile (a fence, an atomic, a re-read) hides behind streaming.
+// ---------------------------------------------------------------------------------------------
+struct Segment { uint32_t tile, c0, c1; };
+
+struct Range { uint32_t beg, end, head_end, tail_beg, nseg, nshared; };
+
+__device__ __forceinline__ Range make_range(const IntParams& P, uint32_t me, uint32_t G) {
+    Range r;
+    r.beg = (uint32_t)(((uint64_t)me * P.total_chunks) / G);
+    r.end = (uint32_t)(((uint64_t)(me + 1) * P.total_chunks) / G);
+    const uint32_t nc = P.nchunks;
+    // head: from beg to the next tile boundary (or end), if beg is inside a tile
+    r.head_end = (r.beg % nc) ? min(r.end, (r.beg / nc + 1) * nc) : r.beg;
+    // tail: from the last tile boundary to end, if end is inside a tile and past the head
+    r.tail_beg = (r.end % nc && (r.end / nc) * nc >= r.head_end) ? (r.end / nc) * nc : r.end;
+    const uint32_t whole = (r.tail_beg - r.head_end) / nc;
+    r.nshared = (r.head_end > r.beg ? 1u : 0u) + (r.end > r.tail_beg ? 1u : 0u);
+    r.nseg = r.nshared + whole;
+    return r;
+}
+__device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& r, uint32_t idx) {
+    const uint32_t nc = P.nchunks;
+    Segment sg;
+    uint32_t g0, g1;   // global chunk ids
+    const bool has_head = r.head_end > r.beg, has_tail = r.end > r.tail_beg;
+    if (has_head && idx == 0) { g0 = r.beg; g1 = r.head_end; }
+    else if (has_tail && idx == (has_head ? 1u : 0u)) { g0 = r.tail_beg; g1 = r.end; }
+    else { g0 = r.head_end + (idx - r.nshared) * nc; g1 = g0 + nc; }
+    sg.tile = g0 / nc;
+    sg.c0 = g0 - sg.tile * nc;
+    sg.c1 = g1 - sg.tile * nc;
+    return sg;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 2: the streaming kernel
+// ---------------------------------------------------------------------------------------------
+template <uint32_t SCHEME, int MM>
+__global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_constant__ IntParams P) {
+    using T = StagedTraits<SCHEME>;
+    using B = IntBox<SCHEME>;
+    constexpr uint32_t STRIDE = B::ROW;
+    constexpr uint32_t stage_bytes = B::STAGE_BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    // activations first, in the workspace's layout, one row after the other
+    uint8_t* xs = smem;
+    uint8_t* stages = smem + P.off_stage;
+    float* red = reinterpret_cast<float*>(smem + P.off_red);          // [RB][8 warps][32 lanes][MM]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P.off_bar);   // full[NS], empty[NS], xbar
+    const uint32_t NS = P.nstages;
+    uint64_t* rbars = bars + 2 * NS + 1;                                // rfull[RB], rempty[RB]
+    uint32_t* misc = reinterpret_cast<uint32_t*>(rbars + 2 * kIntRB);
+    volatile uint32_t* abort_flag = misc;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    griddep_launch_dependents();
+
+    const uint32_t G = gridDim.x, me = blockIdx.x;
+    const Range rg = make_range(P, me, G);
+    const uint32_t nseg = rg.nseg;
+    const uint32_t ku = P.k / 256;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[NS + s]), kIntWarps);
+        }
+        mbar_init(smem_u32(&bars[2 * NS]), 1);
+        for (uint32_t r = 0; r < kIntRB; ++r) {
+            mbar_init(smem_u32(&rbars[r]), kIntWarps);
+            mbar_init(smem_u32(&rbars[kIntRB + r]), 1);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kIntWarps) {
+        // ---------------- producer warp ----------------
+        auto produce = [&](uint32_t tile, uint32_t chunk, uint32_t s) {
+            // rows past n and bytes past the row end arrive as zeros (d = 0: they add nothing)
+            const uint32_t full = smem_u32(&bars[s]);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(full, stage_bytes);
+#pragma unroll
+                for (uint32_t b = 0; b < B::NB; ++b)
+                    tma_load_2d(smem_u32(stages + s * stage_bytes + b * B::BOX_BYTES), &P.wmap,
+                                (int32_t)(((chunk * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(tile * 16), full);
+            }
+        };
+        if (lane == 0) tma_prefetch_desc(&P.wmap);
+        uint32_t s = 0, ph = 1, issued = 0;   // ph: parity to wait for on empty[s] (1 passes on a fresh barrier)
+        bool waited = false, dead = false;
+        for (uint32_t si = 0; si < nseg && !dead; ++si) {
+            const Segment sg = segment_at(P, rg, si);
+            for (uint32_t c = sg.c0; c < sg.c1; ++c, ++issued) {
+                if (issued == NS && !waited) {
+                    // the ring is full of (immutable) weights: only now wait for the previous kernel
+                    waited = true;
+                    griddep_wait();
+                    const uint32_t xbar = smem_u32(&bars[2 * NS]);
+                    if (lane == 0 && !(P.debug & 4u)) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+                    __syncwarp();
+                    if (lane < (uint32_t)MM && !(P.debug & 4u))
+                        bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
+                }
+                if (issued >= NS) {
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars[NS + s]), ph)) {
+                        if (lane == 0) { atomicExch(P.err, 3); *abort_flag = 1u; }
+                        dead = true;
+                        break;
+                    }
+                }
+                produce(sg.tile, c, s);
+                if (++s == NS) { s = 0; ph ^= 1u; }
+            }
+        }
+        if (!waited) {   // fewer chunks than stages: everything is in flight, now fetch the activations
+            griddep_wait();
+            const uint32_t xbar = smem_u32(&bars[2 * NS]);
+            if (lane == 0 && !(P.debug & 4u)) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+            __syncwarp();
+            if (lane < (uint32_t)MM && !(P.debug & 4u))
+                bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
+        }
+        return;
+    }
+
+    if (warp == kIntWarps + 1) {
+        // ---------------- finisher warp ----------------
+        // Adds the 16 partials of every output (2 halves x 8 warps, fixed order) and writes the tile,
+        // or, for a tile shared with other CTAs, runs the publish / count / re-read sequence.  That
+        // sequence is a chain of three global round trips; here it delays nobody, because the
+        // consumer warps only hand over a reduction buffer and go on.
+        griddep_wait();
+        const uint32_t col = lane >> 4, rrow = lane & 15u;
+        uint32_t r = 0, rph = 0;
+        for (uint32_t si = 0; si < nseg; ++si) {
+            const Segment sg = segment_at(P, rg, si);
+            const uint32_t tile = sg.tile, mine = sg.c1 - sg.c0;
+            if (*abort_flag || !mbar_wait(smem_u32(&rbars[r]), rph)) {
+                if (lane == 0) { atomicExch(P.err, 6); *abort_flag = 1u; }
+                break;
+            }
+            const float* rbuf = red + r * (kIntWarps * 32 * MM);
+            float v = 0.f;
+            if (col < (uint32_t)MM) {
+#pragma unroll
+                for (uint32_t wv = 0; wv < kIntWarps; ++wv) {
+                    v += rbuf[(wv * 32 + rrow) * MM + col];
+                    v += rbuf[(wv * 32 + 16 + rrow) * MM + col];
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&rbars[kIntRB + r]));
+            if (++r == kIntRB) { r = 0; rph ^= 1u; }
+            if (P.debug & 8u) continue;
+            const uint32_t orow = tile * 16 + rrow;
+            const bool live = col < (uint32_t)MM && orow < P.n;
+            bool store = mine == P.nchunks;
+            if (!store && P.use_red) {
+                // exactly two CTAs share this tile and y starts at zero: 0 + a + b = 0 + b + a, so a
+                // plain reduction to memory is deterministic and needs no fence, counter or re-read
+                if (live) atomicAdd(reinterpret_cast<float*>(P.y) + (size_t)col * P.n + orow, v);
+            } else if (!store) {
+                // the tile is shared with neighbouring CTAs: publish this part in the slot given by the
+                // CTA's position among the tile's contributors; whoever completes the tile adds the slots
+                const uint32_t first_owner = (uint32_t)((((uint64_t)tile * P.nchunks + 1) * G - 1) / P.total_chunks);
+                const uint32_t last_owner = (uint32_t)((((uint64_t)(tile + 1) * P.nchunks) * G - 1) / P.total_chunks);
+                float* pt = P.partial + ((size_t)tile * P.slots) * (MM * 16);
+                if (col < (uint32_t)MM) pt[((me - first_owner) * MM + col) * 16 + rrow] = v;
+                __threadfence();
+                __syncwarp();
+                uint32_t prev = 0;
+                if (lane == 0) prev = atomicAdd(&P.counters[tile], mine);
+                prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+                if (prev + mine == P.nchunks) {
+                    __threadfence();
+                    v = 0.f;
+                    if (col < (uint32_t)MM)
+                        for (uint32_t sl = 0; sl <= last_owner - first_owner; ++sl)
+                            v += __ldcg(&pt[(sl * MM + col) * 16 + rrow]);
+                    store = true;
+                }
+            }
+            if (store && live) {
+                const size_t o = (size_t)col * P.n + orow;
+                if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v);
+                else reinterpret_cast<float*>(P.y)[o] = v;
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps: lane = (tile row, half of the unit) ----------------
+    griddep_wait();
+    QLane L;
+    L.xstride = P.xq_row_bytes;
+    L.xstride4 = P.xq_row_bytes / 4;
+    L.xh = reinterpret_cast<const int8_t*>(xs);
+    L.xl = L.xh + P.k;
+    L.sb = reinterpret_cast<const float*>(xs + 2 * (size_t)P.k);
+    L.sx = reinterpret_cast<const int*>(xs + 2 * (size_t)P.k + (size_t)(P.k / 32) * 4);
+    L.half = lane >> 4;
+    const uint32_t trow = lane & 15u;
+    bool dead = false;
+    if (!(P.debug & 4u) && !mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+        dead = true;
+        if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
+    }
+    uint32_t s = 0, ph = 0, rr = 0, rrph = 1;   // rrph: a fresh 'empty' barrier passes a wait on parity 1
+    for (uint32_t si = 0; si < nseg; ++si) {
+        const Segment sg = segment_at(P, rg, si);
+        float tot[MM];
+#pragma unroll
+        for (int m = 0; m < MM; ++m) tot[m] = 0.f;
+        for (uint32_t chunk = sg.c0; chunk < sg.c1; ++chunk) {
+            if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
+                dead = true;
+                if (lane == 0) { atomicExch(P.err, 4); *abort_flag = 1u; }
+            }
+            if (!dead) {
+                const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
+                L.row = stages + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                if (warp < cu && !(P.debug & kDebugSkipMath))
+                    QUnit<SCHEME, MM>::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
+            }
+            if (++s == NS) { s = 0; ph ^= 1u; }
+        }
+        // hand the warp's partials to the finisher through the ring of reduction buffers
+        if (!dead && (*abort_flag || !mbar_wait(smem_u32(&rbars[kIntRB + rr]), rrph))) {
+            dead = true;
+            if (lane == 0) { atomicExch(P.err, 7); *abort_flag = 1u; }
+        }
+        if (!dead) {
+            float* rbuf = red + rr * (kIntWarps * 32 * MM);
+#pragma unroll
+            for (int m = 0; m < MM; ++m) rbuf[(warp * 32 + lane) * MM + m] = tot[m];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&rbars[rr]));
+        }
+        if (++rr == kIntRB) { rr = 0; rrph ^= 1u; }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct IntPlan {
+    bool ok;
+    uint32_t grid, ntiles, nchunks, total_chunks, slots, nstages;
+    bool two_way;
+    uint32_t xq_row_bytes, off_stage, off_red, off_bar, smem_bytes;
+    size_t ws_xq, ws_partial, ws_bytes;
+};
+
+template <uint32_t SCHEME>
+static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
+    using T = StagedTraits<SCHEME>;
+    constexpr uint32_t stage_bytes = IntBox<SCHEME>::STAGE_BYTES;
+    IntPlan pl{};
+    pl.ok = false;
+    if (m == 0 || m > 2 || n == 0 || k == 0 || k % (256 * T::AG)) return pl;
+    const uint32_t sms = (uint32_t)sm_count();
+    auto align = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
+    pl.ntiles = (n + 15) / 16;
+    pl.nchunks = (k / 256 + kIntCU - 1) / kIntCU;
+    if ((uint64_t)pl.ntiles * pl.nchunks > 0xFFFFFFFFull / 2) return pl;
+    pl.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;      // a multiple of 16: k % 256 == 0
+    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * m, 128);
+    const uint32_t tail = kIntRB * kIntWarps * 32 * m * 4 + 1024;      // reduction buffers, barriers, flags
+    // two CTAs per SM when that still leaves each a ring of >= 4 stages, else one
+    const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
+    uint32_t per_sm = 2, budget = budget2;
+    if (fixed + tail + 4 * stage_bytes > budget2) { per_sm = 1; budget = budget1; }
+    if (fixed + tail + 2 * stage_bytes > budget) return pl;          // activations do not fit: not this kernel
+    pl.nstages = (budget - fixed - tail) / stage_bytes;
+    if (pl.nstages > 24) pl.nstages = 24;
+    pl.off_stage = fixed;
+    pl.off_red = pl.off_stage + pl.nstages * stage_bytes;
+    pl.off_bar = pl.off_red + kIntRB * kIntWarps * 32 * m * 4;
+    pl.smem_bytes = pl.off_bar + (2 * pl.nstages + 1 + 2 * kIntRB) * 8 + 64;
+    pl.total_chunks = pl.ntiles * pl.nchunks;
+    pl.grid = sms * per_sm;
+    // Slightly fewer tiles than CTAs: one whole tile per CTA beats splitting tiles (no shared tiles).
+    if (pl.ntiles < pl.grid && pl.ntiles * 10 >= pl.grid * 7) pl.grid = pl.ntiles;
+    if (pl.grid > pl.total_chunks) pl.grid = pl.total_chunks;
+    const uint32_t per_cta = pl.total_chunks / pl.grid;              // >= 1
+    pl.two_way = per_cta >= pl.nchunks;                              // a tile is cut by at most one range boundary
+    pl.slots = (pl.nchunks + per_cta - 1) / per_cta + 1;             // contributors a tile can have
+    pl.ws_xq = align((size_t)pl.xq_row_bytes * m, 256);
+    pl.ws_partial = align((size_t)pl.ntiles * pl.slots * m * 16 * 4, 256);
+    pl.ws_bytes = pl.ws_xq + pl.ws_partial + align((size_t)pl.ntiles * 4, 256);
+    pl.ok = true;
+    return pl;
+}
+
+template <typename Kern, typename... Args>
+static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = options().pdl.load() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RLXQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
+    return RLXQ_OK;
+}
+
+template <uint32_t SCHEME, int MM>
+static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
+                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl) {
+    using T = StagedTraits<SCHEME>;
+    Geometry g;
+    geometry(SCHEME, &g);
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return fail(RLXQ_E_WORKSPACE, "integer GEMV needs %zu workspace bytes, got %zu", pl.ws_bytes, ws_bytes);
+    if ((uintptr_t)ws & 15u) return fail(RLXQ_E_ALIGN, "workspace must be 16-byte aligned");
+    IntParams P{};
+    int rcm = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, IntBox<SCHEME>::ROW / 8, 16);
+    if (rcm) return rcm;
+    P.w = w; P.y = y;
+    P.xq = reinterpret_cast<const uint8_t*>(ws);
+    P.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq);
+    P.counters = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq + pl.ws_partial);
+    P.k = k; P.n = n; P.y_bf16 = ybf;
+    P.use_red = (pl.two_way && !ybf) ? 1u : 0u;
+    P.row_bytes = k / g.elems * g.bytes;
+    P.ntiles = pl.ntiles; P.nchunks = pl.nchunks; P.total_chunks = pl.total_chunks; P.slots = pl.slots;
+    P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes;
+    P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
+    P.debug = (uint32_t)options().gemv_debug.load();
+    P.err = device_error_word();
+    if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
+    static std::atomic<uint32_t> attr_set[64];
+    int dev = 0;
+    RLXQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && attr_set[dev].load() == 0) {
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev].store(1);
+    }
+    const uint32_t groups = (k / 8) * MM;
+    int rc = RLXQ_OK;
+    if (!(P.debug & 16u)) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3((groups + 255) / 256), dim3(256), 0, stream, x, (uint32_t)xbf,
+                        (uint32_t)MM, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
+                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u);
+    if (rc) return rc;
+    count_launch();
+    rc = launch_pdl(gemv_int_kernel<SCHEME, MM>, dim3(pl.grid), dim3(kIntThreads), pl.smem_bytes, stream, P);
+    if (rc) return rc;
+    count_launch();
+    return check_launch("gemv_int_kernel");
+}
+
+template <uint32_t SCHEME>
+static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
+                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    const IntPlan pl = plan_int<SCHEME>(m, k, n);
+    if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
+    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl);
+    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl);
+}
+
+bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
+    if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
+    switch (scheme) {
+        case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0>(m, k, n).ok;
+        case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0>(m, k, n).ok;
+        case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K>(m, k, n).ok;
+        case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K>(m, k, n).ok;
+        default: return false;
+    }
+}
+
+size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) {
+    IntPlan pl{};
+    switch (scheme) {
+        case RLXQ_Q4_0: pl = plan_int<RLXQ_Q4_0>(m, k, n); break;
+        case RLXQ_Q8_0: pl = plan_int<RLXQ_Q8_0>(m, k, n); break;
+        case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K>(m, k, n); break;
+        case RLXQ_Q6_K: pl = plan_int<RLXQ_Q6_K>(m, k, n); break;
+        default: break;
+    }
+    return pl.ok ? pl.ws_bytes : 0;
+}
+
+int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    }
+}
+
+}  // namespace rlxq

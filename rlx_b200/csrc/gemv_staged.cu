@@ -8,7 +8,14 @@
 // 16-byte-aligned run of whole blocks, so HBM sees long contiguous bursts and no load
 // instruction is spent on it.  Four consumer warps split every stage by 256-weight units.
 //
-// Arithmetic.  Block quants are small integers, so they are exact in fp16: a byte-permute
+// Arithmetic, batch 1-2 (integer mode).  Each CTA quantises its activation slice once to two
+// int8 limbs per value (15 bits, one f32 scale per 32 values, exact block sums alongside).
+// Weights stay integers: nibbles are masked out four at a time and multiplied with dp4a, which
+// accumulates exactly in int32; one int->float conversion and one FMA per 32-weight block apply
+// d_block * s_block.  Error: only the activation quantisation, |err| <= 1.7e-4 * |x| * |w_row|
+// worst case (about 1e-6 typical), plus f32 accumulation across blocks.
+//
+// Arithmetic, batch 3-8 (tensor mode).  Block quants are small integers, so they are exact in fp16: a byte-permute
 // builds the fp16 pair (1024 + q) from a raw byte and the constant 0x64, two weights per
 // instruction, and mma.sync.m16n8k16 (f16 x f16 -> f32) multiplies a 16-row tile by the
 // activation columns.  The activations are converted once per CTA to fp16 after an exact
@@ -31,113 +38,10 @@
 #include "common.cuh"
 #include "decode.cuh"
 #include "kernels.h"
+#include "staged_common.cuh"
 
 namespace rlxq {
 
-// ---------------------------------------------------------------------------------------------
-// Per-format constants
-// ---------------------------------------------------------------------------------------------
-template <uint32_t SCHEME> struct StagedTraits;
-// UNIT_B : bytes of 256 consecutive weights of one row
-// AG     : 256-weight units per 16-byte-aligned group (bulk copies move whole groups)
-// CU     : units per stage chunk            STRIDE : shared-memory bytes between tile rows
-// STAGES : ring depth                       SUB    : weights per activation-sum block
-// BIAS   : constant removed per weight (fp16 "1024 + q" trick plus the format's own offset)
-template <> struct StagedTraits<RLXQ_Q4_0> {
-    static constexpr uint32_t UNIT_B = 144, AG = 1, CU = 4, STRIDE = 592, STAGES = 4, SUB = 32;
-    static constexpr float BIAS = -1032.f;
-};
-template <> struct StagedTraits<RLXQ_Q8_0> {
-    static constexpr uint32_t UNIT_B = 272, AG = 1, CU = 4, STRIDE = 1104, STAGES = 4, SUB = 32;
-    static constexpr float BIAS = -1152.f;
-};
-template <> struct StagedTraits<RLXQ_Q4_K> {
-    static constexpr uint32_t UNIT_B = 144, AG = 1, CU = 4, STRIDE = 672, STAGES = 4, SUB = 32;
-    static constexpr float BIAS = -1024.f;
-};
-template <> struct StagedTraits<RLXQ_Q6_K> {
-    static constexpr uint32_t UNIT_B = 210, AG = 8, CU = 8, STRIDE = 1680, STAGES = 3, SUB = 16;
-    static constexpr float BIAS = -1056.f;
-};
-
-constexpr uint32_t kConsumerWarps = 4;
-constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
-constexpr uint32_t kWaitLimit = 1u << 22;  // mbarrier try_wait attempts before giving up
-
-struct StagedParams {
-    const void* x;
-    const uint8_t* w;
-    void* y;
-    float* partial;       // [ksl][m][n] when ksl > 1
-    uint32_t* counters;   // [ntiles]     when ksl > 1
-    int* err;             // device error word
-    uint32_t m, k, n;
-    uint32_t x_bf16, y_bf16;
-    uint32_t row_bytes;   // bytes of one weight row
-    uint32_t ntiles;      // ceil(n / 16)
-    uint32_t rg;          // row groups: CTA (rgi, ks) owns tiles rgi, rgi + rg, ...
-    uint32_t ksl;         // k slices
-    uint32_t usl;         // 256-weight units per slice (the last slice may hold fewer)
-    uint32_t xs_stride;   // halfs between activation rows in shared memory
-    uint32_t mp;          // m rounded up to even
-    uint32_t off_sxb, off_stage, off_scratch, off_red, off_bar;  // shared-memory layout
-};
-
-// ---------------------------------------------------------------------------------------------
-// PTX helpers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out (the caller records an error and drains).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void consumer_bar() {  // the four consumer warps only
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t lds_u16(const uint8_t* p) {
-    return *reinterpret_cast<const uint16_t*>(p);
-}
-__device__ __forceinline__ uint32_t lds_u32_2(const uint8_t* p) {  // 2-byte-aligned 32-bit read
-    return lds_u16(p) | (lds_u16(p + 2) << 16);
-}
-__device__ __forceinline__ uint32_t lds_u32(const uint8_t* p) {
-    return *reinterpret_cast<const uint32_t*>(p);
-}
 // fp16 pair (1024 + byte i, 1024 + byte j) of v: 0x64 in the high byte is 1024 with ulp 1.
 __device__ __forceinline__ uint32_t pair01(uint32_t v) { return __byte_perm(v, 0x64646464u, 0x4140); }
 __device__ __forceinline__ uint32_t pair23(uint32_t v) { return __byte_perm(v, 0x64646464u, 0x4342); }
@@ -147,25 +51,24 @@ struct Lane {
     const uint8_t* stage;   // first row of the stage
     const uint8_t* row_lo;  // stage row g      (g = lane / 4)
     const uint8_t* row_hi;  // stage row g + 8
-    const __half* xrow;     // activation row g in shared memory (valid when has_x)
+    const __half* xrow;     // activation row min(g, m-1)... see below
     const float* sxb;       // activation block sums * BIAS, [block][mp]
-    bool has_x;             // g < m
-    bool has_c;             // 2t < mp: this thread's accumulator columns exist
     uint32_t t;             // lane % 4
     uint32_t mp;
 };
 
+// All fragment loads are unconditional.  Columns of the MMA are independent, so a lane whose
+// column does not exist (g >= m) may feed any finite-or-not data: it reads activation row 0 and
+// whatever follows its block's sums; the garbage stays in accumulator columns that are never
+// stored.  Conditional loads here cost a branch each and serialise the unrolled blocks.
 __device__ __forceinline__ uint2 ld_b64(const Lane& L, uint32_t k) {  // 4 activations at k
-    if (!L.has_x) return make_uint2(0u, 0u);
     return *reinterpret_cast<const uint2*>(L.xrow + k);
 }
 __device__ __forceinline__ uint4 ld_b128(const Lane& L, uint32_t k) {  // 8 activations at k
-    if (!L.has_x) return make_uint4(0u, 0u, 0u, 0u);
     return *reinterpret_cast<const uint4*>(L.xrow + k);
 }
 __device__ __forceinline__ float2 ld_sx(const Lane& L, uint32_t block) {
-    if (!L.has_c) return make_float2(0.f, 0.f);
-    return *reinterpret_cast<const float2*>(L.sxb + (size_t)block * L.mp + 2 * L.t);
+    return *reinterpret_cast<const float2*>(L.sxb + block * L.mp + 2 * L.t);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -525,9 +428,7 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
     Lane L;
     L.t = t;
     L.mp = P.mp;
-    L.has_x = g < P.m;
-    L.has_c = 2 * t < P.mp;
-    L.xrow = xs + (size_t)(L.has_x ? g : 0u) * P.xs_stride;
+    L.xrow = xs + (size_t)(g < P.m ? g : 0u) * P.xs_stride;
     L.sxb = sxb;
     float* scratch = scratch_all + warp * 512;  // 2 KB per warp
     bool dead = false;
@@ -546,8 +447,9 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
             L.stage = stages + s * stage_bytes;
             L.row_lo = L.stage + g * T::STRIDE;
             L.row_hi = L.row_lo + 8 * T::STRIDE;
-            for (uint32_t u = warp; u < cu; u += kConsumerWarps)
-                Unit<SCHEME>::run(L, u * T::UNIT_B, (chunk * T::CU + u) * 256, scratch, lane, tot);
+            if (!(P.debug & kDebugSkipMath))
+                for (uint32_t u = warp; u < cu; u += kConsumerWarps)
+                    Unit<SCHEME>::run(L, u * T::UNIT_B, (chunk * T::CU + u) * 256, scratch, lane, tot);
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars[T::STAGES + s]));
         }
@@ -674,8 +576,6 @@ static StagedPlan plan_staged(uint32_t m, uint32_t k, uint32_t n, int64_t force_
     return pl;
 }
 
-static int* device_error_word();
-
 template <uint32_t SCHEME>
 static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                            uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes,
@@ -692,6 +592,7 @@ static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const u
     P.xs_stride = pl.xs_stride; P.mp = pl.mp;
     P.off_sxb = pl.off_sxb; P.off_stage = pl.off_stage; P.off_scratch = pl.off_scratch;
     P.off_red = pl.off_red; P.off_bar = pl.off_bar;
+    P.debug = (uint32_t)options().gemv_debug.load();
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     if (pl.ksl > 1) {
@@ -715,8 +616,7 @@ static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const u
     return check_launch("gemv_staged_kernel");
 }
 
-// One error word per device, allocated on first use (outside any capture), never freed.
-static int* device_error_word() {
+int* device_error_word() {
     static std::atomic<int*> words[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;

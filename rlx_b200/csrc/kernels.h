@@ -12,11 +12,17 @@ int launch_dequant_f32(cudaStream_t stream, uint32_t scheme, const uint8_t* w, u
 int launch_matmul_generic(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
                           void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n);
 
-// Staged tensor-core GEMV (m <= 8).
+// Staged tensor-mode GEMV (m <= 8).
 bool staged_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf);
 size_t staged_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
 int launch_gemv_staged(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
                        void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+// Integer (dp4a) GEMV (m <= 2).
+bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x);
+size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
+int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+
 int staged_device_error(int* value);   // synchronises the device
 int staged_prepare_device();           // allocates the per-device error word (call outside capture)
 

@@ -110,7 +110,9 @@ def test_session_needs_a_cuda_device():
     assert e.value.status == -6 and "no CUDA device" in str(e.value)   # loud, no CPU fallback
 
 
-def test_workspace_bytes_reported_for_split_k():
-    assert R.workspace_bytes(6, 1, 4096, 11008) == 0
-    ws = R.workspace_bytes(6, 1, 11008, 4096)
-    assert ws % 4 == 0
+def test_workspace_bytes_are_modest():
+    """The reference reserves k*n*4 bytes of f32 scratch (rlx-cuda/src/gguf_gpu.rs:35-59); the GEMV
+    paths need the quantised activations and a few partial tiles only."""
+    for s, m, k, n in ((6, 1, 4096, 11008), (6, 1, 11008, 4096), (6, 8, 11008, 4096), (0, 1, 28672, 8192)):
+        ws = R.workspace_bytes(s, m, k, n)
+        assert ws % 16 == 0 and ws < k * n * 4 // 100
