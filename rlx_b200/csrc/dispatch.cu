@@ -46,6 +46,12 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
             return launch_gemv_staged(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
     }
+    // m > 8: tensor-memory GEMM for bf16 activations, the tiled generic kernel otherwise
+    const int64_t gforce = options().gemm_kernel.load();
+    const bool can = gemm_tc_supported(scheme, m, k, n, w, x, xbf);
+    if (gforce == 2 && !can)
+        return fail(RLXQ_E_SHAPE, "the tcgen05 GEMM needs bf16 activations, k %% 256 == 0, Q4_0/Q8_0/Q4_K and 16-byte alignment");
+    if (can && gforce != 1) return launch_gemm_tc(stream, scheme, x, w, y, ybf, m, k, n);
     return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
 }
 

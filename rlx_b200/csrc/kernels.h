@@ -23,6 +23,11 @@ size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
 int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
                     bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
 
+// tcgen05 / tensor-memory GEMM (m > 8, bf16 activations).
+bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf);
+int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
+                   uint32_t m, uint32_t k, uint32_t n);
+
 int staged_device_error(int* value);   // synchronises the device
 int staged_prepare_device();           // allocates the per-device error word (call outside capture)
 
