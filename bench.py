@@ -41,6 +41,9 @@ WORKLOADS = {
     "q4_k_8b_up_gemv": ("q4_k", [(4096, 14336)], "bf16"),
     "q6_k_8b_down_gemv": ("q6_k", [(14336, 4096)], "bf16"),
 }
+# Tensor-parallel SwiGLU FFN at 70B shapes (configuration 3): handled by run_tp_workload.
+TP_WORKLOAD = "q4_k_70b_ffn_tp"
+TP_D_MODEL, TP_D_FFN = 8192, 28672
 SCHEME_IDS = {"q4_k": 0, "q6_k": 2, "q4_0": 6, "q8_0": 7}
 GEOM = {"q4_k": (256, 144), "q6_k": (256, 210), "q4_0": (32, 18), "q8_0": (32, 34)}
 
@@ -53,6 +56,18 @@ def packed_bytes(sch: str, k: int, n: int) -> int:
 def algorithmic_bytes(sch: str, layers, m: int, act_bytes: int) -> list[int]:
     """Per launch: packed W + x + y (f32 y), each once."""
     return [packed_bytes(sch, k, n) + m * k * act_bytes + m * n * 4 for k, n in layers]
+
+
+def finish_ranks(dist, torch) -> None:
+    """Ends a multi-rank run: all ranks meet, flush and leave.  Tearing the NCCL process group down
+    while captured graphs that hold its kernels are alive blocked for minutes on this software stack,
+    so the ranks exit directly once every rank has printed what it has to print."""
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -187,6 +202,178 @@ def workload_config(args, sch, layers, act, rotation):
                   f"({rotation * sum(packed_bytes(sch, k, n) for k, n in layers) / 1e6:.0f} MB) > 2 x 126 MB L2"}
 
 
+
+# --------------------------------------------------------------------------------------------
+# Tensor-parallel FFN (configuration 3): strong scaling, one NCCL all-reduce per step
+# --------------------------------------------------------------------------------------------
+def tp_bytes(m: int) -> int:
+    """Algorithmic bytes of one FFN pass: three packed Q4_K projections + bf16 x + f32 y."""
+    return 3 * packed_bytes("q4_k", TP_D_MODEL, TP_D_FFN) + m * TP_D_MODEL * 2 + m * TP_D_MODEL * 4
+
+
+def tp_config(args, world, rotation):
+    return {"workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
+            "parallelism": f"tp{world}: gate/up column-split, down row-split, all-reduce of f32 partials",
+            "activations": "bf16", "output": "f32",
+            "l2": f"rotating {rotation} distinct shard sets per rank > 2 x 126 MB L2"}
+
+
+def run_tp_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    m, dm, df = args.batch, TP_D_MODEL, TP_D_FFN
+    gate, up, down = (O.fill_weights(O.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, m * dm))).reshape(m, dm)
+    cores = os.cpu_count() or 1
+    steps = min(args.steps, 20)          # a bounded sample: one pass is ~0.7 G multiply-adds per token
+    for _ in range(min(args.warmup, 3)):
+        O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, threads=cores)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, threads=cores)
+    dt = (time.perf_counter() - t0) / steps
+    val = tp_bytes(m) / dt / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": tp_config(args, 1, 1),
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full FFN passes on all {cores} host threads"},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+
+
+def run_tp_workload(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rlxq kernels have no CPU path")
+    import rlx_b200 as R
+    from rlx_b200 import tp
+    from oracle import oracle as O
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    m, dm, df = args.batch, TP_D_MODEL, TP_D_FFN
+    plan = tp.shard_plan(O.Q4_K, dm, df, world, rank)
+    shard_bytes = 2 * plan.gate_up_bytes + plan.down_bytes
+    rotation = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
+    # every rank generates only its own shards: blocks are counter-based, so a shard of the seeded
+    # full tensor is a sub-range of its block stream (gate/up) or a strided set of sub-ranges (down)
+    be, bb = 256, 144
+    ffns = []
+    for r in range(rotation):
+        seeds = [2000 + 10 * r + i for i in range(3)]
+        first = plan.ffn_begin * (dm // be)
+        gu = np.concatenate([O.fill_blocks(O.Q4_K, seeds[0], plan.ffn_local * dm // be, first),
+                             O.fill_blocks(O.Q4_K, seeds[1], plan.ffn_local * dm // be, first)])
+        per_row, loc = df // be, plan.ffn_local // be
+        dn = np.concatenate([O.fill_blocks(O.Q4_K, seeds[2], loc, j * per_row + plan.ffn_begin // be) for j in range(dm)])
+        f = tp.TensorParallelFFN(O.Q4_K, dm, df, rank=rank, world=world, device=dev)
+        f.load_shards(gu, dn)
+        ffns.append(f)
+    x_host = O.fill_normal(78, m * dm).reshape(m, dm)
+    x_dev = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
+    y = torch.empty((m, dm), dtype=torch.float32, device=dev)
+
+    def step(i):
+        ffns[i % rotation].forward(x_dev, out=y)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    sync_all()
+    launches0 = R.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(args.warmup + i)
+    launches = R.launch_count() - launches0
+    graph.replay()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    ev0.record()
+    graph.replay()
+    ev1.record()
+    sync_all()
+    R.device_status()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        lt = torch.tensor([launches], dtype=torch.int64, device=dev)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt.item())
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = tp_bytes(m) / (ms_per_step * 1e-3) / 1e9
+
+    # end to end: x from pinned host memory every step, y back to pinned host memory
+    x_pin = torch.from_numpy(x_host).to(torch.bfloat16).pin_memory()
+    y_pin = torch.empty((m, dm), dtype=torch.float32).pin_memory()
+
+    def e2e_step(i):
+        x_dev.copy_(x_pin, non_blocking=True)
+        ffns[i % rotation].forward(x_dev, out=y)
+        y_pin.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    sync_all()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(args.warmup + i)
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_val = tp_bytes(m) / (e2e_s / args.steps) / 1e9
+    if rank == 0:
+        peak, peak_src = measured_peaks()
+        per_gpu = (shard_bytes + m * dm * 6) / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": tp_config(args, world, rotation),
+            "clocks": clocks,
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": m * dm * 2, "d2h_bytes_per_step": m * dm * 4,
+                    "ms_per_step": e2e_s / args.steps * 1e3,
+                    "api": "TensorParallelFFN.forward: pinned x -> device, rlxq_tp_ffn_partial, all-reduce, y -> pinned host"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_source": peak_src, "frac_of_nominal_8TBs": per_gpu / 8000.0,
+                         "kernel": "gemv_int_kernel (per GPU: its shard bytes / whole step time, all-reduce included)",
+                         "bytes_per_step_per_gpu": shard_bytes + m * dm * 6, "traffic": None},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle as O2
+            cores = os.cpu_count() or 1
+            gate, up, down = (O2.fill_weights(O2.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
+            xx = O2.bf16_bits_to_f32(O2.f32_to_bf16_bits(x_host)).reshape(m, dm)
+            O2.ffn_swiglu(xx, gate, up, down, m, dm, df, O2.Q4_K, O2.Q4_K, threads=cores)
+            t0 = time.perf_counter(); reps = 0
+            while time.perf_counter() - t0 < 8.0 and reps < 20:
+                O2.ffn_swiglu(xx, gate, up, down, m, dm, df, O2.Q4_K, O2.Q4_K, threads=cores); reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {"value": tp_bytes(m) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": f"{reps} full FFN passes, all {cores} host threads", "ms_per_step": dt * 1e3}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        finish_ranks(dist, torch)
+
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
@@ -196,7 +383,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default="q4_0_llama7b_ffn_gemv", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + [TP_WORKLOAD],
+                    help="default: the Q4_0 GEMV pair on one GPU, the tensor-parallel FFN on several")
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -205,6 +393,14 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload is None:
+        args.workload = "q4_0_llama7b_ffn_gemv" if world == 1 else TP_WORKLOAD
+    if args.workload == TP_WORKLOAD:
+        if args.impl == "reference":
+            run_tp_reference_arm(args, rank, world)
+        else:
+            run_tp_workload(args, rank, world, local_rank)
+        return
 
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
@@ -359,7 +555,7 @@ def main() -> None:
             line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        finish_ranks(dist, torch)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,66 @@
+/*
+ * rlxq_tp — tensor-parallel SwiGLU FFN over packed GGUF weights, one rank per GPU.
+ *
+ * The reference has no counterpart: its CUDA context is a process-wide singleton on device 0
+ * (rlx-cuda/src/device.rs:44-60) and its collectives are host emulations
+ * (rlx-driver/src/collective.rs:79-128).  These entry points are what a multi-device helper beside
+ * CudaExecutable would bind.  The FFN itself is the reference's: y = down(up(x) * silu(gate(x)))
+ * (rlx-flow/src/blocks/swiglu.rs:48-52; silu: rlx-cpu/src/naive.rs:54-56).
+ *
+ * gate and up [d_ffn, d_model] are column-parallel (each rank owns d_ffn/world consecutive output
+ * rows), down [d_model, d_ffn] is row-parallel (each rank owns d_ffn/world consecutive k of every
+ * row).  A rank computes an f32 partial [m, d_model]; the caller sums the partials with its
+ * all-reduce (NCCL through the process group the ranks already have).
+ */
+#ifndef RLXQ_TP_H
+#define RLXQ_TP_H
+
+#include "rlxq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rlxq_tp_shard {
+    uint32_t ffn_local;              /* d_ffn / world */
+    uint32_t ffn_begin;              /* rank * ffn_local */
+    uint64_t gate_up_row_bytes;      /* bytes of one row of gate / up (k = d_model) */
+    uint64_t gate_up_byte_offset;    /* this rank's rows start here in the full gate / up */
+    uint64_t gate_up_bytes;          /* ... and span this many bytes (contiguous) */
+    uint64_t down_row_bytes_full;    /* bytes of one full row of down (k = d_ffn) */
+    uint64_t down_row_bytes_local;   /* bytes of this rank's k-slice of one row */
+    uint64_t down_row_byte_offset;   /* offset of the slice inside every full row */
+    uint64_t down_bytes;             /* d_model * down_row_bytes_local */
+} rlxq_tp_shard;
+
+/* Where rank `rank` of `world` finds its shards.  d_ffn must split into `world` slices of whole
+ * 256-weight groups (so every sliced row keeps 16-byte alignment); RLXQ_E_SHAPE otherwise. */
+RLXQ_API int rlxq_tp_shard_plan(uint32_t scheme, uint32_t d_model, uint32_t d_ffn, uint32_t world,
+                                uint32_t rank, rlxq_tp_shard* out);
+
+/* Host-side gather of the k-slice [k_begin, k_begin + k_len) of every row of a packed W[n, k] into
+ * a packed W'[n, k_len] (run once at load time). */
+RLXQ_API int rlxq_tp_slice_k_host(uint32_t scheme, const void* w_full, uint32_t n, uint32_t k,
+                                  uint32_t k_begin, uint32_t k_len, void* w_slice);
+
+/* Scratch for rlxq_tp_ffn_partial. */
+RLXQ_API int rlxq_tp_ffn_workspace_bytes(uint32_t scheme_gate_up, uint32_t scheme_down, uint32_t m,
+                                         uint32_t d_model, uint32_t ffn_local, uint32_t x_dtype, size_t* bytes);
+
+/* One rank's share of the FFN on the caller's stream:
+ *   gu = x . [gate_r ; up_r]^T   (one matmul: gate_up_blocks holds the rank's gate rows followed by
+ *                                 its up rows, 2*ffn_local rows of k = d_model)
+ *   h  = up * silu(gate)         (f32 for m <= 8; rounded to bf16 for m > 8, where it feeds the
+ *                                 tensor-core GEMM, which takes bf16 activations)
+ *   y_partial = h . down_r^T     (down_blocks: d_model rows of k = ffn_local)
+ * x: [m, d_model] f32 or bf16; y_partial: [m, d_model] f32.  workspace 256-byte aligned.
+ * No synchronisation, no allocation: capture-safe like rlxq_matmul. */
+RLXQ_API int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down,
+                                 const void* x, uint32_t x_dtype, const void* gate_up_blocks,
+                                 const void* down_blocks, float* y_partial, uint32_t m, uint32_t d_model,
+                                 uint32_t ffn_local, void* workspace, size_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLXQ_TP_H */

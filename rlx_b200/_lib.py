@@ -34,6 +34,10 @@ _SIGS = {
     "rlxq_launch_count": (u64, []),
     "rlxq_set_option": (C.c_int, [cp, i64]),
     "rlxq_get_option": (C.c_int, [cp, C.POINTER(i64)]),
+    "rlxq_tp_shard_plan": (C.c_int, [u32, u32, u32, u32, u32, vp]),
+    "rlxq_tp_slice_k_host": (C.c_int, [u32, vp, u32, u32, u32, u32, vp]),
+    "rlxq_tp_ffn_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
+    "rlxq_tp_ffn_partial": (C.c_int, [vp, u32, u32, vp, u32, vp, vp, vp, u32, u32, u32, vp, C.c_size_t]),
     "rlxq_graph_new": (vp, [cp]),
     "rlxq_graph_free": (None, [vp]),
     "rlxq_graph_input": (C.c_int, [vp, cp, u32, u32, u32]),

@@ -1,0 +1,105 @@
+"""Tensor-parallel SwiGLU FFN over packed GGUF weights: one process per GPU.
+
+`shard_plan` / `shard_weights` are host logic (rlxq_tp_shard_plan, rlxq_tp_slice_k_host).
+`TensorParallelFFN` holds one rank's shards on its GPU and runs
+    y = all_reduce_sum( down_r( up_r(x) * silu(gate_r(x)) ) )
+with the per-rank part in the C-ABI call rlxq_tp_ffn_partial and the sum through the process
+group the ranks already share (torch.distributed, NCCL on GPUs).  The reference has no device
+collective (rlx-driver/src/collective.rs:79-128 emulates them on the host); the FFN is
+rlx-flow/src/blocks/swiglu.rs:48-52.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+
+
+class Shard(C.Structure):
+    _fields_ = [("ffn_local", C.c_uint32), ("ffn_begin", C.c_uint32),
+                ("gate_up_row_bytes", C.c_uint64), ("gate_up_byte_offset", C.c_uint64),
+                ("gate_up_bytes", C.c_uint64), ("down_row_bytes_full", C.c_uint64),
+                ("down_row_bytes_local", C.c_uint64), ("down_row_byte_offset", C.c_uint64),
+                ("down_bytes", C.c_uint64)]
+
+
+def shard_plan(scheme: int, d_model: int, d_ffn: int, world: int, rank: int) -> Shard:
+    s = Shard()
+    check(lib.rlxq_tp_shard_plan(int(scheme), d_model, d_ffn, world, rank, C.byref(s)))
+    return s
+
+
+def shard_weights(scheme: int, gate: np.ndarray, up: np.ndarray, down: np.ndarray, d_model: int, d_ffn: int,
+                  world: int, rank: int) -> tuple[np.ndarray, np.ndarray, Shard]:
+    """(gate_up_r, down_r, plan): the rank's gate rows followed by its up rows, and its k-slice of
+    every row of down, as packed block bytes."""
+    p = shard_plan(scheme, d_model, d_ffn, world, rank)
+    a, b = p.gate_up_byte_offset, p.gate_up_byte_offset + p.gate_up_bytes
+    gate_up = np.concatenate([gate[a:b], up[a:b]])
+    down_r = np.empty(p.down_bytes, np.uint8)
+    down = np.ascontiguousarray(down)
+    check(lib.rlxq_tp_slice_k_host(int(scheme), down.ctypes.data, d_model, d_ffn, p.ffn_begin, p.ffn_local,
+                                   down_r.ctypes.data))
+    return gate_up, down_r, p
+
+
+def ffn_workspace_bytes(scheme: int, m: int, d_model: int, ffn_local: int, x_dtype: int) -> int:
+    out = C.c_size_t()
+    check(lib.rlxq_tp_ffn_workspace_bytes(int(scheme), int(scheme), m, d_model, ffn_local, x_dtype, C.byref(out)))
+    return out.value
+
+
+class TensorParallelFFN:
+    def __init__(self, scheme: int, d_model: int, d_ffn: int, rank: int = 0, world: int = 1, device=None,
+                 group=None):
+        import torch
+        self.torch = torch
+        self.scheme, self.d_model, self.d_ffn = int(scheme), d_model, d_ffn
+        self.rank, self.world, self.group = rank, world, group
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.plan = shard_plan(scheme, d_model, d_ffn, world, rank)
+        self.gate_up = self.down = None
+        self._ws = {}
+
+    def load(self, gate: np.ndarray, up: np.ndarray, down: np.ndarray) -> None:
+        """Full packed weights in host memory -> this rank's shards on its GPU (one upload each)."""
+        gu, dn, _ = shard_weights(self.scheme, gate, up, down, self.d_model, self.d_ffn, self.world, self.rank)
+        self.gate_up = self.torch.from_numpy(gu).to(self.device)
+        self.down = self.torch.from_numpy(dn).to(self.device)
+
+    def load_shards(self, gate_up: np.ndarray, down: np.ndarray) -> None:
+        self.gate_up = self.torch.from_numpy(gate_up).to(self.device)
+        self.down = self.torch.from_numpy(down).to(self.device)
+
+    def _workspace(self, m: int, x_dtype: int):
+        key = (m, x_dtype)
+        if key not in self._ws:
+            need = ffn_workspace_bytes(self.scheme, m, self.d_model, self.plan.ffn_local, x_dtype)
+            self._ws[key] = self.torch.empty(need + 256, dtype=self.torch.uint8, device=self.device)
+        return self._ws[key]
+
+    def partial(self, x, out=None):
+        """This rank's f32 partial [m, d_model] (no communication)."""
+        torch = self.torch
+        assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.d_model and x.is_contiguous()
+        m = x.shape[0]
+        dt = 0 if x.dtype == torch.float32 else 1
+        if out is None:
+            out = torch.empty((m, self.d_model), dtype=torch.float32, device=x.device)
+        ws = self._workspace(m, dt)
+        base = (ws.data_ptr() + 255) // 256 * 256
+        with torch.cuda.device(x.device):
+            check(lib.rlxq_tp_ffn_partial(torch.cuda.current_stream().cuda_stream, self.scheme, self.scheme,
+                                          x.data_ptr(), dt, self.gate_up.data_ptr(), self.down.data_ptr(),
+                                          out.data_ptr(), m, self.d_model, self.plan.ffn_local, base,
+                                          ws.numel() - (base - ws.data_ptr())))
+        return out
+
+    def forward(self, x, out=None):
+        y = self.partial(x, out)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y

@@ -1,0 +1,119 @@
+"""Tensor-parallel FFN: shard planner and k-slicing on the CPU (incl. a world-size-2 gloo run whose
+per-rank arithmetic is the oracle), and the per-rank CUDA path on one GPU."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from rlx_b200 import tp
+import rlx_b200 as R
+
+
+def _weights(dm, df, seed=1):
+    return (O.fill_weights(O.Q4_K, seed, dm, df), O.fill_weights(O.Q4_K, seed + 1, dm, df),
+            O.fill_weights(O.Q4_K, seed + 2, df, dm))
+
+
+def _oracle_partial(x, gate_up, down, dm, f):
+    m = x.shape[0]
+    gu = O.matmul_bt_mt(x, gate_up, m, dm, 2 * f, O.Q4_K)
+    g, u = gu[:, :f], gu[:, f:]
+    with np.errstate(over="ignore"):
+        silu = (g / (1.0 + np.exp(-g.astype(np.float32)))).astype(np.float32)
+    h = (u * silu).astype(np.float32)
+    return O.matmul_bt_mt(h, down, m, f, dm, O.Q4_K)
+
+
+def test_shard_plan_geometry():
+    p = tp.shard_plan(O.Q4_K, 8192, 28672, 8, 3)
+    assert (p.ffn_local, p.ffn_begin) == (3584, 10752)
+    assert p.gate_up_row_bytes == 4608 and p.gate_up_bytes == 3584 * 4608
+    assert p.down_row_bytes_local == 14 * 144 and p.down_row_byte_offset == 42 * 144
+    assert p.down_bytes == 8192 * 2016
+    with pytest.raises(R.RlxqError):
+        tp.shard_plan(O.Q4_K, 8192, 28672, 3, 0)         # 28672 / 3 is not whole 256-weight groups
+    with pytest.raises(R.RlxqError):
+        tp.shard_plan(O.Q4_K, 8192, 28672, 4, 4)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_shards_partition_the_weights_and_sum_to_the_full_ffn(world):
+    dm, df, m = 512, 2048, 2
+    gate, up, down = _weights(dm, df)
+    x = O.fill_normal(9, m * dm).reshape(m, dm)
+    y_ref = O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K)
+    parts, covered = [], np.zeros(len(down), bool)
+    for r in range(world):
+        gu, dn, p = tp.shard_weights(O.Q4_K, gate, up, down, dm, df, world, r)
+        # the k-slice of down decodes to the matching columns of the full matrix
+        full = O.dequant(O.Q4_K, down, dm * df).reshape(dm, df)
+        assert np.array_equal(O.dequant(O.Q4_K, dn, dm * p.ffn_local).reshape(dm, p.ffn_local),
+                              full[:, p.ffn_begin:p.ffn_begin + p.ffn_local])
+        parts.append(_oracle_partial(x, gu, dn, dm, p.ffn_local))
+    y = O.allreduce_sum(np.stack(parts))
+    wn = O.row_norms(O.Q4_K, down, df, dm)
+    h = O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, want_h=True)[1]
+    bnd = np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * wn[None, :]
+    assert np.max(np.abs(y - y_ref) / bnd) < 1e-5        # only the f32 summation order differs
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+def _gloo_rank(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dm, df, m = 512, 2048, 1
+    gate, up, down = _weights(dm, df)
+    x = O.fill_normal(9, m * dm).reshape(m, dm)
+    gu, dn, p = tp.shard_weights(O.Q4_K, gate, up, down, dm, df, world, rank)
+    y = torch.from_numpy(_oracle_partial(x, gu, dn, dm, p.ffn_local))
+    dist.all_reduce(y)                                    # the exchange step of the path
+    if rank == 0:
+        q.put(y.numpy())
+    dist.destroy_process_group()
+
+
+def test_world_size_two_gloo_all_reduce():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q, port = ctx.Queue(), _free_port()
+    procs = [ctx.Process(target=_gloo_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    y = q.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    dm, df = 512, 2048
+    gate, up, down = _weights(dm, df)
+    x = O.fill_normal(9, dm).reshape(1, dm)
+    y_ref = O.ffn_swiglu(x, gate, up, down, 1, dm, df, O.Q4_K, O.Q4_K)
+    assert np.max(np.abs(y - y_ref)) < 1e-4 * np.max(np.abs(y_ref))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,world", [(1, 1), (1, 2), (2, 4), (8, 2), (64, 2)])
+def test_per_rank_cuda_partials_sum_to_the_oracle_ffn(m, world):
+    """All ranks' shards run one after the other on one GPU; partials are summed in rank order."""
+    import torch
+    dm, df = 1024, 4096
+    gate, up, down = _weights(dm, df, seed=4)
+    x = O.fill_normal(11, m * dm).reshape(m, dm)
+    xb = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)).reshape(m, dm)
+    xd = torch.from_numpy(xb).cuda().to(torch.bfloat16)
+    parts = []
+    for r in range(world):
+        ffn = tp.TensorParallelFFN(O.Q4_K, dm, df, rank=r, world=world)
+        ffn.load(gate, up, down)
+        parts.append(ffn.partial(xd).cpu().numpy())
+    R.device_status()
+    y = O.allreduce_sum(np.stack(parts))
+    y_ref, h = O.ffn_swiglu(xb, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, want_h=True)
+    bnd = np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * O.row_norms(O.Q4_K, down, df, dm)[None, :]
+    assert np.max(np.abs(y - y_ref) / bnd) < 1e-3        # the path's bound, both layers chained
