@@ -102,6 +102,29 @@ RLXQ_API int rlxq_matmul(rlxq_stream_t stream, uint32_t scheme,
                 void* y, uint32_t y_dtype, uint32_t m, uint32_t k, uint32_t n,
                 void* workspace, size_t workspace_bytes);
 
+/* y = x . W^T for batch 1 and 2 (the streaming decode GEMV) without any device allocation and
+ * without a caller workspace.  This entry point has no counterpart in the reference.
+ *
+ * It is meant for callers that cannot obtain device memory when they need the result: a decode
+ * loop that runs after the process has frozen its allocations, a host whose device budget belongs
+ * entirely to another allocator, or code that must stay free of cudaMalloc / cudaFree after
+ * start-up.  The scratch rlxq_matmul would take from `workspace` (quantised activations, a few
+ * partial tiles, tile counters) lives instead in a fixed 2 MiB array inside this library's device
+ * image; every GPU that loads the library carries those 2 MiB until the process ends.
+ *
+ * Same arguments, results and alignment rules as rlxq_matmul with m <= 2 (k a multiple of 256,
+ * 2048 for Q6_K; x and w_blocks 16-byte aligned).  RLXQ_E_SHAPE for m > 2 or an unsupported k,
+ * RLXQ_E_LIMIT when the shape would need more scratch than the array holds (very large n * k/2048).
+ * The first call on each device resolves the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call before any stream capture.  Later calls only launch.
+ * All calls on a device share the one array, which keeps whatever the previous call left; each call
+ * rewrites or zeroes what it depends on, so calls issued one after the other (same stream, or
+ * ordered by events) are independent, but two calls whose kernels may overlap on the GPU race on it
+ * and must not be issued. */
+RLXQ_API int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme,
+                                        const void* x, uint32_t x_dtype, const void* w_blocks,
+                                        void* y, uint32_t y_dtype, uint32_t m, uint32_t k, uint32_t n);
+
 /* Once per device, with that device current and outside any stream capture: allocates the
  * library's per-device error word (4 bytes).  The reference creates its per-process device state
  * in cuda_context() (rlx-cuda/src/device.rs:44-60).  rlxq_matmul calls it lazily if it was not. */

@@ -672,7 +672,7 @@ static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_
 
 template <uint32_t SCHEME, int MM>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl) {
+                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word) {
     using T = StagedTraits<SCHEME>;
     Geometry g;
     geometry(SCHEME, &g);
@@ -693,7 +693,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes;
     P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
     P.debug = (uint32_t)options().gemv_debug.load();
-    P.err = device_error_word();
+    P.err = err_word;
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     static std::atomic<uint32_t> attr_set[64];
     int dev = 0;
@@ -717,11 +717,11 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
 
 template <uint32_t SCHEME>
 static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word) {
     const IntPlan pl = plan_int<SCHEME>(m, k, n);
     if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
-    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl);
-    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl);
+    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word);
+    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word);
 }
 
 bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
@@ -747,15 +747,103 @@ size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) 
     return pl.ok ? pl.ws_bytes : 0;
 }
 
-int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
-                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+static int launch_gemv_int_err(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
+                               void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes,
+                               int* err_word) {
     switch (scheme) {
-        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
-        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
-        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
-        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }
 }
 
+int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                    bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    return launch_gemv_int_err(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word());
+}
+
+// ---------------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library run where cudaMalloc is off the table: inside a latency-critical
+// decode loop whose memory was sized and pinned down at start-up, in a process that has handed its
+// whole device budget to another allocator, or in code reviewed under a "no allocation after
+// initialisation" rule.  rlxq_matmul needs a caller-provided workspace for the batch 1-2 GEMV
+// (quantised activations, a few partial tiles, tile counters); such callers may have nowhere to
+// take it from.  For them the same two kernels run with a workspace that lives in this library's
+// own image: a file-scope device array of fixed size that every GPU loading the library carries
+// until the process exits.
+//
+// In host code `g_static_scratch` is only a handle for the symbol, not an address the GPU can use;
+// the device address is looked up once per device with cudaGetSymbolAddress (with that device
+// current) and that pointer is what the kernels get.
+constexpr size_t kStaticScratchBytes = 2u << 20;          // 2 MiB per GPU
+static __device__ __align__(256) uint8_t g_static_scratch[kStaticScratchBytes];
+static __device__ int g_static_error_word;                // used when the device has no error word yet
+
+struct StaticScratch { uint8_t* scratch; int* err; };
+
+// First call on a device: resolve the two symbols.  No allocation; must happen outside stream
+// capture (symbol lookup may initialise the module on this device).
+static int static_scratch_for_current_device(StaticScratch* out) {
+    static std::atomic<uint8_t*> scratch_ptr[64];
+    static std::atomic<int*> err_ptr[64];
+    int dev = 0;
+    RLXQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RLXQ_E_ARG, "device ordinal %d out of range", dev);
+    uint8_t* sp = scratch_ptr[dev].load();
+    int* ep = err_ptr[dev].load();
+    if (!sp || !ep) {
+        void* a = nullptr;
+        void* b = nullptr;
+        RLXQ_CUDA_TRY(cudaGetSymbolAddress(&a, g_static_scratch));
+        RLXQ_CUDA_TRY(cudaGetSymbolAddress(&b, g_static_error_word));
+        if (!a || !b) return fail(RLXQ_E_CUDA, "cudaGetSymbolAddress returned a null device address");
+        sp = static_cast<uint8_t*>(a);
+        ep = static_cast<int*>(b);
+        scratch_ptr[dev].store(sp);
+        err_ptr[dev].store(ep);
+    }
+    out->scratch = sp;
+    out->err = ep;
+    return RLXQ_OK;
+}
+
 }  // namespace rlxq
+
+using namespace rlxq;
+
+extern "C" int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
+                                          const void* w_blocks, void* y, uint32_t y_dtype, uint32_t m, uint32_t k,
+                                          uint32_t n) {
+    Geometry g;
+    if (!geometry(scheme, &g)) return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    if ((x_dtype != RLXQ_F32 && x_dtype != RLXQ_BF16) || (y_dtype != RLXQ_F32 && y_dtype != RLXQ_BF16))
+        return fail(RLXQ_E_DTYPE, "unknown dtype");
+    if (m == 0 || n == 0) return RLXQ_OK;
+    if (m > 2) return fail(RLXQ_E_SHAPE, "the static-scratch entry point covers batch 1 and 2 only (m=%u)", m);
+    if (k == 0 || k % g.elems) return fail(RLXQ_E_SHAPE, "k=%u is not a positive multiple of the block size %u", k, g.elems);
+    if (!x || !w_blocks || !y) return fail(RLXQ_E_NULL, "null buffer");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)w_blocks & 15u)) return fail(RLXQ_E_ALIGN, "x and w_blocks must be 16-byte aligned");
+    if ((uintptr_t)y & (y_dtype == RLXQ_BF16 ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
+    if (!int_supported(scheme, m, k, n, w_blocks, x))
+        return fail(RLXQ_E_SHAPE, "the streaming GEMV needs k %% 256 == 0 (2048 for Q6_K) and activations that fit in shared memory");
+    const size_t need = int_workspace_bytes(scheme, m, k, n);
+    if (need > kStaticScratchBytes)
+        return fail(RLXQ_E_LIMIT, "this shape needs %zu bytes of scratch; the built-in scratch holds %zu", need,
+                    (size_t)kStaticScratchBytes);
+    StaticScratch ss;
+    int rc = static_scratch_for_current_device(&ss);
+    if (rc) return rc;
+    // Timeouts of bounded waits go to the device's regular error word when it already exists (so
+    // rlxq_device_status sees them); otherwise to a word in this library's image.
+    int* err = device_error_word_if_ready();
+    if (!err) err = ss.err;
+    // The activation quantiser rewrites the quantised activations, zeroes the tile counters and (in
+    // the two-contributor mode) y on every call, and partial tiles are written before they are read,
+    // so nothing left in the scratch by an earlier call is ever consumed.
+    return launch_gemv_int_err((cudaStream_t)stream, scheme, x, x_dtype == RLXQ_BF16, (const uint8_t*)w_blocks, y,
+                               y_dtype == RLXQ_BF16, m, k, n, ss.scratch, kStaticScratchBytes, err);
+}

@@ -616,20 +616,28 @@ static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const u
     return check_launch("gemv_staged_kernel");
 }
 
+static std::atomic<int*> g_error_words[64];
+
 int* device_error_word() {
-    static std::atomic<int*> words[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    int* p = words[dev].load();
+    int* p = g_error_words[dev].load();
     if (!p) {
         int* fresh = nullptr;
         if (cudaMalloc(&fresh, sizeof(int)) != cudaSuccess) return nullptr;
         if (cudaMemset(fresh, 0, sizeof(int)) != cudaSuccess) return nullptr;
         int* expected = nullptr;
-        if (words[dev].compare_exchange_strong(expected, fresh)) p = fresh;
+        if (g_error_words[dev].compare_exchange_strong(expected, fresh)) p = fresh;
         else { cudaFree(fresh); p = expected; }
     }
     return p;
+}
+
+// The word if this device already has one, else null; never allocates.
+int* device_error_word_if_ready() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return g_error_words[dev].load();
 }
 
 int staged_device_error(int* value) {

@@ -128,5 +128,6 @@ __device__ __forceinline__ uint32_t lds_u32(const uint8_t* p) {
 
 // One error word per device, allocated on first use (outside any capture), never freed.
 int* device_error_word();
+int* device_error_word_if_ready();   // never allocates; null if the device has none yet
 
 }  // namespace rlxq
