@@ -41,6 +41,12 @@ WORKLOADS = {
     "q4_k_8b_up_gemv": ("q4_k", [(4096, 14336)], "bf16"),
     "q6_k_8b_down_gemv": ("q6_k", [(14336, 4096)], "bf16"),
 }
+# Prefill GEMMs (configurations 4 and 2): name -> (scheme, m, k, n); bf16 activations and outputs.
+GEMM_WORKLOADS = {
+    "q8_0_prefill_gemm": ("q8_0", 4096, 8192, 28672),
+    "q4_0_prefill_gemm": ("q4_0", 4096, 8192, 28672),
+    "q4_k_8b_prefill_gemm": ("q4_k", 512, 4096, 14336),
+}
 # Tensor-parallel SwiGLU FFN at 70B shapes (configuration 3): handled by run_tp_workload.
 TP_WORKLOAD = "q4_k_70b_ffn_tp"
 TP_D_MODEL, TP_D_FFN = 8192, 28672
@@ -202,6 +208,149 @@ def workload_config(args, sch, layers, act, rotation):
                   f"({rotation * sum(packed_bytes(sch, k, n) for k, n in layers) / 1e6:.0f} MB) > 2 x 126 MB L2"}
 
 
+
+
+# --------------------------------------------------------------------------------------------
+# Prefill GEMM (configurations 4 and 2): compute-bound, TFLOP/s against the dense bf16 peak
+# --------------------------------------------------------------------------------------------
+def run_gemm_workload(args, rank, world, local_rank):
+    sch, m, k, n = GEMM_WORKLOADS[args.workload]
+    if args.gemm_shape:
+        m, k, n = (int(v) for v in args.gemm_shape.split(","))
+    flops = 2.0 * m * k * n
+    cfg = {"workload": args.workload, "scheme": sch, "m": m, "k": k, "n": n, "activations": "bf16", "output": "bf16",
+           "l2": "operands larger than L2: packed W %.0f MB + x %.0f MB + y %.0f MB" %
+                 (packed_bytes(sch, k, n) / 1e6, m * k * 2 / 1e6, m * n * 2 / 1e6)}
+    from oracle import oracle as O
+    sid = O.SCHEMES[sch]
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        # bounded sample of the same workload: 64 token rows x 128 weight rows x all of k, scaled by work
+        cores = os.cpu_count() or 1
+        rb = packed_bytes(sch, k, 1)
+        w = O.fill_weights(sid, 3000, k, 128)
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(79, 64 * k))).reshape(64, k)
+        O.matmul_bt_mt(x, w, 64, k, 128, sid, threads=cores)
+        steps = min(args.steps, 10)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.matmul_bt_mt(x, w, 64, k, 128, sid, threads=cores)
+        dt = (time.perf_counter() - t0) / steps
+        val = 2.0 * 64 * k * 128 / dt / 1e12
+        print(json.dumps({"impl": "reference", "metric": "gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                          "steps": steps, "warmup": args.warmup, "ms_per_step": flops / (val * 1e12) * 1e3,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": cfg,
+                          "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                           "sample": f"64 token rows x 128 weight rows x k={k} per step ({rb * 128} weight bytes), "
+                                                     f"all {cores} host threads; ms_per_step is scaled to the full shape"},
+                          "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rlxq kernels have no CPU path")
+    import rlx_b200 as R
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    w_host = O.fill_weights(sid, 3000 + rank, k, n)
+    wd = torch.from_numpy(w_host).to(dev)
+    x_host = O.fill_normal(79 + rank, m * k).reshape(m, k)
+    xd = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        R.matmul(xd, wd, SCHEME_IDS[sch], n, out=y)
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = R.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    ev0.record()
+    for _ in range(args.steps):
+        R.matmul(xd, wd, SCHEME_IDS[sch], n, out=y)
+    ev1.record()
+    sync_all()
+    R.device_status()
+    launches = R.launch_count() - launches0
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    # end to end: Graph / Session API, x and y in pinned host memory as raw bf16 bytes
+    g = R.Graph("gemm")
+    xi = g.input("x", [m, k], R.DType.BF16)
+    p = g.param("w", [len(w_host)])
+    g.set_outputs([g.dequant_matmul_packed(xi, p, R.QuantScheme(SCHEME_IDS[sch]), n, R.DType.BF16)])
+    c = R.Session(R.Device.Cuda, index=local_rank, exec_mode="graph").compile(g)
+    c.set_param_typed("w", w_host, R.DType.U8)
+    x_pin = xd.cpu().pin_memory()
+    y_pin = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        c.run_raw(["x"], [x_pin.data_ptr()], [m * k * 2], [1], y_pin.data_ptr(), m * n * 2, 1)
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        c.run_raw(["x"], [x_pin.data_ptr()], [m * k * 2], [1], y_pin.data_ptr(), m * n * 2, 1)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    torch.cuda.synchronize()
+    e2e_ok = bool(torch.equal(y_pin, y.cpu()))
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    if rank == 0:
+        peaks = {}
+        pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(pth):
+            with open(pth) as f:
+                peaks = json.load(f)
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) if ms > 100.0 else float(peaks.get("bf16_tflops", 1590.0))
+        src = ("measured (MEASURED_PEAKS.json, %s)" % ("sustained: the timed region is a long back-to-back loop" if ms > 100.0 else "burst")
+               if peaks else "fallback (1.59 PFLOP/s burst / 1.4 sustained, earlier measurement on this pool)")
+        ach = flops / (ms_per_step * 1e-3) / 1e12
+        line = {"metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg, "clocks": clocks,
+                "e2e": {"value": world * flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": m * k * 2,
+                        "d2h_bytes_per_step": m * n * 2, "ms_per_step": e2e_s * 1e3, "matches_resident_path": e2e_ok,
+                        "api": "Session(Device.Cuda).compile(graph).run_typed, pinned host buffers"},
+                "gpu_launches": launches,
+                "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                             "peak_source": src, "frac_of_burst": ach / float(peaks.get("bf16_tflops", 1590.0)),
+                             "frac_of_nominal_2250": ach / 2250.0, "kernel": "gemm_tcgen05_kernel",
+                             "flops_per_launch": flops, "avg_launch_us": ms_per_step * 1e3,
+                             "traffic": packed_bytes(sch, k, n) + m * k * 2 + m * n * 2}}
+        if not args.no_cpu_baseline and world == 1:
+            cores = os.cpu_count() or 1
+            wsub = O.fill_weights(sid, 3000, k, 128)
+            xs = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(79, 64 * k))).reshape(64, k)
+            O.matmul_bt_mt(xs, wsub, 64, k, 128, sid, threads=cores)
+            t0 = time.perf_counter(); reps = 0
+            while time.perf_counter() - t0 < 8.0 and reps < 20:
+                O.matmul_bt_mt(xs, wsub, 64, k, 128, sid, threads=cores); reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {"value": 2.0 * 64 * k * 128 / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"{reps} passes over 64 token rows x 128 weight rows x k={k}, all {cores} host threads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        finish_ranks(dist, torch)
 
 # --------------------------------------------------------------------------------------------
 # Tensor-parallel FFN (configuration 3): strong scaling, one NCCL all-reduce per step
@@ -383,9 +532,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + [TP_WORKLOAD],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + [TP_WORKLOAD],
                     help="default: the Q4_0 GEMV pair on one GPU, the tensor-parallel FFN on several")
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
+    ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -395,6 +545,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload is None:
         args.workload = "q4_0_llama7b_ffn_gemv" if world == 1 else TP_WORKLOAD
+    if args.workload in GEMM_WORKLOADS:
+        run_gemm_workload(args, rank, world, local_rank)
+        return
     if args.workload == TP_WORKLOAD:
         if args.impl == "reference":
             run_tp_reference_arm(args, rank, world)
@@ -546,10 +699,13 @@ def main() -> None:
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "kernel": "gemv_staged_kernel", "bytes_per_launch": bytes_per_launch,
+                         "kernel": "gemv_int_kernel (+ its activation quantiser)", "bytes_per_launch": bytes_per_launch,
                          "avg_launch_us": avg_launch_s * 1e6,
                          "timing": "CUDA events over the timed region / launches (includes inter-launch gaps)",
-                         "traffic": None},
+                         # dram__bytes_read + write per launch from the ncu capture summarised in
+                         # profiles/gemv_int_q4_0_llama7b_ffn_m1.md (25.43 MB for 25.42 MB algorithmic);
+                         # other workloads were not captured
+                         "traffic": 25431000 if args.workload == "q4_0_llama7b_ffn_gemv" and m == 1 else None},
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)

@@ -77,9 +77,6 @@ struct IntParams {
     uint32_t debug;
 };
 
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 // Per-thread view for the integer kernel.
 struct QLane {
     const uint8_t* row;    // this thread's tile row inside the current stage
@@ -652,22 +649,6 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     pl.ws_bytes = pl.ws_xq + pl.ws_partial + align((size_t)pl.ntiles * 4, 256);
     pl.ok = true;
     return pl;
-}
-
-template <typename Kern, typename... Args>
-static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = options().pdl.load() ? 1 : 0;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    RLXQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
-    return RLXQ_OK;
 }
 
 template <uint32_t SCHEME, int MM>

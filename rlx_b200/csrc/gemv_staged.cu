@@ -39,6 +39,7 @@
 #include "decode.cuh"
 #include "kernels.h"
 #include "staged_common.cuh"
+#include "tensormap.cuh"
 
 namespace rlxq {
 
@@ -246,80 +247,60 @@ template <> struct Unit<RLXQ_Q6_K> {
 // ---------------------------------------------------------------------------------------------
 // Activation slice -> fp16 in shared memory, with per-block sums.
 // ---------------------------------------------------------------------------------------------
+// One CTA per activation row (plus one for the zero column when m is odd).  Two passes over the
+// row: its maximum, then the exact power-of-two rescale, the fp16 conversion and the sums per
+// SUB-weight block.  Also clears the split-k tile counters of the main kernel.
 template <uint32_t SUB>
-__device__ void stage_activations(const StagedParams& P, uint32_t k0, uint32_t klen, __half* xs,
-                                  float* sxb, float bias, uint32_t* rowmax, float* inv_scale) {
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    const uint32_t nblk = klen / SUB;
-    for (uint32_t i = tid; i < nblk * P.mp; i += blockDim.x) sxb[i] = 0.f;
-    if (tid < 8) rowmax[tid] = 0u;
-    __syncthreads();
-    const uint32_t groups_per_row = klen / 8;            // 8 activations per thread step
-    const uint32_t total = groups_per_row * P.m;
-    // pass 1: max |x| per row (bit pattern of |x| orders like the value)
-    {
-        uint32_t local[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (uint32_t idx = tid; idx < total; idx += blockDim.x) {
-            const uint32_t r = idx / groups_per_row, c = (idx - r * groups_per_row) * 8;
-            uint32_t mx = 0;
-            if (P.x_bf16) {
-                const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(P.x) + (size_t)r * P.k + k0 + c);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    mx = max(mx, (w[q] << 16) & 0x7FFFFFFFu);
-                    mx = max(mx, w[q] & 0x7FFF0000u);
-                }
-            } else {
-                const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.x) + (size_t)r * P.k + k0 + c);
-                const float4 a = p[0], b = p[1];
-                const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int q = 0; q < 8; ++q) mx = max(mx, __float_as_uint(f[q]) & 0x7FFFFFFFu);
-            }
-#pragma unroll
-            for (uint32_t q = 0; q < 8; ++q) if (q == r) local[q] = max(local[q], mx);
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < 8; ++q) if (q < P.m && local[q]) atomicMax(&rowmax[q], local[q]);
+__global__ void __launch_bounds__(1024) convert_x_f16_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
+                                                             uint32_t mp, uint32_t k, float bias, __half* __restrict__ xh,
+                                                             float* __restrict__ sxb, float* __restrict__ inv,
+                                                             uint32_t* __restrict__ counters, uint32_t ncounters) {
+    griddep_launch_dependents();
+    griddep_wait();
+    __shared__ uint32_t rowmax;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid & 31u;
+    if (r == 0) for (uint32_t i = tid; i < ncounters; i += blockDim.x) counters[i] = 0u;
+    const uint32_t groups = k / 8;
+    if (r >= m) {   // padding column of the block sums
+        for (uint32_t b = tid; b < k / SUB; b += blockDim.x) sxb[(size_t)b * mp + r] = 0.f;
+        return;
     }
+    if (tid == 0) rowmax = 0u;
+    __syncthreads();
+    auto load8 = [&](uint32_t g, float (&f)[8]) {
+        if (x_bf16) {
+            const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)r * k + 8 * g);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { f[2 * q] = __uint_as_float(w[q] << 16); f[2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u); }
+        } else {
+            const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)r * k + 8 * g);
+            const float4 a = p[0], b = p[1];
+            f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        }
+    };
+    uint32_t mx = 0;
+    for (uint32_t g = tid; g < groups; g += blockDim.x) {
+        float f[8];
+        load8(g, f);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mx = max(mx, __float_as_uint(f[q]) & 0x7FFFFFFFu);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if (lane == 0 && mx) atomicMax(&rowmax, mx);
     __syncthreads();
     // exact power-of-two rescale so that the row maximum lands in [2^14, 2^15)
-    float scale[8];
-#pragma unroll
-    for (uint32_t q = 0; q < 8; ++q) {
-        const uint32_t e = (q < P.m ? rowmax[q] : 0u) >> 23;
-        uint32_t sf = 127u;                       // scale = 1 for an all-zero or non-finite row
-        if (e != 0u && e != 255u) sf = min(253u, max(1u, 268u - e));
-        scale[q] = __uint_as_float(sf << 23);
-        if (tid == 0) inv_scale[q] = __uint_as_float((254u - sf) << 23);
-    }
-    // pass 2: convert, store, and sum per SUB-weight block (SUB/8 consecutive lanes per block)
-    for (uint32_t base = warp * 32; base < total; base += nwarps * 32) {
-        const uint32_t idx = base + lane;
-        const bool active = idx < total;
-        const uint32_t r = active ? idx / groups_per_row : 0u;
-        const uint32_t c = active ? (idx - r * groups_per_row) * 8 : 0u;
-        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (active) {
-            if (P.x_bf16) {
-                const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(P.x) + (size_t)r * P.k + k0 + c);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    f[2 * q] = __uint_as_float(w[q] << 16);
-                    f[2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
-                }
-            } else {
-                const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(P.x) + (size_t)r * P.k + k0 + c);
-                const float4 a = p[0], b = p[1];
-                f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
-                f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-            }
-        }
-        float sc = 1.f;
-#pragma unroll
-        for (uint32_t q = 0; q < 8; ++q) if (q == r) sc = scale[q];
+    const uint32_t e = rowmax >> 23;
+    uint32_t sf = 127u;                       // scale = 1 for an all-zero or non-finite row
+    if (e != 0u && e != 255u) sf = min(253u, max(1u, 268u - e));
+    const float sc = __uint_as_float(sf << 23);
+    if (tid == 0) inv[r] = __uint_as_float((254u - sf) << 23);
+    if (r == 0 && tid >= m && tid < 8) inv[tid] = 1.0f;
+    // groups is a multiple of 32, so whole warps stay together and the lanes of one block are adjacent
+    for (uint32_t g = tid; g < groups; g += blockDim.x) {
+        float f[8];
+        load8(g, f);
         __half2 h[4];
         float sum = 0.f;
 #pragma unroll
@@ -328,26 +309,24 @@ __device__ void stage_activations(const StagedParams& P, uint32_t k0, uint32_t k
             const float2 back = __half22float2(h[q]);
             sum += back.x + back.y;
         }
-        if (active) {
-            uint4 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&h[0]); pk.y = *reinterpret_cast<uint32_t*>(&h[1]);
-            pk.z = *reinterpret_cast<uint32_t*>(&h[2]); pk.w = *reinterpret_cast<uint32_t*>(&h[3]);
-            *reinterpret_cast<uint4*>(xs + (size_t)r * P.xs_stride + c) = pk;
-        }
-        // groups_per_row is a multiple of SUB/8, so the lanes of one block share a row and sit
-        // in one aligned lane group
+        uint4 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h[0]); pk.y = *reinterpret_cast<uint32_t*>(&h[1]);
+        pk.z = *reinterpret_cast<uint32_t*>(&h[2]); pk.w = *reinterpret_cast<uint32_t*>(&h[3]);
+        *reinterpret_cast<uint4*>(xh + (size_t)r * k + 8 * g) = pk;
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
         if (SUB == 32) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-        if (active && (lane & (SUB / 8 - 1)) == 0) sxb[(size_t)(c / SUB) * P.mp + r] = bias * sum;
+        if ((lane & (SUB / 8 - 1)) == 0) sxb[(size_t)(8 * g / SUB) * mp + r] = bias * sum;
     }
-    __syncthreads();
 }
 
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
+struct StagedArgs { CUtensorMap wmap; StagedParams p; };
+
 template <uint32_t SCHEME>
-__global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParams P) {
+__global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const __grid_constant__ StagedArgs A) {
+    const StagedParams& P = A.p;
     using T = StagedTraits<SCHEME>;
     extern __shared__ __align__(128) uint8_t smem[];
     __half* xs = reinterpret_cast<__half*>(smem);
@@ -355,12 +334,12 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
     uint8_t* stages = smem + P.off_stage;
     float* scratch_all = reinterpret_cast<float*>(smem + P.off_scratch);
     float* red = reinterpret_cast<float*>(smem + P.off_red);      // [2][4 warps][16][8]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P.off_bar);  // full[STAGES], empty[STAGES]
-    uint32_t* misc = reinterpret_cast<uint32_t*>(bars + 2 * T::STAGES);  // rowmax[8], inv[8], abort, last
-    uint32_t* rowmax = misc;
-    float* inv_scale = reinterpret_cast<float*>(misc + 8);
-    volatile uint32_t* abort_flag = misc + 16;
-    volatile uint32_t* last_flag = misc + 17;
+    const uint32_t NS = P.nstages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P.off_bar);  // full[NS], empty[NS], xbar
+    uint32_t* misc = reinterpret_cast<uint32_t*>(bars + 2 * NS + 1);
+    volatile uint32_t* abort_flag = misc;
+    volatile uint32_t* last_flag = misc + 1;
+    griddep_launch_dependents();
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t ks = blockIdx.x % P.ksl, rgi = blockIdx.x / P.ksl;
@@ -371,10 +350,11 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
     const uint32_t stage_bytes = 16 * T::STRIDE;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < T::STAGES; ++s) {
+        for (uint32_t s = 0; s < NS; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[T::STAGES + s]), kConsumerWarps);
+            mbar_init(smem_u32(&bars[NS + s]), kConsumerWarps);
         }
+        mbar_init(smem_u32(&bars[2 * NS]), 1);
         *abort_flag = 0u;
         *last_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -387,33 +367,40 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
     const uint32_t my_tiles = (P.ntiles > rgi) ? (P.ntiles - rgi + P.rg - 1) / P.rg : 0u;
     const uint32_t total_it = my_tiles * nchunks;
     auto produce = [&](uint32_t it) {
-        // called by the whole producer warp
+        // one 2-D TMA box per stage: 16 rows x (CU units + pad); rows past n and bytes past the row
+        // end arrive as zeros (scale 0: they add nothing)
         const uint32_t tile = rgi + (it / nchunks) * P.rg, chunk = it % nchunks;
-        const uint32_t s = it % T::STAGES;
-        const uint32_t cu = min(T::CU, units - chunk * T::CU);
-        const uint32_t bytes = cu * T::UNIT_B;
+        const uint32_t s = it % NS;
         const uint32_t full = smem_u32(&bars[s]);
-        if (lane == 0) mbar_arrive_expect_tx(full, bytes * 16);
-        __syncwarp();
-        if (lane < 16) {
-            const uint32_t row = min(tile * 16 + lane, P.n - 1);   // tail tile re-reads the last row
-            const uint8_t* src = P.w + (size_t)row * P.row_bytes + (size_t)(u0 + chunk * T::CU) * T::UNIT_B;
-            bulk_g2s(smem_u32(stages + s * stage_bytes + lane * T::STRIDE), src, bytes, full);
+        if (lane == 0) {
+            mbar_arrive_expect_tx(full, stage_bytes);
+            tma_load_2d(smem_u32(stages + s * stage_bytes), &A.wmap, (int32_t)(((u0 + chunk * T::CU) * T::UNIT_B) / 8),
+                        (int32_t)(tile * 16), full);
         }
     };
     if (warp == kConsumerWarps) {
-        for (; prod_it < total_it && prod_it < T::STAGES; ++prod_it) produce(prod_it);
+        // weights never change: fill the ring before waiting for the previous kernel
+        if (lane == 0) tma_prefetch_desc(&A.wmap);
+        for (; prod_it < total_it && prod_it < NS; ++prod_it) produce(prod_it);
+        griddep_wait();
+        // this CTA's slice of the converted activations and of their block sums, by bulk copy
+        const uint32_t klen = units * 256, nblk = klen / T::SUB;
+        const uint32_t xbar = smem_u32(&bars[2 * NS]);
+        if (lane == 0) mbar_arrive_expect_tx(xbar, P.m * klen * 2 + nblk * P.mp * 4);
+        __syncwarp();
+        if (lane < P.m)
+            bulk_g2s(smem_u32(xs + (size_t)lane * P.xs_stride), P.xh_ws + (size_t)lane * P.k + (size_t)u0 * 256, klen * 2, xbar);
+        if (lane == 31)
+            bulk_g2s(smem_u32(sxb), P.sxb_ws + (size_t)(u0 * 256 / T::SUB) * P.mp, nblk * P.mp * 4, xbar);
     }
-
-    stage_activations<T::SUB>(P, u0 * 256, units * 256, xs, sxb, T::BIAS, rowmax, inv_scale);
 
     if (warp == kConsumerWarps) {
         // ---------------- producer warp ----------------
         bool dead = false;
         for (; prod_it < total_it; ++prod_it) {
-            const uint32_t s = prod_it % T::STAGES;
-            const uint32_t ph = ((prod_it / T::STAGES) & 1u) ^ 1u;
-            if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[T::STAGES + s]), ph))) {
+            const uint32_t s = prod_it % NS;
+            const uint32_t ph = ((prod_it / NS) & 1u) ^ 1u;
+            if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[NS + s]), ph))) {
                 dead = true;
                 if (lane == 0) { atomicExch(P.err, 1); *abort_flag = 1u; }
             }
@@ -432,12 +419,17 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
     L.sxb = sxb;
     float* scratch = scratch_all + warp * 512;  // 2 KB per warp
     bool dead = false;
+    griddep_wait();
+    if (!mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+        dead = true;
+        if (lane == 0) { atomicExch(P.err, 8); *abort_flag = 1u; }
+    }
     uint32_t it = 0;
     for (uint32_t ti = 0; ti < my_tiles; ++ti) {
         const uint32_t tile = rgi + ti * P.rg;
         float tot[4] = {0.f, 0.f, 0.f, 0.f};
         for (uint32_t chunk = 0; chunk < nchunks; ++chunk, ++it) {
-            const uint32_t s = it % T::STAGES, ph = (it / T::STAGES) & 1u;
+            const uint32_t s = it % NS, ph = (it / NS) & 1u;
             if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
                 dead = true;
                 if (lane == 0) { atomicExch(P.err, 2); *abort_flag = 1u; }
@@ -451,7 +443,7 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
                 for (uint32_t u = warp; u < cu; u += kConsumerWarps)
                     Unit<SCHEME>::run(L, u * T::UNIT_B, (chunk * T::CU + u) * 256, scratch, lane, tot);
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[T::STAGES + s]));
+            if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
         }
         // cross-warp reduction, fixed order
         float* rbuf = red + (ti & 1u) * (kConsumerWarps * 128);
@@ -469,7 +461,7 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
 #pragma unroll
         for (uint32_t wv = 0; wv < kConsumerWarps; ++wv) v += rbuf[wv * 128 + rrow * 8 + col];
         const bool live = col < P.m && orow < P.n;
-        v *= inv_scale[col];
+        v *= __ldg(P.inv_ws + col);
         if (P.ksl == 1) {
             if (live) {
                 const size_t o = (size_t)col * P.n + orow;
@@ -508,9 +500,9 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const StagedParam
 // ---------------------------------------------------------------------------------------------
 struct StagedPlan {
     bool ok;
-    uint32_t ksl, usl, rg, ntiles, xs_stride, mp;
+    uint32_t ksl, usl, rg, ntiles, xs_stride, mp, nstages;
     uint32_t off_sxb, off_stage, off_scratch, off_red, off_bar, smem_bytes;
-    size_t ws_partial_bytes, ws_bytes;
+    size_t ws_partial_bytes, ws_counter_bytes, ws_xh_bytes, ws_sxb_bytes, ws_bytes;
 };
 
 template <uint32_t SCHEME>
@@ -552,26 +544,38 @@ static StagedPlan plan_staged(uint32_t m, uint32_t k, uint32_t n, int64_t force_
     off += (pl.usl * 256 / T::SUB) * pl.mp * 4;
     off = align(off, 128);
     pl.off_stage = off;
-    off += T::STAGES * 16 * T::STRIDE;
+    // the ring takes what is left of half an SM's shared memory (two CTAs per SM) when that gives
+    // at least three stages, else of a whole one
+    const uint32_t stage_bytes = 16 * T::STRIDE;
+    const uint32_t tail = kConsumerWarps * 2048 + 2 * kConsumerWarps * 128 * 4 + 1024;
+    uint32_t budget = 112u * 1024u;
+    if (off + tail + 3 * stage_bytes > budget) budget = 224u * 1024u;
+    if (off + tail + 2 * stage_bytes > budget) return pl;
+    pl.nstages = (budget - off - tail) / stage_bytes;
+    if (pl.nstages > 16) pl.nstages = 16;
+    off += pl.nstages * stage_bytes;
     off = align(off, 128);
     pl.off_scratch = off;
     off += kConsumerWarps * 2048;
     pl.off_red = off;
     off += 2 * kConsumerWarps * 128 * 4;
     pl.off_bar = off;
-    off += 2 * T::STAGES * 8 + 32 * 4;
+    off += (2 * pl.nstages + 1) * 8 + 64;
     pl.smem_bytes = off;
-    if (pl.smem_bytes > 220 * 1024) return pl;
-    uint32_t occ = (220u * 1024u) / (pl.smem_bytes + 1024u);
-    if (occ > 6) occ = 6;
+    if (pl.smem_bytes > 226 * 1024) return pl;
+    uint32_t occ = (226u * 1024u) / (pl.smem_bytes + 1024u);
+    if (occ > 4) occ = 4;
     if (occ < 1) occ = 1;
     uint32_t rg = (sms * occ) / pl.ksl;
     if (rg < 1) rg = 1;
     if (rg > pl.ntiles) rg = pl.ntiles;
     pl.rg = rg;
-    pl.ws_partial_bytes = pl.ksl > 1 ? (size_t)pl.ksl * m * n * 4 : 0;
-    pl.ws_partial_bytes = (pl.ws_partial_bytes + 255) / 256 * 256;
-    pl.ws_bytes = pl.ksl > 1 ? pl.ws_partial_bytes + (size_t)pl.ntiles * 4 : 0;
+    auto al = [](size_t v) { return (v + 255) / 256 * 256; };
+    pl.ws_partial_bytes = pl.ksl > 1 ? al((size_t)pl.ksl * m * n * 4) : 0;
+    pl.ws_counter_bytes = al((size_t)pl.ntiles * 4);
+    pl.ws_xh_bytes = al((size_t)m * k * 2);
+    pl.ws_sxb_bytes = al((size_t)(k / T::SUB) * pl.mp * 4);
+    pl.ws_bytes = pl.ws_partial_bytes + pl.ws_counter_bytes + pl.ws_xh_bytes + pl.ws_sxb_bytes + 256;
     pl.ok = true;
     return pl;
 }
@@ -593,25 +597,36 @@ static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const u
     P.off_sxb = pl.off_sxb; P.off_stage = pl.off_stage; P.off_scratch = pl.off_scratch;
     P.off_red = pl.off_red; P.off_bar = pl.off_bar;
     P.debug = (uint32_t)options().gemv_debug.load();
+    P.nstages = pl.nstages;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
-    if (pl.ksl > 1) {
-        if (!ws || ws_bytes < pl.ws_bytes)
-            return fail(RLXQ_E_WORKSPACE, "split-k GEMV needs %zu workspace bytes, got %zu", pl.ws_bytes, ws_bytes);
-        if ((uintptr_t)ws & 15u) return fail(RLXQ_E_ALIGN, "workspace must be 16-byte aligned");
-        P.partial = reinterpret_cast<float*>(ws);
-        P.counters = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_partial_bytes);
-        RLXQ_CUDA_TRY(cudaMemsetAsync(P.counters, 0, (size_t)pl.ntiles * 4, stream));
-    }
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return fail(RLXQ_E_WORKSPACE, "tensor-mode GEMV needs %zu workspace bytes, got %zu", pl.ws_bytes, ws_bytes);
+    if ((uintptr_t)ws & 15u) return fail(RLXQ_E_ALIGN, "workspace must be 16-byte aligned");
+    uint8_t* wsb = reinterpret_cast<uint8_t*>(ws);
+    P.partial = reinterpret_cast<float*>(wsb);
+    P.counters = reinterpret_cast<uint32_t*>(wsb + pl.ws_partial_bytes);
+    __half* xh = reinterpret_cast<__half*>(wsb + pl.ws_partial_bytes + pl.ws_counter_bytes);
+    float* sxb = reinterpret_cast<float*>(wsb + pl.ws_partial_bytes + pl.ws_counter_bytes + pl.ws_xh_bytes);
+    float* inv = reinterpret_cast<float*>(wsb + pl.ws_partial_bytes + pl.ws_counter_bytes + pl.ws_xh_bytes + pl.ws_sxb_bytes);
+    P.xh_ws = xh; P.sxb_ws = sxb; P.inv_ws = inv;
+    StagedArgs A{};
+    A.p = P;
+    int rc = encode_weight_map(&A.wmap, w, n, P.row_bytes, T::STRIDE / 8, 16);
+    if (rc) return rc;
     static std::atomic<uint32_t> attr_set[64];
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && attr_set[dev].load() < pl.smem_bytes) {
-        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set[dev].store(220 * 1024);
+    if (dev >= 0 && dev < 64 && attr_set[dev].load() == 0) {
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        attr_set[dev].store(1);
     }
-    (void)T::STAGES;
-    gemv_staged_kernel<SCHEME><<<pl.rg * pl.ksl, kThreads, pl.smem_bytes, stream>>>(P);
+    rc = launch_pdl(convert_x_f16_kernel<T::SUB>, dim3(pl.mp), dim3(1024), 0, stream, x, (uint32_t)xbf, m, pl.mp, k,
+                    (float)T::BIAS, xh, sxb, inv, P.counters, pl.ksl > 1 ? pl.ntiles : 0u);
+    if (rc) return rc;
+    count_launch();
+    rc = launch_pdl(gemv_staged_kernel<SCHEME>, dim3(pl.rg * pl.ksl), dim3(kThreads), pl.smem_bytes, stream, A);
+    if (rc) return rc;
     count_launch();
     return check_launch("gemv_staged_kernel");
 }

@@ -64,6 +64,10 @@ struct StagedParams {
     uint32_t mp;          // m rounded up to even
     uint32_t off_sxb, off_stage, off_scratch, off_red, off_bar;  // shared-memory layout
     uint32_t debug;       // kDebug* bits, 0 in production
+    uint32_t nstages;     // ring depth (runtime: whatever shared memory is left)
+    const __half* xh_ws;  // [m][k] activations as fp16 after the row rescale (written by the converter kernel)
+    const float* sxb_ws;  // [k / SUB][mp] block sums * BIAS
+    const float* inv_ws;  // [8] 1 / row scale
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -124,6 +128,27 @@ __device__ __forceinline__ uint32_t lds_u32_2(const uint8_t* p) {  // 2-byte-ali
 }
 __device__ __forceinline__ uint32_t lds_u32(const uint8_t* p) {
     return *reinterpret_cast<const uint32_t*>(p);
+}
+
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with programmatic stream serialization (unless the "pdl" option is 0): the kernel may become
+// resident while its predecessor drains; it orders itself with griddepcontrol.wait.
+template <typename Kern, typename... Args>
+static int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = options().pdl.load() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    RLXQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, args...));
+    return RLXQ_OK;
 }
 
 // One error word per device, allocated on first use (outside any capture), never freed.
