@@ -36,7 +36,7 @@ namespace rlxq {
 constexpr uint32_t kGemmTileW = 128;    // weight rows per tile (MMA M, tensor-memory lanes)
 constexpr uint32_t kGemmTileX = 256;    // activation rows per tile (MMA N)
 constexpr uint32_t kGemmBK = 64;        // k per pipeline stage (one 128-byte swizzled row of bf16)
-constexpr uint32_t kGemmStages = 4;     // B shared-memory stages == A tensor-memory stages
+constexpr uint32_t kGemmMaxStages = 6;  // B shared-memory stages == A tensor-memory stages (4 or 5, by format)
 constexpr uint32_t kGemmRawStages = 2;  // raw weight boxes (256 weights of 128 rows each)
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------
@@ -109,12 +109,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // The raw box holds 256 weights of 128 rows; RAW_ROW bytes per row (an odd number of 16-byte
 // chunks, so one-row-per-lane 128-bit reads do not conflict).  `S` = which 64 of the 256.
 template <uint32_t SCHEME> struct GemmRaw;
-template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144; };
-template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272; };
-template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144; };
+template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144, STAGES = 5; };
+template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272, STAGES = 4; };
+template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144, STAGES = 5; };
 
 // float(b) for b in 0..255 without the conversion unit: 0x4B000000 | b is 2^23 + b
 __device__ __forceinline__ float u8_to_f32(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
+// float(b) - OFF in one exact subtraction (OFF a small integer)
+template <int OFF>
+__device__ __forceinline__ float u8_minus(uint32_t b) { return __uint_as_float(0x4B000000u | b) - (8388608.0f + (float)OFF); }
 
 template <uint32_t SCHEME, int S> struct Decode64;
 
@@ -145,8 +148,8 @@ template <int S> struct Decode64<RLXQ_Q4_0, S> {
 #pragma unroll
             for (int p = 0; p < 8; ++p) {   // weights 2p, 2p+1: low nibbles of bytes 2p, 2p+1; 16+2p..: high nibbles
                 const uint32_t word = qs[p >> 1] >> (16 * (p & 1));
-                const float l0 = d * (u8_to_f32(word & 0xFu) - 8.0f), l1 = d * (u8_to_f32((word >> 8) & 0xFu) - 8.0f);
-                const float h0 = d * (u8_to_f32((word >> 4) & 0xFu) - 8.0f), h1 = d * (u8_to_f32((word >> 12) & 0xFu) - 8.0f);
+                const float l0 = d * u8_minus<8>(word & 0xFu), l1 = d * u8_minus<8>((word >> 8) & 0xFu);
+                const float h0 = d * u8_minus<8>((word >> 4) & 0xFu), h1 = d * u8_minus<8>((word >> 12) & 0xFu);
                 v[16 * blk + p] = pack_bf16(l0, l1);
                 v[16 * blk + 8 + p] = pack_bf16(h0, h1);
             }
@@ -181,7 +184,7 @@ template <int S> struct Decode64<RLXQ_Q8_0, S> {
 #pragma unroll
             for (int p = 0; p < 16; ++p) {  // int8 -> (q + 128) unsigned -> float, minus 128
                 const uint32_t u = (q[p >> 1] ^ 0x80808080u) >> (16 * (p & 1));
-                v[16 * blk + p] = pack_bf16(d * (u8_to_f32(u & 0xFFu) - 128.0f), d * (u8_to_f32((u >> 8) & 0xFFu) - 128.0f));
+                v[16 * blk + p] = pack_bf16(d * u8_minus<128>(u & 0xFFu), d * u8_minus<128>((u >> 8) & 0xFFu));
             }
         }
     }
@@ -235,7 +238,7 @@ struct GemmParams {
 };
 
 struct GemmBars {
-    uint64_t b_full[kGemmStages], a_full[kGemmStages], stage_free[kGemmStages];
+    uint64_t b_full[kGemmMaxStages], a_full[kGemmMaxStages], stage_free[kGemmMaxStages];
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
     uint64_t d_full, d_free;
     uint32_t tmem_base, abort_flag;
@@ -244,6 +247,7 @@ struct GemmBars {
 template <uint32_t SCHEME>
 __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams P) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
+    constexpr uint32_t kGemmStages = GemmRaw<SCHEME>::STAGES;   // shared memory left after the raw boxes decides
     constexpr uint32_t RAW_BYTES = kGemmTileW * RAW_ROW;
     constexpr uint32_t B_BYTES = kGemmTileX * kGemmBK * 2;           // 32 KB
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
         bars->abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {               // the whole warp allocates all 512 columns: 256 accumulator + 4 x 32 weight stages
+    if (warp == 1) {               // the whole warp allocates all 512 columns: 256 accumulator + up to 8 x 32 weight stages
         tmem_alloc(smem_u32(&bars->tmem_base), 512);
         tmem_relinquish();
     }
@@ -352,20 +356,24 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
         const uint32_t quarter = warp & 3u, parity = (warp - 4) >> 2;
         const uint32_t row = quarter * 32 + lane;                       // weight row of the tile == tensor-memory lane
         const uint32_t lane_addr = (quarter * 32) << 16;
-        uint32_t r = 0, rph = 0, fph = 1;   // fph: parity to wait for on stage_free of this warp's two stages
+        uint32_t r = 0, rph = 0, kbg0 = 0;   // kbg0: k blocks this CTA has gone through before the current group
         bool ok = true;
         for (uint32_t t = blockIdx.x; t < ntiles && ok && !*abort_flag; t += gridDim.x) {
-            for (uint32_t g = 0; g < kgroups && ok; ++g) {
+            for (uint32_t g = 0; g < kgroups && ok; ++g, kbg0 += 4) {
                 if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_full[r]), rph)) { give_up(15); ok = false; break; }
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const uint32_t s = parity + 2 * half;                // sub-block of the group == pipeline stage
-                    if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
-                    tc_fence_after();
+                    const uint32_t sub = parity + 2 * half;              // which 64 weights of the group
+                    const uint32_t kbg = kbg0 + sub;                     // running k-block index -> ring slot and phase
+                    const uint32_t s = kbg % kGemmStages, fph = ((kbg / kGemmStages) & 1u) ^ 1u;
+                    // decode into registers first: only the store needs the stage's tensor-memory columns,
+                    // so the arithmetic stays off the free -> store -> MMA chain
                     uint32_t v[32];
                     if (parity == 0) { if (half == 0) Decode64<SCHEME, 0>::run(rp, v); else Decode64<SCHEME, 2>::run(rp, v); }
                     else             { if (half == 0) Decode64<SCHEME, 1>::run(rp, v); else Decode64<SCHEME, 3>::run(rp, v); }
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
+                    tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * s, v);
                     tmem_st_wait();
                     tc_fence_before();
@@ -373,7 +381,6 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                     if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[s]));
                 }
                 if (!ok) break;
-                fph ^= 1u;                                               // each stage is used once per group
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars->raw_empty[r]));
                 if (++r == kGemmRawStages) { r = 0; rph ^= 1u; }
@@ -445,7 +452,7 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     P.xtiles = (m + kGemmTileX - 1) / kGemmTileX;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
-    const size_t smem = 1024 + (size_t)kGemmStages * kGemmTileX * kGemmBK * 2 + (size_t)kGemmRawStages * RAW_STRIDE +
+    const size_t smem = 1024 + (size_t)GemmRaw<SCHEME>::STAGES * kGemmTileX * kGemmBK * 2 + (size_t)kGemmRawStages * RAW_STRIDE +
                         sizeof(GemmBars) + 64;
     static std::atomic<uint32_t> attr_set[64];
     int dev = 0;
