@@ -292,7 +292,8 @@ template <uint32_t SUB>
 __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
                                                          uint32_t k, int bias, uint8_t* __restrict__ xq,
                                                          uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
-                                                         uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count) {
+                                                         uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count,
+                                                         uint32_t swiglu_pair) {
     griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
     griddep_wait();                // x (and the counters) may still be in use by the previous kernel
     const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
@@ -303,7 +304,17 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
     if (gtid >= total) return;                          // whole warps leave together
     const uint32_t r = gtid / groups_per_row, c = (gtid - r * groups_per_row) * 8;
     float f[8];
-    if (x_bf16) {
+    if (swiglu_pair) {
+        // x is [m][2k] f32 = [gate | up] of a SwiGLU FFN: the activation is up * silu(gate)
+        // (rlx-cpu/src/naive.rs:54-56, rlx-cuda/src/unfuse.rs:254-293), formed here instead of in a kernel of its own
+        const float* row = reinterpret_cast<const float*>(x) + (size_t)r * 2 * k;
+        const float4 g0 = *reinterpret_cast<const float4*>(row + c), g1 = *reinterpret_cast<const float4*>(row + c + 4);
+        const float4 u0 = *reinterpret_cast<const float4*>(row + k + c), u1 = *reinterpret_cast<const float4*>(row + k + c + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = u[q] * (g[q] / (1.0f + expf(-g[q])));
+    } else if (x_bf16) {
         const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)r * k + c);
         const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -653,7 +664,7 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
 
 template <uint32_t SCHEME, int MM>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word) {
+                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair) {
     using T = StagedTraits<SCHEME>;
     Geometry g;
     geometry(SCHEME, &g);
@@ -687,7 +698,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     int rc = RLXQ_OK;
     if (!(P.debug & 16u)) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3((groups + 255) / 256), dim3(256), 0, stream, x, (uint32_t)xbf,
                         (uint32_t)MM, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
-                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u);
+                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u, pair ? 1u : 0u);
     if (rc) return rc;
     count_launch();
     rc = launch_pdl(gemv_int_kernel<SCHEME, MM>, dim3(pl.grid), dim3(kIntThreads), pl.smem_bytes, stream, P);
@@ -698,11 +709,11 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
 
 template <uint32_t SCHEME>
 static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word) {
+                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word, bool pair) {
     const IntPlan pl = plan_int<SCHEME>(m, k, n);
     if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
-    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word);
-    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word);
+    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
 }
 
 bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
@@ -730,12 +741,12 @@ size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) 
 
 static int launch_gemv_int_err(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w,
                                void* y, bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes,
-                               int* err_word) {
+                               int* err_word, bool pair = false) {
     switch (scheme) {
-        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
-        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
-        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
-        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word);
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }
 }
@@ -743,6 +754,13 @@ static int launch_gemv_int_err(cudaStream_t stream, uint32_t scheme, const void*
 int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
                     bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
     return launch_gemv_int_err(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word());
+}
+
+// y = (up * silu(gate)) . W^T with gu = [gate | up] ([m][2k] f32): the SwiGLU product is formed by the
+// activation quantiser, so the row-parallel down projection of an FFN needs no kernel in between.
+int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
+                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    return launch_gemv_int_err(stream, scheme, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word(), true);
 }
 
 // ---------------------------------------------------------------------------------------------

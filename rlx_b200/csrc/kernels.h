@@ -28,6 +28,9 @@ bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
                    uint32_t m, uint32_t k, uint32_t n);
 
+int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
+                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+
 int staged_device_error(int* value);   // synchronises the device
 int staged_prepare_device();           // allocates the per-device error word (call outside capture)
 
