@@ -112,6 +112,14 @@ template <uint32_t SCHEME> struct GemmRaw;
 template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144, STAGES = 5; };
 template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272, STAGES = 4; };
 template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144, STAGES = 5; };
+// Q6_K super-blocks are 210 bytes: group g of a row starts at byte 210 g, which is only 2-byte aligned.
+// The box starts at the 16-byte boundary below it and is 240 bytes wide (15 chunks: conflict-free, and
+// 14 + 210 <= 240); the decoder is compiled for each of the eight possible offsets 2 (g mod 8).
+template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STAGES = 4; };
+template <uint32_t SCHEME> __device__ __forceinline__ uint32_t gemm_raw_x(uint32_t g) {   // box start, 8-byte elements
+    if (SCHEME == RLXQ_Q6_K) return ((210u * g) & ~15u) / 8u;
+    return g * (GemmRaw<SCHEME>::ROW / 8u);
+}
 
 // float(b) for b in 0..255 without the conversion unit: 0x4B000000 | b is 2^23 + b
 __device__ __forceinline__ float u8_to_f32(uint32_t b) { return __uint_as_float(0x4B000000u | b) - 8388608.0f; }
@@ -221,6 +229,95 @@ template <int S> struct Decode64<RLXQ_Q4_K, S> {
     }
 };
 
+
+// Words of a row buffer at compile-time byte offsets: loads the 16-byte chunks covering [B0, B0 + LEN)
+// and hands out the 32-bit little-endian word at any even byte offset inside.
+template <int B0, int LEN> struct Span {
+    static constexpr int C0 = B0 / 16, C1 = (B0 + LEN + 15) / 16;
+    uint32_t w[4 * (C1 - C0) + 1];
+    __device__ __forceinline__ void load(const uint8_t* row) {
+#pragma unroll
+        for (int c = C0; c < C1; ++c) {
+            const uint4 t = *reinterpret_cast<const uint4*>(row + 16 * c);
+            w[4 * (c - C0)] = t.x; w[4 * (c - C0) + 1] = t.y; w[4 * (c - C0) + 2] = t.z; w[4 * (c - C0) + 3] = t.w;
+        }
+        w[4 * (C1 - C0)] = 0;
+    }
+    template <int B> __device__ __forceinline__ uint32_t word() const {
+        constexpr int rel = B - 16 * C0;
+        if (rel % 4 == 0) return w[rel / 4];
+        return __funnelshift_r(w[rel / 4], w[rel / 4 + 1], 16);
+    }
+};
+
+// S = which 64 of the 256 weights, O = byte offset of the super-block inside the 240-byte row buffer.
+// Layout ql[128] | qh[64] | sc[16] (i8) | d (f16) and element order as rlx-gguf/src/lib.rs:1070-1114.
+template <int S, int O> struct Decode64Q6 {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        constexpr int h = S / 2;
+        Span<O + 64 * h, 64> ql;
+        Span<O + 128 + 32 * h, 32> qh;
+        Span<O + 192 + 8 * h + 4 * (S % 2), 4> sc;
+        Span<O + 208, 2> dd;
+        ql.load(row); qh.load(row); sc.load(row); dd.load(row);
+        const float d = f16_bits_to_f32(dd.template word<O + 208>() & 0xFFFFu);
+        const uint32_t scw = sc.template word<O + 192 + 8 * h + 4 * (S % 2)>();   // scales 2 g4, 2 g4 + 1 of both groups
+        const float s00 = d * (float)(int8_t)(scw & 0xFFu), s01 = d * (float)(int8_t)((scw >> 8) & 0xFFu);
+        const float s10 = d * (float)(int8_t)((scw >> 16) & 0xFFu), s11 = d * (float)(int8_t)(scw >> 24);
+#pragma unroll
+        for (int gsel = 0; gsel < 2; ++gsel) {
+            const int g4 = 2 * (S % 2) + gsel;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t qlw = gsel == 0 ? word_ql<0>(ql, i) : word_ql<1>(ql, i);
+                const uint32_t qhw = word_qh(qh, i);
+                const uint32_t lo = (qlw >> (4 * (g4 >> 1))) & 0x0F0F0F0Fu;
+                const uint32_t hi = (g4 < 2 ? (qhw << (4 - 2 * g4)) : (qhw >> (2 * g4 - 4))) & 0x30303030u;
+                const uint32_t mw = lo | hi;
+                const float ds = gsel == 0 ? (i < 4 ? s00 : s01) : (i < 4 ? s10 : s11);
+                v[16 * gsel + 2 * i] = pack_bf16(ds * u8_minus<32>(mw & 0xFFu), ds * u8_minus<32>((mw >> 8) & 0xFFu));
+                v[16 * gsel + 2 * i + 1] = pack_bf16(ds * u8_minus<32>((mw >> 16) & 0xFFu), ds * u8_minus<32>(mw >> 24));
+            }
+        }
+    }
+    // word i (0..7) of the 32 ql bytes of group (g4 & 1) = GSEL (within this half) / of the 32 qh bytes
+    template <int GSEL> __device__ static __forceinline__ uint32_t word_ql(const Span<O + 64 * (S / 2), 64>& ql, int i) {
+        constexpr int base = O + 64 * (S / 2) + 32 * GSEL;
+        switch (i) {
+            case 0: return ql.template word<base>();      case 1: return ql.template word<base + 4>();
+            case 2: return ql.template word<base + 8>();  case 3: return ql.template word<base + 12>();
+            case 4: return ql.template word<base + 16>(); case 5: return ql.template word<base + 20>();
+            case 6: return ql.template word<base + 24>(); default: return ql.template word<base + 28>();
+        }
+    }
+    __device__ static __forceinline__ uint32_t word_qh(const Span<O + 128 + 32 * (S / 2), 32>& qh, int i) {
+        constexpr int base = O + 128 + 32 * (S / 2);
+        switch (i) {
+            case 0: return qh.template word<base>();      case 1: return qh.template word<base + 4>();
+            case 2: return qh.template word<base + 8>();  case 3: return qh.template word<base + 12>();
+            case 4: return qh.template word<base + 16>(); case 5: return qh.template word<base + 20>();
+            case 6: return qh.template word<base + 24>(); default: return qh.template word<base + 28>();
+        }
+    }
+};
+
+// Dispatch on the (warp-uniform) offset of group g inside its row buffer.
+template <int S>
+__device__ __forceinline__ void decode64_q6(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
+    switch (g & 7u) {
+        case 0: Decode64Q6<S, 0>::run(row, v); break;   case 1: Decode64Q6<S, 2>::run(row, v); break;
+        case 2: Decode64Q6<S, 4>::run(row, v); break;   case 3: Decode64Q6<S, 6>::run(row, v); break;
+        case 4: Decode64Q6<S, 8>::run(row, v); break;   case 5: Decode64Q6<S, 10>::run(row, v); break;
+        case 6: Decode64Q6<S, 12>::run(row, v); break;  default: Decode64Q6<S, 14>::run(row, v); break;
+    }
+}
+
+template <uint32_t SCHEME, int S>
+__device__ __forceinline__ void decode64(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
+    if constexpr (SCHEME == RLXQ_Q6_K) decode64_q6<S>(row, g, v);
+    else Decode64<SCHEME, S>::run(row, v);
+}
+
 // ---- kernel -----------------------------------------------------------------------------------
 constexpr uint32_t kGemmWarps = 16;
 constexpr uint32_t kGemmBlock = kGemmWarps * 32;
@@ -321,7 +418,7 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_empty[r]), ph)) { give_up(12); ok = false; break; }
                     const uint32_t full = smem_u32(&bars->raw_full[r]);
                     mbar_arrive_expect_tx(full, RAW_BYTES);
-                    tma_load_2d(smem_u32(raw_stage + r * RAW_STRIDE), &P.wmap, (int32_t)(g * (RAW_ROW / 8)), (int32_t)(wt * kGemmTileW), full);
+                    tma_load_2d(smem_u32(raw_stage + r * RAW_STRIDE), &P.wmap, (int32_t)gemm_raw_x<SCHEME>(g), (int32_t)(wt * kGemmTileW), full);
                     if (++r == kGemmRawStages) { r = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -370,8 +467,8 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                     // decode into registers first: only the store needs the stage's tensor-memory columns,
                     // so the arithmetic stays off the free -> store -> MMA chain
                     uint32_t v[32];
-                    if (parity == 0) { if (half == 0) Decode64<SCHEME, 0>::run(rp, v); else Decode64<SCHEME, 2>::run(rp, v); }
-                    else             { if (half == 0) Decode64<SCHEME, 1>::run(rp, v); else Decode64<SCHEME, 3>::run(rp, v); }
+                    if (parity == 0) { if (half == 0) decode64<SCHEME, 0>(rp, g, v); else decode64<SCHEME, 2>(rp, g, v); }
+                    else             { if (half == 0) decode64<SCHEME, 1>(rp, g, v); else decode64<SCHEME, 3>(rp, g, v); }
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
                     tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * s, v);
@@ -430,7 +527,8 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
-    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K) return false;
+    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K) return false;
+    if (scheme == RLXQ_Q6_K && k % 2048) return false;   // rows must stay 16-byte aligned
     if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
     return true;
 }
@@ -475,7 +573,8 @@ int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const ui
         case RLXQ_Q4_0: return launch_gemm_t<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n);
         case RLXQ_Q8_0: return launch_gemm_t<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n);
         case RLXQ_Q4_K: return launch_gemm_t<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n);
-        default: return fail(RLXQ_E_SCHEME, "the tcgen05 GEMM covers Q4_0, Q8_0 and Q4_K");
+        case RLXQ_Q6_K: return launch_gemm_t<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n);
+        default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }
 }
 

@@ -42,7 +42,8 @@ def _run(s, w, xb, n, y_bf16=False, kernel=0):
 
 
 SHAPES = [("q4_0", 256, 256, 128), ("q4_0", 9, 512, 130), ("q8_0", 300, 512, 200), ("q8_0", 512, 1024, 256),
-          ("q4_k", 512, 1024, 384), ("q4_k", 130, 2048, 77), ("q4_0", 1000, 4096, 640)]
+          ("q4_k", 512, 1024, 384), ("q4_k", 130, 2048, 77), ("q4_0", 1000, 4096, 640),
+          ("q6_k", 256, 2048, 128), ("q6_k", 300, 4096, 200), ("q6_k", 64, 6144, 131)]
 
 
 @pytest.mark.parametrize("sch,m,k,n", SHAPES)
@@ -83,7 +84,8 @@ def test_gemm_is_deterministic_and_matches_generic_kernel():
     assert_within_tolerance(a, g, bound(s, w, x, n), tol=_tol(k), what="tc vs generic")
 
 
-@pytest.mark.parametrize("sch,m,k,n", [("q4_k", 512, 4096, 14336), ("q8_0", 4096, 8192, 28672), ("q4_0", 4096, 8192, 28672)])
+@pytest.mark.parametrize("sch,m,k,n", [("q4_k", 512, 4096, 14336), ("q6_k", 512, 14336, 4096),
+                                       ("q8_0", 4096, 8192, 28672), ("q4_0", 4096, 8192, 28672)])
 def test_prefill_configurations_sampled(sch, m, k, n):
     """Configurations 2 (M=512) and 4 (M=4096) at full size on the GPU; the oracle checks three
     bands of 64 output columns for 96 sampled token rows (the CPU needs minutes for all of it)."""
