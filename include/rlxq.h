@@ -77,8 +77,10 @@ RLXQ_API int rlxq_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32
 RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t* bytes);
 
 /* Replaces dequant_gguf_scratch_bytes (rlx-cuda/src/gguf_gpu.rs:35-59) at plan time: the
- * scratch rlxq_matmul needs for this shape: 0 unless the GEMV splits k over several CTAs, and
- * then a few partial output rows (ksl*m*n*4 bytes); the reference reserves k*n*4 bytes. */
+ * scratch rlxq_matmul needs for this shape.  For m <= 8 that is the converted activations
+ * (a few bytes per element of x), the partial output tiles of CTAs that share a row tile and
+ * their counters: tens to hundreds of KiB.  The tensor-core GEMM needs none.  The reference
+ * reserves k*n*4 bytes. */
 RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
                          uint32_t x_dtype, uint32_t y_dtype, size_t* bytes);
 
@@ -146,6 +148,10 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
  *                  GEMV, 3 = force the staged integer GEMV (2, 3: error if the shape does not allow it)
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
+ *   "gemm_tile_x": 0 = automatic, 128 or 256 = activation rows per tile of the tcgen05 GEMM
+ *   "gemv_inline_q": 0 = automatic, 1 = the integer GEMV always runs its activation quantiser as a
+ *                  kernel of its own, 2 = the streaming kernel quantises the activations itself
+ *                  whenever the shape allows it
  *   "gemv_kslices": 0 = automatic, n > 0 = split k over n CTAs per row tile in the staged GEMV
  *   "pdl": 1 (default) = launch the GEMV kernels with programmatic stream serialization so a
  *          kernel's weight prefetch overlaps the tail of its predecessor, 0 = plain launches

@@ -146,6 +146,17 @@ int rlxq_set_option(const char* key, int64_t value) {
     if (!strcmp(key, "gemv_kslices")) { options().gemv_kslices = value; return RLXQ_OK; }
     if (!strcmp(key, "gemv_debug")) { options().gemv_debug = value; return RLXQ_OK; }
     if (!strcmp(key, "pdl")) { options().pdl = value; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_early")) { options().gemv_early = value < 0 ? 0 : value; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_inline_q")) {
+        if (value < 0 || value > 2) return fail(RLXQ_E_ARG, "gemv_inline_q must be 0, 1 or 2");
+        options().gemv_inline_q = value;
+        return RLXQ_OK;
+    }
+    if (!strcmp(key, "gemm_tile_x")) {
+        if (value != 0 && value != 128 && value != 256) return fail(RLXQ_E_ARG, "gemm_tile_x must be 0, 128 or 256");
+        options().gemm_tile_x = value;
+        return RLXQ_OK;
+    }
     return fail(RLXQ_E_ARG, "unknown option '%s'", key);
 }
 
@@ -156,6 +167,9 @@ int rlxq_get_option(const char* key, int64_t* value) {
     if (!strcmp(key, "gemv_kslices")) { *value = options().gemv_kslices; return RLXQ_OK; }
     if (!strcmp(key, "gemv_debug")) { *value = options().gemv_debug; return RLXQ_OK; }
     if (!strcmp(key, "pdl")) { *value = options().pdl; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_early")) { *value = options().gemv_early; return RLXQ_OK; }
+    if (!strcmp(key, "gemv_inline_q")) { *value = options().gemv_inline_q; return RLXQ_OK; }
+    if (!strcmp(key, "gemm_tile_x")) { *value = options().gemm_tile_x; return RLXQ_OK; }
     return fail(RLXQ_E_ARG, "unknown option '%s'", key);
 }
 

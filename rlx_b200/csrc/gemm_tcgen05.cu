@@ -34,7 +34,7 @@
 namespace rlxq {
 
 constexpr uint32_t kGemmTileW = 128;    // weight rows per tile (MMA M, tensor-memory lanes)
-constexpr uint32_t kGemmTileX = 256;    // activation rows per tile (MMA N)
+constexpr uint32_t kGemmTileXMax = 256; // activation rows per tile (MMA N): 256, or 128 when that fills more SMs
 constexpr uint32_t kGemmBK = 64;        // k per pipeline stage (one 128-byte swizzled row of bf16)
 constexpr uint32_t kGemmMaxStages = 6;  // B shared-memory stages == A tensor-memory stages (4 or 5, by format)
 constexpr uint32_t kGemmRawStages = 2;  // raw weight boxes (256 weights of 128 rows each)
@@ -98,7 +98,9 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
     return d;
 }
 // Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, M = 128, N = 256.
-constexpr uint32_t kGemmIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kGemmTileX >> 3) << 17) | ((kGemmTileW >> 4) << 24);
+template <uint32_t TX> struct GemmIdesc {
+    static constexpr uint32_t value = (1u << 4) | (1u << 7) | (1u << 10) | ((TX >> 3) << 17) | ((kGemmTileW >> 4) << 24);
+};
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);       // .x (low half) = lo
@@ -341,7 +343,7 @@ struct GemmBars {
     uint32_t tmem_base, abort_flag;
 };
 
-template <uint32_t SCHEME>
+template <uint32_t SCHEME, uint32_t kGemmTileX>
 __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams P) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
     constexpr uint32_t kGemmStages = GemmRaw<SCHEME>::STAGES;   // shared memory left after the raw boxes decides
@@ -440,7 +442,7 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                     const uint64_t bdesc = kmajor_sw128_desc(smem_u32(b_stage + s * B_BYTES));
 #pragma unroll
                     for (uint32_t j = 0; j < kGemmBK / 16; ++j)
-                        tc_mma_ts(tmem_d, tmem_a + 32 * s + 8 * j, bdesc + 2 * j, kGemmIdesc, (kb | j) ? 1u : 0u);
+                        tc_mma_ts(tmem_d, tmem_a + 32 * s + 8 * j, bdesc + 2 * j, GemmIdesc<kGemmTileX>::value, (kb | j) ? 1u : 0u);
                     tc_commit(smem_u32(&bars->stage_free[s]));     // frees the B stage and the A columns when the MMAs retire
                     if (++s == kGemmStages) { s = 0; ph ^= 1u; }
                 }
@@ -533,7 +535,7 @@ bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
     return true;
 }
 
-template <uint32_t SCHEME>
+template <uint32_t SCHEME, uint32_t TX>
 static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
                          uint32_t k, uint32_t n) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
@@ -541,39 +543,51 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     Geometry g;
     geometry(SCHEME, &g);
     GemmParams P{};
-    int rc = encode_bf16_kmajor_map(&P.xmap, x, m, k, kGemmTileX);
+    int rc = encode_bf16_kmajor_map(&P.xmap, x, m, k, TX);
     if (rc) return rc;
     rc = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, RAW_ROW / 8, kGemmTileW);
     if (rc) return rc;
     P.y = y; P.m = m; P.n = n; P.k = k; P.y_bf16 = ybf;
     P.wtiles = (n + kGemmTileW - 1) / kGemmTileW;
-    P.xtiles = (m + kGemmTileX - 1) / kGemmTileX;
+    P.xtiles = (m + TX - 1) / TX;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
-    const size_t smem = 1024 + (size_t)GemmRaw<SCHEME>::STAGES * kGemmTileX * kGemmBK * 2 + (size_t)kGemmRawStages * RAW_STRIDE +
+    const size_t smem = 1024 + (size_t)GemmRaw<SCHEME>::STAGES * TX * kGemmBK * 2 + (size_t)kGemmRawStages * RAW_STRIDE +
                         sizeof(GemmBars) + 64;
     static std::atomic<uint32_t> attr_set[64];
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && attr_set[dev].load() == 0) {
-        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<SCHEME, TX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev].store(1);
     }
     uint32_t grid = (uint32_t)sm_count();
     const uint32_t ntiles = P.wtiles * P.xtiles;
     if (grid > ntiles) grid = ntiles;
-    gemm_tcgen05_kernel<SCHEME><<<grid, kGemmBlock, smem, stream>>>(P);
+    gemm_tcgen05_kernel<SCHEME, TX><<<grid, kGemmBlock, smem, stream>>>(P);
     count_launch();
     return check_launch("gemm_tcgen05_kernel");
+}
+
+// 256-row activation tiles halve the activation traffic per FLOP; 128-row tiles are used when the
+// wider ones would leave more than a quarter of the SMs without a tile.
+template <uint32_t SCHEME>
+static int launch_gemm_s(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
+                         uint32_t k, uint32_t n) {
+    const uint32_t wt = (n + kGemmTileW - 1) / kGemmTileW, sms = (uint32_t)sm_count();
+    const int64_t force = options().gemm_tile_x.load();
+    const bool narrow = force ? force == 128 : (wt * ((m + 255) / 256) * 4 < sms * 3);
+    if (narrow) return launch_gemm_t<SCHEME, 128>(stream, x, w, y, ybf, m, k, n);
+    return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n);
 }
 
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
                    uint32_t m, uint32_t k, uint32_t n) {
     switch (scheme) {
-        case RLXQ_Q4_0: return launch_gemm_t<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q8_0: return launch_gemm_t<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q4_K: return launch_gemm_t<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q6_K: return launch_gemm_t<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n);
+        case RLXQ_Q4_0: return launch_gemm_s<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n);
+        case RLXQ_Q8_0: return launch_gemm_s<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n);
+        case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n);
+        case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }
 }

@@ -1,31 +1,32 @@
 // Streaming decode GEMV for batch 1-2: integer dot products (dp4a) on raw block quants.
 //
-// Two kernels per call.
+// The activations are quantised once to two int8 limbs per value, X = round(x / s_b) in
+// [-16256, 16256] = 128*h + l, one f32 scale s_b per 32 values, with the integer block sums the
+// formats' offsets need.  Weights are never converted: four 4-bit (or 8-, 6-bit) quants are masked
+// into one register and multiplied against four activations by one dp4a, exact in int32; one
+// int->float conversion and one FMA per 32-weight block apply d_block * s_block (f32 from there on).
 //
-// 1. quantise_x_kernel (tiny): the activations are quantised once to two int8 limbs per value,
-//    X = round(x / s_b) in [-16256, 16256] = 128*h + l, one f32 scale s_b per 32 values, with the
-//    integer block sums the formats' offsets need, into the call's workspace.  It also clears
-//    the tile counters of the main kernel.
+// gemv_int_kernel (the streaming kernel).  Persistent CTAs, two per SM.  All CTAs together walk one
+// global list of work items, (16-row weight tile, 2048-weight chunk), split into equal contiguous
+// ranges ("stream-K"), so every SM streams the same number of bytes whatever n and k are.  Per CTA
+// a producer warp keeps a ring of shared-memory stages full, one 2-D TMA box (16 rows x one chunk)
+// and one mbarrier per stage; the ring takes all the shared memory the CTA has.  Eight consumer
+// warps take one 256-weight unit of the stage each; a finisher warp adds their partial sums and
+// writes the tile, so the consumers never wait on global memory.
 //
-// 2. gemv_int_kernel (the streaming kernel).  Persistent CTAs, two per SM.  All CTAs together
-//    walk one global list of work items, (16-row weight tile, 2048-weight chunk), split into
-//    equal contiguous ranges ("stream-K"), so every SM streams the same number of bytes whatever
-//    n and k are.  Per CTA a producer warp keeps a ring of shared-memory stages full with 1-D
-//    bulk async copies (cp.async.bulk + mbarrier complete_tx; one copy = one row's 16-byte-
-//    aligned run of whole blocks; the ring takes all the shared memory the CTA has, about 90 KB
-//    in flight per CTA) and eight consumer warps take one 256-weight unit of the stage each.
-//    The quantised activations arrive by bulk copy too.  Weights are never converted: four 4-bit
-//    (or 8-, 6-bit) quants are masked into one register and multiplied against four activations
-//    by one dp4a, exact in int32; one int->float conversion and one FMA per 32-weight block apply
-//    d_block * s_block (f32 from there on).  A thread owns (tile row, half of a unit): the two
-//    halves of a warp read the same activation words (broadcast) and contiguous, 8-byte-aligned
-//    weight words.  A tile whose chunks fall into more than one CTA's range is finished by the
-//    CTA that arrives last at the tile's counter: it adds the partial tiles in chunk order, so the
-//    result does not depend on timing and no CTA waits for another.
+// Two ways to run it:
+//  * single-kernel mode (m*k <= 12288, tiles shared by at most two CTAs): the consumer warps
+//    quantise the activations themselves into shared memory.  Two ring stages are requested before
+//    the dependency wait (weights are immutable, so they overlap the previous kernel's tail), then
+//    the activation loads, then the rest of the ring: a load issued behind a full ring of weight
+//    requests waits for microseconds in the SM's memory queue.  A tile shared by two CTAs is
+//    completed through a token exchange that needs no zeroed memory.
+//  * two-kernel mode (everything else): quantise_x_kernel writes the quantised activations to the
+//    workspace, clears the tile counters (and y for the two-contributor add mode); the streaming
+//    kernel fetches them by bulk copy.
 //
-// Both kernels use programmatic dependent launch: the streaming kernel is made resident while
-// its predecessor drains and prefetches its first weight stages (weights are immutable) before
-// griddepcontrol.wait, so back-to-back launches do not pay the pipeline fill each time.
+// All kernels use programmatic dependent launch: the streaming kernel is made resident while its
+// predecessor drains and requests weight stages before griddepcontrol.wait.
 //
 // Error: the activation quantisation only; |y - y_exact| <= 2^-15 * sqrt(32) * |x| * |w_row|
 // = 1.7e-4 * |x| * |w_row| in the worst case, about 1e-6 typically, plus f32 accumulation over
@@ -34,6 +35,8 @@
 //
 // Replaces, for m <= 2, the reference's dequantise-everything + cublasSgemm
 // (rlx-cuda/src/gguf_gpu.rs:62-134).
+#include <chrono>
+
 #include "common.cuh"
 #include "decode.cuh"
 #include "kernels.h"
@@ -45,17 +48,19 @@ namespace rlxq {
 constexpr uint32_t kIntWarps = 8;                      // consumer warps
 constexpr uint32_t kIntThreads = (kIntWarps + 2) * 32; // + one producer warp + one finisher warp
 constexpr uint32_t kIntRB = 4;                         // ring of reduction buffers between consumers and finisher
+constexpr uint32_t kInlineGroups = 6;                   // single-kernel mode: groups of 8 activations a consumer thread quantises
 constexpr uint32_t kIntCU = 8;                         // 256-weight units per stage = one per warp
 
 // A stage is NB boxes of 16 rows x UB units, each box fetched by ONE 2-D TMA request (a request
 // per row costs about 250 cycles of issue time each and caps the stream near 3 TB/s; one box per
-// request does not).  A box row is UB units plus 16 bytes (read from the next units, or zero past
-// the row end) so that rows do not all start on the same shared-memory bank; Q6_K's 1680-byte
-// rows already do not.  TMA boxes are at most 256 eight-byte elements wide, hence two for Q8_0.
+// request does not).  A box row is UB units plus 16 bytes (32 for Q4_0, whose lane mapping wants a
+// row pitch of 8 words mod 32), read from the next units or zero past the row end, so that rows do
+// not all start on the same shared-memory bank; Q6_K's 1680-byte rows already do not.  TMA boxes
+// are at most 256 eight-byte elements wide, hence two for Q8_0.
 template <uint32_t SCHEME> struct IntBox {
     static constexpr uint32_t NB = (SCHEME == RLXQ_Q8_0) ? 2u : 1u;
     static constexpr uint32_t UB = kIntCU / NB;                               // units per box
-    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : 16u);
+    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : SCHEME == RLXQ_Q4_0 ? 32u : 16u);
     static constexpr uint32_t BOX_BYTES = 16 * ROW;
     static constexpr uint32_t STAGE_BYTES = NB * BOX_BYTES;
 };
@@ -71,35 +76,73 @@ struct IntParams {
     uint32_t k, n, y_bf16;
     uint32_t use_red;      // shared tiles have exactly two contributors: add them into zeroed f32 y
     uint32_t row_bytes, ntiles, nchunks, total_chunks, slots;
+    uint32_t chunks_q, chunks_r;   // total_chunks = grid * chunks_q + chunks_r: the first chunks_r CTAs take one more
     uint32_t nstages;
     uint32_t xq_row_bytes; // bytes of one row of xq
     uint32_t off_stage, off_red, off_bar;
     uint32_t debug;
+    // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
+    // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
+    uint32_t inline_q;
+    const void* x;         // [MM][k] activations, f32 or bf16 (single-kernel mode)
+    uint32_t x_bf16;
+    unsigned long long* flags;   // [ntiles] rendezvous words of shared tiles (single-kernel mode)
+    unsigned long long token;    // odd, unique to this call
+    uint32_t early;              // single-kernel mode: stages requested before the dependency wait
+    uint32_t tslot;              // development builds: which trace slot this launch writes
 };
 
-// Per-thread view for the integer kernel.
+// Per-thread view for the integer kernel.  Everything is a 32-bit shared-memory byte address: the
+// inner loops then run on 32-bit address arithmetic and ld.shared, never on generic 64-bit pointers.
 struct QLane {
-    const uint8_t* row;    // this thread's tile row inside the current stage
-    const int8_t* xh;      // high limbs of activation row 0
-    const int8_t* xl;      // low limbs of activation row 0
-    const float* sb;       // [k/32]  scale of each 32-value activation block
-    const int* sx;         // [k/SUB] offset-premultiplied integer block sums (format specific)
-    uint32_t xstride;      // bytes between activation rows (all four arrays of a row move together)
-    uint32_t xstride4;     // the same in 4-byte words
-    uint32_t half;         // which half of a 256-weight unit this thread handles
+    uint32_t row;      // this thread's tile row inside the current stage
+    uint32_t xh, xl;   // limb planes of activation row 0, already advanced to this thread's half (+128 * half)
+    uint32_t sb;       // f32 scale per 32 activations, advanced by 16 * half
+    uint32_t sx;       // i32 offset-premultiplied block sums, advanced to this thread's half
+    uint32_t xstride;  // bytes between activation rows (all four arrays of a row move together)
+    uint32_t half;     // which half of a 256-weight unit this thread handles
+    uint32_t lane;
+    uint32_t row_pitch; // bytes between tile rows inside a stage
 };
 
-__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
-__device__ __forceinline__ uint2 lds64(const void* p) { return *reinterpret_cast<const uint2*>(p); }
+#ifdef RLXQ_TRACE
+// Timeline instrumentation for development builds only (never compiled into the shipped library).
+__device__ unsigned long long g_trace[4][512][16];
+__device__ unsigned long long g_trace_q[4][4];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define RLXQ_T(slot, ev) do { if (blockIdx.x < 512) g_trace[(slot) & 3][blockIdx.x][ev] = gtime(); } while (0)
+#else
+#define RLXQ_T(slot, ev) do { } while (0)
+#endif
 
-// Sum over 32 weights of q * X for one activation row: q words against the two limb planes.
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float ldsf(uint32_t a) { return __uint_as_float(lds32(a)); }
+
+// Sum over 4*NW weights of q * X for one activation row: q words against the two limb planes.
 template <int NW>
-__device__ __forceinline__ int dot_limbs(const uint32_t (&q)[NW], const int8_t* xh, const int8_t* xl,
-                                         uint32_t k, int init_low) {
+__device__ __forceinline__ int dot_limbs(const uint32_t (&q)[NW], uint32_t xh, uint32_t xl, int init_low) {
     int ah = 0, al = init_low;
 #pragma unroll
     for (int i = 0; i < NW; i += 4) {
-        const uint4 h = lds128(xh + k + 4 * i), l = lds128(xl + k + 4 * i);
+        const uint4 h = lds128(xh + 4 * i), l = lds128(xl + 4 * i);
         ah = __dp4a((int)q[i], (int)h.x, ah);         al = __dp4a((int)q[i], (int)l.x, al);
         ah = __dp4a((int)q[i + 1], (int)h.y, ah);     al = __dp4a((int)q[i + 1], (int)l.y, al);
         ah = __dp4a((int)q[i + 2], (int)h.z, ah);     al = __dp4a((int)q[i + 2], (int)l.z, al);
@@ -110,51 +153,108 @@ __device__ __forceinline__ int dot_limbs(const uint32_t (&q)[NW], const int8_t* 
 
 template <uint32_t SCHEME, int MM> struct QUnit;
 
-// ---- Q4_0: unit = 8 blocks of 18 bytes; a thread takes 4 consecutive blocks (72 bytes) ----
+// In every run(): u = unit inside the box row, kb = index of the unit's first weight in the row.
+
+// Defaults of the per-format mappings: a lane is (tile row = lane & 15, half of the unit = lane >> 4)
+// and keeps one accumulator per activation row.
+template <int MM> struct QUnitRowHalf {
+    static constexpr int NT = 1;                                           // accumulators per activation row
+    static constexpr uint32_t STRIDE_ROWS = 1;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane & 15u; }
+    __device__ static __forceinline__ void finalize(float (&)[MM], uint32_t) {}
+};
+
+// ---- Q4_0: unit = 8 blocks of 18 bytes.  Lane = (block b = lane & 7, row group rq = lane >> 3): it
+// takes block b of the four tile rows rq, rq + 4, rq + 8, rq + 12.  The 32 activations of block b stay
+// in registers for all four rows, so a weight costs a quarter of the shared-memory traffic a
+// (row, half-unit) mapping pays for re-reading activations; with a row pitch of 8 words mod 32 the
+// weight reads of a warp fall on 32 different banks.  The eight block sums of a row meet in finalize().
 template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
-    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
-        const uint8_t* p = L.row + u * 144 + 72 * L.half;
-        uint32_t w[18];
+    static constexpr int NT = 4;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 3; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[NT * MM]) {
+        const uint32_t b = L.lane & 7u, odd = b & 1u;
+        const uint32_t sh = 16u + 16u * odd, dsh = 16u * odd;
+        // an even block starts on a word (d, then the quants from byte 2); an odd one two bytes into a word
+        const uint32_t p = L.row + u * 144 + 36 * (b >> 1) + 16 * odd;
+        const uint32_t kx = kb + 32 * b;
+        uint4 xh[MM][2], xl[MM][2];
+        float sbv[MM];
+        int sxv[MM];
 #pragma unroll
-        for (int i = 0; i < 9; ++i) { const uint2 v = lds64(p + 8 * i); w[2 * i] = v.x; w[2 * i + 1] = v.y; }
+        for (int m = 0; m < MM; ++m) {
+            const uint32_t o = m * L.xstride;
+            xh[m][0] = lds128(L.xh + o + kx); xh[m][1] = lds128(L.xh + o + kx + 16);
+            xl[m][0] = lds128(L.xl + o + kx); xl[m][1] = lds128(L.xl + o + kx + 16);
+            sbv[m] = ldsf(L.sb + o + (kx >> 3));
+            sxv[m] = (int)lds32(L.sx + o + (kx >> 3));   // -8 * sum(X): the format's offset
+        }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int base = (j >> 1) * 9;            // two blocks = 36 bytes = 9 words
-            uint32_t qs[4], dbits;
-            if ((j & 1) == 0) {                       // block starts on a word: d | qs shifted by 2 bytes
-                dbits = w[base] & 0xFFFFu;
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t pr = p + 4 * i * L.row_pitch;
+            uint32_t w[5];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) qs[i] = __funnelshift_r(w[base + i], w[base + i + 1], 16);
-            } else {                                  // block starts 2 bytes into word base+4
-                dbits = w[base + 4] >> 16;
+            for (int j = 0; j < 5; ++j) w[j] = lds32(pr + 4 * j);
+            const float d = f16_bits_to_f32((w[0] >> dsh) & 0xFFFFu);
+            uint32_t lo[4], hi[4];                    // low nibbles: weights 0..15 of the block, high: 16..31
 #pragma unroll
-                for (int i = 0; i < 4; ++i) qs[i] = w[base + 5 + i];
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t qs = __funnelshift_rc(w[j], w[j + 1], sh);
+                lo[j] = qs & 0x0F0F0F0Fu;
+                hi[j] = (qs >> 4) & 0x0F0F0F0Fu;
             }
-            // low nibbles are weights 0..15 of the block, high nibbles 16..31
-            uint32_t q[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { q[i] = qs[i] & 0x0F0F0F0Fu; q[4 + i] = (qs[i] >> 4) & 0x0F0F0F0Fu; }
-            const float d = f16_bits_to_f32(dbits);
-            const uint32_t blk = (kb >> 5) + 4 * L.half + j;
 #pragma unroll
             for (int m = 0; m < MM; ++m) {
-                // sx holds -8 * sum(X): the format's offset
-                const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, L.sx[m * L.xstride4 + blk]);
-                tot[m] = fmaf(d * L.sb[m * L.xstride4 + blk], (float)c, tot[m]);
+                int ah = 0, al = sxv[m];
+                ah = __dp4a((int)lo[0], (int)xh[m][0].x, ah);  al = __dp4a((int)lo[0], (int)xl[m][0].x, al);
+                ah = __dp4a((int)lo[1], (int)xh[m][0].y, ah);  al = __dp4a((int)lo[1], (int)xl[m][0].y, al);
+                ah = __dp4a((int)lo[2], (int)xh[m][0].z, ah);  al = __dp4a((int)lo[2], (int)xl[m][0].z, al);
+                ah = __dp4a((int)lo[3], (int)xh[m][0].w, ah);  al = __dp4a((int)lo[3], (int)xl[m][0].w, al);
+                ah = __dp4a((int)hi[0], (int)xh[m][1].x, ah);  al = __dp4a((int)hi[0], (int)xl[m][1].x, al);
+                ah = __dp4a((int)hi[1], (int)xh[m][1].y, ah);  al = __dp4a((int)hi[1], (int)xl[m][1].y, al);
+                ah = __dp4a((int)hi[2], (int)xh[m][1].z, ah);  al = __dp4a((int)hi[2], (int)xl[m][1].z, al);
+                ah = __dp4a((int)hi[3], (int)xh[m][1].w, ah);  al = __dp4a((int)hi[3], (int)xl[m][1].w, al);
+                tot[i * MM + m] = fmaf(d * sbv[m], (float)(ah * 128 + al), tot[i * MM + m]);
             }
         }
+    }
+    // Adds the eight block lanes of every row (a fixed butterfly: the order never changes) and hands
+    // lane l < 16 the total of tile row l in tot[0 .. MM); lanes 16..31 get zero.
+    __device__ static __forceinline__ void finalize(float (&tot)[NT * MM], uint32_t lane) {
+#pragma unroll
+        for (int t = 0; t < NT * MM; ++t) {
+            float v = tot[t];
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+            tot[t] = v;
+        }
+        // tile row l = rq + 4 i lives in lane group rq = l & 3 as accumulator i = l >> 2
+        float out[MM];
+#pragma unroll
+        for (int m = 0; m < MM; ++m) out[m] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int m = 0; m < MM; ++m) {
+                const float v = __shfl_sync(0xFFFFFFFFu, tot[i * MM + m], (lane & 3u) * 8u);
+                if (lane < 16u && (lane >> 2) == (uint32_t)i) out[m] = v;
+            }
+#pragma unroll
+        for (int m = 0; m < MM; ++m) tot[m] = out[m];
     }
 };
 
 // ---- Q8_0: unit = 8 blocks of 34 bytes; a thread takes 4 consecutive blocks (136 bytes) ----
-template <int MM> struct QUnit<RLXQ_Q8_0, MM> {
+template <int MM> struct QUnit<RLXQ_Q8_0, MM> : QUnitRowHalf<MM> {
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
-        const uint8_t* p = L.row + u * 272 + 136 * L.half;
+        const uint32_t p = L.row + u * 272 + 136 * L.half;
+        const uint32_t xh = L.xh + kb, xl = L.xl + kb, sb = L.sb + (kb >> 3);
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {              // two blocks = 68 bytes = 17 words at a time
             uint32_t w[18];
 #pragma unroll
-            for (int i = 0; i < 9; ++i) { const uint2 v = lds64(p + 68 * jj - 4 * jj + 8 * i); w[2 * i] = v.x; w[2 * i + 1] = v.y; }
+            for (int i = 0; i < 9; ++i) { const uint2 v = lds64(p + 64 * jj + 8 * i); w[2 * i] = v.x; w[2 * i + 1] = v.y; }
             // jj = 0 reads bytes [0, 72): words 0..17 hold blocks 0 and 1 (17 words) plus one spare.
             // jj = 1 reads bytes [64, 136): block 2 starts at byte 68, i.e. at word 1 of this window.
             const int o = jj;                          // word offset of the block pair inside w[]
@@ -171,11 +271,12 @@ template <int MM> struct QUnit<RLXQ_Q8_0, MM> {
                     for (int i = 0; i < 8; ++i) q[i] = w[o + 9 + i];
                 }
                 const float d = f16_bits_to_f32(dbits);
-                const uint32_t blk = (kb >> 5) + 4 * L.half + 2 * jj + j;
+                const int bj = 2 * jj + j;
 #pragma unroll
                 for (int m = 0; m < MM; ++m) {
-                    const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, 0);
-                    tot[m] = fmaf(d * L.sb[m * L.xstride4 + blk], (float)c, tot[m]);
+                    const uint32_t ox = m * L.xstride;
+                    const int c = dot_limbs<8>(q, xh + ox + 32 * bj, xl + ox + 32 * bj, 0);
+                    tot[m] = fmaf(d * ldsf(sb + ox + 4 * bj), (float)c, tot[m]);
                 }
             }
         }
@@ -183,9 +284,9 @@ template <int MM> struct QUnit<RLXQ_Q8_0, MM> {
 };
 
 // ---- Q4_K: unit = one 144-byte super-block; a thread takes sub-blocks 4*half .. 4*half+3 ----
-template <int MM> struct QUnit<RLXQ_Q4_K, MM> {
+template <int MM> struct QUnit<RLXQ_Q4_K, MM> : QUnitRowHalf<MM> {
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
-        const uint8_t* p = L.row + u * 144;
+        const uint32_t p = L.row + u * 144;
         const uint4 hd = lds128(p);                   // d, dmin, 12 scale bytes
         const float d = f16_bits_to_f32(hd.x & 0xFFFFu), dmin = f16_bits_to_f32(hd.x >> 16);
         uint32_t scb, mnb;                            // four 6-bit scales / mins, one per byte
@@ -196,9 +297,10 @@ template <int MM> struct QUnit<RLXQ_Q4_K, MM> {
             scb = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
             mnb = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
         }
+        const uint32_t xh = L.xh + kb, xl = L.xl + kb, sb = L.sb + (kb >> 3), sx = L.sx + (kb >> 3);
 #pragma unroll
         for (int pp = 0; pp < 2; ++pp) {              // a pair of sub-blocks shares 32 bytes
-            const uint8_t* qp = p + 16 + 64 * L.half + 32 * pp;
+            const uint32_t qp = p + 16 + 64 * L.half + 32 * pp;
             const uint4 a = lds128(qp), b = lds128(qp + 16);
             const uint32_t raw[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
@@ -209,13 +311,13 @@ template <int MM> struct QUnit<RLXQ_Q4_K, MM> {
                 const int js = 2 * pp + nib;          // sub-block index within this half
                 const float dsc = d * (float)((scb >> (8 * js)) & 0xFFu);
                 const float dmn = dmin * (float)((mnb >> (8 * js)) & 0xFFu);
-                const uint32_t blk = (kb >> 5) + 4 * L.half + js;
 #pragma unroll
                 for (int m = 0; m < MM; ++m) {
-                    const int c = dot_limbs<8>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, blk * 32, 0);
-                    const float sbv = L.sb[m * L.xstride4 + blk];
+                    const uint32_t ox = m * L.xstride;
+                    const int c = dot_limbs<8>(q, xh + ox + 32 * js, xl + ox + 32 * js, 0);
+                    const float sbv = ldsf(sb + ox + 4 * js);
                     // sx holds sum(X) of the block: the min term is dmin * m * s_b * sum(X)
-                    const float sxf = sbv * (float)L.sx[m * L.xstride4 + blk];
+                    const float sxf = sbv * (float)(int)lds32(sx + ox + 4 * js);
                     tot[m] = fmaf(dsc * sbv, (float)c, fmaf(-dmn, sxf, tot[m]));
                 }
             }
@@ -224,32 +326,34 @@ template <int MM> struct QUnit<RLXQ_Q4_K, MM> {
 };
 
 // ---- Q6_K: unit = one 210-byte super-block (only 2-byte aligned); a thread takes one half ----
-template <int MM> struct QUnit<RLXQ_Q6_K, MM> {
+template <int MM> struct QUnit<RLXQ_Q6_K, MM> : QUnitRowHalf<MM> {
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
         // 210*u is 2 mod 4 for odd u: read aligned words from 2 bytes earlier and funnel-shift.
         const uint32_t odd = u & 1u, sh = odd * 16u;
-        const uint8_t* pa = L.row + u * 210 - 2 * odd;
+        const uint32_t pa = L.row + u * 210 - 2 * odd;
         const uint32_t h = L.half;
         uint32_t ql[16], qh[8], scw[2];
         {
             uint32_t a[17];
 #pragma unroll
-            for (int i = 0; i < 17; ++i) a[i] = *reinterpret_cast<const uint32_t*>(pa + 64 * h + 4 * i);
+            for (int i = 0; i < 17; ++i) a[i] = lds32(pa + 64 * h + 4 * i);
 #pragma unroll
             for (int i = 0; i < 16; ++i) ql[i] = __funnelshift_r(a[i], a[i + 1], sh);
             uint32_t b[9];
 #pragma unroll
-            for (int i = 0; i < 9; ++i) b[i] = *reinterpret_cast<const uint32_t*>(pa + 128 + 32 * h + 4 * i);
+            for (int i = 0; i < 9; ++i) b[i] = lds32(pa + 128 + 32 * h + 4 * i);
 #pragma unroll
             for (int i = 0; i < 8; ++i) qh[i] = __funnelshift_r(b[i], b[i + 1], sh);
             uint32_t c3[3];
 #pragma unroll
-            for (int i = 0; i < 3; ++i) c3[i] = *reinterpret_cast<const uint32_t*>(pa + 192 + 8 * h + 4 * i);
+            for (int i = 0; i < 3; ++i) c3[i] = lds32(pa + 192 + 8 * h + 4 * i);
             scw[0] = __funnelshift_r(c3[0], c3[1], sh);
             scw[1] = __funnelshift_r(c3[1], c3[2], sh);
         }
-        const uint32_t dw = *reinterpret_cast<const uint32_t*>(pa + 208);
+        const uint32_t dw = lds32(pa + 208);
         const float d = f16_bits_to_f32((dw >> sh) & 0xFFFFu);
+        // here the sums are per 16 values: L.sx was advanced by 32 * half (8 sums of 4 bytes)
+        const uint32_t xh = L.xh + kb, xl = L.xl + kb, sb = L.sb + (kb >> 3), sx = L.sx + (kb >> 2);
 #pragma unroll
         for (int g4 = 0; g4 < 4; ++g4) {              // four interleaved 32-weight groups per half
             const int nib = g4 >> 1, ps = g4 & 1;
@@ -265,12 +369,13 @@ template <int MM> struct QUnit<RLXQ_Q6_K, MM> {
                 }
                 const int si = 2 * g4 + i;            // scale index inside the half
                 const float ds = d * (float)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFFu);
-                const uint32_t ke = kb + 128 * h + 32 * g4 + 16 * i;
+                const int ke = 32 * g4 + 16 * i;      // first weight of the sub-block inside this half
 #pragma unroll
                 for (int m = 0; m < MM; ++m) {
                     // sx holds -32 * sum(X) per 16 values
-                    const int c = dot_limbs<4>(q, L.xh + m * L.xstride, L.xl + m * L.xstride, ke, L.sx[m * L.xstride4 + (ke >> 4)]);
-                    tot[m] = fmaf(ds * L.sb[m * L.xstride4 + (ke >> 5)], (float)c, tot[m]);
+                    const uint32_t ox = m * L.xstride;
+                    const int c = dot_limbs<4>(q, xh + ox + ke, xl + ox + ke, (int)lds32(sx + ox + 4 * si));
+                    tot[m] = fmaf(ds * ldsf(sb + ox + 4 * g4), (float)c, tot[m]);
                 }
             }
         }
@@ -288,33 +393,42 @@ template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
 // Kernel 1: activations -> two int8 limbs + per-32 scale + per-SUB integer sums (workspace).
 // One thread per 8 values; the scale is local to a 32-value block (four lanes).
 // ---------------------------------------------------------------------------------------------
-template <uint32_t SUB>
-__global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
-                                                         uint32_t k, int bias, uint8_t* __restrict__ xq,
-                                                         uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
-                                                         uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count,
-                                                         uint32_t swiglu_pair) {
-    griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
-    griddep_wait();                // x (and the counters) may still be in use by the previous kernel
-    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
-    for (uint32_t i = gtid; i < ntiles; i += gridDim.x * blockDim.x) counters[i] = 0u;
-    for (uint32_t i = gtid; i < y_count; i += gridDim.x * blockDim.x) y_zero[i] = 0.f;   // two-contributor add mode
-    const uint32_t groups_per_row = k / 8;
-    const uint32_t total = groups_per_row * m;          // a multiple of 32
-    if (gtid >= total) return;                          // whole warps leave together
-    const uint32_t r = gtid / groups_per_row, c = (gtid - r * groups_per_row) * 8;
-    float f[8];
-    if (swiglu_pair) {
-        // x is [m][2k] f32 = [gate | up] of a SwiGLU FFN: the activation is up * silu(gate)
-        // (rlx-cpu/src/naive.rs:54-56, rlx-cuda/src/unfuse.rs:254-293), formed here instead of in a kernel of its own
-        const float* row = reinterpret_cast<const float*>(x) + (size_t)r * 2 * k;
-        const float4 g0 = *reinterpret_cast<const float4*>(row + c), g1 = *reinterpret_cast<const float4*>(row + c + 4);
-        const float4 u0 = *reinterpret_cast<const float4*>(row + k + c), u1 = *reinterpret_cast<const float4*>(row + k + c + 4);
-        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+// 16-byte global load that stays where it is written relative to the other asm statements (the
+// single-kernel mode wants its activation loads in the memory queue ahead of the weight requests).
+__device__ __forceinline__ uint4 ldg128_here(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// The raw 32 bytes (f32) or 16 bytes (bf16) of the eight activations x[r][c .. c+8).
+__device__ __forceinline__ void load_raw8(const void* __restrict__ x, uint32_t x_bf16, uint32_t k, uint32_t r,
+                                          uint32_t c, uint4 (&raw)[2]) {
+    if (x_bf16) {
+        raw[0] = ldg128_here(reinterpret_cast<const uint16_t*>(x) + (size_t)r * k + c);
+    } else {
+        const float* p = reinterpret_cast<const float*>(x) + (size_t)r * k + c;
+        raw[0] = ldg128_here(p);
+        raw[1] = ldg128_here(p + 4);
+    }
+}
+__device__ __forceinline__ void raw8_to_f32(const uint4 (&raw)[2], uint32_t x_bf16, float (&f)[8]) {
+    if (x_bf16) {
+        const uint32_t wv[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
 #pragma unroll
-        for (int q = 0; q < 8; ++q) f[q] = u[q] * (g[q] / (1.0f + expf(-g[q])));
-    } else if (x_bf16) {
+        for (int q = 0; q < 4; ++q) {
+            f[2 * q] = __uint_as_float(wv[q] << 16);
+            f[2 * q + 1] = __uint_as_float(wv[q] & 0xFFFF0000u);
+        }
+    } else {
+        f[0] = __uint_as_float(raw[0].x); f[1] = __uint_as_float(raw[0].y); f[2] = __uint_as_float(raw[0].z); f[3] = __uint_as_float(raw[0].w);
+        f[4] = __uint_as_float(raw[1].x); f[5] = __uint_as_float(raw[1].y); f[6] = __uint_as_float(raw[1].z); f[7] = __uint_as_float(raw[1].w);
+    }
+}
+
+// Reads the eight activations x[r][c .. c+8) (f32 or bf16) as f32.
+__device__ __forceinline__ void load_group8(const void* __restrict__ x, uint32_t x_bf16, uint32_t k, uint32_t r,
+                                            uint32_t c, float (&f)[8]) {
+    if (x_bf16) {
         const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + (size_t)r * k + c);
         const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -328,6 +442,27 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
         f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
     }
+}
+
+// The SwiGLU form: x is [m][2k] f32 = [gate | up] of an FFN and the activation is up * silu(gate)
+// (rlx-cpu/src/naive.rs:54-56, rlx-cuda/src/unfuse.rs:254-293), formed here instead of in a kernel of its own.
+__device__ __forceinline__ void load_group8_swiglu(const void* __restrict__ x, uint32_t k, uint32_t r, uint32_t c,
+                                                   float (&f)[8]) {
+    const float* row = reinterpret_cast<const float*>(x) + (size_t)r * 2 * k;
+    const float4 g0 = *reinterpret_cast<const float4*>(row + c), g1 = *reinterpret_cast<const float4*>(row + c + 4);
+    const float4 u0 = *reinterpret_cast<const float4*>(row + k + c), u1 = *reinterpret_cast<const float4*>(row + k + c + 4);
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) f[q] = u[q] * (g[q] / (1.0f + expf(-g[q])));
+}
+
+// Quantises eight activations (columns c .. c+8 of a row) into row_dst
+// ([h: k][l: k][s_b: k/32 f32][sums: k/SUB i32]).  The four lanes 4j .. 4j+3 of a warp must hold the
+// four groups of one 32-value block.
+template <uint32_t SUB>
+__device__ __forceinline__ void quantise_store8(const float (&f)[8], uint32_t k, int bias, uint32_t c,
+                                                uint8_t* row_dst, uint32_t lane) {
     float amax = 0.f;
 #pragma unroll
     for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
@@ -347,53 +482,96 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
         hw[q >> 2] |= ((uint32_t)hq & 0xFFu) << (8 * (q & 3));
         lw[q >> 2] |= ((uint32_t)lq & 0xFFu) << (8 * (q & 3));
     }
-    uint8_t* row = xq + (size_t)r * xq_row_bytes;
-    *reinterpret_cast<uint2*>(row + c) = make_uint2(hw[0], hw[1]);
-    *reinterpret_cast<uint2*>(row + k + c) = make_uint2(lw[0], lw[1]);
+    *reinterpret_cast<uint2*>(row_dst + c) = make_uint2(hw[0], hw[1]);
+    *reinterpret_cast<uint2*>(row_dst + k + c) = make_uint2(lw[0], lw[1]);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     if (SUB == 32) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-    float* sb = reinterpret_cast<float*>(row + 2 * (size_t)k);
-    int* sx = reinterpret_cast<int*>(row + 2 * (size_t)k + (size_t)(k / 32) * 4);
+    float* sb = reinterpret_cast<float*>(row_dst + 2 * (size_t)k);
+    int* sx = reinterpret_cast<int*>(row_dst + 2 * (size_t)k + (size_t)(k / 32) * 4);
     if ((lane & 3u) == 0) sb[c / 32] = s;
     if ((lane & (SUB / 8 - 1)) == 0) sx[c / SUB] = bias * sum;
 }
 
+template <uint32_t SUB>
+__global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
+                                                         uint32_t k, int bias, uint8_t* __restrict__ xq,
+                                                         uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
+                                                         uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count,
+                                                         uint32_t swiglu_pair) {
+#ifdef RLXQ_TRACE
+    const uint32_t tslot = swiglu_pair >> 8;
+    swiglu_pair &= 0xFFu;
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][0] = gtime();
+#endif
+    griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
+    const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
+    griddep_wait();                // x (and the counters) may still be in use by the previous kernel
+#ifdef RLXQ_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][1] = gtime();
+#endif
+    for (uint32_t i = gtid; i < ntiles; i += gridDim.x * blockDim.x) counters[i] = 0u;
+    for (uint32_t i = gtid; i < y_count; i += gridDim.x * blockDim.x) y_zero[i] = 0.f;   // two-contributor add mode
+    const uint32_t groups_per_row = k / 8;
+    const uint32_t total = groups_per_row * m;          // a multiple of 32
+    if (gtid >= total) return;                          // whole warps leave together
+    const uint32_t r = gtid / groups_per_row, c = (gtid - r * groups_per_row) * 8;
+    float f[8];
+    if (swiglu_pair) load_group8_swiglu(x, k, r, c, f);
+    else load_group8(x, x_bf16, k, r, c, f);
+    quantise_store8<SUB>(f, k, bias, c, xq + (size_t)r * xq_row_bytes, lane);
+#ifdef RLXQ_TRACE
+    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][2] = gtime();
+#endif
+}
+
 // ---------------------------------------------------------------------------------------------
-// Work list ("stream-K").  All (tile, chunk) items form one list, chunk-major inside a tile; CTA i
-// takes the contiguous range [i*T/G, (i+1)*T/G), so every CTA streams the same number of bytes
-// (+-1 chunk) whatever n and k are.  A range cuts at most two tiles: its head and its tail.  Those
+// Work list ("stream-K").  All (tile, chunk) items form one list, chunk-major inside a tile; the T
+// items are dealt to the G CTAs as contiguous ranges of T/G items, the first T mod G ranges one
+// longer, so every CTA streams the same number of bytes (+-1 chunk) whatever n and k are.  A range cuts at most two tiles: its head and its tail.  Those
 // two shared segments are processed FIRST, the whole tiles between them afterwards, so that the
 // latency of finishing a shared tile (a fence, an atomic, a re-read) hides behind streaming.
 // ---------------------------------------------------------------------------------------------
 struct Segment { uint32_t tile, c0, c1; };
 
-struct Range { uint32_t beg, end, head_end, tail_beg, nseg, nshared; };
+// A CTA's range: its cut head tile (chunks head_c0 .. nchunks of tile head_tile) if has_head, its cut
+// tail tile (chunks 0 .. tail_c1 of tile tail_tile) if has_tail, and nwhole whole tiles from first_whole.
+struct Range { uint32_t len, has_head, has_tail, head_tile, head_c0, head_c1, tail_tile, tail_c1, first_whole, nseg, nshared; };
 
-__device__ __forceinline__ Range make_range(const IntParams& P, uint32_t me, uint32_t G) {
-    Range r;
-    r.beg = (uint32_t)(((uint64_t)me * P.total_chunks) / G);
-    r.end = (uint32_t)(((uint64_t)(me + 1) * P.total_chunks) / G);
+__device__ __forceinline__ Range make_range(const IntParams& P, uint32_t me) {
+    // CTA i takes chunks [i*q + min(i, r), ...): the first r CTAs one chunk more (q, r from the host)
+    Range rg;
     const uint32_t nc = P.nchunks;
-    // head: from beg to the next tile boundary (or end), if beg is inside a tile
-    r.head_end = (r.beg % nc) ? min(r.end, (r.beg / nc + 1) * nc) : r.beg;
+    const uint32_t beg = me * P.chunks_q + min(me, P.chunks_r);
+    const uint32_t end = beg + P.chunks_q + (me < P.chunks_r ? 1u : 0u);
+    rg.len = end - beg;
+    const uint32_t bt = beg / nc, et = end / nc;
+    const uint32_t bc = beg - bt * nc, ec = end - et * nc;
+    // head: from beg to the next tile boundary (or to end, for a range inside one tile), if beg is inside a tile
+    const uint32_t head_end = bc ? min(end, (bt + 1) * nc) : beg;
+    rg.has_head = bc ? 1u : 0u;
+    rg.head_tile = bt;
+    rg.head_c0 = bc;
+    rg.head_c1 = head_end - bt * nc;
     // tail: from the last tile boundary to end, if end is inside a tile and past the head
-    r.tail_beg = (r.end % nc && (r.end / nc) * nc >= r.head_end) ? (r.end / nc) * nc : r.end;
-    const uint32_t whole = (r.tail_beg - r.head_end) / nc;
-    r.nshared = (r.head_end > r.beg ? 1u : 0u) + (r.end > r.tail_beg ? 1u : 0u);
-    r.nseg = r.nshared + whole;
-    return r;
+    rg.has_tail = (ec && et * nc >= head_end) ? 1u : 0u;
+    rg.tail_tile = et;
+    rg.tail_c1 = ec;
+    rg.first_whole = bc ? bt + 1 : bt;
+    const uint32_t nwhole = et > rg.first_whole ? et - rg.first_whole : 0u;
+    rg.nshared = rg.has_head + rg.has_tail;
+    rg.nseg = rg.nshared + nwhole;
+    return rg;
 }
-__device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& r, uint32_t idx) {
-    const uint32_t nc = P.nchunks;
+// The CTA whose range holds chunk g (the inverse of the split in make_range).
+__device__ __forceinline__ uint32_t owner_of(const IntParams& P, uint32_t g) {
+    const uint32_t big = P.chunks_r * (P.chunks_q + 1);
+    return g < big ? g / (P.chunks_q + 1) : P.chunks_r + (g - big) / P.chunks_q;
+}
+__device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& rg, uint32_t idx) {
     Segment sg;
-    uint32_t g0, g1;   // global chunk ids
-    const bool has_head = r.head_end > r.beg, has_tail = r.end > r.tail_beg;
-    if (has_head && idx == 0) { g0 = r.beg; g1 = r.head_end; }
-    else if (has_tail && idx == (has_head ? 1u : 0u)) { g0 = r.tail_beg; g1 = r.end; }
-    else { g0 = r.head_end + (idx - r.nshared) * nc; g1 = g0 + nc; }
-    sg.tile = g0 / nc;
-    sg.c0 = g0 - sg.tile * nc;
-    sg.c1 = g1 - sg.tile * nc;
+    if (rg.has_head && idx == 0) { sg.tile = rg.head_tile; sg.c0 = rg.head_c0; sg.c1 = rg.head_c1; }
+    else if (rg.has_tail && idx == rg.has_head) { sg.tile = rg.tail_tile; sg.c0 = 0; sg.c1 = rg.tail_c1; }
+    else { sg.tile = rg.first_whole + (idx - rg.nshared); sg.c0 = 0; sg.c1 = P.nchunks; }
     return sg;
 }
 
@@ -404,6 +582,7 @@ template <uint32_t SCHEME, int MM>
 __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_constant__ IntParams P) {
     using T = StagedTraits<SCHEME>;
     using B = IntBox<SCHEME>;
+    using QU = QUnit<SCHEME, MM>;
     constexpr uint32_t STRIDE = B::ROW;
     constexpr uint32_t stage_bytes = B::STAGE_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -419,9 +598,13 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     griddep_launch_dependents();
+    if (tid == 0) { RLXQ_T(P.tslot, 0); tma_prefetch_desc(&P.wmap); }
+#ifdef RLXQ_TRACE
+    const long long c_entry = clock64();
+#endif
 
     const uint32_t G = gridDim.x, me = blockIdx.x;
-    const Range rg = make_range(P, me, G);
+    const Range rg = make_range(P, me);
     const uint32_t nseg = rg.nseg;
     const uint32_t ku = P.k / 256;
 
@@ -439,6 +622,10 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    if (tid == 0) RLXQ_T(P.tslot, 1);
+    // The first fill of the ring is spread over the warps, one stage each: a TMA request occupies its
+    // issuing thread for a few hundred cycles, and one thread issuing them all delays the stream's start.
+    const uint32_t pre = min(min(NS, kIntWarps), rg.len);
 
     if (warp == kIntWarps) {
         // ---------------- producer warp ----------------
@@ -453,7 +640,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                                 (int32_t)(((chunk * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(tile * 16), full);
             }
         };
-        if (lane == 0) tma_prefetch_desc(&P.wmap);
         uint32_t s = 0, ph = 1, issued = 0;   // ph: parity to wait for on empty[s] (1 passes on a fresh barrier)
         bool waited = false, dead = false;
         for (uint32_t si = 0; si < nseg && !dead; ++si) {
@@ -462,11 +648,13 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 if (issued == NS && !waited) {
                     // the ring is full of (immutable) weights: only now wait for the previous kernel
                     waited = true;
+                    if (lane == 0) RLXQ_T(P.tslot, 2);
                     griddep_wait();
+                    if (lane == 0) RLXQ_T(P.tslot, 3);
                     const uint32_t xbar = smem_u32(&bars[2 * NS]);
-                    if (lane == 0 && !(P.debug & 4u)) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+                    if (lane == 0 && !(P.debug & 4u) && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
                     __syncwarp();
-                    if (lane < (uint32_t)MM && !(P.debug & 4u))
+                    if (lane < (uint32_t)MM && !(P.debug & 4u) && !P.inline_q)
                         bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
                 }
                 if (issued >= NS) {
@@ -476,16 +664,18 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                         break;
                     }
                 }
-                produce(sg.tile, c, s);
+                if (issued >= pre) produce(sg.tile, c, s);   // the first `pre` stages were requested by the consumer warps
                 if (++s == NS) { s = 0; ph ^= 1u; }
             }
         }
         if (!waited) {   // fewer chunks than stages: everything is in flight, now fetch the activations
+            if (lane == 0) RLXQ_T(P.tslot, 2);
             griddep_wait();
+            if (lane == 0) RLXQ_T(P.tslot, 3);
             const uint32_t xbar = smem_u32(&bars[2 * NS]);
-            if (lane == 0 && !(P.debug & 4u)) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+            if (lane == 0 && !(P.debug & 4u) && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
             __syncwarp();
-            if (lane < (uint32_t)MM && !(P.debug & 4u))
+            if (lane < (uint32_t)MM && !(P.debug & 4u) && !P.inline_q)
                 bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
         }
         return;
@@ -523,15 +713,35 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             const uint32_t orow = tile * 16 + rrow;
             const bool live = col < (uint32_t)MM && orow < P.n;
             bool store = mine == P.nchunks;
-            if (!store && P.use_red) {
+            if (!store && P.inline_q) {
+                // Exactly two CTAs share this tile: the one holding its first chunks (role 0) and the one
+                // holding its last (role 1).  Each publishes its part and swaps its token into the tile's
+                // word; the one that finds the other's token there came second and completes the tile.
+                // The word may hold anything on entry: a token is unique to (call, role), so stale
+                // contents are never mistaken for it, and the word is left at zero for a replay of the
+                // same captured launch.
+                const uint32_t role = sg.c0 ? 1u : 0u;
+                float* pt = P.partial + (size_t)tile * 2 * (MM * 16);
+                if (col < (uint32_t)MM) pt[(role * MM + col) * 16 + rrow] = v;
+                __threadfence();
+                __syncwarp();
+                unsigned long long old = 0ull;
+                if (lane == 0) old = atomicExch(&P.flags[tile], P.token + 2ull * role);
+                old = __shfl_sync(0xFFFFFFFFu, old, 0);
+                if (old == P.token + 2ull * (1u - role)) {
+                    __threadfence();
+                    if (col < (uint32_t)MM) v += __ldcg(&pt[((1u - role) * MM + col) * 16 + rrow]);
+                    if (lane == 0) P.flags[tile] = 0ull;
+                    store = true;
+                }
+            } else if (!store && P.use_red) {
                 // exactly two CTAs share this tile and y starts at zero: 0 + a + b = 0 + b + a, so a
                 // plain reduction to memory is deterministic and needs no fence, counter or re-read
                 if (live) atomicAdd(reinterpret_cast<float*>(P.y) + (size_t)col * P.n + orow, v);
             } else if (!store) {
                 // the tile is shared with neighbouring CTAs: publish this part in the slot given by the
                 // CTA's position among the tile's contributors; whoever completes the tile adds the slots
-                const uint32_t first_owner = (uint32_t)((((uint64_t)tile * P.nchunks + 1) * G - 1) / P.total_chunks);
-                const uint32_t last_owner = (uint32_t)((((uint64_t)(tile + 1) * P.nchunks) * G - 1) / P.total_chunks);
+                const uint32_t first_owner = owner_of(P, tile * P.nchunks), last_owner = owner_of(P, (tile + 1) * P.nchunks - 1);
                 float* pt = P.partial + ((size_t)tile * P.slots) * (MM * 16);
                 if (col < (uint32_t)MM) pt[((me - first_owner) * MM + col) * 16 + rrow] = v;
                 __threadfence();
@@ -554,42 +764,109 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 else reinterpret_cast<float*>(P.y)[o] = v;
             }
         }
+        if (lane == 0) RLXQ_T(P.tslot, 9);
         return;
     }
 
     // ---------------- consumer warps: lane = (tile row, half of the unit) ----------------
+    auto request_first_stage = [&](uint32_t w0, uint32_t w1) {
+        if (warp >= w0 && warp < min(w1, pre) && lane == 0) {
+            uint32_t i = warp, si = 0;
+            Segment sg = segment_at(P, rg, 0);
+            while (i >= sg.c1 - sg.c0) { i -= sg.c1 - sg.c0; sg = segment_at(P, rg, ++si); }
+            const uint32_t full = smem_u32(&bars[warp]);
+            mbar_arrive_expect_tx(full, stage_bytes);
+#pragma unroll
+            for (uint32_t b = 0; b < B::NB; ++b)
+                tma_load_2d(smem_u32(stages + warp * stage_bytes + b * B::BOX_BYTES), &P.wmap,
+                            (int32_t)((((sg.c0 + i) * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(sg.tile * 16), full);
+        }
+    };
+    // Two-kernel mode: the weights are requested before the dependency wait (they are immutable).  In
+    // single-kernel mode the activations have to come through the same memory path first: requests
+    // behind tens of KB of weight traffic per SM wait for microseconds, so the weights go second.
+    const uint32_t early = P.inline_q ? P.early : pre;   // stages requested before the dependency wait
+    request_first_stage(0, early);
     griddep_wait();
+    if (tid == 0) RLXQ_T(P.tslot, 4);
     QLane L;
-    L.xstride = P.xq_row_bytes;
-    L.xstride4 = P.xq_row_bytes / 4;
-    L.xh = reinterpret_cast<const int8_t*>(xs);
-    L.xl = L.xh + P.k;
-    L.sb = reinterpret_cast<const float*>(xs + 2 * (size_t)P.k);
-    L.sx = reinterpret_cast<const int*>(xs + 2 * (size_t)P.k + (size_t)(P.k / 32) * 4);
     L.half = lane >> 4;
-    const uint32_t trow = lane & 15u;
+    L.xstride = P.xq_row_bytes;
+    L.lane = lane;
+    L.row_pitch = STRIDE;
+    // formats mapped (row, half) read from their half's offset on; Q4_0 indexes by block instead
+    const uint32_t hoff = (QU::NT == 1) ? L.half : 0u;
+    L.xh = smem_u32(xs) + 128 * hoff;
+    L.xl = L.xh + P.k;
+    L.sb = smem_u32(xs) + 2 * P.k + 16 * hoff;
+    L.sx = smem_u32(xs) + 2 * P.k + (P.k / 32) * 4 + (32 / T::SUB) * 16 * hoff;
+    const uint32_t trow = QU::first_row(lane), stages_u32 = smem_u32(stages);
     bool dead = false;
-    if (!(P.debug & 4u) && !mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+    if (P.inline_q) {
+        if (!(P.debug & 4u)) {
+            // every load is issued before the first value is used: one trip to L2, not one per group
+            const uint32_t gpr = P.k / 8, total = gpr * MM;   // whole warps stay together: gpr % 32 == 0
+            uint4 raw[kInlineGroups][2];
+#pragma unroll
+            for (uint32_t i = 0; i < kInlineGroups; ++i) {
+                const uint32_t g = tid + i * kIntWarps * 32;
+                if (g < total) {
+                    const uint32_t r = (MM > 1 && g >= gpr) ? 1u : 0u;
+                    load_raw8(P.x, P.x_bf16, P.k, r, (g - r * gpr) * 8, raw[i]);
+                }
+            }
+            request_first_stage(early, pre);
+#pragma unroll
+            for (uint32_t i = 0; i < kInlineGroups; ++i) {
+                const uint32_t g = tid + i * kIntWarps * 32;
+                if (g < total) {
+                    const uint32_t r = (MM > 1 && g >= gpr) ? 1u : 0u;
+                    float f[8];
+                    raw8_to_f32(raw[i], P.x_bf16, f);
+                    quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
+                                            xs + r * P.xq_row_bytes, lane);
+                }
+            }
+        }
+        else request_first_stage(early, pre);
+        consumer_bar_n<kIntWarps * 32>();
+    } else if (!(P.debug & 4u) && !mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
         dead = true;
         if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
     }
     uint32_t s = 0, ph = 0, rr = 0, rrph = 1;   // rrph: a fresh 'empty' barrier passes a wait on parity 1
+    if (tid == 0) RLXQ_T(P.tslot, 5);
+#ifdef RLXQ_TRACE
+    bool first_stage = true;
+    long long t_wait = 0, t_math = 0;
+#endif
     for (uint32_t si = 0; si < nseg; ++si) {
         const Segment sg = segment_at(P, rg, si);
-        float tot[MM];
+        float tot[QU::NT * MM];
 #pragma unroll
-        for (int m = 0; m < MM; ++m) tot[m] = 0.f;
+        for (int m = 0; m < QU::NT * MM; ++m) tot[m] = 0.f;
         for (uint32_t chunk = sg.c0; chunk < sg.c1; ++chunk) {
+#ifdef RLXQ_TRACE
+            const long long tw0 = clock64();
+#endif
             if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
                 dead = true;
                 if (lane == 0) { atomicExch(P.err, 4); *abort_flag = 1u; }
             }
+#ifdef RLXQ_TRACE
+            const long long tw1 = clock64();
+            t_wait += tw1 - tw0;
+            if (tid == 0 && first_stage) { RLXQ_T(P.tslot, 6); first_stage = false; }
+#endif
             if (!dead) {
                 const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
-                L.row = stages + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                L.row = stages_u32 + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
                 if (warp < cu && !(P.debug & kDebugSkipMath))
-                    QUnit<SCHEME, MM>::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
+                    QU::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
                 __syncwarp();
+#ifdef RLXQ_TRACE
+                t_math += clock64() - tw1;
+#endif
                 if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
             }
             if (++s == NS) { s = 0; ph ^= 1u; }
@@ -601,6 +878,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         }
         if (!dead) {
             float* rbuf = red + rr * (kIntWarps * 32 * MM);
+            QU::finalize(tot, lane);
 #pragma unroll
             for (int m = 0; m < MM; ++m) rbuf[(warp * 32 + lane) * MM + m] = tot[m];
             __syncwarp();
@@ -608,6 +886,10 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         }
         if (++rr == kIntRB) { rr = 0; rrph ^= 1u; }
     }
+    if (tid == 0) RLXQ_T(P.tslot, 8);
+#ifdef RLXQ_TRACE
+    if (tid == 0 && blockIdx.x < 512) { g_trace[P.tslot & 3][blockIdx.x][10] = (unsigned long long)t_wait; g_trace[P.tslot & 3][blockIdx.x][11] = (unsigned long long)t_math; g_trace[P.tslot & 3][blockIdx.x][12] = rg.len; g_trace[P.tslot & 3][blockIdx.x][13] = (unsigned long long)(clock64() - c_entry); }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -618,7 +900,7 @@ struct IntPlan {
     uint32_t grid, ntiles, nchunks, total_chunks, slots, nstages;
     bool two_way;
     uint32_t xq_row_bytes, off_stage, off_red, off_bar, smem_bytes;
-    size_t ws_xq, ws_partial, ws_bytes;
+    size_t ws_xq, ws_partial, ws_counters, ws_bytes;
 };
 
 template <uint32_t SCHEME>
@@ -657,9 +939,18 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     pl.slots = (pl.nchunks + per_cta - 1) / per_cta + 1;             // contributors a tile can have
     pl.ws_xq = align((size_t)pl.xq_row_bytes * m, 256);
     pl.ws_partial = align((size_t)pl.ntiles * pl.slots * m * 16 * 4, 256);
-    pl.ws_bytes = pl.ws_xq + pl.ws_partial + align((size_t)pl.ntiles * 4, 256);
+    pl.ws_counters = align((size_t)pl.ntiles * 4, 256);
+    pl.ws_bytes = pl.ws_xq + pl.ws_partial + pl.ws_counters + align((size_t)pl.ntiles * 8, 256);   // + rendezvous words
     pl.ok = true;
     return pl;
+}
+
+// Odd 64-bit values, a different one (and one two above it) for every call of this process; the
+// starting point differs from process to process.
+static unsigned long long next_call_token() {
+    static std::atomic<unsigned long long> epoch{
+        ((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() * 0x9E3779B97F4A7C15ull) >> 2};
+    return (epoch.fetch_add(1) << 2) | 1ull;
 }
 
 template <uint32_t SCHEME, int MM>
@@ -682,9 +973,21 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.use_red = (pl.two_way && !ybf) ? 1u : 0u;
     P.row_bytes = k / g.elems * g.bytes;
     P.ntiles = pl.ntiles; P.nchunks = pl.nchunks; P.total_chunks = pl.total_chunks; P.slots = pl.slots;
+    P.chunks_q = pl.total_chunks / pl.grid; P.chunks_r = pl.total_chunks % pl.grid;
     P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes;
     P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
     P.debug = (uint32_t)options().gemv_debug.load();
+    // One kernel instead of two when every shared tile has exactly two contributors and re-quantising
+    // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
+    // dependent-launch hop and a copy on the critical path of a call that lasts only microseconds.
+    const int64_t iq = options().gemv_inline_q.load();
+    P.inline_q = (!pair && pl.two_way && (uint64_t)k * MM <= kInlineGroups * kIntWarps * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
+    if (P.inline_q) P.use_red = 0u;
+    P.x = x; P.x_bf16 = xbf ? 1u : 0u;
+    P.flags = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq + pl.ws_partial + pl.ws_counters);
+    P.token = next_call_token();
+    P.early = (uint32_t)options().gemv_early.load();
+    P.tslot = (uint32_t)(P.token >> 2) & 3u;
     P.err = err_word;
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     static std::atomic<uint32_t> attr_set[64];
@@ -696,11 +999,16 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     }
     const uint32_t groups = (k / 8) * MM;
     int rc = RLXQ_OK;
-    if (!(P.debug & 16u)) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3((groups + 255) / 256), dim3(256), 0, stream, x, (uint32_t)xbf,
+    const uint32_t qgrid = (groups + 255) / 256;
+    if (!(P.debug & 16u) && !P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
                         (uint32_t)MM, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
-                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u, pair ? 1u : 0u);
+                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u,
+#ifdef RLXQ_TRACE
+                        (P.tslot << 8) |
+#endif
+                        (pair ? 1u : 0u));
     if (rc) return rc;
-    count_launch();
+    if (!P.inline_q) count_launch();
     rc = launch_pdl(gemv_int_kernel<SCHEME, MM>, dim3(pl.grid), dim3(kIntThreads), pl.smem_bytes, stream, P);
     if (rc) return rc;
     count_launch();
@@ -814,6 +1122,15 @@ static int static_scratch_for_current_device(StaticScratch* out) {
 
 using namespace rlxq;
 
+#ifdef RLXQ_TRACE
+extern "C" RLXQ_API int rlxq_debug_trace(unsigned long long* main_events, unsigned long long* q_events) {
+    RLXQ_CUDA_TRY(cudaDeviceSynchronize());
+    RLXQ_CUDA_TRY(cudaMemcpyFromSymbol(main_events, g_trace, sizeof(g_trace)));
+    RLXQ_CUDA_TRY(cudaMemcpyFromSymbol(q_events, g_trace_q, sizeof(g_trace_q)));
+    return RLXQ_OK;
+}
+#endif
+
 extern "C" int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
                                           const void* w_blocks, void* y, uint32_t y_dtype, uint32_t m, uint32_t k,
                                           uint32_t n) {
@@ -840,9 +1157,10 @@ extern "C" int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme,
     // rlxq_device_status sees them); otherwise to a word in this library's image.
     int* err = device_error_word_if_ready();
     if (!err) err = ss.err;
-    // The activation quantiser rewrites the quantised activations, zeroes the tile counters and (in
-    // the two-contributor mode) y on every call, and partial tiles are written before they are read,
-    // so nothing left in the scratch by an earlier call is ever consumed.
+    // Nothing an earlier call left in the scratch is ever consumed: partial tiles are written before
+    // they are read; in two-kernel mode the quantiser rewrites the activations and zeroes the tile
+    // counters (and y in the two-contributor add mode); in single-kernel mode the rendezvous words
+    // are only ever compared with this call's own tokens.
     return launch_gemv_int_err((cudaStream_t)stream, scheme, x, x_dtype == RLXQ_BF16, (const uint8_t*)w_blocks, y,
                                y_dtype == RLXQ_BF16, m, k, n, ss.scratch, kStaticScratchBytes, err);
 }

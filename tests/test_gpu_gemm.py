@@ -19,6 +19,7 @@ pytestmark = pytest.mark.gpu
 def _reset_options():
     yield
     R.set_option("gemm_kernel", 0)
+    R.set_option("gemm_tile_x", 0)
 
 
 def _tol(k):
@@ -53,6 +54,18 @@ def test_tensor_memory_gemm_matches_oracle(sch, m, k, n):
     y = _run(s, w, xb, n, kernel=2)
     ref = O.matmul_bt_mt(x, w, m, k, n, s)
     assert_within_tolerance(y, ref, bound(s, w, x, n), tol=_tol(k), what=f"gemm {sch} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("tile_x", [128, 256])
+@pytest.mark.parametrize("sch,m,k,n", [("q4_k", 300, 1024, 384), ("q6_k", 129, 2048, 200), ("q8_0", 640, 512, 130)])
+def test_both_activation_tile_widths_match_oracle(sch, m, k, n, tile_x):
+    """The GEMM picks 128- or 256-row activation tiles by how many SMs they fill; both are held to the oracle."""
+    s = O.SCHEMES[sch]
+    w, xb, x = _case(s, m, k, n, seed=70 + m)
+    R.set_option("gemm_tile_x", tile_x)
+    y = _run(s, w, xb, n, kernel=2)
+    ref = O.matmul_bt_mt(x, w, m, k, n, s)
+    assert_within_tolerance(y, ref, bound(s, w, x, n), tol=_tol(k), what=f"gemm {sch} tile_x={tile_x}")
 
 
 def test_generic_kernel_for_large_m_matches_oracle():

@@ -25,6 +25,7 @@ def _reset_options():
     R.set_option("gemv_kernel", 0)
     R.set_option("gemm_kernel", 0)
     R.set_option("gemv_kslices", 0)
+    R.set_option("gemv_inline_q", 0)
 
 
 def _run(scheme, w, x, n, x_bf16=False, y_bf16=False):
@@ -156,6 +157,54 @@ def test_integer_gemv_matches_oracle(sch, m, k, n, x_bf16):
     assert_within_tolerance(y, ref, bound(s, w, x, n), tol=2e-5, what=f"integer {sch} {m}x{k}x{n}")
 
 
+@pytest.mark.parametrize("sch,m,k,n", [("q4_0", 1, 4096, 2000), ("q4_0", 2, 2304, 5000), ("q8_0", 1, 1024, 4100),
+                                       ("q4_k", 2, 4096, 3000), ("q6_k", 1, 2048, 4500), ("q4_0", 1, 11008, 700)])
+@pytest.mark.parametrize("fill", [0x00, 0xFF, 0x5A])
+def test_integer_gemv_one_and_two_kernel_modes_agree_on_any_workspace(sch, m, k, n, fill):
+    """The integer GEMV runs as one kernel (activations quantised by the streaming kernel, shared tiles
+    completed through a token exchange) or as two (a quantiser kernel in front).  Both quantise the same
+    way, so they must agree to the last bit whatever the workspace held, call after call."""
+    import torch
+    s = O.SCHEMES[sch]
+    R.set_option("gemv_kernel", 3)
+    w, x = make_case(s, m, k, n, seed=1300 + m + n)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    ws = torch.full((R.workspace_bytes(s, m, k, n) + 16,), fill, dtype=torch.uint8, device="cuda")
+    outs = []
+    for mode in (1, 2, 2, 1, 2):
+        R.set_option("gemv_inline_q", mode)
+        outs.append(R.matmul(xd, wd, s, n, workspace=ws).cpu().numpy())
+        R.device_status()
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    assert_within_tolerance(outs[0], reference(s, w, x, n), bound(s, w, x, n), tol=2e-5, what=f"integer {sch} modes")
+
+
+def test_integer_gemv_single_kernel_mode_replays_in_a_cuda_graph():
+    """A captured launch carries the same token on every replay; the kernel leaves the rendezvous words clean."""
+    import torch
+    s, m, k, n = O.Q4_0, 1, 4096, 5000
+    R.set_option("gemv_kernel", 3)
+    R.set_option("gemv_inline_q", 2)
+    w, x = make_case(s, m, k, n, seed=77)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    ws = torch.full((R.workspace_bytes(s, m, k, n) + 16,), 0xC3, dtype=torch.uint8, device="cuda")
+    y = torch.empty((m, n), device="cuda")
+    R.matmul(xd, wd, s, n, out=y, workspace=ws)
+    torch.cuda.synchronize()
+    want = y.cpu().numpy().copy()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(3):
+            R.matmul(xd, wd, s, n, out=y, workspace=ws)
+    for _ in range(4):
+        y.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(y.cpu().numpy(), want)
+    R.device_status()
+
+
 @pytest.mark.parametrize("sch,k", [("q4_0", 2048), ("q8_0", 1536), ("q4_k", 2560), ("q6_k", 8192)])
 @pytest.mark.parametrize("ksl", [1, 2, 3])
 @pytest.mark.parametrize("kern,m", [(2, 3), (3, 2)])
@@ -265,6 +314,11 @@ def test_launch_counter_counts_kernels():
     R.matmul(x, wd, s, 16)
     assert R.launch_count() == before + 1      # generic kernel: one launch
     R.set_option("gemv_kernel", 3)
+    R.set_option("gemv_inline_q", 1)
     before = R.launch_count()
     R.matmul(x, wd, s, 16)
     assert R.launch_count() == before + 2      # integer GEMV: activation quantiser + streaming kernel
+    R.set_option("gemv_inline_q", 2)
+    before = R.launch_count()
+    R.matmul(x, wd, s, 16)
+    assert R.launch_count() == before + 1      # integer GEMV, single-kernel mode
