@@ -217,6 +217,20 @@ class CompiledGraph:
             self._h, n, (C.c_char_p * n)(*[s.encode() for s in names]), (C.c_void_p * n)(*ptrs),
             (C.c_uint64 * n)(*nbytes), (C.c_uint32 * n)(*dtypes), out_ptr, out_bytes, out_dtype))
 
+    def bind_raw(self, names, ptrs, nbytes, dtypes, out_ptr: int, out_bytes: int, out_dtype: int):
+        """run_raw with the argument arrays built once: returns a callable for a decode loop that runs
+        the same host buffers every step."""
+        n = len(names)
+        args = (self._h, n, (C.c_char_p * n)(*[s.encode() for s in names]), (C.c_void_p * n)(*ptrs),
+                (C.c_uint64 * n)(*nbytes), (C.c_uint32 * n)(*dtypes), out_ptr, out_bytes, out_dtype)
+        fn = lib.rlxq_compiled_run_typed
+
+        def step(_keep=self) -> None:
+            rc = fn(*args)
+            if rc:
+                check(rc)
+        return step
+
     @property
     def arena_bytes(self) -> int:
         return int(lib.rlxq_compiled_arena_bytes(self._h))

@@ -74,6 +74,7 @@ private:
     cudaGraphExec_t graph_exec_ = nullptr;
     void* pinned_ = nullptr;          // staging for pageable host buffers
     uint64_t pinned_bytes_ = 0;
+    bool io_in_graph_ = false;        // Graph mode, small I/O: the captured graph copies to and from pinned_
 };
 
 class Session {
@@ -86,5 +87,6 @@ private:
 };
 
 int launch_swiglu_mul(cudaStream_t stream, const float* gate, const float* up, float* out, uint64_t n);
+int launch_copy_bytes(cudaStream_t stream, void* dst, const void* src, uint64_t bytes);
 
 }  // namespace rlxq
