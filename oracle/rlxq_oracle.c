@@ -19,6 +19,10 @@ int rlxo_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32_t* block
         case RLXO_Q6_K: e = 256; b = 210; break; /* 128 ql, 64 qh, 16 i8 scales, f16 d */
         case RLXO_Q4_0: e = 32;  b = 18;  break; /* f16 d, 16 nibble bytes */
         case RLXO_Q8_0: e = 32;  b = 34;  break; /* f16 d, 32 i8 */
+        case RLXO_Q5_K: e = 256; b = 176; break; /* f16 d, f16 dmin, 12 scale bytes, 32 high-bit bytes, 128 nibble bytes */
+        case RLXO_Q8_K: e = 256; b = 292; break; /* f32 d, 256 i8, 16 i16 block sums */
+        case RLXO_Q2_K: e = 256; b = 84;  break; /* as the reference reads it: f16 d, f16 dmin, 16 scale bytes, 64 quant bytes */
+        case RLXO_Q3_K: e = 256; b = 110; break; /* as the reference reads it: f16 d, 12 scale bytes, 32 high-mask bytes, 64 quant bytes */
         default: return -1;
     }
     if (block_elems) *block_elems = e;
@@ -188,6 +192,112 @@ static void dequant_q6_k_block_impl(const uint8_t* block, float* out, int unsign
     }
 }
 
+/* rlx-gguf/src/lib.rs:783-816: Q4_K's scales and nibbles plus a fifth bit per weight from the
+ * 32-byte plane qh (bit 2*pair for the low-nibble sub-block, bit 2*pair+1 for the high one);
+ * per element one multiply and one subtract, each rounded. */
+static void dequant_q5_k_block(const uint8_t* block, float* out) {
+    float d = read_f16_le(block), dmin = read_f16_le(block + 2);
+    const uint8_t* scales = block + 4;
+    const uint8_t* qh = block + 16;
+    const uint8_t* qs = block + 48;
+    int is = 0, oi = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int j = 0; j < 8; j += 2) {
+        uint8_t sc0, m0, sc1, m1;
+        rlxo_q4k_unpack_scale_min(j, scales, &sc0, &m0);
+        rlxo_q4k_unpack_scale_min(j + 1, scales, &sc1, &m1);
+        float d0 = d * (float)sc0, m0f = dmin * (float)m0;
+        float d1 = d * (float)sc1, m1f = dmin * (float)m1;
+        for (int l = 0; l < 32; l++) {
+            int q = (qs[is + l] & 0x0F) + ((qh[l] & u1) ? 16 : 0);
+            float t = d0 * (float)q;
+            out[oi++] = t - m0f;
+        }
+        for (int l = 0; l < 32; l++) {
+            int q = (qs[is + l] >> 4) + ((qh[l] & u2) ? 16 : 0);
+            float t = d1 * (float)q;
+            out[oi++] = t - m1f;
+        }
+        is += 32;
+        u1 = (uint8_t)(u1 << 2);
+        u2 = (uint8_t)(u2 << 2);
+    }
+}
+
+/* rlx-gguf/src/lib.rs:848-854 (block) and :1121-1140 (tensor): f32 scale, 256 i8; the 16 i16
+ * block sums at the end are not read. */
+static void dequant_q8_k_block(const uint8_t* block, float* out) {
+    float d;
+    memcpy(&d, block, 4);   /* little-endian host */
+    for (int i = 0; i < 256; i++) out[i] = d * (float)(int8_t)block[4 + i];
+}
+
+/* rlx-gguf/src/lib.rs:857-886.  Layout as that decoder reads it: f16 d at 0, f16 dmin at 2,
+ * 16 scale bytes (low nibble scale, high nibble min) at 4, 64 quant bytes at 20.  Two halves of
+ * 128 weights; in each, four 2-bit planes (shift 0, 2, 4, 6) of 32 bytes, 16 weights per scale. */
+static void dequant_q2_k_block(const uint8_t* block, float* out) {
+    float d = read_f16_le(block), mn = read_f16_le(block + 2);
+    const uint8_t* q = block + 20;
+    int is = 0, oi = 0;
+    for (int half = 0; half < 2; half++) {
+        for (int shift = 0; shift < 8; shift += 2) {
+            uint8_t sc = block[4 + is++];
+            float dl = d * (float)(sc & 0xF), ml = mn * (float)(sc >> 4);
+            for (int l = 0; l < 16; l++) {
+                float t = dl * (float)((q[l] >> shift) & 3);
+                out[oi++] = t - ml;
+            }
+            sc = block[4 + is++];
+            dl = d * (float)(sc & 0xF);
+            ml = mn * (float)(sc >> 4);
+            for (int l = 0; l < 16; l++) {
+                float t = dl * (float)((q[l + 16] >> shift) & 3);
+                out[oi++] = t - ml;
+            }
+        }
+        q += 32;
+    }
+}
+
+/* rlx-gguf/src/lib.rs:889-930.  f16 d at 0, 12 scale bytes at 2 (sixteen 6-bit scales: low four
+ * bits in bytes 0..7, high two bits in bytes 8..11), 32 high-mask bytes at 14, 64 quant bytes at
+ * 46.  A weight is ((q >> shift) & 3) - (mask bit set ? 0 : 4), scaled by d * (scale - 32). */
+static void dequant_q3_k_block(const uint8_t* block, float* out) {
+    const uint32_t KMASK1 = 0x03030303u, KMASK2 = 0x0f0f0f0fu;
+    float d_all = read_f16_le(block);
+    const uint8_t* hm = block + 14;
+    const uint8_t* q = block + 46;
+    uint32_t aux[4];
+    for (int i = 0; i < 3; i++)
+        aux[i] = (uint32_t)block[2 + 4 * i] | ((uint32_t)block[3 + 4 * i] << 8) |
+                 ((uint32_t)block[4 + 4 * i] << 16) | ((uint32_t)block[5 + 4 * i] << 24);
+    uint32_t tmp = aux[2];
+    aux[2] = ((aux[0] >> 4) & KMASK2) | (((tmp >> 4) & KMASK1) << 4);
+    aux[3] = ((aux[1] >> 4) & KMASK2) | (((tmp >> 6) & KMASK1) << 4);
+    aux[0] = (aux[0] & KMASK2) | ((tmp & KMASK1) << 4);
+    aux[1] = (aux[1] & KMASK2) | (((tmp >> 2) & KMASK1) << 4);
+    int8_t scales[16];
+    for (int i = 0; i < 16; i++) scales[i] = (int8_t)((aux[i >> 2] >> (8 * (i & 3))) & 0xFF);
+    int is = 0, oi = 0;
+    uint8_t m = 1;
+    for (int half = 0; half < 2; half++) {
+        for (int shift = 0; shift < 8; shift += 2) {
+            float dl = d_all * (float)(int8_t)(scales[is++] - 32);
+            for (int l = 0; l < 16; l++) {
+                int h = (hm[l] & m) ? 0 : 4;
+                out[oi++] = dl * (float)(int8_t)((int8_t)((q[l] >> shift) & 3) - h);
+            }
+            dl = d_all * (float)(int8_t)(scales[is++] - 32);
+            for (int l = 0; l < 16; l++) {
+                int h = (hm[l + 16] & m) ? 0 : 4;
+                out[oi++] = dl * (float)(int8_t)((int8_t)((q[l + 16] >> shift) & 3) - h);
+            }
+            m = (uint8_t)(m << 1);
+        }
+        q += 32;
+    }
+}
+
 /* rlx-cpu/src/gguf_matmul.rs:25-37 with the Q6_K arm taken from the signed full-tensor
  * decoder (the per-block decoder the reference calls there reads the scales unsigned). */
 static void dequant_block(uint32_t scheme, const uint8_t* block, float* out) {
@@ -196,6 +306,10 @@ static void dequant_block(uint32_t scheme, const uint8_t* block, float* out) {
         case RLXO_Q6_K: dequant_q6_k_block_impl(block, out, 0); break;
         case RLXO_Q4_0: dequant_q4_0_block(block, out); break;
         case RLXO_Q8_0: dequant_q8_0_block(block, out); break;
+        case RLXO_Q5_K: dequant_q5_k_block(block, out); break;
+        case RLXO_Q8_K: dequant_q8_k_block(block, out); break;
+        case RLXO_Q2_K: dequant_q2_k_block(block, out); break;
+        case RLXO_Q3_K: dequant_q3_k_block(block, out); break;
         default: break;
     }
 }
@@ -389,6 +503,31 @@ int rlxo_fill_blocks(uint32_t scheme, uint64_t seed, uint64_t first_block, uint6
                 for (int j = 0; j < 16; j++) /* i8 in [-64, 63] */
                     b[192 + j] = (uint8_t)(int8_t)((int)(b[192 + j] & 127) - 64);
                 put_u16(b + 208, gen_scale_f16(&s));
+                break;
+            case RLXO_Q5_K:
+                put_u16(b, gen_scale_f16(&s));
+                put_u16(b + 2, gen_scale_f16(&s));
+                gen_bytes(&s, b + 4, 12 + 32 + 128);   /* scales, fifth-bit plane, nibbles: all uniform */
+                break;
+            case RLXO_Q8_K: {
+                float d = 1e-3f + 9e-3f * u01(splitmix64(&s));
+                memcpy(b, &d, 4);
+                gen_bytes(&s, b + 4, 256);
+                for (int g = 0; g < 16; g++) {          /* block sums, as a quantiser would have written them */
+                    int sum = 0;
+                    for (int l = 0; l < 16; l++) sum += (int8_t)b[4 + 16 * g + l];
+                    put_u16(b + 260 + 2 * g, (uint16_t)(int16_t)sum);
+                }
+                break;
+            }
+            case RLXO_Q2_K:
+                put_u16(b, gen_scale_f16(&s));
+                put_u16(b + 2, gen_scale_f16(&s));
+                gen_bytes(&s, b + 4, 16 + 64);
+                break;
+            case RLXO_Q3_K:
+                put_u16(b, gen_scale_f16(&s));
+                gen_bytes(&s, b + 2, 12 + 32 + 64);
                 break;
             default: return -1;
         }

@@ -21,10 +21,14 @@ from ._lib import RlxqError, check, lib
 
 
 class QuantScheme(enum.IntEnum):
-    """GGUF schemes of rlx_ir::quant::QuantScheme that this path covers, with the ids of
-    include/rlxq.h (0 and 2 are the reference's own, rlx-cuda/src/gguf_host.rs:24-34)."""
+    """The GGUF schemes of rlx_ir::quant::QuantScheme (is_gguf), with the ids of include/rlxq.h
+    (0..5 are the reference's own, rlx-cuda/src/gguf_host.rs:24-34)."""
     GgufQ4K = 0
+    GgufQ5K = 1
     GgufQ6K = 2
+    GgufQ8K = 3
+    GgufQ2K = 4
+    GgufQ3K = 5
     GgufQ4_0 = 6
     GgufQ8_0 = 7
 

@@ -40,6 +40,10 @@ inline bool geometry(uint32_t scheme, Geometry* g) {
         case RLXQ_Q6_K: *g = {256, 210}; return true;
         case RLXQ_Q4_0: *g = {32, 18}; return true;
         case RLXQ_Q8_0: *g = {32, 34}; return true;
+        case RLXQ_Q5_K: *g = {256, 176}; return true;
+        case RLXQ_Q8_K: *g = {256, 292}; return true;
+        case RLXQ_Q2_K: *g = {256, 84}; return true;
+        case RLXQ_Q3_K: *g = {256, 110}; return true;
         default: return false;
     }
 }

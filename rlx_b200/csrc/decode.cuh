@@ -107,7 +107,85 @@ __device__ __forceinline__ float4 decode4_exact<RLXQ_Q6_K>(const uint8_t* b, uin
     return r;
 }
 
+// Q5_K (rlx-gguf/src/lib.rs:783-816, 1019-1068): d | dmin | 12 scale bytes | qh[32] | qs[128].
+// Sub-block j = 2*pair + hi takes nibble hi of qs[32*pair + l] plus 16 if bit j of qh[l] is set.
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q5_K>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const float dmin = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t pair = t >> 6, within = t & 63u, hi = within >> 5, l = within & 31u;
+    uint32_t sc, mn;
+    q4k_scale_min((int)(2 * pair + hi), b + 4, sc, mn);
+    const float dj = __fmul_rn(d, (float)sc);
+    const float mj = __fmul_rn(dmin, (float)mn);
+    const uint32_t w = ld_u32_2(b + 48 + 32 * pair + l) >> (hi ? 4 : 0);
+    const uint32_t hb = ld_u32_2(b + 16 + l) >> (2 * pair + hi);
+    float4 r;
+    r.x = __fsub_rn(__fmul_rn(dj, (float)((w & 0xF) + ((hb & 1u) << 4))), mj);
+    r.y = __fsub_rn(__fmul_rn(dj, (float)(((w >> 8) & 0xF) + (((hb >> 8) & 1u) << 4))), mj);
+    r.z = __fsub_rn(__fmul_rn(dj, (float)(((w >> 16) & 0xF) + (((hb >> 16) & 1u) << 4))), mj);
+    r.w = __fsub_rn(__fmul_rn(dj, (float)(((w >> 24) & 0xF) + (((hb >> 24) & 1u) << 4))), mj);
+    return r;
+}
+
+// Q8_K (rlx-gguf/src/lib.rs:848-854, 1121-1140): f32 d | 256 i8 | 16 i16 block sums (not read).
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q8_K>(const uint8_t* b, uint32_t t) {
+    const float d = __uint_as_float(ld_u32_2(b));
+    const uint32_t w = ld_u32_2(b + 4 + t);
+    float4 r;
+    r.x = __fmul_rn(d, (float)(int8_t)(w & 0xFF));
+    r.y = __fmul_rn(d, (float)(int8_t)((w >> 8) & 0xFF));
+    r.z = __fmul_rn(d, (float)(int8_t)((w >> 16) & 0xFF));
+    r.w = __fmul_rn(d, (float)(int8_t)(w >> 24));
+    return r;
+}
+
+// Q2_K as the reference reads it (rlx-gguf/src/lib.rs:857-886): d | dmin | 16 scale bytes | q[64].
+// Per 128-weight half four 2-bit planes of 32 bytes; 16 weights share a (scale, min) nibble pair.
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q2_K>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const float mn = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t half = t >> 7, r7 = t & 127u, plane = r7 >> 5, within = r7 & 31u, sub = within >> 4, l = within & 15u;
+    const uint32_t sc = b[4 + 8 * half + 2 * plane + sub];
+    const float dl = __fmul_rn(d, (float)(sc & 0xFu));
+    const float ml = __fmul_rn(mn, (float)(sc >> 4));
+    const uint32_t w = ld_u32_2(b + 20 + 32 * half + 16 * sub + l) >> (2 * plane);
+    float4 r;
+    r.x = __fsub_rn(__fmul_rn(dl, (float)(w & 3u)), ml);
+    r.y = __fsub_rn(__fmul_rn(dl, (float)((w >> 8) & 3u)), ml);
+    r.z = __fsub_rn(__fmul_rn(dl, (float)((w >> 16) & 3u)), ml);
+    r.w = __fsub_rn(__fmul_rn(dl, (float)((w >> 24) & 3u)), ml);
+    return r;
+}
+
+// Q3_K as the reference reads it (rlx-gguf/src/lib.rs:889-930): d | 12 scale bytes | hmask[32] | q[64].
+// Sixteen 6-bit scales: scale i has its low four bits in nibble (i >> 3) of byte (i & 7) and its high
+// two bits at position 2 * (i >> 2) of byte 8 + (i & 3).  Weight = ((q >> 2*plane) & 3) - (mask bit ? 0 : 4).
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q3_K>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const uint32_t half = t >> 7, r7 = t & 127u, plane = r7 >> 5, within = r7 & 31u, sub = within >> 4, l = within & 15u;
+    const uint32_t is = 8 * half + 2 * plane + sub;
+    const uint32_t low4 = (b[2 + (is & 7u)] >> (4 * (is >> 3))) & 0xFu;
+    const uint32_t high2 = (b[10 + (is & 3u)] >> (2 * (is >> 2))) & 3u;
+    const float dl = __fmul_rn(d, (float)((int)(low4 | (high2 << 4)) - 32));
+    const uint32_t w = ld_u32_2(b + 46 + 32 * half + 16 * sub + l) >> (2 * plane);
+    const uint32_t hm = ld_u32_2(b + 14 + 16 * sub + l) >> (4 * half + plane);
+    float4 r;
+    r.x = __fmul_rn(dl, (float)((int)(w & 3u) - ((hm & 1u) ? 0 : 4)));
+    r.y = __fmul_rn(dl, (float)((int)((w >> 8) & 3u) - (((hm >> 8) & 1u) ? 0 : 4)));
+    r.z = __fmul_rn(dl, (float)((int)((w >> 16) & 3u) - (((hm >> 16) & 1u) ? 0 : 4)));
+    r.w = __fmul_rn(dl, (float)((int)((w >> 24) & 3u) - (((hm >> 24) & 1u) ? 0 : 4)));
+    return r;
+}
+
 template <uint32_t SCHEME> struct SchemeTraits;
+template <> struct SchemeTraits<RLXQ_Q5_K> { static constexpr uint32_t kElems = 256, kBytes = 176; };
+template <> struct SchemeTraits<RLXQ_Q8_K> { static constexpr uint32_t kElems = 256, kBytes = 292; };
+template <> struct SchemeTraits<RLXQ_Q2_K> { static constexpr uint32_t kElems = 256, kBytes = 84; };
+template <> struct SchemeTraits<RLXQ_Q3_K> { static constexpr uint32_t kElems = 256, kBytes = 110; };
 template <> struct SchemeTraits<RLXQ_Q8_0> { static constexpr uint32_t kElems = 32, kBytes = 34; };
 template <> struct SchemeTraits<RLXQ_Q4_0> { static constexpr uint32_t kElems = 32, kBytes = 18; };
 template <> struct SchemeTraits<RLXQ_Q4_K> { static constexpr uint32_t kElems = 256, kBytes = 144; };

@@ -71,6 +71,53 @@ def known_answers() -> list[dict]:
     out.append(dict(name="q6_k_matmul_zero", cite="rlx-runtime/tests/dequant_matmul_gguf.rs:131-174",
                     scheme="q6_k", n_elems=256, bytes=b.hex(),
                     matmul=dict(m=1, k=256, n=1, x="ones", expected=[0.0], abs_tol=1e-4)))
+
+    # ---- the other GGUF schemes of QuantScheme::is_gguf ----
+    # rlx-gguf/src/lib.rs:1293-1306  Q2_K: d = 1, min = 0, every scale byte 0x01, every 2-bit field 3 -> 3.0
+    b = f16_bytes(1.0) + f16_bytes(0.0) + bytes([0x01] * 16) + bytes([0xFF] * 64)
+    out.append(dict(name="q2_k_constant_three", cite="rlx-gguf/src/lib.rs:1293-1306", scheme="q2_k",
+                    n_elems=256, bytes=b.hex(), expected=[3.0] * 256, tol=1e-4))
+
+    # rlx-gguf/src/lib.rs:1308-1315  Q3_K: an all-zero block decodes to finite values
+    out.append(dict(name="q3_k_zero_block_is_finite", cite="rlx-gguf/src/lib.rs:1308-1315", scheme="q3_k",
+                    n_elems=256, bytes=bytes(110).hex(), finite_only=True))
+
+    # rlx-gguf/src/lib.rs:1317-1334  Q8_K: d = 0.25 (f32), q[i] = i - 128, zero block sums
+    q8 = [(i - 128) for i in range(256)]
+    b = struct.pack("<f", 0.25) + bytes((q & 0xFF) for q in q8) + bytes(32)
+    out.append(dict(name="q8_k_quarter_ramp", cite="rlx-gguf/src/lib.rs:1317-1334", scheme="q8_k",
+                    n_elems=256, bytes=b.hex(), expected=[0.25 * q for q in q8], tol=1e-6))
+
+    def seq_dot(xrow, wrow):     # the tests' own reference: f32 accumulate in order
+        acc = np.float32(0.0)
+        for a, w in zip(xrow, wrow):
+            acc = np.float32(acc + np.float32(a * w))
+        return float(acc)
+
+    # rlx-runtime/tests/dequant_matmul_gguf.rs:43-127 and rlx-cuda/tests/basic.rs:200-247
+    # Q8_K through the graph: scale 0.0625, q[i] = i - 128, m = 2, k = 256, n = 1,
+    # x[i] = i * 0.001 - 0.5 (f32), expected = in-order f32 dot with scale * q; |diff| < 1e-3
+    b = struct.pack("<f", 0.0625) + bytes((q & 0xFF) for q in q8) + bytes(32)
+    x = [np.float32(np.float32(i) * np.float32(0.001)) - np.float32(0.5) for i in range(2 * 256)]
+    wref = [np.float32(np.float32(0.0625) * np.float32(q)) for q in q8]
+    out.append(dict(name="q8_k_matmul_ramp", cite="rlx-runtime/tests/dequant_matmul_gguf.rs:43-127; rlx-cuda/tests/basic.rs:200-247",
+                    scheme="q8_k", n_elems=256, bytes=b.hex(),
+                    matmul=dict(m=2, k=256, n=1, x=[float(v) for v in x],
+                                expected=[seq_dot(x[r * 256:(r + 1) * 256], wref) for r in range(2)], abs_tol=1e-3)))
+
+    # rlx-runtime/tests/dequant_matmul_gguf.rs:176-241  layout regression: n = 4 distinct rows,
+    # scale 1, q = clamp(1000 j + i - 128), x[i] = 0.01 (i + 1); relative error < 1e-4
+    blocks, wrows = b"", []
+    for j in range(4):
+        qj = [max(-128, min(127, j * 1000 + i - 128)) for i in range(256)]
+        blocks += struct.pack("<f", 1.0) + bytes((q & 0xFF) for q in qj) + bytes(32)
+        wrows.append([np.float32(q) for q in qj])
+    x = [np.float32(np.float32(0.01) * np.float32(np.float32(i) + np.float32(1.0))) for i in range(2 * 256)]
+    out.append(dict(name="q8_k_layout_n4", cite="rlx-runtime/tests/dequant_matmul_gguf.rs:176-241",
+                    scheme="q8_k", n_elems=1024, bytes=blocks.hex(),
+                    matmul=dict(m=2, k=256, n=4, x=[float(v) for v in x],
+                                expected=[seq_dot(x[r * 256:(r + 1) * 256], wrows[c]) for r in range(2) for c in range(4)],
+                                rel_tol=1e-4)))
     return out
 
 
@@ -84,6 +131,10 @@ SEEDED = [
     ("q4_k_m5", "q4_k", 5, 256, 33, 32),
     ("q6_k_m1", "q6_k", 1, 512, 19, 41),
     ("q6_k_m2", "q6_k", 2, 2048, 9, 42),
+    ("q5_k_m2", "q5_k", 2, 512, 11, 51),
+    ("q8_k_m1", "q8_k", 1, 256, 13, 61),
+    ("q2_k_m3", "q2_k", 3, 512, 9, 71),
+    ("q3_k_m2", "q3_k", 2, 768, 7, 81),
 ]
 
 

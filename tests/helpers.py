@@ -5,7 +5,7 @@ import numpy as np
 
 from oracle import oracle as O
 
-SCHEMES = {"q4_k": O.Q4_K, "q6_k": O.Q6_K, "q4_0": O.Q4_0, "q8_0": O.Q8_0}
+SCHEMES = dict(O.SCHEMES)
 
 # The path's matmul tolerance: |y - y_ref| <= 1e-3 * ||x_row||_2 * ||w_row||_2 per element,
 # y_ref from the f32 oracle on the same (bf16-widened where applicable) inputs.

@@ -40,9 +40,14 @@ def test_geometry_matches_reference_table():
     assert R.scheme_geometry(R.QuantScheme.GgufQ6K) == (256, 210)
     assert R.scheme_geometry(R.QuantScheme.GgufQ4_0) == (32, 18)
     assert R.scheme_geometry(R.QuantScheme.GgufQ8_0) == (32, 34)
-    with pytest.raises(R.RlxqError) as e:
-        R.scheme_geometry(1)      # Q5_K: an id of the reference that this path does not cover
-    assert e.value.status == -1
+    assert R.scheme_geometry(R.QuantScheme.GgufQ5K) == (256, 176)
+    assert R.scheme_geometry(R.QuantScheme.GgufQ8K) == (256, 292)
+    assert R.scheme_geometry(R.QuantScheme.GgufQ2K) == (256, 84)
+    assert R.scheme_geometry(R.QuantScheme.GgufQ3K) == (256, 110)
+    for bad in (8, 9, 100):
+        with pytest.raises(R.RlxqError) as e:
+            R.scheme_geometry(bad)
+        assert e.value.status == -1
 
 
 def test_packed_bytes_of_benchmark_shapes():

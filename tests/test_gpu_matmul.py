@@ -58,7 +58,7 @@ def _kernels_for(s, m, k):
     """Kernel selectors that accept this shape: 1 generic, 2 staged tensor mode, 3 staged integer, 0 auto."""
     unit = 2048 if s == O.Q6_K else 256
     ks = [1, 0]
-    if k % unit == 0 and m <= 8:
+    if s in (O.Q4_0, O.Q8_0, O.Q4_K, O.Q6_K) and k % unit == 0 and m <= 8:
         ks.append(2)
         if m <= 2:
             ks.append(3)
@@ -79,12 +79,13 @@ def test_committed_fixtures_all_kernels():
 def test_reference_known_answer_matmuls():
     with open(os.path.join(GOLDEN, "known_answers.json")) as f:
         cases = [c for c in json.load(f) if "matmul" in c]
-    assert len(cases) == 2
+    assert len(cases) == 4
     for case in cases:
         s = O.SCHEMES[case["scheme"]]
         mm = case["matmul"]
         w = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8).copy()
-        x = np.ones((mm["m"], mm["k"]), np.float32)
+        x = (np.ones((mm["m"], mm["k"]), np.float32) if mm["x"] == "ones"
+             else np.array(mm["x"], np.float32).reshape(mm["m"], mm["k"]))
         for kern in _kernels_for(s, mm["m"], mm["k"]):
             R.set_option("gemv_kernel", kern)
             y = _run(s, w, x, mm["n"]).ravel()

@@ -20,6 +20,8 @@ def _load_known():
 def test_reference_known_answers(case):
     s = O.SCHEMES[case["scheme"]]
     blocks = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8).copy()
+    if case.get("finite_only"):
+        assert np.isfinite(O.dequant(s, blocks, case["n_elems"])).all()
     if "expected" in case:
         got = O.dequant(s, blocks, case["n_elems"])
         exp = np.array(case["expected"], np.float32)
@@ -29,7 +31,8 @@ def test_reference_known_answers(case):
             assert np.max(np.abs(got - exp)) < case["tol"]
     if "matmul" in case:
         mm = case["matmul"]
-        x = np.ones((mm["m"], mm["k"]), np.float32)
+        x = (np.ones((mm["m"], mm["k"]), np.float32) if mm["x"] == "ones"
+             else np.array(mm["x"], np.float32).reshape(mm["m"], mm["k"]))
         y = O.matmul_bt(x, blocks, mm["m"], mm["k"], mm["n"], s).ravel()
         exp = np.array(mm["expected"], np.float32)
         if "rel_tol" in mm:
@@ -90,10 +93,66 @@ def formula_decode(scheme, blocks, n_elems):
             scg = np.take_along_axis(sc, np.broadcast_to(idx, (nb, 2, 32)), axis=2)
             out[:, :, g, :] = ((d * scg).astype(f) * q).astype(f)
         return out.ravel()
+    if scheme == O.Q5_K:
+        # d, dmin, 12 scale bytes (as Q4_K), 32 bytes of fifth bits (bit j of byte l belongs to
+        # weight l of sub-block j), 128 nibble bytes (as Q4_K)
+        d = B[:, 0:2].copy().view("<f2").astype(f)
+        dmin = B[:, 2:4].copy().view("<f2").astype(f)
+        s = B[:, 4:16].astype(np.uint32)
+        sc = np.zeros((nb, 8), np.uint32)
+        mn = np.zeros((nb, 8), np.uint32)
+        for j in range(8):
+            if j < 4:
+                sc[:, j], mn[:, j] = s[:, j] & 63, s[:, j + 4] & 63
+            else:
+                sc[:, j] = (s[:, j + 4] & 15) | ((s[:, j - 4] >> 6) << 4)
+                mn[:, j] = (s[:, j + 4] >> 4) | ((s[:, j] >> 6) << 4)
+        qh = B[:, 16:48].astype(np.uint32)                                  # [nb, 32]
+        fifth = np.stack([(qh >> j) & 1 for j in range(8)], axis=1) * 16    # [nb, 8, 32]
+        qs = B[:, 48:].reshape(nb, 4, 32)
+        q = (np.stack([qs & 15, qs >> 4], axis=2).reshape(nb, 8, 32) + fifth).astype(f)
+        dsc = (d * sc.astype(f))[:, :, None]
+        dm = (dmin * mn.astype(f))[:, :, None]
+        return ((dsc * q).astype(f) - dm).astype(f).ravel()
+    if scheme == O.Q8_K:
+        d = B[:, 0:4].copy().view("<f4")
+        q = B[:, 4:260].copy().view(np.int8).astype(f)
+        return (d * q).astype(f).ravel()
+    if scheme == O.Q2_K:
+        # d, dmin, 16 bytes (scale | min << 4) for 16-weight groups, 64 quant bytes: two halves of
+        # 32 bytes, each holding four 2-bit planes; group g of a half = plane g // 2, bytes 16 (g % 2) ..
+        d = B[:, 0:2].copy().view("<f2").astype(f)
+        mn = B[:, 2:4].copy().view("<f2").astype(f)
+        scb = B[:, 4:20].astype(np.uint32).reshape(nb, 2, 4, 2)             # half, plane, sub
+        q = B[:, 20:84].astype(np.uint32).reshape(nb, 2, 1, 2, 16)          # half, -, sub, l
+        planes = (q >> (2 * np.arange(4, dtype=np.uint32))[None, None, :, None, None]) & 3   # [nb,2,4,2,16]
+        dl = (d[:, :, None, None] * (scb & 15).astype(f))[..., None]
+        ml = (mn[:, :, None, None] * (scb >> 4).astype(f))[..., None]
+        return ((dl * planes.astype(f)).astype(f) - ml).astype(f).ravel()
+    if scheme == O.Q3_K:
+        # d, 12 scale bytes, 32 mask bytes, 64 quant bytes.  Scale i (0..15): low nibble field from
+        # bytes 0..7 (i < 8: low nibble of byte i, else high nibble of byte i - 8), two more bits from
+        # bytes 8..11 (bits 2 (i // 4) of byte 8 + i % 4); value = field - 32.
+        d = B[:, 0:2].copy().view("<f2").astype(f)
+        sb = B[:, 2:14].astype(np.int32)
+        sc = np.zeros((nb, 16), np.int32)
+        for i in range(16):
+            low = (sb[:, i] & 15) if i < 8 else (sb[:, i - 8] >> 4)
+            high = (sb[:, 8 + i % 4] >> (2 * (i // 4))) & 3
+            sc[:, i] = (low | (high << 4)) - 32
+        hm = B[:, 14:46].astype(np.int32).reshape(nb, 1, 1, 2, 16)          # -, -, sub, l
+        q = B[:, 46:110].astype(np.int32).reshape(nb, 2, 1, 2, 16)          # half, -, sub, l
+        plane = np.arange(4).reshape(1, 1, 4, 1, 1)
+        half = np.arange(2).reshape(1, 2, 1, 1, 1)
+        two = (q >> (2 * plane)) & 3
+        bit = (hm >> (4 * half + plane)) & 1
+        val = (two - 4 * (1 - bit)).astype(f)                                # [nb, 2, 4, 2, 16]
+        dl = (d[:, :, None, None] * sc.reshape(nb, 2, 4, 2).astype(f))[..., None]
+        return (dl * val).astype(f).ravel()
     raise ValueError(scheme)
 
 
-@pytest.mark.parametrize("sch", ["q8_0", "q4_0", "q4_k", "q6_k"])
+@pytest.mark.parametrize("sch", ["q8_0", "q4_0", "q4_k", "q6_k", "q5_k", "q8_k", "q2_k", "q3_k"])
 def test_oracle_matches_formula_decoder_bit_exact(sch):
     s = O.SCHEMES[sch]
     be, _ = O.GEOMETRY[s]
@@ -190,7 +249,7 @@ def test_fused_equals_dequant_then_dot(sch, m, k, n):
 def test_seeded_fixtures_reproduce():
     z = np.load(os.path.join(GOLDEN, "seeded_small.npz"))
     names = sorted({k.split(".")[0] for k in z.files})
-    assert len(names) == 8
+    assert len(names) == 12
     for nm in names:
         s, m, k, n, seed = (int(v) for v in z[f"{nm}.meta"])
         w = O.fill_weights(s, seed, k, n)
