@@ -49,6 +49,11 @@ GEMM_WORKLOADS = {
 }
 # Tensor-parallel SwiGLU FFN at 70B shapes (configuration 3): handled by run_tp_workload.
 TP_WORKLOAD = "q4_k_70b_ffn_tp"
+# Tied LM head (greedy decode): name -> (scheme, n_embd, n_vocab); bf16 hidden state, exact re-ranking on.
+LM_WORKLOADS = {
+    "q4_k_lm_head_128k_argmax": ("q4_k", 4096, 128256),
+    "q6_k_lm_head_128k_argmax": ("q6_k", 4096, 128256),
+}
 TP_D_MODEL, TP_D_FFN = 8192, 28672
 SCHEME_IDS = {"q4_k": 0, "q6_k": 2, "q4_0": 6, "q8_0": 7}
 GEOM = {"q4_k": (256, 144), "q6_k": (256, 210), "q4_0": (32, 18), "q8_0": (32, 34)}
@@ -526,13 +531,125 @@ def run_tp_workload(args, rank, world, local_rank):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+def run_lm_workload(args, rank, world, local_rank):
+    """Greedy token selection over a packed tied embedding: one rlxq_lm_head_argmax per step."""
+    import torch
+    if world != 1:
+        raise SystemExit("the LM-head workload is single-GPU")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rlxq kernels have no CPU path")
+    import rlx_b200 as R
+    from oracle import oracle as O      # input generation and the cpu_baseline leg only
+    sch, k, n = LM_WORKLOADS[args.workload]
+    sid = SCHEME_IDS[sch]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    wb = packed_bytes(sch, k, n)
+    step_bytes = wb + k * 2 + 8
+    rotation = max(2, -(-2 * L2_BYTES // wb) + 1)
+    w_host = O.fill_weights(sid, 4242, k, n)
+    wsets = [torch.from_numpy(w_host).to(dev)] + [torch.from_numpy(O.fill_weights(sid, 4243 + r, k, n)).to(dev)
+                                                   for r in range(rotation - 1)]
+    h_host = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(99, k))).ravel()
+    h_dev = torch.from_numpy(h_host).to(dev).to(torch.bfloat16)
+    ws = torch.empty(R.lm_head_workspace_bytes(sid, k, n, 1, 1), dtype=torch.uint8, device=dev)
+    res = []
+
+    def step(i, exact=True):
+        res.append(R.gguf_tied_lm_argmax(h_dev, wsets[i % rotation], k, n, sid, exact=exact, workspace=ws))
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    launches0 = R.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(args.warmup + i)
+    launches = R.launch_count() - launches0
+    graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record(); graph.replay(); ev1.record()
+    torch.cuda.synchronize()
+    R.device_status()
+    clocks = sampler.stop()
+    ms_per_step = ev0.elapsed_time(ev1) / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    # the same without the exact re-ranking (logits carry the GEMV's rounding), for comparison
+    gfast = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gfast):
+        for i in range(args.steps):
+            step(args.warmup + i, exact=False)
+    gfast.replay()
+    torch.cuda.synchronize()
+    ev0.record(); gfast.replay(); ev1.record()
+    torch.cuda.synchronize()
+    fast_ms = ev0.elapsed_time(ev1) / args.steps
+    # end to end: hidden state from pinned host memory, token id and logit back to the host
+    h_pin = torch.from_numpy(h_host).to(torch.bfloat16).pin_memory()
+    h_stage = torch.empty_like(h_dev)
+    out_pin = torch.empty(2, dtype=torch.float32).pin_memory()     # token id (exact in f32 below 2^24) and logit
+
+    def e2e_step(i):
+        h_stage.copy_(h_pin, non_blocking=True)
+        idx, val = R.gguf_tied_lm_argmax(h_stage, wsets[i % rotation], k, n, sid, exact=True, workspace=ws)
+        out_pin[0:1].copy_(idx, non_blocking=True)
+        out_pin[1:2].copy_(val, non_blocking=True)
+        torch.cuda.synchronize()
+        return int(out_pin[0]), float(out_pin[1])
+
+    for i in range(3):
+        e2e_step(i)
+    t0 = time.perf_counter()
+    e2e_n = max(2, min(args.steps, 50))
+    for i in range(e2e_n):
+        got = e2e_step(i)
+    e2e_s = (time.perf_counter() - t0) / e2e_n
+    first = e2e_step(0)
+    peak, peak_src = measured_peaks()
+    line = {
+        "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "scheme": sch, "n_embd": k, "n_vocab": n, "hidden": "bf16",
+                   "selection": "argmax, winners re-evaluated in the reference's f32 order (RLXQ_LM_EXACT)",
+                   "without_exact_reranking": {"ms_per_step": fast_ms, "value": step_bytes / (fast_ms * 1e-3) / 1e9},
+                   "l2": f"rotating {rotation} distinct embedding copies ({rotation * wb // 10**6} MB) > 2 x 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": k * 2, "d2h_bytes_per_step": 16,
+                "ms_per_step": e2e_s * 1e3, "api": "rlx_b200.gguf_tied_lm_argmax, pinned host buffers",
+                "token": first[0], "logit": first[1]},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                     "peak_source": peak_src, "kernel": "gemv_int_kernel (the logits); selection kernels included in the time",
+                     "bytes_per_launch": step_bytes, "avg_launch_us": ms_per_step * 1e3, "traffic": None},
+    }
+    if not args.no_cpu_baseline:
+        rows = 16384                                   # bounded sample: the first rows of the same embedding
+        sub = w_host[:packed_bytes(sch, k, rows)]
+        cores = os.cpu_count() or 1
+        O.lm_argmax(h_host, sub, k, rows, sid)
+        t0 = time.perf_counter(); reps = 0
+        while time.perf_counter() - t0 < 6.0 and reps < 20:
+            O.lm_argmax(h_host, sub, k, rows, sid); reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": (packed_bytes(sch, k, rows) + k * 4) / dt / 1e9, "unit": "GB/s", "cores": cores,
+                                "kind": "port", "sample": f"{reps} argmax passes over the first {rows} of {n} rows, rows split "
+                                f"over {cores} host threads (the reference scans on one thread)"}
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + [TP_WORKLOAD],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(LM_WORKLOADS) + [TP_WORKLOAD],
                     help="default: the Q4_0 GEMV pair on one GPU, the tensor-parallel FFN on several")
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
@@ -547,6 +664,9 @@ def main() -> None:
         args.workload = "q4_0_llama7b_ffn_gemv" if world == 1 else TP_WORKLOAD
     if args.workload in GEMM_WORKLOADS:
         run_gemm_workload(args, rank, world, local_rank)
+        return
+    if args.workload in LM_WORKLOADS:
+        run_lm_workload(args, rank, world, local_rank)
         return
     if args.workload == TP_WORKLOAD:
         if args.impl == "reference":
@@ -705,9 +825,9 @@ def main() -> None:
                          "avg_launch_us": avg_launch_s * 1e6,
                          "timing": "CUDA events over the timed region / launches (includes inter-launch gaps)",
                          # dram__bytes_read + write per launch from the ncu capture summarised in
-                         # profiles/gemv_int_q4_0_llama7b_ffn_m1.md (25.43 MB for 25.42 MB algorithmic);
+                         # profiles/gemv_int_q4_0_llama7b_ffn_m1.md (25.46 MB for 25.42 MB algorithmic);
                          # other workloads were not captured
-                         "traffic": 25431000 if args.workload == "q4_0_llama7b_ffn_gemv" and m == 1 else None},
+                         "traffic": 25460000 if args.workload == "q4_0_llama7b_ffn_gemv" and m == 1 else None},
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)

@@ -186,6 +186,35 @@ def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+def lm_logits(hidden: np.ndarray, w: np.ndarray, n_embd: int, n_vocab: int, scheme: int) -> np.ndarray:
+    """hidden . W[j,:] for every row j with row_dot_gguf's arithmetic (rlx-cpu/src/lm_head.rs:46-76): the same
+    in-order f32 multiply-then-add as gguf_matmul_bt with m = 1, so that function is reused."""
+    h = np.ascontiguousarray(hidden, np.float32).reshape(1, n_embd)
+    return matmul_bt_mt(h, w, 1, n_embd, n_vocab, scheme).ravel()
+
+
+def lm_argmax(hidden: np.ndarray, w: np.ndarray, n_embd: int, n_vocab: int, scheme: int):
+    """gguf_tied_lm_argmax (rlx-cpu/src/lm_head.rs:223-251): strict '>' scan from (0, -inf)."""
+    logits = lm_logits(hidden, w, n_embd, n_vocab, scheme)
+    best_idx, best_val = 0, np.float32(-np.inf)
+    v = np.where(np.isnan(logits), -np.inf, logits)
+    j = int(np.argmax(v))                      # first maximum, as the scan finds it
+    if v[j] > best_val:
+        best_idx, best_val = j, logits[j]
+    return best_idx, np.float32(best_val), logits
+
+
+def lm_topk(hidden: np.ndarray, w: np.ndarray, n_embd: int, n_vocab: int, scheme: int, cap: int):
+    """gguf_tied_lm_topk (rlx-cpu/src/lm_head.rs:172-199): the cap best (id, logit), best first.  The
+    reference leaves the order of equal logits to an unstable selection; here equal logits are ordered
+    by token id, which is one of the orders it may produce."""
+    logits = lm_logits(hidden, w, n_embd, n_vocab, scheme)
+    cap = max(1, min(cap, n_vocab))
+    ok = np.flatnonzero(~np.isnan(logits))
+    order = ok[np.lexsort((ok, -logits[ok].astype(np.float64)))][:cap]
+    return [(int(j), np.float32(logits[j])) for j in order], logits
+
+
 def row_norms(scheme: int, w: np.ndarray, k: int, n: int) -> np.ndarray:
     """||w_row||_2 per output row, in float64, for the matmul tolerance."""
     wf = dequant(scheme, w, k * n).reshape(n, k).astype(np.float64)

@@ -137,6 +137,56 @@ def matmul(x, w_blocks, scheme: int, n: int, out=None, out_dtype=None, workspace
     return out
 
 
+# ------------------------------------------------------------------ tied LM head
+LM_MAX_CAP = 64
+
+
+def lm_head_workspace_bytes(scheme: int, n_embd: int, n_vocab: int, x_dtype: int = 0, cap: int = 1) -> int:
+    out = C.c_size_t()
+    check(lib.rlxq_lm_head_workspace_bytes(int(scheme), n_embd, n_vocab, x_dtype, cap, C.byref(out)))
+    return out.value
+
+
+def gguf_tied_lm_topk(hidden, w_bytes, n_embd: int, n_vocab: int, scheme: int, cap: int, exact: bool = True,
+                      workspace=None):
+    """rlx_cpu::lm_head::gguf_tied_lm_topk (rlx-cpu/src/lm_head.rs:172-199) on the GPU: the `cap` best
+    (token id, logit) pairs, best first.  hidden: CUDA tensor [n_embd], f32 or bf16; w_bytes: CUDA uint8
+    tensor holding the packed embedding [n_vocab, n_embd].  Returns two CUDA tensors: int32 token ids (-1 where
+    fewer than cap rows could be chosen) and f32 logits."""
+    torch = _torch()
+    assert hidden.is_cuda and hidden.is_contiguous() and hidden.numel() == n_embd
+    assert w_bytes.is_cuda and w_bytes.dtype == torch.uint8 and w_bytes.is_contiguous()
+    cap = max(1, min(cap, n_vocab))          # the reference clamps the same way
+    need = lm_head_workspace_bytes(scheme, n_embd, n_vocab, _dt(hidden, torch), cap)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=hidden.device)
+    idx = torch.empty(cap, dtype=torch.int32, device=hidden.device)
+    val = torch.empty(cap, dtype=torch.float32, device=hidden.device)
+    with torch.cuda.device(hidden.device):
+        check(lib.rlxq_lm_head_topk(_stream_ptr(torch), int(scheme), hidden.data_ptr(), _dt(hidden, torch),
+                                    w_bytes.data_ptr(), n_embd, n_vocab, cap, 1 if exact else 0,
+                                    workspace.data_ptr(), need, idx.data_ptr(), val.data_ptr()))
+    return idx, val
+
+
+def gguf_tied_lm_argmax(hidden, w_bytes, n_embd: int, n_vocab: int, scheme: int, exact: bool = True, workspace=None):
+    """rlx_cpu::lm_head::gguf_tied_lm_argmax (rlx-cpu/src/lm_head.rs:223-251) on the GPU: (token id, logit)
+    as two one-element CUDA tensors; nothing is copied to the host."""
+    torch = _torch()
+    assert hidden.is_cuda and hidden.is_contiguous() and hidden.numel() == n_embd
+    assert w_bytes.is_cuda and w_bytes.dtype == torch.uint8 and w_bytes.is_contiguous()
+    need = lm_head_workspace_bytes(scheme, n_embd, n_vocab, _dt(hidden, torch), 1)
+    if workspace is None or workspace.numel() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=hidden.device)
+    idx = torch.empty(1, dtype=torch.int32, device=hidden.device)
+    val = torch.empty(1, dtype=torch.float32, device=hidden.device)
+    with torch.cuda.device(hidden.device):
+        check(lib.rlxq_lm_head_argmax(_stream_ptr(torch), int(scheme), hidden.data_ptr(), _dt(hidden, torch),
+                                      w_bytes.data_ptr(), n_embd, n_vocab, 1 if exact else 0,
+                                      workspace.data_ptr(), need, idx.data_ptr(), val.data_ptr()))
+    return idx, val
+
+
 # ------------------------------------------------------------------ Graph / Session mirror
 class Graph:
     """rlx_ir::Graph restricted to this path's ops."""
@@ -257,4 +307,5 @@ class Session:
 
 __all__ = ["QuantScheme", "DType", "Device", "Graph", "Session", "CompiledGraph", "RlxqError",
            "dequant_f32", "matmul", "scheme_geometry", "packed_bytes", "workspace_bytes",
-           "set_option", "get_option", "launch_count", "device_status"]
+           "set_option", "get_option", "launch_count", "device_status",
+           "gguf_tied_lm_argmax", "gguf_tied_lm_topk", "lm_head_workspace_bytes", "LM_MAX_CAP"]

@@ -5,6 +5,9 @@ known_answers.json
     recipes and assertions in its unit tests (read as text; the reference is Rust and
     cannot be executed in this image).  Each entry names the test it restates.
 
+lm_head_cases.json
+    The reference's LM-head unit tests (rlx-cpu/src/lm_head.rs:254-335), restated the same way.
+
 seeded_small.npz
     Seeded block bytes and activations at small shapes together with the CPU oracle's
     dequantised weights and matmul outputs.  These are ORACLE-generated (a regression
@@ -121,6 +124,42 @@ def known_answers() -> list[dict]:
     return out
 
 
+def lm_head_cases() -> list[dict]:
+    """The reference's LM-head unit tests (rlx-cpu/src/lm_head.rs:254-335) restated: Q8_K rows with
+    scale 1 and q = clamp(10 j + i - 128), hidden[i] = 0.01 i.  Expected logits are computed here with
+    plain f32 in-order arithmetic, not with the oracle."""
+    def build(n):
+        blocks, rows = b"", []
+        for j in range(n):
+            qj = [max(-128, min(127, j * 10 + i - 128)) for i in range(256)]
+            blocks += struct.pack("<f", 1.0) + bytes((q & 0xFF) for q in qj) + bytes(32)
+            rows.append([np.float32(q) for q in qj])
+        return blocks, rows
+    hidden = [np.float32(np.float32(0.01) * np.float32(i)) for i in range(256)]
+
+    def seq_dot(wrow):
+        acc = np.float32(0.0)
+        for a, w in zip(hidden, wrow):
+            acc = np.float32(acc + np.float32(a * w))
+        return float(acc)
+
+    out = []
+    # lm_head.rs:308-335 argmax_matches_matmul_on_q8k: n = 8, the argmax equals the matmul's, |val - logit| < 1e-3
+    blocks, rows = build(8)
+    logits = [seq_dot(r) for r in rows]
+    out.append(dict(name="lm_argmax_q8k_n8", cite="rlx-cpu/src/lm_head.rs:308-335", scheme="q8_k", n_embd=256,
+                    n_vocab=8, bytes=blocks.hex(), hidden=[float(h) for h in hidden], logits=logits,
+                    argmax=int(np.argmax(np.array(logits, np.float32))), val_tol=1e-3))
+    # lm_head.rs:277-305 topk_early_exit_matches_full_sort_gguf: n = 64, cap = 8; rows 26..63 saturate to
+    # all-127 and tie for the best score, so any eight of them are a correct answer; scores must be equal
+    blocks, rows = build(64)
+    logits = [seq_dot(r) for r in rows]
+    out.append(dict(name="lm_topk_q8k_n64_cap8", cite="rlx-cpu/src/lm_head.rs:277-305", scheme="q8_k", n_embd=256,
+                    n_vocab=64, cap=8, bytes=blocks.hex(), hidden=[float(h) for h in hidden], logits=logits,
+                    top_scores=sorted(logits, reverse=True)[:8]))
+    return out
+
+
 SEEDED = [
     # (name, scheme, m, k, n, seed) — small enough to commit, ragged on purpose
     ("q8_0_m1", "q8_0", 1, 256, 24, 11),
@@ -155,6 +194,8 @@ def seeded() -> dict[str, np.ndarray]:
 def main() -> None:
     with open(os.path.join(HERE, "known_answers.json"), "w") as f:
         json.dump(known_answers(), f, indent=1)
+    with open(os.path.join(HERE, "lm_head_cases.json"), "w") as f:
+        json.dump(lm_head_cases(), f, indent=1)
     np.savez_compressed(os.path.join(HERE, "seeded_small.npz"), **seeded())
     print("wrote known_answers.json and seeded_small.npz")
 
