@@ -1,0 +1,37 @@
+/*
+ * rlxq — fused GGUF dequant + grouped matmul for MoE expert stacks, on the GPU.
+ *
+ * Replaces run_dequant_grouped_matmul_gguf_gpu (rlx-cuda/src/gguf_gpu.rs:142-280), the lowering of
+ * Op::DequantGroupedMatMul (rlx-ir/src/op.rs:860-871; CPU semantics gguf_grouped_matmul_bt,
+ * rlx-cpu/src/gguf_matmul.rs:102-139): y[i,:] = x[i,:] . W_e^T with e = expert_idx[i], where
+ * w_blocks holds num_experts contiguous packed slabs, expert e at [e*slab, (e+1)*slab), each slab a
+ * [n,k] matrix in the layout rlxq_matmul takes.  The reference copies x and the expert ids to the
+ * host, counting-sorts the rows there, runs dequantise + sgemm per expert and copies back; here the
+ * counting sort (grouped_moe_sort_plan, gguf_matmul.rs:178-205) runs on the device and one kernel
+ * walks every expert's rows, so nothing crosses PCIe and nothing synchronises.
+ */
+#ifndef RLXQ_MOE_H
+#define RLXQ_MOE_H
+
+#include "rlxq.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Scratch for rlxq_grouped_matmul: expert offsets, the row permutation, per-expert cursors. */
+RLXQ_API int rlxq_grouped_workspace_bytes(uint32_t m, uint32_t num_experts, size_t* bytes);
+
+/* x: [m,k] f32 or bf16; expert_idx: [m] f32-encoded expert ids, as the reference's graph input
+ * (rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:92-105); y: [m,n] f32 or bf16.  A row whose id
+ * is not in [0, num_experts) gets zeros (the reference only debug-asserts the range).
+ * k must be a multiple of the block size and k*n of it too (whole blocks per slab row). */
+RLXQ_API int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
+                                 const void* w_blocks, const float* expert_idx, void* y, uint32_t y_dtype,
+                                 uint32_t m, uint32_t k, uint32_t n, uint32_t num_experts,
+                                 void* workspace, size_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLXQ_MOE_H */

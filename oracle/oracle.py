@@ -186,6 +186,27 @@ def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+def grouped_matmul_bt(x: np.ndarray, w: np.ndarray, expert_idx: np.ndarray, m: int, k: int, n: int,
+                      num_experts: int, scheme: int) -> np.ndarray:
+    """gguf_grouped_matmul_bt (rlx-cpu/src/gguf_matmul.rs:102-139): counting-sort the rows by expert
+    (grouped_moe_sort_plan, :178-205), one fused matmul per expert over its slab, unpermute (:207-218).
+    The arithmetic is the C oracle's matmul; only the routing is done here."""
+    be, bb = GEOMETRY[scheme]
+    slab = k * n // be * bb
+    assert w.size == num_experts * slab and expert_idx.size == m
+    x = np.ascontiguousarray(x, np.float32).reshape(m, k)
+    ids = expert_idx.astype(np.float32)
+    out = np.zeros((m, n), np.float32)
+    for e in range(num_experts):
+        rows = np.flatnonzero(ids.astype(np.int64) == e) if m else np.array([], np.int64)
+        rows = rows[(ids[rows] >= 0)]
+        if rows.size == 0:
+            continue
+        out[rows] = matmul_bt_mt(np.ascontiguousarray(x[rows]), np.ascontiguousarray(w[e * slab:(e + 1) * slab]),
+                                 rows.size, k, n, scheme)
+    return out
+
+
 def lm_logits(hidden: np.ndarray, w: np.ndarray, n_embd: int, n_vocab: int, scheme: int) -> np.ndarray:
     """hidden . W[j,:] for every row j with row_dot_gguf's arithmetic (rlx-cpu/src/lm_head.rs:46-76): the same
     in-order f32 multiply-then-add as gguf_matmul_bt with m = 1, so that function is reused."""

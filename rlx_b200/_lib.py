@@ -1,4 +1,4 @@
-"""ctypes binding of librlxq.so, the C-ABI library (include/rlxq.h, rlxq_session.h, rlxq_tp.h, rlxq_lm.h).
+"""ctypes binding of librlxq.so, the C-ABI library (include/rlxq.h, rlxq_session.h, rlxq_tp.h, rlxq_lm.h, rlxq_moe.h).
 
 The library is the product: if it is missing or does not load, importing this module raises.
 There is no Python or CPU fallback for any compute entry point.
@@ -42,6 +42,8 @@ _SIGS = {
     "rlxq_lm_head_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_lm_head_topk": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, u32, vp, C.c_size_t, vp, vp]),
     "rlxq_lm_head_argmax": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, vp, C.c_size_t, vp, vp]),
+    "rlxq_grouped_workspace_bytes": (C.c_int, [u32, u32, C.POINTER(C.c_size_t)]),
+    "rlxq_grouped_matmul": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, vp, C.c_size_t]),
     "rlxq_graph_new": (vp, [cp]),
     "rlxq_graph_free": (None, [vp]),
     "rlxq_graph_input": (C.c_int, [vp, cp, u32, u32, u32]),

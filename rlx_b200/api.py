@@ -137,6 +137,30 @@ def matmul(x, w_blocks, scheme: int, n: int, out=None, out_dtype=None, workspace
     return out
 
 
+# ------------------------------------------------------------------ MoE expert stacks
+def grouped_matmul(x, w_blocks, expert_idx, scheme: int, n: int, num_experts: int, out=None, out_dtype=None,
+                   workspace=None):
+    """Op::DequantGroupedMatMul: y[i] = x[i] . W_e^T with e = expert_idx[i] (f32-encoded, as the reference's
+    graph input); w_blocks holds num_experts packed [n, k] slabs back to back.  CUDA tensors in and out."""
+    torch = _torch()
+    assert x.is_cuda and x.dim() == 2 and x.is_contiguous()
+    assert w_blocks.is_cuda and w_blocks.dtype == torch.uint8 and w_blocks.is_contiguous()
+    assert expert_idx.is_cuda and expert_idx.dtype == torch.float32 and expert_idx.is_contiguous()
+    m, k = x.shape
+    assert expert_idx.numel() == m
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype or torch.float32, device=x.device)
+    need = C.c_size_t()
+    check(lib.rlxq_grouped_workspace_bytes(m, num_experts, C.byref(need)))
+    if workspace is None or workspace.numel() < need.value:
+        workspace = torch.empty(max(need.value, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.rlxq_grouped_matmul(_stream_ptr(torch), int(scheme), x.data_ptr(), _dt(x, torch), w_blocks.data_ptr(),
+                                      expert_idx.data_ptr(), out.data_ptr(), _dt(out, torch), m, k, n, num_experts,
+                                      workspace.data_ptr(), need.value))
+    return out
+
+
 # ------------------------------------------------------------------ tied LM head
 LM_MAX_CAP = 64
 
@@ -308,4 +332,4 @@ class Session:
 __all__ = ["QuantScheme", "DType", "Device", "Graph", "Session", "CompiledGraph", "RlxqError",
            "dequant_f32", "matmul", "scheme_geometry", "packed_bytes", "workspace_bytes",
            "set_option", "get_option", "launch_count", "device_status",
-           "gguf_tied_lm_argmax", "gguf_tied_lm_topk", "lm_head_workspace_bytes", "LM_MAX_CAP"]
+           "grouped_matmul", "gguf_tied_lm_argmax", "gguf_tied_lm_topk", "lm_head_workspace_bytes", "LM_MAX_CAP"]

@@ -1,0 +1,196 @@
+// Fused GGUF dequant + grouped matmul for MoE expert stacks (Op::DequantGroupedMatMul).
+//
+// Replaces the reference's host-sorted lowering (rlx-cuda/src/gguf_gpu.rs:142-280): D2H of x and the
+// expert ids, counting sort on the CPU, per-expert dequantise + sgemm, H2D of the result.  Here:
+//   moe_sort_kernel     one CTA: rows per expert (shared-memory atomics), exclusive scan, row
+//                       permutation grouped by expert -- grouped_moe_sort_plan
+//                       (rlx-cpu/src/gguf_matmul.rs:178-205) without the copy of x: the matmul
+//                       kernel reads the rows through the permutation instead
+//   moe_grouped_kernel  grid (weight-row tiles, experts): a warp owns one weight row of one expert,
+//                       decodes it four weights per lane at a time (the bit-exact decoders) and
+//                       multiplies it into up to eight of that expert's activation rows per pass;
+//                       results go straight to the rows' original positions (the unpermute of
+//                       grouped_moe_unpermute_out, gguf_matmul.rs:207-218, is the store address)
+// Decode-sized batches (a handful of rows per expert) stream every routed expert's weights once.
+// Accumulation is f32 in a different order from the CPU loop; same tolerance as the general kernel.
+#include "common.cuh"
+#include "decode.cuh"
+#include "rlxq_moe.h"
+
+namespace rlxq {
+
+constexpr uint32_t kMoeInvalid = 0xFFFFFFFFu;
+
+// offsets[0..E] (exclusive scan of the counts), perm[sorted position] = original row.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict__ expert_idx, uint32_t m, uint32_t E,
+                                                        uint32_t* __restrict__ offsets, uint32_t* __restrict__ cursor,
+                                                        uint32_t* __restrict__ perm) {
+    extern __shared__ uint32_t cnt[];          // [E]
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0u;
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
+        const float f = expert_idx[i];
+        if (f >= 0.f && f < (float)E) atomicAdd(&cnt[(uint32_t)f], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {                    // E is small (tens to hundreds): a serial scan is enough
+        uint32_t run = 0;
+        for (uint32_t e = 0; e < E; ++e) {
+            offsets[e] = run;
+            cursor[e] = run;
+            run += cnt[e];
+        }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    __threadfence_block();
+    // cursor lives in global memory (this CTA is its only user); atomics hand out the slots
+    for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
+        const float f = expert_idx[i];
+        if (f >= 0.f && f < (float)E) perm[atomicAdd(&cursor[(uint32_t)f], 1u)] = i;
+    }
+}
+
+template <bool XBF16>
+__device__ __forceinline__ float4 moe_load_x4(const void* x, uint64_t idx) {
+    if constexpr (XBF16) {
+        const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(x) + idx);
+        return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u),
+                           __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+    } else {
+        return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + idx);
+    }
+}
+
+template <uint32_t SCHEME, bool XBF16, bool YBF16>
+__global__ void __launch_bounds__(256) moe_grouped_kernel(const void* __restrict__ x, const uint8_t* __restrict__ w,
+                                                          void* __restrict__ y, const uint32_t* __restrict__ offsets,
+                                                          const uint32_t* __restrict__ perm, uint32_t k, uint32_t n) {
+    constexpr uint32_t E = SchemeTraits<SCHEME>::kElems, B = SchemeTraits<SCHEME>::kBytes;
+    constexpr int MT = 8;
+    const uint32_t e = blockIdx.y;
+    const uint32_t r0 = offsets[e], r1 = offsets[e + 1];
+    if (r0 == r1) return;                                   // nobody routed here: the slab is never read
+    const uint32_t lane = threadIdx.x & 31u, wpc = blockDim.x >> 5;
+    const uint64_t row_bytes = (uint64_t)(k / E) * B;
+    const uint8_t* slab = w + (uint64_t)e * n * row_bytes;
+    for (uint32_t row = blockIdx.x * wpc + (threadIdx.x >> 5); row < n; row += gridDim.x * wpc) {
+        const uint8_t* wr = slab + (uint64_t)row * row_bytes;
+        for (uint32_t c0 = r0; c0 < r1; c0 += MT) {         // eight of the expert's rows per pass
+            const uint32_t mt = min((uint32_t)MT, r1 - c0);
+            uint32_t src[MT];
+            float acc[MT];
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                src[i] = (uint32_t)i < mt ? perm[c0 + i] : 0u;
+                acc[i] = 0.f;
+            }
+            for (uint32_t el = lane * 4; el < k; el += 128) {
+                const float4 wv = decode4_exact<SCHEME>(wr + (uint64_t)(el / E) * B, el % E);
+#pragma unroll
+                for (int i = 0; i < MT; ++i) {
+                    if ((uint32_t)i < mt) {
+                        const float4 xv = moe_load_x4<XBF16>(x, (uint64_t)src[i] * k + el);
+                        acc[i] = fmaf(wv.x, xv.x, acc[i]);
+                        acc[i] = fmaf(wv.y, xv.y, acc[i]);
+                        acc[i] = fmaf(wv.z, xv.z, acc[i]);
+                        acc[i] = fmaf(wv.w, xv.w, acc[i]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xFFFFFFFFu, acc[i], o);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < MT; ++i) {
+                    if ((uint32_t)i < mt) {
+                        const uint64_t o = (uint64_t)src[i] * n + row;
+                        if constexpr (YBF16) reinterpret_cast<uint16_t*>(y)[o] = (uint16_t)f32_to_bf16_bits(acc[i]);
+                        else reinterpret_cast<float*>(y)[o] = acc[i];
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <uint32_t SCHEME>
+static void launch_grouped_s(cudaStream_t s, dim3 grid, bool xbf, bool ybf, const void* x, const uint8_t* w, void* y,
+                             const uint32_t* offsets, const uint32_t* perm, uint32_t k, uint32_t n) {
+    if (xbf && ybf) moe_grouped_kernel<SCHEME, true, true><<<grid, 256, 0, s>>>(x, w, y, offsets, perm, k, n);
+    else if (xbf) moe_grouped_kernel<SCHEME, true, false><<<grid, 256, 0, s>>>(x, w, y, offsets, perm, k, n);
+    else if (ybf) moe_grouped_kernel<SCHEME, false, true><<<grid, 256, 0, s>>>(x, w, y, offsets, perm, k, n);
+    else moe_grouped_kernel<SCHEME, false, false><<<grid, 256, 0, s>>>(x, w, y, offsets, perm, k, n);
+}
+
+static size_t grouped_ws(uint32_t m, uint32_t E, size_t* off_cursor, size_t* off_perm) {
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    size_t off = up(((size_t)E + 1) * 4);
+    if (off_cursor) *off_cursor = off;
+    off += up((size_t)E * 4);
+    if (off_perm) *off_perm = off;
+    off += up((size_t)m * 4);
+    return off;
+}
+
+}  // namespace rlxq
+
+using namespace rlxq;
+
+extern "C" int rlxq_grouped_workspace_bytes(uint32_t m, uint32_t num_experts, size_t* bytes) {
+    if (!bytes) return fail(RLXQ_E_NULL, "bytes is null");
+    if (num_experts == 0 || num_experts > 8192) return fail(RLXQ_E_LIMIT, "num_experts=%u must be in [1, 8192]", num_experts);
+    *bytes = grouped_ws(m, num_experts, nullptr, nullptr);
+    return RLXQ_OK;
+}
+
+extern "C" int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
+                                   const void* w_blocks, const float* expert_idx, void* y, uint32_t y_dtype, uint32_t m,
+                                   uint32_t k, uint32_t n, uint32_t num_experts, void* workspace, size_t workspace_bytes) {
+    Geometry g;
+    if (!geometry(scheme, &g)) return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    if ((x_dtype != RLXQ_F32 && x_dtype != RLXQ_BF16) || (y_dtype != RLXQ_F32 && y_dtype != RLXQ_BF16))
+        return fail(RLXQ_E_DTYPE, "unknown dtype");
+    if (k == 0 || k % g.elems) return fail(RLXQ_E_SHAPE, "k=%u is not a positive multiple of the block size %u", k, g.elems);
+    if (num_experts == 0 || num_experts > 8192) return fail(RLXQ_E_LIMIT, "num_experts=%u must be in [1, 8192]", num_experts);
+    if (m == 0 || n == 0) return RLXQ_OK;
+    if (!x || !w_blocks || !expert_idx || !y || !workspace) return fail(RLXQ_E_NULL, "null buffer");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)workspace & 15u)) return fail(RLXQ_E_ALIGN, "x and workspace must be 16-byte aligned");
+    if ((uintptr_t)w_blocks & 1u) return fail(RLXQ_E_ALIGN, "w_blocks must be 2-byte aligned");
+    if ((uintptr_t)y & (y_dtype == RLXQ_BF16 ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
+    size_t off_cursor = 0, off_perm = 0;
+    const size_t need = grouped_ws(m, num_experts, &off_cursor, &off_perm);
+    if (workspace_bytes < need) return fail(RLXQ_E_WORKSPACE, "grouped matmul needs %zu workspace bytes, got %zu", need, workspace_bytes);
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    uint32_t* offsets = reinterpret_cast<uint32_t*>(ws);
+    uint32_t* cursor = reinterpret_cast<uint32_t*>(ws + off_cursor);
+    uint32_t* perm = reinterpret_cast<uint32_t*>(ws + off_perm);
+    const bool xbf = x_dtype == RLXQ_BF16, ybf = y_dtype == RLXQ_BF16;
+    // rows with an id outside [0, num_experts) are in no group: their outputs stay zero
+    RLXQ_CUDA_TRY(cudaMemsetAsync(y, 0, (size_t)m * n * (ybf ? 2 : 4), s));
+    moe_sort_kernel<<<1, 1024, num_experts * sizeof(uint32_t), s>>>(expert_idx, m, num_experts, offsets, cursor, perm);
+    count_launch();
+    const uint32_t wpc = 8;
+    unsigned gx = (n + wpc - 1) / wpc;
+    const unsigned cap = (unsigned)sm_count() * 8;
+    if (gx > cap) gx = cap;
+    const dim3 grid(gx, num_experts);
+    const uint8_t* w = (const uint8_t*)w_blocks;
+    switch (scheme) {
+        case RLXQ_Q4_K: launch_grouped_s<RLXQ_Q4_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q5_K: launch_grouped_s<RLXQ_Q5_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q6_K: launch_grouped_s<RLXQ_Q6_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q8_K: launch_grouped_s<RLXQ_Q8_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q2_K: launch_grouped_s<RLXQ_Q2_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q3_K: launch_grouped_s<RLXQ_Q3_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q4_0: launch_grouped_s<RLXQ_Q4_0>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q8_0: launch_grouped_s<RLXQ_Q8_0>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    }
+    count_launch();
+    return check_launch("moe_grouped_kernel");
+}

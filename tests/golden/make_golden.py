@@ -5,6 +5,9 @@ known_answers.json
     recipes and assertions in its unit tests (read as text; the reference is Rust and
     cannot be executed in this image).  Each entry names the test it restates.
 
+grouped_matmul_case.json
+    The reference's MoE grouped-matmul graph test (rlx-runtime/tests/dequant_grouped_matmul_gguf.rs).
+
 lm_head_cases.json
     The reference's LM-head unit tests (rlx-cpu/src/lm_head.rs:254-335), restated the same way.
 
@@ -124,6 +127,29 @@ def known_answers() -> list[dict]:
     return out
 
 
+def grouped_case() -> dict:
+    """rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:82-128: three Q8_K experts with scales 0.25, 0.5, 1
+    (every block q[i] = i - 128), k = 256, n = 4, m = 5 rows routed [1, 0, 2, 1, 0], x[i] = 0.01 (i + 1);
+    expected = per-row in-order f32 dot with the routed expert's dequantised rows; relative error < 1e-4."""
+    k, n, m, scales, route = 256, 4, 5, [0.25, 0.5, 1.0], [1, 0, 2, 1, 0]
+    q = [i - 128 for i in range(256)]
+    packed = b""
+    for sc in scales:
+        for _ in range(n):
+            packed += struct.pack("<f", sc) + bytes((v & 0xFF) for v in q) + bytes(32)
+    x = [np.float32(np.float32(0.01) * np.float32(np.float32(i) + np.float32(1.0))) for i in range(m * k)]
+    exp = []
+    for r in range(m):
+        wrow = [np.float32(np.float32(scales[route[r]]) * np.float32(v)) for v in q]
+        acc = np.float32(0.0)
+        for a, w in zip(x[r * k:(r + 1) * k], wrow):
+            acc = np.float32(acc + np.float32(a * w))
+        exp += [float(acc)] * n
+    return dict(name="grouped_q8k_three_experts", cite="rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:82-128",
+                scheme="q8_k", m=m, k=k, n=n, num_experts=3, expert_idx=[float(v) for v in route],
+                bytes=packed.hex(), x=[float(v) for v in x], expected=exp, rel_tol=1e-4)
+
+
 def lm_head_cases() -> list[dict]:
     """The reference's LM-head unit tests (rlx-cpu/src/lm_head.rs:254-335) restated: Q8_K rows with
     scale 1 and q = clamp(10 j + i - 128), hidden[i] = 0.01 i.  Expected logits are computed here with
@@ -196,6 +222,8 @@ def main() -> None:
         json.dump(known_answers(), f, indent=1)
     with open(os.path.join(HERE, "lm_head_cases.json"), "w") as f:
         json.dump(lm_head_cases(), f, indent=1)
+    with open(os.path.join(HERE, "grouped_matmul_case.json"), "w") as f:
+        json.dump(grouped_case(), f, indent=1)
     np.savez_compressed(os.path.join(HERE, "seeded_small.npz"), **seeded())
     print("wrote known_answers.json and seeded_small.npz")
 

@@ -1,0 +1,119 @@
+"""Op::DequantGroupedMatMul (MoE expert stacks): y[i] = x[i] . W_{expert_idx[i]}^T.
+
+CPU part: the oracle against the reference's graph test (restated in tests/golden/grouped_matmul_case.json).
+GPU part: rlxq_grouped_matmul through the C ABI against the oracle, every scheme, ragged routings.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _case():
+    with open(os.path.join(GOLDEN, "grouped_matmul_case.json")) as f:
+        c = json.load(f)
+    w = np.frombuffer(bytes.fromhex(c["bytes"]), np.uint8).copy()
+    x = np.array(c["x"], np.float32).reshape(c["m"], c["k"])
+    idx = np.array(c["expert_idx"], np.float32)
+    return c, w, x, idx
+
+
+def _close(y, c):
+    exp = np.array(c["expected"], np.float32)
+    return np.all(np.abs(y.ravel() - exp) / np.maximum(np.abs(exp), 1.0) < c["rel_tol"])
+
+
+def test_oracle_reproduces_the_reference_grouped_test():
+    c, w, x, idx = _case()
+    y = O.grouped_matmul_bt(x, w, idx, c["m"], c["k"], c["n"], c["num_experts"], O.SCHEMES[c["scheme"]])
+    assert _close(y, c)
+    # routing to the wrong expert would be off by the ratio of the scales
+    wrong = O.grouped_matmul_bt(x, w, np.roll(idx, 1), c["m"], c["k"], c["n"], c["num_experts"], O.SCHEMES[c["scheme"]])
+    assert not _close(wrong, c)
+
+
+def test_oracle_grouped_equals_per_row_matmul():
+    s, m, k, n, E = O.Q4_K, 7, 512, 9, 4
+    w = O.fill_weights(s, 3, k, n * E)          # E slabs of [n, k] back to back
+    x = O.fill_normal(5, m * k).reshape(m, k)
+    idx = np.array([3, 0, 0, 2, 3, 3, 0], np.float32)
+    y = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    slab = w.size // E
+    for i in range(m):
+        e = int(idx[i])
+        ref = O.matmul_bt(x[i:i + 1], w[e * slab:(e + 1) * slab], 1, k, n, s)
+        assert np.array_equal(y[i], ref.ravel())
+
+
+# ------------------------------------------------------------------ GPU
+def _gpu(x, w, idx, s, n, E, x_bf16=False, y_bf16=False):
+    import torch
+    import rlx_b200 as R
+    xd = torch.from_numpy(x).cuda()
+    if x_bf16:
+        xd = xd.to(torch.bfloat16)
+    y = R.grouped_matmul(xd, torch.from_numpy(w).cuda(), torch.from_numpy(idx).cuda(), s, n, E,
+                         out_dtype=torch.bfloat16 if y_bf16 else torch.float32)
+    R.device_status()
+    return y.float().cpu().numpy()
+
+
+@pytest.mark.gpu
+def test_gpu_reference_grouped_test():
+    c, w, x, idx = _case()
+    y = _gpu(x, w, idx, O.SCHEMES[c["scheme"]], c["n"], c["num_experts"])
+    assert _close(y, c)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sch", ["q4_0", "q8_0", "q4_k", "q6_k", "q5_k", "q8_k", "q2_k", "q3_k"])
+@pytest.mark.parametrize("m,k,n,E,x_bf16", [(1, 256, 5, 1, False), (8, 512, 33, 8, False), (37, 1024, 20, 5, True),
+                                            (64, 2048, 130, 16, False)])
+def test_gpu_grouped_matches_oracle(sch, m, k, n, E, x_bf16):
+    from tests.helpers import assert_within_tolerance
+    s = O.SCHEMES[sch]
+    w = O.fill_weights(s, 40 + m, k, n * E)
+    x = O.fill_normal(41 + m, m * k).reshape(m, k)
+    if x_bf16:
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)).reshape(m, k)
+    rng = np.random.default_rng(m + E)
+    idx = rng.integers(0, E, m).astype(np.float32)            # ragged: some experts get no rows, some many
+    y = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16)
+    ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    slab = w.size // E
+    wn = np.stack([O.row_norms(s, w[e * slab:(e + 1) * slab], k, n) for e in range(E)])    # [E, n]
+    xn = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
+    bnd = xn[:, None] * wn[idx.astype(np.int64)]
+    assert_within_tolerance(y, ref, bnd, tol=2e-5, what=f"grouped {sch} m={m} E={E}")
+
+
+@pytest.mark.gpu
+def test_gpu_grouped_routing_edges():
+    import torch
+    import rlx_b200 as R
+    s, m, k, n, E = O.Q8_0, 20, 256, 12, 6
+    w = O.fill_weights(s, 2, k, n * E)
+    x = O.fill_normal(3, m * k).reshape(m, k)
+    # all rows to one expert (more than eight: several passes), and ids out of range / NaN -> zero rows
+    idx = np.full(m, 4, np.float32)
+    y = _gpu(x, w, idx, s, n, E)
+    ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    assert np.allclose(y, ref, rtol=0, atol=2e-5 * np.abs(ref).max() + 1e-6)
+    idx[3], idx[7], idx[11] = 6.0, -1.0, np.nan
+    y = _gpu(x, w, idx, s, n, E)
+    assert np.all(y[[3, 7, 11]] == 0) and np.any(y[4] != 0)
+    # bf16 output is the rounding of the f32 output
+    idx = (np.arange(m) % E).astype(np.float32)
+    yf = _gpu(x, w, idx, s, n, E)
+    yb = _gpu(x, w, idx, s, n, E, y_bf16=True)
+    assert np.array_equal(yb, torch.from_numpy(yf).to(torch.bfloat16).float().numpy())
+    # errors
+    from rlx_b200._lib import lib
+    assert lib.rlxq_grouped_matmul(None, s, None, 0, None, None, None, 0, 4, 100, 4, 2, None, 0) == -2   # k % 32
+    assert lib.rlxq_grouped_matmul(None, s, None, 0, None, None, None, 0, 4, 256, 4, 0, None, 0) == -11  # no experts
+    assert lib.rlxq_grouped_matmul(None, 99, None, 0, None, None, None, 0, 4, 256, 4, 2, None, 0) == -1
