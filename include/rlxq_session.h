@@ -47,6 +47,13 @@ RLXQ_API int rlxq_graph_dequant_matmul(rlxq_graph* g, int x_node, int w_node, ui
  * (rlx-cuda/src/unfuse.rs:254-293): out = up * silu(gate), elementwise on two [m,n] f32 nodes. */
 RLXQ_API int rlxq_graph_swiglu_mul(rlxq_graph* g, int gate_node, int up_node);
 
+/* g.add_node(Op::DequantGroupedMatMul{scheme}, [x, w_packed, expert_idx], Shape([m, n], F32))
+ * (rlx-ir/src/op.rs:860-871; usage rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:92-105): w_node is
+ * a U8 param holding num_experts packed [n, k] slabs, expert_idx_node an f32 input with one id per
+ * row of x.  Output dtype is f32. */
+RLXQ_API int rlxq_graph_dequant_grouped_matmul(rlxq_graph* g, int x_node, int w_node, int expert_idx_node,
+                                               uint32_t scheme, uint32_t n, uint32_t num_experts);
+
 /* Graph::set_outputs — one output node. */
 RLXQ_API int rlxq_graph_set_output(rlxq_graph* g, int node);
 

@@ -50,6 +50,7 @@ _SIGS = {
     "rlxq_graph_param_u8": (C.c_int, [vp, cp, u64]),
     "rlxq_graph_dequant_matmul": (C.c_int, [vp, C.c_int, C.c_int, u32, u32, u32]),
     "rlxq_graph_swiglu_mul": (C.c_int, [vp, C.c_int, C.c_int]),
+    "rlxq_graph_dequant_grouped_matmul": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, u32, u32, u32]),
     "rlxq_graph_set_output": (C.c_int, [vp, C.c_int]),
     "rlxq_session_compile": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp)]),
     "rlxq_compiled_free": (None, [vp]),

@@ -241,6 +241,11 @@ class Graph:
     def swiglu_mul(self, gate: int, up: int) -> int:
         return check(lib.rlxq_graph_swiglu_mul(self._h, gate, up))
 
+    def dequant_grouped_matmul_packed(self, x: int, w_packed: int, expert_idx: int, scheme: QuantScheme, n: int,
+                                      num_experts: int) -> int:
+        """add_node(Op::DequantGroupedMatMul{scheme}, [x, w_packed, expert_idx], Shape([m, n], F32))."""
+        return check(lib.rlxq_graph_dequant_grouped_matmul(self._h, x, w_packed, expert_idx, int(scheme), n, num_experts))
+
     def set_outputs(self, nodes: Sequence[int]) -> None:
         if len(nodes) != 1:
             raise ValueError("one output node")

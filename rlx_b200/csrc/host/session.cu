@@ -5,6 +5,7 @@
 #include <new>
 
 #include "../../../include/rlxq_session.h"
+#include "../../../include/rlxq_moe.h"
 #include "../common.cuh"
 #include "../kernels.h"
 
@@ -69,6 +70,35 @@ int Graph::swiglu_mul(int gate, int up) {
     return (int)nodes_.size() - 1;
 }
 
+// Op::DequantGroupedMatMul (rlx-ir/src/op.rs:860-871): inputs [x, packed expert stack, expert_idx].
+int Graph::dequant_grouped_matmul(int x, int w, int idx, uint32_t scheme, uint32_t n, uint32_t num_experts) {
+    const int nn = (int)nodes_.size();
+    if (x < 0 || w < 0 || idx < 0 || x >= nn || w >= nn || idx >= nn)
+        return fail(RLXQ_E_ARG, "dequant_grouped_matmul: bad input node id");
+    const Node& xn = nodes_[x];
+    const Node& wn = nodes_[w];
+    const Node& in = nodes_[idx];
+    if (wn.op != OpKind::Param) return fail(RLXQ_E_ARG, "dequant_grouped_matmul: weight must be a U8 param node");
+    if (xn.op == OpKind::Param || in.op == OpKind::Param)
+        return fail(RLXQ_E_ARG, "dequant_grouped_matmul: x and expert_idx must be value nodes");
+    if (in.dtype != RLXQ_F32 || (uint64_t)in.rows * in.cols != xn.rows)
+        return fail(RLXQ_E_SHAPE, "dequant_grouped_matmul: expert_idx must hold one f32 per row of x");
+    if (num_experts == 0) return fail(RLXQ_E_ARG, "dequant_grouped_matmul: no experts");
+    uint64_t slab = 0;
+    int rc = rlxq_packed_bytes(scheme, xn.cols, n, &slab);
+    if (rc) return rc;
+    if (slab * num_experts != wn.bytes)
+        return fail(RLXQ_E_SHAPE, "dequant_grouped_matmul: param '%s' holds %llu bytes, %u slabs of W[%u,%u] need %llu",
+                    wn.name.c_str(), (unsigned long long)wn.bytes, num_experts, n, xn.cols,
+                    (unsigned long long)(slab * num_experts));
+    Node nd;
+    nd.op = OpKind::DequantGroupedMatMul; nd.rows = xn.rows; nd.cols = n; nd.dtype = RLXQ_F32; nd.scheme = scheme;
+    nd.in0 = x; nd.in1 = w; nd.in2 = idx; nd.experts = num_experts;
+    nd.bytes = (uint64_t)nd.rows * n * 4;
+    nodes_.push_back(nd);
+    return (int)nodes_.size() - 1;
+}
+
 int Graph::set_output(int node) {
     if (node < 0 || node >= (int)nodes_.size() || nodes_[node].op == OpKind::Param)
         return fail(RLXQ_E_ARG, "set_output: bad node id");
@@ -106,6 +136,12 @@ int Session::compile(const Graph& g, ExecMode mode, CompiledGraph** out) {
             size_t need = 0;
             const Node& xn = c->nodes_[nd.in0];
             rc = rlxq_workspace_bytes(nd.scheme, nd.rows, xn.cols, nd.cols, xn.dtype, nd.dtype, &need);
+            if (rc) { delete c; return rc; }
+            if (need > ws) ws = need;
+        }
+        if (nd.op == OpKind::DequantGroupedMatMul) {
+            size_t need = 0;
+            rc = rlxq_grouped_workspace_bytes(nd.rows, nd.experts, &need);
             if (rc) { delete c; return rc; }
             if (need > ws) ws = need;
         }
@@ -170,6 +206,13 @@ int CompiledGraph::enqueue_steps(cudaStream_t s) {
             int rc = rlxq_matmul((rlxq_stream_t)s, nd.scheme, arena_ + offsets_[nd.in0], xn.dtype,
                                  arena_ + offsets_[nd.in1], arena_ + offsets_[i], nd.dtype, nd.rows,
                                  xn.cols, nd.cols, ws_bytes_ ? arena_ + ws_off_ : nullptr, ws_bytes_);
+            if (rc) return rc;
+        } else if (nd.op == OpKind::DequantGroupedMatMul) {
+            const Node& xn = nodes_[nd.in0];
+            int rc = rlxq_grouped_matmul((rlxq_stream_t)s, nd.scheme, arena_ + offsets_[nd.in0], xn.dtype,
+                                         arena_ + offsets_[nd.in1], (const float*)(arena_ + offsets_[nd.in2]),
+                                         arena_ + offsets_[i], nd.dtype, nd.rows, xn.cols, nd.cols, nd.experts,
+                                         arena_ + ws_off_, ws_bytes_);
             if (rc) return rc;
         } else if (nd.op == OpKind::SwigluMul) {
             int rc = launch_swiglu_mul(s, (const float*)(arena_ + offsets_[nd.in0]),
@@ -247,6 +290,7 @@ int CompiledGraph::run_typed(uint32_t n_inputs, const char* const* names, const 
         uint64_t launches = 0;
         for (const Node& nd : nodes_) {
             if (nd.op == OpKind::DequantMatMul || nd.op == OpKind::SwigluMul) ++launches;
+            if (nd.op == OpKind::DequantGroupedMatMul) launches += 2;
             if (io_in_graph_ && nd.op == OpKind::Input && nd.bytes) ++launches;
         }
         if (io_in_graph_ && nodes_[output_].bytes) ++launches;
@@ -297,6 +341,11 @@ int rlxq_graph_dequant_matmul(rlxq_graph* g, int x_node, int w_node, uint32_t sc
 int rlxq_graph_swiglu_mul(rlxq_graph* g, int gate_node, int up_node) {
     if (!g) return fail(RLXQ_E_NULL, "null argument");
     return g->g.swiglu_mul(gate_node, up_node);
+}
+int rlxq_graph_dequant_grouped_matmul(rlxq_graph* g, int x_node, int w_node, int expert_idx_node, uint32_t scheme,
+                                      uint32_t n, uint32_t num_experts) {
+    if (!g) return fail(RLXQ_E_NULL, "null argument");
+    return g->g.dequant_grouped_matmul(x_node, w_node, expert_idx_node, scheme, n, num_experts);
 }
 int rlxq_graph_set_output(rlxq_graph* g, int node) {
     if (!g) return fail(RLXQ_E_NULL, "null argument");

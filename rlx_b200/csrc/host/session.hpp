@@ -11,7 +11,7 @@
 
 namespace rlxq {
 
-enum class OpKind { Input, Param, DequantMatMul, SwigluMul };
+enum class OpKind { Input, Param, DequantMatMul, SwigluMul, DequantGroupedMatMul };
 
 struct Node {
     OpKind op;
@@ -21,7 +21,8 @@ struct Node {
     uint32_t dtype = 0;    // RLXQ_F32 / RLXQ_BF16 (element type of the node's value)
     uint32_t scheme = 0;   // DequantMatMul
     uint64_t bytes = 0;    // size of the node's device slot
-    int in0 = -1, in1 = -1;
+    int in0 = -1, in1 = -1, in2 = -1;
+    uint32_t experts = 0;  // DequantGroupedMatMul
 };
 
 class Graph {
@@ -31,6 +32,7 @@ public:
     int param(const std::string& name, uint64_t bytes);                    // Shape([bytes], U8)
     int dequant_matmul(int x, int w, uint32_t scheme, uint32_t n, uint32_t out_dtype);
     int swiglu_mul(int gate, int up);
+    int dequant_grouped_matmul(int x, int w, int expert_idx, uint32_t scheme, uint32_t n, uint32_t num_experts);
     int set_output(int node);
     const std::vector<Node>& nodes() const { return nodes_; }
     int output() const { return output_; }

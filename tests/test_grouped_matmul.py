@@ -71,6 +71,30 @@ def test_gpu_reference_grouped_test():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["stream", "graph"])
+def test_gpu_reference_grouped_test_through_the_graph_api(mode):
+    """The reference's test as it is written there: Graph -> Session -> set_param_typed -> run with two inputs."""
+    import rlx_b200 as R
+    c, w, x, idx = _case()
+    g = R.Graph("dq_grouped_matmul_q8k")
+    x_in = g.input("x", [c["m"], c["k"]], R.DType.F32)
+    w_packed = g.param("w_packed", [w.size], R.DType.U8)
+    idx_in = g.input("expert_idx", [c["m"], 1], R.DType.F32)
+    y = g.dequant_grouped_matmul_packed(x_in, w_packed, idx_in, R.QuantScheme.GgufQ8K, c["n"], c["num_experts"])
+    g.set_outputs([y])
+    compiled = R.Session(R.Device.Cuda, exec_mode=mode).compile(g)
+    compiled.set_param_typed("w_packed", w, R.DType.U8)
+    for _ in range(2):
+        actual = compiled.run([("x", x), ("expert_idx", idx)], (c["m"], c["n"]))
+        assert _close(actual, c)
+    # a param that does not hold num_experts slabs is rejected when the node is built
+    bad = g.param("w_bad", [w.size - 292], R.DType.U8)
+    with pytest.raises(R.RlxqError) as e:
+        g.dequant_grouped_matmul_packed(x_in, bad, idx_in, R.QuantScheme.GgufQ8K, c["n"], c["num_experts"])
+    assert e.value.status == -2
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("sch", ["q4_0", "q8_0", "q4_k", "q6_k", "q5_k", "q8_k", "q2_k", "q3_k"])
 @pytest.mark.parametrize("m,k,n,E,x_bf16", [(1, 256, 5, 1, False), (8, 512, 33, 8, False), (37, 1024, 20, 5, True),
                                             (64, 2048, 130, 16, False)])
