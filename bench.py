@@ -531,6 +531,117 @@ def run_tp_workload(args, rank, world, local_rank):
 # --------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------
+# MoE decode: name -> (scheme, k, n, experts, rows routed per step); f32 activations.
+MOE_WORKLOADS = {
+    "q4_k_moe_8x_top2_decode": ("q4_k", 4096, 14336, 8, 2),
+    "q4_k_moe_64x_top8_decode": ("q4_k", 2048, 1408, 64, 8),
+}
+
+
+def run_moe_workload(args, rank, world, local_rank):
+    """Op::DequantGroupedMatMul at decode sizes: `rows` tokens each routed to a different expert."""
+    import torch
+    if world != 1:
+        raise SystemExit("the MoE workload is single-GPU")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the rlxq kernels have no CPU path")
+    import rlx_b200 as R
+    from oracle import oracle as O      # input generation and the cpu_baseline leg only
+    import numpy as np
+    sch, k, n, E, rows = MOE_WORKLOADS[args.workload]
+    sid = SCHEME_IDS[sch]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    slab = packed_bytes(sch, k, n)
+    step_bytes = rows * (slab + k * 4 + n * 4)              # the routed experts only: the others are never read
+    rotation = max(2, -(-2 * L2_BYTES // (E * slab)) + 1)
+    w_host = O.fill_weights(sid, 777, k, n * E)
+    stacks = [torch.from_numpy(w_host).to(dev)] + [torch.from_numpy(O.fill_weights(sid, 778 + r, k, n * E)).to(dev)
+                                                    for r in range(rotation - 1)]
+    x_host = O.fill_normal(5, rows * k).reshape(rows, k)
+    x_dev = torch.from_numpy(x_host).to(dev)
+    routes = [torch.from_numpy(np.array([(7 * s + 3 * r) % E for r in range(rows)], np.float32)).to(dev) for s in range(8)]
+    y = torch.empty((rows, n), dtype=torch.float32, device=dev)
+    wsb = torch.empty(1 << 22, dtype=torch.uint8, device=dev)
+
+    def step(i):
+        R.grouped_matmul(x_dev, stacks[i % rotation], routes[i % 8], sid, n, E, out=y, workspace=wsb)
+
+    if os.environ.get("RLXQ_BENCH_GENERAL_GROUPED"):       # development switch: time the general grouped kernel
+        R.set_option("gemv_kernel", 1)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    launches0 = R.launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(args.steps):
+            step(args.warmup + i)
+    launches = R.launch_count() - launches0
+    graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record(); graph.replay(); ev1.record()
+    torch.cuda.synchronize()
+    R.device_status()
+    clocks = sampler.stop()
+    ms_per_step = ev0.elapsed_time(ev1) / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    # end to end: activations and routing from pinned host memory, outputs back to the host
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    r_pin = routes[1].cpu().pin_memory()
+    y_pin = torch.empty((rows, n), dtype=torch.float32).pin_memory()
+    x_st, r_st = torch.empty_like(x_dev), torch.empty_like(routes[0])
+
+    def e2e_step(i):
+        x_st.copy_(x_pin, non_blocking=True)
+        r_st.copy_(r_pin, non_blocking=True)
+        R.grouped_matmul(x_st, stacks[i % rotation], r_st, sid, n, E, out=y, workspace=wsb)
+        y_pin.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    e2e_n = max(2, min(args.steps, 50))
+    t0 = time.perf_counter()
+    for i in range(e2e_n):
+        e2e_step(i)
+    e2e_s = (time.perf_counter() - t0) / e2e_n
+    peak, peak_src = measured_peaks()
+    line = {
+        "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "scheme": sch, "k": k, "n": n, "experts": E, "rows_per_step": rows,
+                   "routing": "each row to a different expert, changing every step",
+                   "l2": f"rotating {rotation} expert stacks of {E * slab // 10**6} MB > 2 x 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": rows * k * 4 + rows * 4,
+                "d2h_bytes_per_step": rows * n * 4, "ms_per_step": e2e_s * 1e3,
+                "api": "rlx_b200.grouped_matmul, pinned host buffers"},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                     "peak_source": peak_src, "kernel": "grouped matmul kernels of one step", "bytes_per_launch": step_bytes,
+                     "avg_launch_us": ms_per_step * 1e3, "traffic": None},
+    }
+    if not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        idx = routes[1].cpu().numpy()
+        O.grouped_matmul_bt(x_host, w_host, idx, rows, k, n, E, sid)
+        t0 = time.perf_counter(); reps = 0
+        while time.perf_counter() - t0 < 6.0 and reps < 20:
+            O.grouped_matmul_bt(x_host, w_host, idx, rows, k, n, E, sid); reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        line["cpu_baseline"] = {"value": step_bytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                                "sample": f"{reps} full steps, each expert's rows split over {cores} host threads "
+                                          "(the reference runs them on one thread)"}
+    print(json.dumps(line), flush=True)
+
+
 def run_lm_workload(args, rank, world, local_rank):
     """Greedy token selection over a packed tied embedding: one rlxq_lm_head_argmax per step."""
     import torch
@@ -649,7 +760,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(LM_WORKLOADS) + [TP_WORKLOAD],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(LM_WORKLOADS) + sorted(MOE_WORKLOADS) + [TP_WORKLOAD],
                     help="default: the Q4_0 GEMV pair on one GPU, the tensor-parallel FFN on several")
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
@@ -667,6 +778,9 @@ def main() -> None:
         return
     if args.workload in LM_WORKLOADS:
         run_lm_workload(args, rank, world, local_rank)
+        return
+    if args.workload in MOE_WORKLOADS:
+        run_moe_workload(args, rank, world, local_rank)
         return
     if args.workload == TP_WORKLOAD:
         if args.impl == "reference":

@@ -8,7 +8,8 @@
  * [n,k] matrix in the layout rlxq_matmul takes.  The reference copies x and the expert ids to the
  * host, counting-sorts the rows there, runs dequantise + sgemm per expert and copies back; here the
  * counting sort (grouped_moe_sort_plan, gguf_matmul.rs:178-205) runs on the device and one kernel
- * walks every expert's rows, so nothing crosses PCIe and nothing synchronises.
+ * walks every expert's rows, so nothing crosses PCIe and nothing synchronises.  Up to 8 rows (decode)
+ * go row by row through the streaming GEMV, the expert picked on the device.
  */
 #ifndef RLXQ_MOE_H
 #define RLXQ_MOE_H
@@ -19,8 +20,10 @@
 extern "C" {
 #endif
 
-/* Scratch for rlxq_grouped_matmul: expert offsets, the row permutation, per-expert cursors. */
-RLXQ_API int rlxq_grouped_workspace_bytes(uint32_t m, uint32_t num_experts, size_t* bytes);
+/* Scratch for rlxq_grouped_matmul: expert offsets, the row permutation, per-expert cursors, or (decode
+ * sizes) the streaming GEMV's own scratch. */
+RLXQ_API int rlxq_grouped_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t num_experts,
+                                          size_t* bytes);
 
 /* x: [m,k] f32 or bf16; expert_idx: [m] f32-encoded expert ids, as the reference's graph input
  * (rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:92-105); y: [m,n] f32 or bf16.  A row whose id

@@ -42,7 +42,7 @@ _SIGS = {
     "rlxq_lm_head_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_lm_head_topk": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, u32, vp, C.c_size_t, vp, vp]),
     "rlxq_lm_head_argmax": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, vp, C.c_size_t, vp, vp]),
-    "rlxq_grouped_workspace_bytes": (C.c_int, [u32, u32, C.POINTER(C.c_size_t)]),
+    "rlxq_grouped_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_grouped_matmul": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, vp, C.c_size_t]),
     "rlxq_graph_new": (vp, [cp]),
     "rlxq_graph_free": (None, [vp]),

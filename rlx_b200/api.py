@@ -151,7 +151,7 @@ def grouped_matmul(x, w_blocks, expert_idx, scheme: int, n: int, num_experts: in
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype or torch.float32, device=x.device)
     need = C.c_size_t()
-    check(lib.rlxq_grouped_workspace_bytes(m, num_experts, C.byref(need)))
+    check(lib.rlxq_grouped_workspace_bytes(int(scheme), m, k, n, num_experts, C.byref(need)))
     if workspace is None or workspace.numel() < need.value:
         workspace = torch.empty(max(need.value, 16), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):

@@ -89,6 +89,11 @@ struct IntParams {
     unsigned long long* flags;   // [ntiles] rendezvous words of shared tiles (single-kernel mode)
     unsigned long long token;    // odd, unique to this call
     uint32_t early;              // single-kernel mode: stages requested before the dependency wait
+    // Expert-indirect mode (MoE decode): W is a stack of [n, k] slabs and this launch multiplies by slab
+    // (uint32_t)*expert_sel, read on the device after the dependency wait; ids outside [0, num_experts)
+    // make the kernel return at once (the caller has zeroed y).
+    const float* expert_sel;
+    uint32_t num_experts;
     uint32_t tslot;              // development builds: which trace slot this launch writes
 };
 
@@ -627,8 +632,22 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     // issuing thread for a few hundred cycles, and one thread issuing them all delays the stream's start.
     const uint32_t pre = min(min(NS, kIntWarps), rg.len);
 
+    // expert-indirect mode: every role learns the slab after the dependency wait (nothing is requested
+    // before it) and leaves at once when the id is out of range
+    auto resolve_expert = [&](uint32_t& row_off) -> bool {
+        row_off = 0u;
+        if (!P.expert_sel) return true;
+        griddep_wait();
+        const float f = *P.expert_sel;
+        if (!(f >= 0.f && f < (float)P.num_experts)) return false;
+        row_off = (uint32_t)f * P.n;
+        return true;
+    };
+
     if (warp == kIntWarps) {
         // ---------------- producer warp ----------------
+        uint32_t row_off;
+        if (!resolve_expert(row_off)) return;
         auto produce = [&](uint32_t tile, uint32_t chunk, uint32_t s) {
             // rows past n and bytes past the row end arrive as zeros (d = 0: they add nothing)
             const uint32_t full = smem_u32(&bars[s]);
@@ -637,7 +656,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
 #pragma unroll
                 for (uint32_t b = 0; b < B::NB; ++b)
                     tma_load_2d(smem_u32(stages + s * stage_bytes + b * B::BOX_BYTES), &P.wmap,
-                                (int32_t)(((chunk * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(tile * 16), full);
+                                (int32_t)(((chunk * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(row_off + tile * 16), full);
             }
         };
         uint32_t s = 0, ph = 1, issued = 0;   // ph: parity to wait for on empty[s] (1 passes on a fresh barrier)
@@ -683,6 +702,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
 
     if (warp == kIntWarps + 1) {
         // ---------------- finisher warp ----------------
+        { uint32_t ro; if (!resolve_expert(ro)) return; }
         // Adds the 16 partials of every output (2 halves x 8 warps, fixed order) and writes the tile,
         // or, for a tile shared with other CTAs, runs the publish / count / re-read sequence.  That
         // sequence is a chain of three global round trips; here it delays nobody, because the
@@ -769,6 +789,8 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     }
 
     // ---------------- consumer warps: lane = (tile row, half of the unit) ----------------
+    uint32_t row_off;
+    if (!resolve_expert(row_off)) return;
     auto request_first_stage = [&](uint32_t w0, uint32_t w1) {
         if (warp >= w0 && warp < min(w1, pre) && lane == 0) {
             uint32_t i = warp, si = 0;
@@ -779,7 +801,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
 #pragma unroll
             for (uint32_t b = 0; b < B::NB; ++b)
                 tma_load_2d(smem_u32(stages + warp * stage_bytes + b * B::BOX_BYTES), &P.wmap,
-                            (int32_t)((((sg.c0 + i) * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(sg.tile * 16), full);
+                            (int32_t)((((sg.c0 + i) * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(row_off + sg.tile * 16), full);
         }
     };
     // Two-kernel mode: the weights are requested before the dependency wait (they are immutable).  In
@@ -955,7 +977,8 @@ static unsigned long long next_call_token() {
 
 template <uint32_t SCHEME, int MM>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair) {
+                        uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair,
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0) {
     using T = StagedTraits<SCHEME>;
     Geometry g;
     geometry(SCHEME, &g);
@@ -963,7 +986,8 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
         return fail(RLXQ_E_WORKSPACE, "integer GEMV needs %zu workspace bytes, got %zu", pl.ws_bytes, ws_bytes);
     if ((uintptr_t)ws & 15u) return fail(RLXQ_E_ALIGN, "workspace must be 16-byte aligned");
     IntParams P{};
-    int rcm = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, IntBox<SCHEME>::ROW / 8, 16);
+    int rcm = encode_weight_map(&P.wmap, w, expert_sel ? (uint64_t)n * num_experts : n, (uint64_t)k / g.elems * g.bytes,
+                                IntBox<SCHEME>::ROW / 8, 16);
     if (rcm) return rcm;
     P.w = w; P.y = y;
     P.xq = reinterpret_cast<const uint8_t*>(ws);
@@ -983,10 +1007,13 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     const int64_t iq = options().gemv_inline_q.load();
     P.inline_q = (!pair && pl.two_way && (uint64_t)k * MM <= kInlineGroups * kIntWarps * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
+    P.expert_sel = expert_sel;
+    P.num_experts = num_experts;
+    if (expert_sel && !P.inline_q) return fail(RLXQ_E_SHAPE, "expert-indirect GEMV needs the single-kernel mode");
     P.x = x; P.x_bf16 = xbf ? 1u : 0u;
     P.flags = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq + pl.ws_partial + pl.ws_counters);
     P.token = next_call_token();
-    P.early = (uint32_t)options().gemv_early.load();
+    P.early = expert_sel ? 0u : (uint32_t)options().gemv_early.load();   // an indirect launch cannot prefetch before it knows its slab
     P.tslot = (uint32_t)(P.token >> 2) & 3u;
     P.err = err_word;
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
@@ -1017,10 +1044,11 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
 
 template <uint32_t SCHEME>
 static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
-                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word, bool pair) {
+                        uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word, bool pair,
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0) {
     const IntPlan pl = plan_int<SCHEME>(m, k, n);
     if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
-    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
     return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
 }
 
@@ -1062,6 +1090,34 @@ static int launch_gemv_int_err(cudaStream_t stream, uint32_t scheme, const void*
 int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
                     bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
     return launch_gemv_int_err(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word());
+}
+
+// One row of an MoE decode step: y[n] = x[k] . W_e^T where W is a stack of num_experts [n, k] slabs and
+// e = (uint32_t)*expert_sel is read on the device.  Needs the single-kernel mode (k <= 12288, tiles shared
+// by at most two CTAs); int_expert_supported tells.
+bool int_expert_supported(uint32_t scheme, uint32_t k, uint32_t n, const void* w, const void* x) {
+    if (!int_supported(scheme, 1, k, n, w, x)) return false;
+    if ((uint64_t)k > kInlineGroups * kIntWarps * 32u * 8u || options().gemv_inline_q.load() == 1) return false;
+    switch (scheme) {
+        case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0>(1, k, n).two_way;
+        case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0>(1, k, n).two_way;
+        case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K>(1, k, n).two_way;
+        case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K>(1, k, n).two_way;
+        default: return false;
+    }
+}
+
+int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w_stack, void* y,
+                           bool ybf, uint32_t k, uint32_t n, uint32_t num_experts, const float* expert_sel, void* ws,
+                           size_t ws_bytes) {
+    int* err = device_error_word();
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
+        default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    }
 }
 
 // y = (up * silu(gate)) . W^T with gu = [gate | up] ([m][2k] f32): the SwiGLU product is formed by the

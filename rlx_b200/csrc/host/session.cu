@@ -141,7 +141,7 @@ int Session::compile(const Graph& g, ExecMode mode, CompiledGraph** out) {
         }
         if (nd.op == OpKind::DequantGroupedMatMul) {
             size_t need = 0;
-            rc = rlxq_grouped_workspace_bytes(nd.rows, nd.experts, &need);
+            rc = rlxq_grouped_workspace_bytes(nd.scheme, nd.rows, c->nodes_[nd.in0].cols, nd.cols, nd.experts, &need);
             if (rc) { delete c; return rc; }
             if (need > ws) ws = need;
         }

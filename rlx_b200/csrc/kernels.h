@@ -28,6 +28,12 @@ bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
                    uint32_t m, uint32_t k, uint32_t n);
 
+// One MoE decode row: the slab of the weight stack is chosen by *expert_sel on the device.
+bool int_expert_supported(uint32_t scheme, uint32_t k, uint32_t n, const void* w, const void* x);
+int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w_stack, void* y,
+                           bool ybf, uint32_t k, uint32_t n, uint32_t num_experts, const float* expert_sel, void* ws,
+                           size_t ws_bytes);
+
 int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
                            uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
 

@@ -11,10 +11,15 @@
 //                       multiplies it into up to eight of that expert's activation rows per pass;
 //                       results go straight to the rows' original positions (the unpermute of
 //                       grouped_moe_unpermute_out, gguf_matmul.rs:207-218, is the store address)
-// Decode-sized batches (a handful of rows per expert) stream every routed expert's weights once.
 // Accumulation is f32 in a different order from the CPU loop; same tolerance as the general kernel.
+//
+// Decode (m <= 8 rows, Q4_0 / Q8_0 / Q4_K / Q6_K, k a multiple of 256 up to 12288) skips both kernels:
+// every row is one launch of the streaming integer GEMV over the whole stack seen as an
+// [experts * n, k] matrix, with the slab picked on the device from expert_idx[i] (gemv_int.cu,
+// expert-indirect mode), so a routed expert's weights come through the TMA ring at GEMV speed.
 #include "common.cuh"
 #include "decode.cuh"
+#include "kernels.h"
 #include "rlxq_moe.h"
 
 namespace rlxq {
@@ -126,24 +131,32 @@ static void launch_grouped_s(cudaStream_t s, dim3 grid, bool xbf, bool ybf, cons
     else moe_grouped_kernel<SCHEME, false, false><<<grid, 256, 0, s>>>(x, w, y, offsets, perm, k, n);
 }
 
-static size_t grouped_ws(uint32_t m, uint32_t E, size_t* off_cursor, size_t* off_perm) {
+constexpr uint32_t kMoeDecodeRows = 8;      // up to this many rows go row by row through the streaming GEMV
+
+static size_t grouped_ws(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t E, size_t* off_cursor,
+                         size_t* off_perm) {
     auto up = [](size_t v) { return (v + 255) / 256 * 256; };
     size_t off = up(((size_t)E + 1) * 4);
     if (off_cursor) *off_cursor = off;
     off += up((size_t)E * 4);
     if (off_perm) *off_perm = off;
     off += up((size_t)m * 4);
-    return off;
+    const size_t gemv = m <= kMoeDecodeRows ? up(int_workspace_bytes(scheme, 1, k, n)) : 0;   // the decode path's scratch
+    return off > gemv ? off : gemv;
 }
 
 }  // namespace rlxq
 
 using namespace rlxq;
 
-extern "C" int rlxq_grouped_workspace_bytes(uint32_t m, uint32_t num_experts, size_t* bytes) {
+extern "C" int rlxq_grouped_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t num_experts,
+                                            size_t* bytes) {
     if (!bytes) return fail(RLXQ_E_NULL, "bytes is null");
+    Geometry g;
+    if (!geometry(scheme, &g)) return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
+    if (k == 0 || k % g.elems) return fail(RLXQ_E_SHAPE, "k=%u is not a positive multiple of the block size %u", k, g.elems);
     if (num_experts == 0 || num_experts > 8192) return fail(RLXQ_E_LIMIT, "num_experts=%u must be in [1, 8192]", num_experts);
-    *bytes = grouped_ws(m, num_experts, nullptr, nullptr);
+    *bytes = grouped_ws(scheme, m, k, n, num_experts, nullptr, nullptr);
     return RLXQ_OK;
 }
 
@@ -162,7 +175,7 @@ extern "C" int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const 
     if ((uintptr_t)w_blocks & 1u) return fail(RLXQ_E_ALIGN, "w_blocks must be 2-byte aligned");
     if ((uintptr_t)y & (y_dtype == RLXQ_BF16 ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
     size_t off_cursor = 0, off_perm = 0;
-    const size_t need = grouped_ws(m, num_experts, &off_cursor, &off_perm);
+    const size_t need = grouped_ws(scheme, m, k, n, num_experts, &off_cursor, &off_perm);
     if (workspace_bytes < need) return fail(RLXQ_E_WORKSPACE, "grouped matmul needs %zu workspace bytes, got %zu", need, workspace_bytes);
     cudaStream_t s = (cudaStream_t)stream;
     uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
@@ -172,6 +185,18 @@ extern "C" int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const 
     const bool xbf = x_dtype == RLXQ_BF16, ybf = y_dtype == RLXQ_BF16;
     // rows with an id outside [0, num_experts) are in no group: their outputs stay zero
     RLXQ_CUDA_TRY(cudaMemsetAsync(y, 0, (size_t)m * n * (ybf ? 2 : 4), s));
+    const uint8_t* wst = (const uint8_t*)w_blocks;
+    const size_t xes = xbf ? 2 : 4, yes = ybf ? 2 : 4;
+    if (m <= kMoeDecodeRows && options().gemv_kernel.load() != 1 && ((size_t)k * xes) % 16 == 0 &&
+        (uint64_t)n * num_experts <= 0x7FFFFFFFull && int_expert_supported(scheme, k, n, wst, x)) {
+        for (uint32_t i = 0; i < m; ++i) {
+            int rc = launch_gemv_int_expert(s, scheme, (const uint8_t*)x + (size_t)i * k * xes, xbf, wst,
+                                            (uint8_t*)y + (size_t)i * n * yes, ybf, k, n, num_experts, expert_idx + i,
+                                            workspace, workspace_bytes);
+            if (rc) return rc;
+        }
+        return RLXQ_OK;
+    }
     moe_sort_kernel<<<1, 1024, num_experts * sizeof(uint32_t), s>>>(expert_idx, m, num_experts, offsets, cursor, perm);
     count_launch();
     const uint32_t wpc = 8;

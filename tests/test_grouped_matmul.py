@@ -117,6 +117,43 @@ def test_gpu_grouped_matches_oracle(sch, m, k, n, E, x_bf16):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("sch", ["q4_0", "q8_0", "q4_k", "q6_k"])
+@pytest.mark.parametrize("m,k,n,E,x_bf16", [(1, 4096, 4800, 4, False), (2, 2048, 4100, 8, True), (8, 4096, 4736, 3, False),
+                                            (5, 6144, 4800, 2, False)])
+def test_gpu_decode_rows_take_the_streaming_gemv(sch, m, k, n, E, x_bf16):
+    """Up to eight rows: one expert-indirect launch of the integer GEMV per row (k a multiple of 2048 here so
+    that Q6_K qualifies too); the general grouped kernel must agree with it to the path's tolerance."""
+    import rlx_b200 as R
+    from tests.helpers import assert_within_tolerance
+    s = O.SCHEMES[sch]
+    w = O.fill_weights(s, 60 + m, k, n * E)
+    x = O.fill_normal(61 + m, m * k).reshape(m, k)
+    if x_bf16:
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)).reshape(m, k)
+    idx = np.array([(3 * i + 1) % E for i in range(m)], np.float32)
+    if m >= 5:
+        idx[2] = idx[0]                                    # two rows on the same expert
+        idx[4] = float(E)                                  # out of range: a zero row
+    before = R.launch_count()
+    y = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16)
+    assert R.launch_count() - before == m                  # one kernel per row, no sort kernel
+    ref = O.grouped_matmul_bt(x, w, np.where(idx < E, idx, -1).astype(np.float32), m, k, n, E, s)
+    slab = w.size // E
+    wn = np.stack([O.row_norms(s, w[e * slab:(e + 1) * slab], k, n) for e in range(E)])
+    xn = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
+    bnd = xn[:, None] * wn[np.minimum(idx, E - 1).astype(np.int64)]
+    assert_within_tolerance(y, ref, bnd, tol=2e-5, what=f"moe decode {sch} m={m}")
+    if m >= 5:
+        assert np.all(y[4] == 0)
+    R.set_option("gemv_kernel", 1)                         # the general grouped kernel on the same inputs
+    try:
+        y2 = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16)
+    finally:
+        R.set_option("gemv_kernel", 0)
+    assert_within_tolerance(y2, ref, bnd, tol=2e-5, what=f"moe general {sch} m={m}")
+
+
+@pytest.mark.gpu
 def test_gpu_grouped_routing_edges():
     import torch
     import rlx_b200 as R
