@@ -4,7 +4,7 @@
 // y[m,n] = x[m,k] . W^T is computed transposed, tile by tile: D[128 weight rows, 256 activation
 // rows] += A[128, 64] . B[256, 64]^T per 64-wide k block.
 //   * A (weights) never exists in memory.  The raw GGUF blocks of 128 rows x 256 weights arrive in
-//     shared memory through one 2-D TMA box; eight decode warps (one thread per weight row, which
+//     shared memory through one 2-D TMA box; eight decode warps, twelve for Q6_K (one thread per weight row, which
 //     is also that thread's tensor-memory lane) turn 64 weights at a time into bf16(d * q) in
 //     registers and store them to tensor memory with tcgen05.st.  d * q is formed in f32 exactly as
 //     the reference decoder does (rlx-gguf/src/lib.rs:574-597, 974-1013) and rounded once to bf16.
@@ -111,13 +111,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // The raw box holds 256 weights of 128 rows; RAW_ROW bytes per row (an odd number of 16-byte
 // chunks, so one-row-per-lane 128-bit reads do not conflict).  `S` = which 64 of the 256.
 template <uint32_t SCHEME> struct GemmRaw;
-template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144, STAGES = 5; };
-template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272, STAGES = 4; };
-template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144, STAGES = 5; };
+// GROUPS: decode warp groups (four warps each).  Two keep pace with the MMA for the cheap decoders (more only
+// add contention: measured 917 against 950 TFLOP/s for Q8_0); Q6_K's decoder is the slow one and gains 10 % from three.
+template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272, STAGES = 4, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 2; };
 // Q6_K super-blocks are 210 bytes: group g of a row starts at byte 210 g, which is only 2-byte aligned.
 // The box starts at the 16-byte boundary below it and is 240 bytes wide (15 chunks: conflict-free, and
 // 14 + 210 <= 240); the decoder is compiled for each of the eight possible offsets 2 (g mod 8).
-template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STAGES = 4; };
+template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STAGES = 4, GROUPS = 3; };
 template <uint32_t SCHEME> __device__ __forceinline__ uint32_t gemm_raw_x(uint32_t g) {   // box start, 8-byte elements
     if (SCHEME == RLXQ_Q6_K) return ((210u * g) & ~15u) / 8u;
     return g * (GemmRaw<SCHEME>::ROW / 8u);
@@ -321,11 +323,12 @@ __device__ __forceinline__ void decode64(const uint8_t* row, uint32_t g, uint32_
 }
 
 // ---- kernel -----------------------------------------------------------------------------------
-constexpr uint32_t kGemmWarps = 16;
-constexpr uint32_t kGemmBlock = kGemmWarps * 32;
+constexpr uint32_t kGemmMaxDecodeGroups = 3;
+constexpr uint32_t kGemmMaxBlock = (4 + 4 * kGemmMaxDecodeGroups + 4) * 32;   // B TMA, MMA, raw TMA, spare | decode | epilogue
 // warp roles: 0 = activation (B) TMA producer, 1 = MMA issuer and tensor-memory owner,
-// 2 = raw weight TMA producer, 3 = idle, 4..11 = decode (tensor-memory lane quarter = warp % 4,
-// sub-blocks of parity (warp - 4) / 4), 12..15 = epilogue (lane quarter = warp % 4)
+// 2 = raw weight TMA producer, 3 = idle, then GROUPS x 4 decode warps (tensor-memory lane quarter =
+// warp % 4; group (warp - 4) / 4 takes the 64-wide k blocks whose running index is its number modulo
+// GROUPS), then 4 epilogue warps (lane quarter = warp % 4).
 
 struct GemmParams {
     CUtensorMap xmap;      // x[m, k] bf16, box 256 rows x 64 columns, 128-byte swizzle
@@ -344,9 +347,10 @@ struct GemmBars {
 };
 
 template <uint32_t SCHEME, uint32_t kGemmTileX>
-__global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams P) {
+__global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams P) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
     constexpr uint32_t kGemmStages = GemmRaw<SCHEME>::STAGES;   // shared memory left after the raw boxes decides
+    constexpr uint32_t kGemmDecodeGroups = GemmRaw<SCHEME>::GROUPS;
     constexpr uint32_t RAW_BYTES = kGemmTileW * RAW_ROW;
     constexpr uint32_t B_BYTES = kGemmTileX * kGemmBK * 2;           // 32 KB
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -369,7 +373,7 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
         }
         for (uint32_t r = 0; r < kGemmRawStages; ++r) {
             mbar_init(smem_u32(&bars->raw_full[r]), 1);
-            mbar_init(smem_u32(&bars->raw_empty[r]), 8);
+            mbar_init(smem_u32(&bars->raw_empty[r]), 4 * kGemmDecodeGroups);
         }
         mbar_init(smem_u32(&bars->d_full), 1);
         mbar_init(smem_u32(&bars->d_free), 4);
@@ -450,9 +454,11 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                 tc_commit(smem_u32(&bars->d_full));
             }
         }
-    } else if (warp >= 4 && warp < 12) {
+    } else if (warp >= 4 && warp < 4 + 4 * kGemmDecodeGroups) {
         // ---------------- decode: raw blocks -> bf16 rows in tensor memory ----------------
-        const uint32_t quarter = warp & 3u, parity = (warp - 4) >> 2;
+        // Group grp takes the k blocks whose running index is grp modulo the number of groups, so the
+        // groups alternate whatever the number of 64-wide blocks per raw group (4) is.
+        const uint32_t quarter = warp & 3u, grp = (warp - 4) >> 2;
         const uint32_t row = quarter * 32 + lane;                       // weight row of the tile == tensor-memory lane
         const uint32_t lane_addr = (quarter * 32) << 16;
         uint32_t r = 0, rph = 0, kbg0 = 0;   // kbg0: k blocks this CTA has gone through before the current group
@@ -462,15 +468,17 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                 if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_full[r]), rph)) { give_up(15); ok = false; break; }
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const uint32_t sub = parity + 2 * half;              // which 64 weights of the group
-                    const uint32_t kbg = kbg0 + sub;                     // running k-block index -> ring slot and phase
+                for (uint32_t sub = 0; sub < 4; ++sub) {                 // which 64 weights of the group
+                    const uint32_t kbg = kbg0 + sub;                     // running k-block index -> owner, ring slot, phase
+                    if (kbg % kGemmDecodeGroups != grp) continue;
                     const uint32_t s = kbg % kGemmStages, fph = ((kbg / kGemmStages) & 1u) ^ 1u;
                     // decode into registers first: only the store needs the stage's tensor-memory columns,
                     // so the arithmetic stays off the free -> store -> MMA chain
                     uint32_t v[32];
-                    if (parity == 0) { if (half == 0) decode64<SCHEME, 0>(rp, g, v); else decode64<SCHEME, 2>(rp, g, v); }
-                    else             { if (half == 0) decode64<SCHEME, 1>(rp, g, v); else decode64<SCHEME, 3>(rp, g, v); }
+                    if (sub == 0) decode64<SCHEME, 0>(rp, g, v);
+                    else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
+                    else if (sub == 2) decode64<SCHEME, 2>(rp, g, v);
+                    else decode64<SCHEME, 3>(rp, g, v);
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
                     tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * s, v);
@@ -485,7 +493,7 @@ __global__ void __launch_bounds__(kGemmBlock, 1) gemm_tcgen05_kernel(const __gri
                 if (++r == kGemmRawStages) { r = 0; rph ^= 1u; }
             }
         }
-    } else if (warp >= 12) {
+    } else if (warp >= 4 + 4 * kGemmDecodeGroups) {
         // ---------------- epilogue: accumulator -> y ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t lane_addr = (quarter * 32) << 16;
@@ -564,7 +572,7 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     uint32_t grid = (uint32_t)sm_count();
     const uint32_t ntiles = P.wtiles * P.xtiles;
     if (grid > ntiles) grid = ntiles;
-    gemm_tcgen05_kernel<SCHEME, TX><<<grid, kGemmBlock, smem, stream>>>(P);
+    gemm_tcgen05_kernel<SCHEME, TX><<<grid, (4 + 4 * GemmRaw<SCHEME>::GROUPS + 4) * 32, smem, stream>>>(P);
     count_launch();
     return check_launch("gemm_tcgen05_kernel");
 }
