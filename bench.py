@@ -642,6 +642,71 @@ def run_moe_workload(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_upload_workload(args, rank, world, local_rank):
+    """GGUF file -> device: one step uploads every tensor of a synthetic 1 GB file of Q4_K blocks."""
+    import struct
+    import tempfile
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    import rlx_b200 as R
+    from oracle import oracle as O      # input generation only
+    torch.cuda.set_device(local_rank)
+    k, n, count = 8192, 28672, 8                                  # eight 132 MB projections
+    w = O.fill_weights(0, 9, k, n)
+    tmp = tempfile.NamedTemporaryFile(suffix=".gguf", delete=False)
+    names = [f"blk.{i}.ffn_up.weight" for i in range(count)]
+    head = struct.pack("<IIQQ", 0x46554747, 3, count, 0)
+    stride = (w.size + 31) // 32 * 32
+    for i, nm in enumerate(names):
+        b = nm.encode()
+        head += struct.pack("<Q", len(b)) + b + struct.pack("<IQQIQ", 2, k, n, 12, i * stride)
+    head += bytes((-len(head)) % 32)
+    with open(tmp.name, "wb") as fh:
+        fh.write(head)
+        for _ in range(count):
+            fh.write(w.tobytes() + bytes(stride - w.size))
+    f = R.GgufFile(tmp.name)
+    total = sum(f.get(nm).nbytes for nm in names)
+    dst = [torch.empty(f.get(nm).nbytes, dtype=torch.uint8, device="cuda") for nm in names]
+    from rlx_b200._lib import lib, check
+
+    def step():
+        for nm, d in zip(names, dst):
+            check(lib.rlxq_gguf_upload_tensor(f._h, nm.encode(), d.data_ptr(), d.numel(), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    steps = max(2, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    ok = bool(np.array_equal(dst[-1].cpu().numpy(), w))
+    # the reference's way: read the whole data segment into memory, slice, upload from pageable memory
+    t0 = time.perf_counter()
+    whole = np.fromfile(tmp.name, dtype=np.uint8, offset=f.data_start)
+    for i, d in enumerate(dst):
+        d.copy_(torch.from_numpy(whole[i * stride:i * stride + w.size]))
+    torch.cuda.synchronize()
+    ref_dt = time.perf_counter() - t0
+    os.unlink(tmp.name)
+    print(json.dumps({
+        "metric": "gguf_upload_gbs", "value": total / dt / 1e9, "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u8", "data": "synthetic",
+        "config": {"workload": args.workload, "file": f"{count} Q4_K tensors of {k} x {n}, {total // 10**6} MB, page cache warm",
+                   "path": "four reader threads: pread -> 8 MiB pinned buffers (two per reader) -> cudaMemcpyAsync on one stream"},
+        "e2e": {"value": total / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": total, "d2h_bytes_per_step": 0,
+                "matches_file": ok},
+        "gpu_launches": 0,
+        "cpu_baseline": {"value": total / ref_dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": "once: whole data segment read into memory, tensors sliced and copied from pageable memory "
+                                   "(the reference's GgufFile::from_reader + set_param_bytes)"}}), flush=True)
+
+
 def run_lm_workload(args, rank, world, local_rank):
     """Greedy token selection over a packed tied embedding: one rlxq_lm_head_argmax per step."""
     import torch
@@ -760,7 +825,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(LM_WORKLOADS) + sorted(MOE_WORKLOADS) + [TP_WORKLOAD],
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + sorted(GEMM_WORKLOADS) + sorted(LM_WORKLOADS) + sorted(MOE_WORKLOADS) + [TP_WORKLOAD, "gguf_upload"],
                     help="default: the Q4_0 GEMV pair on one GPU, the tensor-parallel FFN on several")
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
@@ -781,6 +846,9 @@ def main() -> None:
         return
     if args.workload in MOE_WORKLOADS:
         run_moe_workload(args, rank, world, local_rank)
+        return
+    if args.workload == "gguf_upload":
+        run_upload_workload(args, rank, world, local_rank)
         return
     if args.workload == TP_WORKLOAD:
         if args.impl == "reference":

@@ -1,4 +1,4 @@
-"""ctypes binding of librlxq.so, the C-ABI library (include/rlxq.h, rlxq_session.h, rlxq_tp.h, rlxq_lm.h, rlxq_moe.h).
+"""ctypes binding of librlxq.so, the C-ABI library (include/rlxq.h, rlxq_session.h, rlxq_tp.h, rlxq_lm.h, rlxq_moe.h, rlxq_gguf.h).
 
 The library is the product: if it is missing or does not load, importing this module raises.
 There is no Python or CPU fallback for any compute entry point.
@@ -44,6 +44,18 @@ _SIGS = {
     "rlxq_lm_head_argmax": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, vp, C.c_size_t, vp, vp]),
     "rlxq_grouped_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_grouped_matmul": (C.c_int, [vp, u32, vp, u32, vp, vp, vp, u32, u32, u32, u32, u32, vp, C.c_size_t]),
+    "rlxq_gguf_open": (C.c_int, [cp, C.POINTER(vp)]),
+    "rlxq_gguf_close": (None, [vp]),
+    "rlxq_gguf_version": (u32, [vp]),
+    "rlxq_gguf_alignment": (u64, [vp]),
+    "rlxq_gguf_tensor_count": (u64, [vp]),
+    "rlxq_gguf_data_start": (u64, [vp]),
+    "rlxq_gguf_tensor_name": (C.c_int, [vp, u64, C.POINTER(cp)]),
+    "rlxq_gguf_find": (C.c_int, [vp, cp, vp]),
+    "rlxq_gguf_meta_u64": (C.c_int, [vp, cp, C.POINTER(u64)]),
+    "rlxq_gguf_meta_str": (C.c_int, [vp, cp, C.POINTER(cp)]),
+    "rlxq_gguf_read_tensor": (C.c_int, [vp, cp, vp, u64]),
+    "rlxq_gguf_upload_tensor": (C.c_int, [vp, cp, vp, u64, vp]),
     "rlxq_graph_new": (vp, [cp]),
     "rlxq_graph_free": (None, [vp]),
     "rlxq_graph_input": (C.c_int, [vp, cp, u32, u32, u32]),

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _declared_symbols():
     names = []
-    for h in ("rlxq.h", "rlxq_session.h", "rlxq_tp.h", "rlxq_lm.h", "rlxq_moe.h"):
+    for h in ("rlxq.h", "rlxq_session.h", "rlxq_tp.h", "rlxq_lm.h", "rlxq_moe.h", "rlxq_gguf.h"):
         text = open(os.path.join(ROOT, "include", h)).read()
         names += re.findall(r"^RLXQ_API [^;(]*?\b(rlxq_[a-z0-9_]+)\(", text, flags=re.M)
     return names
