@@ -53,12 +53,14 @@ def test_known_answer_graphs():
         mm = case["matmul"]
         packed = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8).copy()
         scheme = QuantScheme(O.SCHEMES[case["scheme"]])
-        y = _single(scheme, mm["m"], mm["k"], mm["n"], packed, np.ones((mm["m"], mm["k"]), np.float32))
+        x = (np.ones((mm["m"], mm["k"]), np.float32) if mm["x"] == "ones"
+             else np.array(mm["x"], np.float32).reshape(mm["m"], mm["k"]))
+        y = _single(scheme, mm["m"], mm["k"], mm["n"], packed, x).ravel()
         exp = np.array(mm["expected"], np.float32)
         if "rel_tol" in mm:
-            assert abs(y[0, 0] - exp[0]) / max(abs(exp[0]), 1.0) < mm["rel_tol"]
+            assert np.all(np.abs(y - exp) / np.maximum(np.abs(exp), 1.0) < mm["rel_tol"]), case["name"]
         else:
-            assert abs(y[0, 0] - exp[0]) < mm["abs_tol"]
+            assert np.all(np.abs(y - exp) < mm["abs_tol"]), case["name"]
 
 
 def test_decode_shapes_through_the_session():
