@@ -365,8 +365,8 @@ def tp_bytes(m: int) -> int:
     return 3 * packed_bytes("q4_k", TP_D_MODEL, TP_D_FFN) + m * TP_D_MODEL * 2 + m * TP_D_MODEL * 4
 
 
-def tp_config(args, world, rotation):
-    return {"workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
+def tp_config(args, world, rotation, reduce_kind="nccl"):
+    return {"all_reduce": reduce_kind if world > 1 else "none", "workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
             "parallelism": f"tp{world}: gate/up column-split, down row-split, all-reduce of f32 partials",
             "activations": "bf16", "output": "f32",
             "l2": f"rotating {rotation} distinct shard sets per rank > 2 x 126 MB L2"}
@@ -430,6 +430,16 @@ def run_tp_workload(args, rank, world, local_rank):
     x_host = O.fill_normal(78, m * dm).reshape(m, dm)
     x_dev = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
     y = torch.empty((m, dm), dtype=torch.float32, device=dev)
+    # decode-sized partials are summed by the one-shot peer-memory all-reduce; larger ones, or when the peer
+    # mapping cannot be set up (or RLXQ_TP_ALLREDUCE=nccl), by the process group's
+    reduce_kind = "nccl"
+    if world > 1 and os.environ.get("RLXQ_TP_ALLREDUCE", "peer") == "peer":
+        pr = tp.PeerAllReduce(rank, world)
+        if pr.available:
+            for f in ffns:
+                f.peer_reduce = pr
+            if pr.fits(y):
+                reduce_kind = "peer memory, one shot, rank order"
 
     def step(i):
         ffns[i % rotation].forward(x_dev, out=y)
@@ -501,7 +511,7 @@ def run_tp_workload(args, rank, world, local_rank):
         line = {
             "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": tp_config(args, world, rotation),
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": tp_config(args, world, rotation, reduce_kind),
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": m * dm * 2, "d2h_bytes_per_step": m * dm * 4,
                     "ms_per_step": e2e_s / args.steps * 1e3,

@@ -60,6 +60,29 @@ RLXQ_API int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, 
                                  const void* down_blocks, float* y_partial, uint32_t m, uint32_t d_model,
                                  uint32_t ffn_local, void* workspace, size_t workspace_bytes);
 
+/* ---- sum all-reduce of a small f32 vector over peer memory (NVLink), for the decode step ----
+ *
+ * No counterpart in the reference (its collectives run on the host, rlx-driver/src/collective.rs:79-128;
+ * the summation order here is theirs: rank 0, 1, ... world-1).  One process per GPU.  Set-up, once:
+ * every rank allocates a buffer with rlxq_tp_comm_alloc, exports its handle, the ranks exchange the
+ * handles through whatever channel they share (torch.distributed, MPI, a file) and open each other's
+ * with rlxq_tp_ipc_open.  Per step: rlxq_tp_allreduce_sum on every rank.  world <= 8. */
+RLXQ_API int rlxq_tp_comm_bytes(uint32_t max_elems, size_t* bytes);
+RLXQ_API int rlxq_tp_comm_alloc(uint32_t max_elems, void** buf);       /* cudaMalloc + zero; not capture-safe */
+RLXQ_API int rlxq_tp_comm_free(void* buf);
+RLXQ_API int rlxq_tp_ipc_export(const void* buf, uint8_t handle[64]);  /* cudaIpcGetMemHandle */
+RLXQ_API int rlxq_tp_ipc_open(const uint8_t handle[64], void** buf);   /* cudaIpcOpenMemHandle, peer access enabled */
+RLXQ_API int rlxq_tp_ipc_close(void* buf);
+
+/* dst[i] = sum over ranks r = 0..world-1 of src_r[i], the same bits on every rank.  bufs: host array of
+ * `world` device pointers, bufs[rank] this rank's own buffer, the others as opened through IPC.  elems a
+ * multiple of 4, at most the max_elems the buffers were allocated for; src, dst 16-byte aligned; src and
+ * dst may be the same.  One kernel on the caller's stream, capture-safe (the step counter lives in the
+ * buffer).  A rank whose peer does not arrive within a bounded wait records a device error (reported by
+ * rlxq_device_status) and leaves dst unwritten; it never hangs. */
+RLXQ_API int rlxq_tp_allreduce_sum(rlxq_stream_t stream, uint32_t rank, uint32_t world, void* const* bufs,
+                                   uint32_t max_elems, const float* src, float* dst, uint32_t elems);
+
 #ifdef __cplusplus
 }
 #endif

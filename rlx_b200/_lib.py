@@ -39,6 +39,13 @@ _SIGS = {
     "rlxq_tp_slice_k_host": (C.c_int, [u32, vp, u32, u32, u32, u32, vp]),
     "rlxq_tp_ffn_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_tp_ffn_partial": (C.c_int, [vp, u32, u32, vp, u32, vp, vp, vp, u32, u32, u32, vp, C.c_size_t]),
+    "rlxq_tp_comm_bytes": (C.c_int, [u32, C.POINTER(C.c_size_t)]),
+    "rlxq_tp_comm_alloc": (C.c_int, [u32, C.POINTER(vp)]),
+    "rlxq_tp_comm_free": (C.c_int, [vp]),
+    "rlxq_tp_ipc_export": (C.c_int, [vp, vp]),
+    "rlxq_tp_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),
+    "rlxq_tp_ipc_close": (C.c_int, [vp]),
+    "rlxq_tp_allreduce_sum": (C.c_int, [vp, u32, u32, C.POINTER(vp), u32, vp, vp, u32]),
     "rlxq_lm_head_workspace_bytes": (C.c_int, [u32, u32, u32, u32, u32, C.POINTER(C.c_size_t)]),
     "rlxq_lm_head_topk": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, u32, vp, C.c_size_t, vp, vp]),
     "rlxq_lm_head_argmax": (C.c_int, [vp, u32, vp, u32, vp, u32, u32, u32, vp, C.c_size_t, vp, vp]),

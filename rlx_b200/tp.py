@@ -51,6 +51,76 @@ def ffn_workspace_bytes(scheme: int, m: int, d_model: int, ffn_local: int, x_dty
     return out.value
 
 
+class PeerAllReduce:
+    """Sum all-reduce of small f32 tensors over NVLink peer memory (rlxq_tp_allreduce_sum): every rank
+    allocates a buffer, the ranks exchange CUDA IPC handles through the process group and map each
+    other's buffers.  `available` is False when the mapping could not be set up (the caller then keeps
+    using the process group's all-reduce)."""
+
+    MAX_ELEMS = 1 << 16            # 256 KiB of f32: the decode sizes; larger tensors go through the library
+
+    def __init__(self, rank: int, world: int, group=None, max_elems: int = MAX_ELEMS):
+        import torch
+        import torch.distributed as dist
+        self.rank, self.world, self.max_elems = rank, world, max_elems
+        self.available = False
+        self._own = None
+        self._peers = {}
+        if world < 2 or world > 8:
+            return
+        ok, handle = 1, bytes(64)
+        try:
+            own = C.c_void_p()
+            check(lib.rlxq_tp_comm_alloc(max_elems, C.byref(own)))
+            self._own = own.value
+            hb = (C.c_uint8 * 64)()
+            check(lib.rlxq_tp_ipc_export(self._own, hb))
+            handle = bytes(hb)
+        except Exception:
+            ok = 0
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (ok, handle), group=group)
+        if all(g[0] for g in gathered):
+            try:
+                for r, (_, h) in enumerate(gathered):
+                    if r == rank:
+                        continue
+                    p = C.c_void_p()
+                    check(lib.rlxq_tp_ipc_open((C.c_uint8 * 64).from_buffer_copy(h), C.byref(p)))
+                    self._peers[r] = p.value
+            except Exception:
+                ok = 0
+        else:
+            ok = 0
+        flags = [None] * world
+        dist.all_gather_object(flags, ok, group=group)       # all ranks use it, or none does
+        self.available = all(flags)
+        if self.available:
+            ptrs = [self._own if r == rank else self._peers[r] for r in range(world)]
+            self._bufs = (C.c_void_p * world)(*ptrs)
+        torch.cuda.synchronize()
+
+    def __call__(self, t) -> None:
+        """In place: t <- sum over ranks of t, rank order, identical bits on every rank."""
+        import torch
+        assert self.available and t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()
+        with torch.cuda.device(t.device):
+            check(lib.rlxq_tp_allreduce_sum(torch.cuda.current_stream().cuda_stream, self.rank, self.world, self._bufs,
+                                            self.max_elems, t.data_ptr(), t.data_ptr(), t.numel()))
+
+    def fits(self, t) -> bool:
+        return self.available and t.numel() <= self.max_elems and t.numel() % 4 == 0
+
+    def close(self) -> None:
+        for p in self._peers.values():
+            lib.rlxq_tp_ipc_close(p)
+        self._peers = {}
+        if self._own:
+            lib.rlxq_tp_comm_free(self._own)
+            self._own = None
+        self.available = False
+
+
 class TensorParallelFFN:
     def __init__(self, scheme: int, d_model: int, d_ffn: int, rank: int = 0, world: int = 1, device=None,
                  group=None):
@@ -62,6 +132,14 @@ class TensorParallelFFN:
         self.plan = shard_plan(scheme, d_model, d_ffn, world, rank)
         self.gate_up = self.down = None
         self._ws = {}
+        self.peer_reduce = None         # set by enable_peer_allreduce()
+
+    def enable_peer_allreduce(self) -> bool:
+        """Use the one-shot NVLink all-reduce for partials of up to 64 K values (decode); a collective over
+        the group, so every rank must call it.  Returns whether it is in use."""
+        if self.world > 1 and self.peer_reduce is None:
+            self.peer_reduce = PeerAllReduce(self.rank, self.world, self.group)
+        return bool(self.peer_reduce and self.peer_reduce.available)
 
     def load(self, gate: np.ndarray, up: np.ndarray, down: np.ndarray) -> None:
         """Full packed weights in host memory -> this rank's shards on its GPU (one upload each)."""
@@ -100,6 +178,9 @@ class TensorParallelFFN:
     def forward(self, x, out=None):
         y = self.partial(x, out)
         if self.world > 1:
-            import torch.distributed as dist
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            if self.peer_reduce is not None and self.peer_reduce.fits(y):
+                self.peer_reduce(y)
+            else:
+                import torch.distributed as dist
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y

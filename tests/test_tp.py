@@ -117,3 +117,77 @@ def test_per_rank_cuda_partials_sum_to_the_oracle_ffn(m, world):
     y_ref, h = O.ffn_swiglu(xb, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, want_h=True)
     bnd = np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * O.row_norms(O.Q4_K, down, df, dm)[None, :]
     assert np.max(np.abs(y - y_ref) / bnd) < 1e-3        # the path's bound, both layers chained
+
+
+# ------------------------------------------------------------------ peer-memory all-reduce (needs two GPUs)
+def _peer_worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        pr = tp.PeerAllReduce(rank, world)
+        assert pr.available, "peer mapping could not be set up"
+        results = {}
+        for step, n in enumerate((8192, 16, 65536, 8192)):
+            part = O.fill_normal(100 * step + rank, n)
+            t = torch.from_numpy(part).cuda()
+            pr(t)
+            torch.cuda.synchronize()
+            results[f"eager{step}"] = t.cpu().numpy()
+        # captured once, replayed: the step counter lives on the device
+        part = O.fill_normal(900 + rank, 8192)
+        src = torch.from_numpy(part).cuda()
+        t = torch.empty_like(src)
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            t.copy_(src); pr(t)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=s):
+                t.copy_(src)
+                pr(t)
+                t.mul_(1.0)
+        for rep in range(3):
+            g.replay()
+            torch.cuda.synchronize()
+            results[f"graph{rep}"] = t.cpu().numpy()
+        R.device_status()
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
+        dist.barrier()
+        pr.close()
+    finally:
+        os._exit(0)      # tearing the NCCL group down after graph capture can block for minutes
+
+
+@pytest.mark.gpu
+def test_peer_memory_all_reduce_two_gpus(tmp_path):
+    """rlxq_tp_allreduce_sum on two GPUs: bit-identical on both ranks and equal to the sum in rank order
+    (rlx-driver/src/collective.rs:107-127), eager and through a replayed CUDA graph."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_peer_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+        assert p.exitcode == 0
+    got = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    for step, n in enumerate((8192, 16, 65536, 8192)):
+        parts = np.stack([O.fill_normal(100 * step + r, n) for r in range(world)])
+        want = O.allreduce_sum(parts)
+        for r in range(world):
+            assert np.array_equal(got[r][f"eager{step}"], want), (step, r)
+    parts = np.stack([O.fill_normal(900 + r, 8192) for r in range(world)])
+    want = O.allreduce_sum(parts)
+    for rep in range(3):
+        for r in range(world):
+            assert np.array_equal(got[r][f"graph{rep}"], want), (rep, r)
