@@ -152,7 +152,7 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  * RLX_CUDA_* environment keys (rlx-ir/src/env.rs:57-104).  Keys:
  *   "gemv_kernel": 0 = automatic (integer kernel for m <= 2, tensor-mode kernel for m <= 8),
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
- *                  GEMV, 3 = force the staged integer GEMV (2, 3: error if the shape does not allow it)
+ *                  GEMV, 3 = force the staged integer GEMV (m <= 4; 2, 3: error if the shape does not allow it)
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
  *   "gemm_tile_x": 0 = automatic, 128 or 256 = activation rows per tile of the tcgen05 GEMM
  *   "gemv_inline_q": 0 = automatic, 1 = the integer GEMV always runs its activation quantiser as a

@@ -14,7 +14,7 @@ size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t 
     if (m <= 8) {
         // large enough for whichever GEMV kernel the dispatcher (or a forced option) picks
         const size_t a = staged_workspace_bytes(scheme, m, k, n);
-        const size_t b = m <= 2 ? int_workspace_bytes(scheme, m, k, n) : 0;
+        const size_t b = m <= 4 ? int_workspace_bytes(scheme, m, k, n) : 0;
         return a > b ? a : b;
     }
     return 0;
@@ -32,15 +32,17 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     if ((uintptr_t)x & 15u) return fail(RLXQ_E_ALIGN, "x must be 16-byte aligned");
     if ((uintptr_t)y & (ybf ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
     if (m <= 8) {
-        // 0 = automatic: integer kernel for batch 1-2, tensor-mode kernel for 3-8, generic otherwise
+        // 0 = automatic: integer kernel for batch 1-2, tensor-mode kernel for 3-8, generic otherwise.  The integer
+        // kernel also runs batch 3-4 (one CTA per SM, 18 us against the tensor-mode kernel's 15 us on the 4096 ->
+        // 11008 Q4_0 shape), but only when asked for with gemv_kernel = 3.
         const int64_t force = options().gemv_kernel.load();
-        const bool can_int = m <= 2 && int_supported(scheme, m, k, n, w, x);
+        const bool can_int = m <= 4 && int_supported(scheme, m, k, n, w, x);
         const bool can_tc = staged_supported(scheme, m, k, n, w, x, xbf);
         if (force == 3 && !can_int)
             return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
         if (force == 2 && !can_tc)
             return fail(RLXQ_E_SHAPE, "staged GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
-        if (force == 3 || (force == 0 && can_int))
+        if (force == 3 || (force == 0 && can_int && m <= 2))
             return launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 2 || (force == 0 && can_tc))
             return launch_gemv_staged(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);

@@ -48,7 +48,8 @@ namespace rlxq {
 constexpr uint32_t kIntWarps = 8;                      // consumer warps
 constexpr uint32_t kIntThreads = (kIntWarps + 2) * 32; // + one producer warp + one finisher warp
 constexpr uint32_t kIntRB = 4;                         // ring of reduction buffers between consumers and finisher
-constexpr uint32_t kInlineGroups = 6;                   // single-kernel mode: groups of 8 activations a consumer thread quantises
+// single-kernel mode: groups of 8 activations a consumer thread quantises (8 for the four-row kernel)
+constexpr uint32_t inline_groups(int mm) { return mm > 2 ? 8u : 6u; }
 constexpr uint32_t kIntCU = 8;                         // 256-weight units per stage = one per warp
 
 // A stage is NB boxes of 16 rows x UB units, each box fetched by ONE 2-D TMA request (a request
@@ -74,6 +75,7 @@ struct IntParams {
     uint32_t* counters;    // [ntiles] chunks finished per tile
     int* err;
     uint32_t k, n, y_bf16;
+    uint32_t m_real;       // activation rows actually present (3 runs with the four-row kernel)
     uint32_t use_red;      // shared tiles have exactly two contributors: add them into zeroed f32 y
     uint32_t row_bytes, ntiles, nchunks, total_chunks, slots;
     uint32_t chunks_q, chunks_r;   // total_chunks = grid * chunks_q + chunks_r: the first chunks_r CTAs take one more
@@ -708,7 +710,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         // sequence is a chain of three global round trips; here it delays nobody, because the
         // consumer warps only hand over a reduction buffer and go on.
         griddep_wait();
-        const uint32_t col = lane >> 4, rrow = lane & 15u;
+        // a lane finishes tile row rrow of activation rows col = 2 cp + (lane >> 4), cp = 0 .. NC-1
+        constexpr int NC = (MM + 1) / 2;
+        const uint32_t chalf = lane >> 4, rrow = lane & 15u;
         uint32_t r = 0, rph = 0;
         for (uint32_t si = 0; si < nseg; ++si) {
             const Segment sg = segment_at(P, rg, si);
@@ -718,12 +722,17 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 break;
             }
             const float* rbuf = red + r * (kIntWarps * 32 * MM);
-            float v = 0.f;
-            if (col < (uint32_t)MM) {
+            float v[NC];
 #pragma unroll
-                for (uint32_t wv = 0; wv < kIntWarps; ++wv) {
-                    v += rbuf[(wv * 32 + rrow) * MM + col];
-                    v += rbuf[(wv * 32 + 16 + rrow) * MM + col];
+            for (int cp = 0; cp < NC; ++cp) {
+                const uint32_t col = 2 * cp + chalf;
+                v[cp] = 0.f;
+                if (col < (uint32_t)MM) {
+#pragma unroll
+                    for (uint32_t wv = 0; wv < kIntWarps; ++wv) {
+                        v[cp] += rbuf[(wv * 32 + rrow) * MM + col];
+                        v[cp] += rbuf[(wv * 32 + 16 + rrow) * MM + col];
+                    }
                 }
             }
             __syncwarp();
@@ -731,7 +740,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             if (++r == kIntRB) { r = 0; rph ^= 1u; }
             if (P.debug & 8u) continue;
             const uint32_t orow = tile * 16 + rrow;
-            const bool live = col < (uint32_t)MM && orow < P.n;
             bool store = mine == P.nchunks;
             if (!store && P.inline_q) {
                 // Exactly two CTAs share this tile: the one holding its first chunks (role 0) and the one
@@ -742,7 +750,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 // same captured launch.
                 const uint32_t role = sg.c0 ? 1u : 0u;
                 float* pt = P.partial + (size_t)tile * 2 * (MM * 16);
-                if (col < (uint32_t)MM) pt[(role * MM + col) * 16 + rrow] = v;
+#pragma unroll
+                for (int cp = 0; cp < NC; ++cp)
+                    if (2 * cp + chalf < (uint32_t)MM) pt[(role * MM + 2 * cp + chalf) * 16 + rrow] = v[cp];
                 __threadfence();
                 __syncwarp();
                 unsigned long long old = 0ull;
@@ -750,20 +760,28 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 old = __shfl_sync(0xFFFFFFFFu, old, 0);
                 if (old == P.token + 2ull * (1u - role)) {
                     __threadfence();
-                    if (col < (uint32_t)MM) v += __ldcg(&pt[((1u - role) * MM + col) * 16 + rrow]);
+#pragma unroll
+                    for (int cp = 0; cp < NC; ++cp)
+                        if (2 * cp + chalf < (uint32_t)MM) v[cp] += __ldcg(&pt[((1u - role) * MM + 2 * cp + chalf) * 16 + rrow]);
                     if (lane == 0) P.flags[tile] = 0ull;
                     store = true;
                 }
             } else if (!store && P.use_red) {
                 // exactly two CTAs share this tile and y starts at zero: 0 + a + b = 0 + b + a, so a
                 // plain reduction to memory is deterministic and needs no fence, counter or re-read
-                if (live) atomicAdd(reinterpret_cast<float*>(P.y) + (size_t)col * P.n + orow, v);
+#pragma unroll
+                for (int cp = 0; cp < NC; ++cp) {
+                    const uint32_t col = 2 * cp + chalf;
+                    if (col < P.m_real && orow < P.n) atomicAdd(reinterpret_cast<float*>(P.y) + (size_t)col * P.n + orow, v[cp]);
+                }
             } else if (!store) {
                 // the tile is shared with neighbouring CTAs: publish this part in the slot given by the
                 // CTA's position among the tile's contributors; whoever completes the tile adds the slots
                 const uint32_t first_owner = owner_of(P, tile * P.nchunks), last_owner = owner_of(P, (tile + 1) * P.nchunks - 1);
                 float* pt = P.partial + ((size_t)tile * P.slots) * (MM * 16);
-                if (col < (uint32_t)MM) pt[((me - first_owner) * MM + col) * 16 + rrow] = v;
+#pragma unroll
+                for (int cp = 0; cp < NC; ++cp)
+                    if (2 * cp + chalf < (uint32_t)MM) pt[((me - first_owner) * MM + 2 * cp + chalf) * 16 + rrow] = v[cp];
                 __threadfence();
                 __syncwarp();
                 uint32_t prev = 0;
@@ -771,17 +789,27 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
                 if (prev + mine == P.nchunks) {
                     __threadfence();
-                    v = 0.f;
-                    if (col < (uint32_t)MM)
-                        for (uint32_t sl = 0; sl <= last_owner - first_owner; ++sl)
-                            v += __ldcg(&pt[(sl * MM + col) * 16 + rrow]);
+#pragma unroll
+                    for (int cp = 0; cp < NC; ++cp) {
+                        const uint32_t col = 2 * cp + chalf;
+                        v[cp] = 0.f;
+                        if (col < (uint32_t)MM)
+                            for (uint32_t sl = 0; sl <= last_owner - first_owner; ++sl)
+                                v[cp] += __ldcg(&pt[(sl * MM + col) * 16 + rrow]);
+                    }
                     store = true;
                 }
             }
-            if (store && live) {
-                const size_t o = (size_t)col * P.n + orow;
-                if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v);
-                else reinterpret_cast<float*>(P.y)[o] = v;
+            if (store) {
+#pragma unroll
+                for (int cp = 0; cp < NC; ++cp) {
+                    const uint32_t col = 2 * cp + chalf;
+                    if (col < P.m_real && orow < P.n) {
+                        const size_t o = (size_t)col * P.n + orow;
+                        if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v[cp]);
+                        else reinterpret_cast<float*>(P.y)[o] = v[cp];
+                    }
+                }
             }
         }
         if (lane == 0) RLXQ_T(P.tslot, 9);
@@ -827,13 +855,14 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     if (P.inline_q) {
         if (!(P.debug & 4u)) {
             // every load is issued before the first value is used: one trip to L2, not one per group
-            const uint32_t gpr = P.k / 8, total = gpr * MM;   // whole warps stay together: gpr % 32 == 0
+            const uint32_t gpr = P.k / 8, total = gpr * P.m_real;   // whole warps stay together: gpr % 32 == 0
+            constexpr uint32_t kInlineGroups = inline_groups(MM);
             uint4 raw[kInlineGroups][2];
 #pragma unroll
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
                 const uint32_t g = tid + i * kIntWarps * 32;
                 if (g < total) {
-                    const uint32_t r = (MM > 1 && g >= gpr) ? 1u : 0u;
+                    const uint32_t r = MM > 1 ? g / gpr : 0u;
                     load_raw8(P.x, P.x_bf16, P.k, r, (g - r * gpr) * 8, raw[i]);
                 }
             }
@@ -842,7 +871,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
                 const uint32_t g = tid + i * kIntWarps * 32;
                 if (g < total) {
-                    const uint32_t r = (MM > 1 && g >= gpr) ? 1u : 0u;
+                    const uint32_t r = MM > 1 ? g / gpr : 0u;
                     float f[8];
                     raw8_to_f32(raw[i], P.x_bf16, f);
                     quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
@@ -931,25 +960,27 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     constexpr uint32_t stage_bytes = IntBox<SCHEME>::STAGE_BYTES;
     IntPlan pl{};
     pl.ok = false;
-    if (m == 0 || m > 2 || n == 0 || k == 0 || k % (256 * T::AG)) return pl;
+    if (m == 0 || m > 4 || n == 0 || k == 0 || k % (256 * T::AG)) return pl;
+    const uint32_t mm = m > 2 ? 4u : m;                                // rows the kernel template carries
     const uint32_t sms = (uint32_t)sm_count();
     auto align = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
     pl.ntiles = (n + 15) / 16;
     pl.nchunks = (k / 256 + kIntCU - 1) / kIntCU;
     if ((uint64_t)pl.ntiles * pl.nchunks > 0xFFFFFFFFull / 2) return pl;
     pl.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;      // a multiple of 16: k % 256 == 0
-    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * m, 128);
-    const uint32_t tail = kIntRB * kIntWarps * 32 * m * 4 + 1024;      // reduction buffers, barriers, flags
+    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * mm, 128);
+    const uint32_t tail = kIntRB * kIntWarps * 32 * mm * 4 + 1024;     // reduction buffers, barriers, flags
     // two CTAs per SM when that still leaves each a ring of >= 4 stages, else one
     const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     uint32_t per_sm = 2, budget = budget2;
-    if (fixed + tail + 4 * stage_bytes > budget2) { per_sm = 1; budget = budget1; }
+    // the four-row kernel keeps 64 activation words in registers: one CTA per SM
+    if (mm > 2 || fixed + tail + 4 * stage_bytes > budget2) { per_sm = 1; budget = budget1; }
     if (fixed + tail + 2 * stage_bytes > budget) return pl;          // activations do not fit: not this kernel
     pl.nstages = (budget - fixed - tail) / stage_bytes;
     if (pl.nstages > 24) pl.nstages = 24;
     pl.off_stage = fixed;
     pl.off_red = pl.off_stage + pl.nstages * stage_bytes;
-    pl.off_bar = pl.off_red + kIntRB * kIntWarps * 32 * m * 4;
+    pl.off_bar = pl.off_red + kIntRB * kIntWarps * 32 * mm * 4;
     pl.smem_bytes = pl.off_bar + (2 * pl.nstages + 1 + 2 * kIntRB) * 8 + 64;
     pl.total_chunks = pl.ntiles * pl.nchunks;
     pl.grid = sms * per_sm;
@@ -959,8 +990,8 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     const uint32_t per_cta = pl.total_chunks / pl.grid;              // >= 1
     pl.two_way = per_cta >= pl.nchunks;                              // a tile is cut by at most one range boundary
     pl.slots = (pl.nchunks + per_cta - 1) / per_cta + 1;             // contributors a tile can have
-    pl.ws_xq = align((size_t)pl.xq_row_bytes * m, 256);
-    pl.ws_partial = align((size_t)pl.ntiles * pl.slots * m * 16 * 4, 256);
+    pl.ws_xq = align((size_t)pl.xq_row_bytes * mm, 256);
+    pl.ws_partial = align((size_t)pl.ntiles * pl.slots * mm * 16 * 4, 256);
     pl.ws_counters = align((size_t)pl.ntiles * 4, 256);
     pl.ws_bytes = pl.ws_xq + pl.ws_partial + pl.ws_counters + align((size_t)pl.ntiles * 8, 256);   // + rendezvous words
     pl.ok = true;
@@ -978,7 +1009,7 @@ static unsigned long long next_call_token() {
 template <uint32_t SCHEME, int MM>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                         uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair,
-                        const float* expert_sel = nullptr, uint32_t num_experts = 0) {
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0, uint32_t m_real = (uint32_t)MM) {
     using T = StagedTraits<SCHEME>;
     Geometry g;
     geometry(SCHEME, &g);
@@ -993,7 +1024,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.xq = reinterpret_cast<const uint8_t*>(ws);
     P.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq);
     P.counters = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq + pl.ws_partial);
-    P.k = k; P.n = n; P.y_bf16 = ybf;
+    P.k = k; P.n = n; P.y_bf16 = ybf; P.m_real = m_real;
     P.use_red = (pl.two_way && !ybf) ? 1u : 0u;
     P.row_bytes = k / g.elems * g.bytes;
     P.ntiles = pl.ntiles; P.nchunks = pl.nchunks; P.total_chunks = pl.total_chunks; P.slots = pl.slots;
@@ -1005,7 +1036,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
     // dependent-launch hop and a copy on the critical path of a call that lasts only microseconds.
     const int64_t iq = options().gemv_inline_q.load();
-    P.inline_q = (!pair && pl.two_way && (uint64_t)k * MM <= kInlineGroups * kIntWarps * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
+    P.inline_q = (!pair && pl.two_way && (uint64_t)k * m_real <= inline_groups(MM) * kIntWarps * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
     P.expert_sel = expert_sel;
     P.num_experts = num_experts;
@@ -1024,12 +1055,12 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
         RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[dev].store(1);
     }
-    const uint32_t groups = (k / 8) * MM;
+    const uint32_t groups = (k / 8) * m_real;
     int rc = RLXQ_OK;
     const uint32_t qgrid = (groups + 255) / 256;
     if (!(P.debug & 16u) && !P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
-                        (uint32_t)MM, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
-                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? (uint32_t)MM * n : 0u,
+                        m_real, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
+                        P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? m_real * n : 0u,
 #ifdef RLXQ_TRACE
                         (P.tslot << 8) |
 #endif
@@ -1049,7 +1080,8 @@ static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint
     const IntPlan pl = plan_int<SCHEME>(m, k, n);
     if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
     if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
-    return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+    if (m == 2) return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+    return launch_int_t<SCHEME, 4>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, m);
 }
 
 bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
@@ -1097,7 +1129,7 @@ int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
 // by at most two CTAs); int_expert_supported tells.
 bool int_expert_supported(uint32_t scheme, uint32_t k, uint32_t n, const void* w, const void* x) {
     if (!int_supported(scheme, 1, k, n, w, x)) return false;
-    if ((uint64_t)k > kInlineGroups * kIntWarps * 32u * 8u || options().gemv_inline_q.load() == 1) return false;
+    if ((uint64_t)k > inline_groups(1) * kIntWarps * 32u * 8u || options().gemv_inline_q.load() == 1) return false;
     switch (scheme) {
         case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0>(1, k, n).two_way;
         case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0>(1, k, n).two_way;

@@ -60,7 +60,7 @@ def _kernels_for(s, m, k):
     ks = [1, 0]
     if s in (O.Q4_0, O.Q8_0, O.Q4_K, O.Q6_K) and k % unit == 0 and m <= 8:
         ks.append(2)
-        if m <= 2:
+        if m <= 4:
             ks.append(3)
     return ks
 
@@ -143,6 +143,9 @@ INT_SHAPES = [
     ("q8_0", 1, 256, 16), ("q8_0", 2, 768, 33), ("q8_0", 1, 4096, 100),
     ("q4_k", 1, 256, 1), ("q4_k", 1, 512, 19), ("q4_k", 2, 1280, 40), ("q4_k", 1, 4096, 31),
     ("q6_k", 1, 2048, 9), ("q6_k", 2, 2048, 16), ("q6_k", 1, 6144, 37),
+    # three and four rows: the four-row kernel (one CTA per SM, activations of a block in registers for Q4_0)
+    ("q4_0", 4, 4096, 130), ("q4_0", 3, 2304, 50), ("q4_0", 4, 11008, 33), ("q8_0", 4, 1024, 77), ("q8_0", 3, 4096, 40),
+    ("q4_k", 4, 4096, 31), ("q4_k", 3, 1280, 100), ("q6_k", 4, 2048, 16), ("q6_k", 3, 6144, 37),
 ]
 
 
