@@ -99,6 +99,27 @@ class PeerAllReduce:
             ptrs = [self._own if r == rank else self._peers[r] for r in range(world)]
             self._bufs = (C.c_void_p * world)(*ptrs)
         torch.cuda.synchronize()
+        if self.available:
+            # One trial against the process group's all-reduce before anything relies on the mapping: a rank
+            # that sees a timeout or a different sum votes it down and every rank falls back together.
+            good = 1
+            try:
+                t = torch.arange(1024, dtype=torch.float32, device="cuda") * float(rank + 1)
+                want = t.clone()
+                dist.all_reduce(want, group=group)
+                for _ in range(2):                      # both data slots
+                    got = t.clone()
+                    self(got)
+                    torch.cuda.synchronize()
+                    err = C.c_int(0)
+                    if lib.rlxq_device_status(C.byref(err)) != 0 or not torch.equal(got, want):
+                        good = 0
+            except Exception:
+                good = 0
+            votes = [None] * world
+            dist.all_gather_object(votes, good, group=group)
+            if not all(votes):
+                self.available = False
 
     def __call__(self, t) -> None:
         """In place: t <- sum over ranks of t, rank order, identical bits on every rank."""
