@@ -152,6 +152,11 @@ int rlxq_set_option(const char* key, int64_t value) {
         options().gemv_inline_q = value;
         return RLXQ_OK;
     }
+    if (!strcmp(key, "gemm_streamk")) {
+        if (value < 0 || value > 2) return fail(RLXQ_E_ARG, "gemm_streamk must be 0, 1 or 2");
+        options().gemm_streamk = value;
+        return RLXQ_OK;
+    }
     if (!strcmp(key, "gemm_tile_x")) {
         if (value != 0 && value != 128 && value != 256) return fail(RLXQ_E_ARG, "gemm_tile_x must be 0, 128 or 256");
         options().gemm_tile_x = value;
@@ -169,6 +174,7 @@ int rlxq_get_option(const char* key, int64_t* value) {
     if (!strcmp(key, "pdl")) { *value = options().pdl; return RLXQ_OK; }
     if (!strcmp(key, "gemv_early")) { *value = options().gemv_early; return RLXQ_OK; }
     if (!strcmp(key, "gemv_inline_q")) { *value = options().gemv_inline_q; return RLXQ_OK; }
+    if (!strcmp(key, "gemm_streamk")) { *value = options().gemm_streamk; return RLXQ_OK; }
     if (!strcmp(key, "gemm_tile_x")) { *value = options().gemm_tile_x; return RLXQ_OK; }
     return fail(RLXQ_E_ARG, "unknown option '%s'", key);
 }

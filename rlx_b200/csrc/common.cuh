@@ -28,6 +28,7 @@ struct Options {
     std::atomic<int64_t> gemv_debug{0};
     std::atomic<int64_t> pdl{1};
     std::atomic<int64_t> gemm_tile_x{0};
+    std::atomic<int64_t> gemm_streamk{0};
     std::atomic<int64_t> gemv_inline_q{0};
     std::atomic<int64_t> gemv_early{2};
 };

@@ -17,7 +17,7 @@ size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t 
         const size_t b = m <= 4 ? int_workspace_bytes(scheme, m, k, n) : 0;
         return a > b ? a : b;
     }
-    return 0;
+    return gemm_tc_workspace_bytes(m, k, n);      // partial tiles of the stream-K split, when the shape wants it
 }
 
 int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
@@ -53,7 +53,7 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     const bool can = gemm_tc_supported(scheme, m, k, n, w, x, xbf);
     if (gforce == 2 && !can)
         return fail(RLXQ_E_SHAPE, "the tcgen05 GEMM needs bf16 activations, k %% 256 == 0, Q4_0/Q8_0/Q4_K and 16-byte alignment");
-    if (can && gforce != 1) return launch_gemm_tc(stream, scheme, x, w, y, ybf, m, k, n);
+    if (can && gforce != 1) return launch_gemm_tc(stream, scheme, x, w, y, ybf, m, k, n, ws, ws_bytes);
     return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
 }
 

@@ -34,7 +34,7 @@
 namespace rlxq {
 
 constexpr uint32_t kGemmTileW = 128;    // weight rows per tile (MMA M, tensor-memory lanes)
-constexpr uint32_t kGemmTileXMax = 256; // activation rows per tile (MMA N): 256, or 128 when that fills more SMs
+// activation rows per tile (MMA N): a template parameter, 256, or 128 when that fills more SMs
 constexpr uint32_t kGemmBK = 64;        // k per pipeline stage (one 128-byte swizzled row of bf16)
 constexpr uint32_t kGemmMaxStages = 6;  // B shared-memory stages == A tensor-memory stages (4 or 5, by format)
 constexpr uint32_t kGemmRawStages = 2;  // raw weight boxes (256 weights of 128 rows each)
@@ -131,6 +131,47 @@ __device__ __forceinline__ float u8_to_f32(uint32_t b) { return __uint_as_float(
 template <int OFF>
 __device__ __forceinline__ float u8_minus(uint32_t b) { return __uint_as_float(0x4B000000u | b) - (8388608.0f + (float)OFF); }
 
+// The decoders are bound by instruction issue (two decode warps share a scheduler with the MMA pace of one
+// k block per 512 cycles), so they work on pairs: one byte-permute per weight builds the float 2^23 + byte
+// straight from the raw word, and the arithmetic uses the packed two-float instructions of this architecture.
+// Every step rounds exactly as the scalar f32 expression it replaces.
+__device__ __forceinline__ uint64_t f32x2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t f32x2_splat(float f) { return f32x2(__float_as_uint(f), __float_as_uint(f)); }
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// two floats -> bf16 pair, the first in the low half
+__device__ __forceinline__ uint32_t bf16x2_of(uint64_t v) {
+    uint32_t lo, hi, d;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+    return d;
+}
+// bytes 2 H and 2 H + 1 of u -> (2^23 + byte, 2^23 + byte)
+template <int H> __device__ __forceinline__ uint64_t magic_pair(uint32_t u) {
+    return f32x2(__byte_perm(u, 0x4B000000u, 0x7440 + 2 * H), __byte_perm(u, 0x4B000000u, 0x7441 + 2 * H));
+}
+// (byte - OFF) * scale for bytes 2 H, 2 H + 1 of u, as a bf16 pair
+template <int H> __device__ __forceinline__ uint32_t scaled_pair(uint32_t u, uint64_t neg_off, uint64_t scale) {
+    return bf16x2_of(mul_f32x2(add_f32x2(magic_pair<H>(u), neg_off), scale));
+}
+
 template <uint32_t SCHEME, int S> struct Decode64;
 
 template <int S> struct Decode64<RLXQ_Q4_0, S> {
@@ -156,14 +197,14 @@ template <int S> struct Decode64<RLXQ_Q4_0, S> {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) qs[i] = w[W0 + 5 + i];
             }
-            const float d = f16_bits_to_f32(dbits);
+            const uint64_t d2 = f32x2_splat(f16_bits_to_f32(dbits)), off = f32x2_splat(-(8388608.0f + 8.0f));
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {   // weights 2p, 2p+1: low nibbles of bytes 2p, 2p+1; 16+2p..: high nibbles
-                const uint32_t word = qs[p >> 1] >> (16 * (p & 1));
-                const float l0 = d * u8_minus<8>(word & 0xFu), l1 = d * u8_minus<8>((word >> 8) & 0xFu);
-                const float h0 = d * u8_minus<8>((word >> 4) & 0xFu), h1 = d * u8_minus<8>((word >> 12) & 0xFu);
-                v[16 * blk + p] = pack_bf16(l0, l1);
-                v[16 * blk + 8 + p] = pack_bf16(h0, h1);
+            for (int i = 0; i < 4; ++i) {   // weights 4i..4i+3: low nibbles of bytes 4i..; weights 16+4i..: high nibbles
+                const uint32_t lo = qs[i] & 0x0F0F0F0Fu, hi = (qs[i] >> 4) & 0x0F0F0F0Fu;
+                v[16 * blk + 2 * i] = scaled_pair<0>(lo, off, d2);
+                v[16 * blk + 2 * i + 1] = scaled_pair<1>(lo, off, d2);
+                v[16 * blk + 8 + 2 * i] = scaled_pair<0>(hi, off, d2);
+                v[16 * blk + 8 + 2 * i + 1] = scaled_pair<1>(hi, off, d2);
             }
         }
     }
@@ -192,11 +233,12 @@ template <int S> struct Decode64<RLXQ_Q8_0, S> {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) q[i] = w[W0 + 9 + i];
             }
-            const float d = f16_bits_to_f32(dbits);
+            const uint64_t d2 = f32x2_splat(f16_bits_to_f32(dbits)), off = f32x2_splat(-(8388608.0f + 128.0f));
 #pragma unroll
-            for (int p = 0; p < 16; ++p) {  // int8 -> (q + 128) unsigned -> float, minus 128
-                const uint32_t u = (q[p >> 1] ^ 0x80808080u) >> (16 * (p & 1));
-                v[16 * blk + p] = pack_bf16(d * u8_minus<128>(u & 0xFFu), d * u8_minus<128>((u >> 8) & 0xFFu));
+            for (int i = 0; i < 8; ++i) {   // int8 -> (q + 128) unsigned -> float, minus 128
+                const uint32_t u = q[i] ^ 0x80808080u;
+                v[16 * blk + 2 * i] = scaled_pair<0>(u, off, d2);
+                v[16 * blk + 2 * i + 1] = scaled_pair<1>(u, off, d2);
             }
         }
     }
@@ -224,11 +266,15 @@ template <int S> struct Decode64<RLXQ_Q4_K, S> {
         const uint4 a = *reinterpret_cast<const uint4*>(row + 16 + 32 * S);
         const uint4 b = *reinterpret_cast<const uint4*>(row + 32 + 32 * S);
         const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint64_t off = f32x2_splat(-8388608.0f);
+        const uint64_t dl2 = f32x2_splat(dl), ml2 = f32x2_splat(-ml), dh2 = f32x2_splat(dh), mh2 = f32x2_splat(-mh);
 #pragma unroll
-        for (int p = 0; p < 16; ++p) {
-            const uint32_t word = qs[p >> 1] >> (16 * (p & 1));
-            v[p] = pack_bf16(fmaf(dl, u8_to_f32(word & 0xFu), -ml), fmaf(dl, u8_to_f32((word >> 8) & 0xFu), -ml));
-            v[16 + p] = pack_bf16(fmaf(dh, u8_to_f32((word >> 4) & 0xFu), -mh), fmaf(dh, u8_to_f32((word >> 12) & 0xFu), -mh));
+        for (int i = 0; i < 8; ++i) {       // fma(scale, nibble, -min), the nibble exact in f32
+            const uint32_t lo = qs[i] & 0x0F0F0F0Fu, hi = (qs[i] >> 4) & 0x0F0F0F0Fu;
+            v[2 * i] = bf16x2_of(fma_f32x2(dl2, add_f32x2(magic_pair<0>(lo), off), ml2));
+            v[2 * i + 1] = bf16x2_of(fma_f32x2(dl2, add_f32x2(magic_pair<1>(lo), off), ml2));
+            v[16 + 2 * i] = bf16x2_of(fma_f32x2(dh2, add_f32x2(magic_pair<0>(hi), off), mh2));
+            v[16 + 2 * i + 1] = bf16x2_of(fma_f32x2(dh2, add_f32x2(magic_pair<1>(hi), off), mh2));
         }
     }
 };
@@ -278,9 +324,10 @@ template <int S, int O> struct Decode64Q6 {
                 const uint32_t lo = (qlw >> (4 * (g4 >> 1))) & 0x0F0F0F0Fu;
                 const uint32_t hi = (g4 < 2 ? (qhw << (4 - 2 * g4)) : (qhw >> (2 * g4 - 4))) & 0x30303030u;
                 const uint32_t mw = lo | hi;
-                const float ds = gsel == 0 ? (i < 4 ? s00 : s01) : (i < 4 ? s10 : s11);
-                v[16 * gsel + 2 * i] = pack_bf16(ds * u8_minus<32>(mw & 0xFFu), ds * u8_minus<32>((mw >> 8) & 0xFFu));
-                v[16 * gsel + 2 * i + 1] = pack_bf16(ds * u8_minus<32>((mw >> 16) & 0xFFu), ds * u8_minus<32>(mw >> 24));
+                const uint64_t ds = f32x2_splat(gsel == 0 ? (i < 4 ? s00 : s01) : (i < 4 ? s10 : s11));
+                const uint64_t off = f32x2_splat(-(8388608.0f + 32.0f));
+                v[16 * gsel + 2 * i] = scaled_pair<0>(mw, off, ds);
+                v[16 * gsel + 2 * i + 1] = scaled_pair<1>(mw, off, ds);
             }
         }
     }
@@ -335,15 +382,184 @@ struct GemmParams {
     CUtensorMap wmap;      // W[n, row_bytes / 8] eight-byte elements, box 128 rows x one 256-weight group
     void* y;
     int* err;
-    uint32_t m, n, k, y_bf16;
+    uint32_t m, n, k, y_bf16, y_vec;      // y_vec: y rows can be written in aligned 16-byte pieces
     uint32_t wtiles, xtiles;
+    // Work split.  streamk == 0: CTA c takes whole tiles c, c + grid, ...  streamk == 1: the units
+    // (tile, 256-weight k group), tile-major, are dealt as contiguous ranges of units_q units (the first
+    // units_r CTAs one more), so every SM gets the same work however many tiles there are; a tile cut
+    // by range boundaries is completed by the last of its contributors to arrive (partial tiles in
+    // `partial`, one slot per CTA and end of its range; arrival counters in `counters`, zeroed by the host).
+    uint32_t streamk, kgroups, units_q, units_r;
+    float* partial;
+    uint32_t* counters;
 };
+
+#ifdef RLXQ_TRACE
+// Timeline instrumentation for development builds only (never compiled into the shipped library).
+__device__ unsigned long long g_gemm_trace[256][32];
+__device__ __forceinline__ unsigned long long gemm_gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define GT(i) do { if (blockIdx.x < 256) g_gemm_trace[blockIdx.x][i] = gemm_gtime(); } while (0)
+#define GTV(i, v) do { if (blockIdx.x < 256) g_gemm_trace[blockIdx.x][i] = (unsigned long long)(v); } while (0)
+#else
+#define GT(i) do {} while (0)
+#define GTV(i, v) do {} while (0)
+#endif
+
+struct GemmSeg { uint32_t tile, g0, g1; };     // k groups [g0, g1) of one tile
+
+__device__ __forceinline__ uint32_t gemm_range_start(const GemmParams& P, uint32_t c) {
+    return c * P.units_q + min(c, P.units_r);
+}
+// The CTA whose range holds unit u.
+__device__ __forceinline__ uint32_t gemm_owner(const GemmParams& P, uint32_t u) {
+    const uint32_t big = P.units_r * (P.units_q + 1);
+    return u < big ? u / (P.units_q + 1) : P.units_r + (u - big) / P.units_q;
+}
+// Iteration over this CTA's segments, in the order every warp role walks them.
+__device__ __forceinline__ void gemm_seg_init(const GemmParams& P, uint32_t& cur, uint32_t& lim) {
+    if (P.streamk) { cur = gemm_range_start(P, blockIdx.x); lim = gemm_range_start(P, blockIdx.x + 1); }
+    else { cur = blockIdx.x; lim = P.wtiles * P.xtiles; }
+}
+__device__ __forceinline__ bool gemm_seg_next(const GemmParams& P, uint32_t& cur, uint32_t lim, GemmSeg& sg) {
+    if (cur >= lim) return false;
+    if (P.streamk) {
+        sg.tile = cur / P.kgroups;
+        sg.g0 = cur - sg.tile * P.kgroups;
+        sg.g1 = min(P.kgroups, sg.g0 + (lim - cur));
+        cur += sg.g1 - sg.g0;
+    } else {
+        sg.tile = cur; sg.g0 = 0; sg.g1 = P.kgroups;
+        cur += gridDim.x;
+    }
+    return true;
+}
+
+// Where an epilogue pass writes: y (bf16 or f32, row pitch n) or a partial tile (f32, row pitch 128).
+struct GemmDst {
+    uint8_t* base;
+    size_t ld;                        // elements per activation row
+    uint32_t m0, mlim, n0, nlim;      // first row / column of the tile in the destination, and its extents
+};
+constexpr uint32_t kGemmEpiStage = 2 * 8192;   // two 8 KB transposition buffers
+
+// Thirty-two accumulator columns (activation rows 32 c ..) of the 128 weight rows -> destination.  A thread
+// owns one weight row, so its values lie one destination row apart; written directly, a warp's store is
+// 64 or 128 bytes and each thread issues one store per value.  Here the columns are transposed through
+// shared memory 8 KB at a time and leave as 16-byte pieces, a warp covering whole 256- or 512-byte row
+// segments.  One named barrier per pass: the two buffers alternate, and a thread can only write a
+// buffer again after the barrier of the pass in between, which everybody reaches after reading it.
+template <bool F32>
+__device__ __forceinline__ void gemm_store_vec(uint8_t* stage, uint32_t epi_tid, uint32_t row, const uint32_t (&v)[32],
+                                               const GemmDst& d, uint32_t c) {
+    constexpr uint32_t ES = F32 ? 4u : 2u, CP = 8192u / (kGemmTileW * ES), PR = kGemmTileW * ES / 16u, NPASS = 32u / CP;
+#pragma unroll
+    for (uint32_t h = 0; h < NPASS; ++h) {
+        uint8_t* buf = stage + ((NPASS == 1u ? c : h) & 1u) * 8192u;
+#pragma unroll
+        for (uint32_t j = 0; j < CP; ++j) {
+            if (F32) *reinterpret_cast<uint32_t*>(buf + (j * kGemmTileW + row) * 4u) = v[h * CP + j];
+            else *reinterpret_cast<uint16_t*>(buf + (j * kGemmTileW + row) * 2u) = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[h * CP + j]));
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+            const uint32_t p = epi_tid + 128u * q, j = p / PR, pc = p % PR;
+            const uint32_t mi = d.m0 + 32u * c + h * CP + j, ni = d.n0 + pc * (16u / ES);
+            if (mi < d.mlim && ni < d.nlim) {
+                const uint4 t = *reinterpret_cast<const uint4*>(buf + j * (kGemmTileW * ES) + pc * 16u);
+                *reinterpret_cast<uint4*>(d.base + ((size_t)mi * d.ld + ni) * ES) = t;
+            }
+        }
+    }
+}
+
+// Four values of activation row mi, weight rows ni .. ni + 3, into y.
+__device__ __forceinline__ void gemm_store4(const GemmParams& P, uint32_t mi, uint32_t ni, float4 a) {
+    if (mi >= P.m || ni >= P.n) return;
+    const size_t o = (size_t)mi * P.n + ni;
+    if (P.y_vec) {                       // n is a multiple of 4 at least and the rows are aligned
+        if (P.y_bf16) {
+            uint2 t;
+            t.x = f32_to_bf16_bits(a.x) | (f32_to_bf16_bits(a.y) << 16);
+            t.y = f32_to_bf16_bits(a.z) | (f32_to_bf16_bits(a.w) << 16);
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(P.y) + o) = t;
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.y) + o) = a;
+        }
+        return;
+    }
+    const float e[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        if (ni + i < P.n) {
+            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o + i] = (uint16_t)f32_to_bf16_bits(e[i]);
+            else reinterpret_cast<float*>(P.y)[o + i] = e[i];
+        }
+    }
+}
+
+// Thirty-two accumulator columns plus the same columns of another contributor's published part -> y.  The
+// other part's 16-byte pieces follow the piece order of the transposition buffers: piece p of a 16-column
+// pass is floats [4 p, 4 p + 4) of that pass, in the buffer and in the part alike.
+__device__ __forceinline__ void gemm_add_store(uint8_t* stage, uint32_t epi_tid, uint32_t row, const uint32_t (&v)[32],
+                                               const uint4* other, const GemmParams& P, uint32_t m0, uint32_t n0) {
+#pragma unroll
+    for (uint32_t h = 0; h < 2; ++h) {
+        uint8_t* buf = stage + h * 8192u;
+#pragma unroll
+        for (uint32_t j = 0; j < 16; ++j) *reinterpret_cast<uint32_t*>(buf + (j * kGemmTileW + row) * 4u) = v[16 * h + j];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+            const uint32_t p = epi_tid + 128u * q;
+            const float4 own = *reinterpret_cast<const float4*>(buf + p * 16u);
+            const uint4 ot = __ldcg(other + 512u * h + p);
+            float4 r;
+            r.x = own.x + __uint_as_float(ot.x); r.y = own.y + __uint_as_float(ot.y);
+            r.z = own.z + __uint_as_float(ot.z); r.w = own.w + __uint_as_float(ot.w);
+            gemm_store4(P, m0 + 16 * h + (p >> 5), n0 + 4 * (p & 31u), r);
+        }
+    }
+}
+
+// The last contributor of a cut tile adds all parts in contributor order (its own included, re-read from
+// memory: the sum then never depends on who came last).  Sixteen activation rows (8 KB of every part) at a
+// time, in 16-byte pieces: a warp reads 512 contiguous bytes of each part.  Kept out of line: it runs once
+// per cut tile and would otherwise raise the register need of the whole kernel.
+__device__ __noinline__ void gemm_reduce_parts(const GemmParams& P, uint32_t tile_x, uint32_t c_first, uint32_t c_last,
+                                               uint32_t u0, uint32_t m0, uint32_t n0, uint32_t epi_tid) {
+    for (uint32_t col0 = 0; col0 < tile_x && m0 + col0 < P.m; col0 += 16) {
+        float4 acc[4];
+        for (uint32_t cc = c_first; cc <= c_last; ++cc) {
+            const uint32_t sid = 2 * cc + (gemm_range_start(P, cc) > u0 ? 0u : 1u);
+            const uint4* src = reinterpret_cast<const uint4*>(P.partial + (size_t)sid * (kGemmTileW * tile_x) + (size_t)col0 * kGemmTileW) + epi_tid;
+            uint4 pv[4];
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) pv[q] = __ldcg(src + 128u * q);
+#pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                const float4 f = make_float4(__uint_as_float(pv[q].x), __uint_as_float(pv[q].y), __uint_as_float(pv[q].z), __uint_as_float(pv[q].w));
+                if (cc == c_first) acc[q] = f;
+                else { acc[q].x += f.x; acc[q].y += f.y; acc[q].z += f.z; acc[q].w += f.w; }
+            }
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+            const uint32_t p = epi_tid + 128u * q;
+            gemm_store4(P, m0 + col0 + (p >> 5), n0 + 4 * (p & 31u), acc[q]);
+        }
+    }
+}
 
 struct GemmBars {
     uint64_t b_full[kGemmMaxStages], a_full[kGemmMaxStages], stage_free[kGemmMaxStages];
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
     uint64_t d_full, d_free;
-    uint32_t tmem_base, abort_flag;
+    uint32_t tmem_base, abort_flag, epi_prev, epi_prev1;   // epi_prev, epi_prev1: arrival counts of alternate segments
 };
 
 template <uint32_t SCHEME, uint32_t kGemmTileX>
@@ -359,13 +575,13 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     uint8_t* raw_stage = smem + kGemmStages * B_BYTES;                // kGemmRawStages x RAW_BYTES (128-aligned)
     GemmBars* bars = reinterpret_cast<GemmBars*>(raw_stage + kGemmRawStages * ((RAW_BYTES + 127) / 128 * 128));
     constexpr uint32_t RAW_STRIDE = (RAW_BYTES + 127) / 128 * 128;
+    uint8_t* epi_stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(bars + 1) + 15) & ~(uintptr_t)15);
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t kblocks = P.k / kGemmBK, kgroups = P.k / 256;
-    const uint32_t ntiles = P.wtiles * P.xtiles;
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     if (tid == 0) {
+        GT(0);
         for (uint32_t s = 0; s < kGemmStages; ++s) {
             mbar_init(smem_u32(&bars->b_full[s]), 1);
             mbar_init(smem_u32(&bars->a_full[s]), 4);
@@ -389,6 +605,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_d = tmem_base, tmem_a = tmem_base + 256;
+    if (tid == 0) GT(1);
 
     auto give_up = [&](int code) {
         if (lane == 0) { atomicExch(P.err, code); *abort_flag = 1u; }
@@ -398,15 +615,24 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         // ---------------- activation tiles (B operand) ----------------
         if (lane == 0) {
             tma_prefetch_desc(&P.xmap);
+#ifdef RLXQ_TRACE
+            bool tr_first = false;
+#endif
             uint32_t s = 0, ph = 1;      // parity to wait for on stage_free (1 passes on a fresh barrier)
-            for (uint32_t t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
-                const uint32_t xt = t % P.xtiles;
+            uint32_t cur, lim;
+            gemm_seg_init(P, cur, lim);
+            GemmSeg sg;
+            while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+                const uint32_t xt = sg.tile % P.xtiles;
                 bool ok = true;
-                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                for (uint32_t kb = 4 * sg.g0; kb < 4 * sg.g1; ++kb) {
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), ph)) { give_up(11); ok = false; break; }
                     const uint32_t full = smem_u32(&bars->b_full[s]);
                     mbar_arrive_expect_tx(full, B_BYTES);
                     tma_load_2d(smem_u32(b_stage + s * B_BYTES), &P.xmap, (int32_t)(kb * kGemmBK), (int32_t)(xt * kGemmTileX), full);
+#ifdef RLXQ_TRACE
+                    if (!tr_first) { tr_first = true; GT(2); }
+#endif
                     if (++s == kGemmStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -417,10 +643,13 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         if (lane == 0) {
             tma_prefetch_desc(&P.wmap);
             uint32_t r = 0, ph = 1;
-            for (uint32_t t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
-                const uint32_t wt = t / P.xtiles;
+            uint32_t cur, lim;
+            gemm_seg_init(P, cur, lim);
+            GemmSeg sg;
+            while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+                const uint32_t wt = sg.tile / P.xtiles;
                 bool ok = true;
-                for (uint32_t g = 0; g < kgroups; ++g) {
+                for (uint32_t g = sg.g0; g < sg.g1; ++g) {
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_empty[r]), ph)) { give_up(12); ok = false; break; }
                     const uint32_t full = smem_u32(&bars->raw_full[r]);
                     mbar_arrive_expect_tx(full, RAW_BYTES);
@@ -434,14 +663,37 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t s = 0, ph = 0, dph = 1;   // dph: parity to wait for on d_free (1 passes the first time)
-            for (uint32_t t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
+#ifdef RLXQ_TRACE
+            long long tr_wb = 0, tr_wa = 0, tr_wd = 0; uint32_t tr_n = 0, tr_seg = 0;
+#endif
+            uint32_t cur, lim;
+            gemm_seg_init(P, cur, lim);
+            GemmSeg sg;
+            while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+#ifdef RLXQ_TRACE
+                const long long td0 = clock64();
+#endif
                 if (!mbar_wait(smem_u32(&bars->d_free), dph)) { give_up(13); break; }
+#ifdef RLXQ_TRACE
+                tr_wd += clock64() - td0;
+#endif
                 dph ^= 1u;
                 tc_fence_after();
                 bool ok = true;
-                for (uint32_t kb = 0; kb < kblocks; ++kb) {
+                for (uint32_t kb = 0; kb < 4 * (sg.g1 - sg.g0); ++kb) {    // the first MMA of a segment overwrites the accumulator
+#ifdef RLXQ_TRACE
+                    const long long t0 = clock64();
+                    if (!mbar_wait(smem_u32(&bars->b_full[s]), ph)) { give_up(14); ok = false; break; }
+                    const long long t1 = clock64();
+                    if (tr_n == 0) GT(3);
+                    if (!mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(14); ok = false; break; }
+                    tr_wb += t1 - t0; tr_wa += clock64() - t1;
+                    if (tr_n == 0) GT(4);
+                    ++tr_n;
+#else
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->b_full[s]), ph) ||
                         !mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(14); ok = false; break; }
+#endif
                     tc_fence_after();
                     const uint64_t bdesc = kmajor_sw128_desc(smem_u32(b_stage + s * B_BYTES));
 #pragma unroll
@@ -452,7 +704,15 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&bars->d_full));
+#ifdef RLXQ_TRACE
+                if (tr_seg == 0) GT(5);
+                GT(18);
+                ++tr_seg;
+#endif
             }
+#ifdef RLXQ_TRACE
+            GTV(12, tr_wb); GTV(13, tr_wa); GTV(14, tr_n); GTV(19, tr_wd);
+#endif
         }
     } else if (warp >= 4 && warp < 4 + 4 * kGemmDecodeGroups) {
         // ---------------- decode: raw blocks -> bf16 rows in tensor memory ----------------
@@ -463,9 +723,22 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         const uint32_t lane_addr = (quarter * 32) << 16;
         uint32_t r = 0, rph = 0, kbg0 = 0;   // kbg0: k blocks this CTA has gone through before the current group
         bool ok = true;
-        for (uint32_t t = blockIdx.x; t < ntiles && ok && !*abort_flag; t += gridDim.x) {
-            for (uint32_t g = 0; g < kgroups && ok; ++g, kbg0 += 4) {
+#ifdef RLXQ_TRACE
+        long long tr_wr = 0, tr_wf = 0, tr_dec = 0, tr_st = 0, tr_all0 = clock64(); bool tr_first = false;
+#endif
+        uint32_t cur, lim;
+        gemm_seg_init(P, cur, lim);
+        GemmSeg sg;
+        while (ok && !*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+            for (uint32_t g = sg.g0; g < sg.g1 && ok; ++g, kbg0 += 4) {
+#ifdef RLXQ_TRACE
+                const long long tq0 = clock64();
+#endif
                 if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_full[r]), rph)) { give_up(15); ok = false; break; }
+#ifdef RLXQ_TRACE
+                tr_wr += clock64() - tq0;
+                if (!tr_first && warp == 4 && lane == 0) GT(10);
+#endif
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
 #pragma unroll
                 for (uint32_t sub = 0; sub < 4; ++sub) {                 // which 64 weights of the group
@@ -475,14 +748,34 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     // decode into registers first: only the store needs the stage's tensor-memory columns,
                     // so the arithmetic stays off the free -> store -> MMA chain
                     uint32_t v[32];
+#ifdef RLXQ_TRACE
+                    const long long td0 = clock64();
+#endif
                     if (sub == 0) decode64<SCHEME, 0>(rp, g, v);
                     else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
                     else if (sub == 2) decode64<SCHEME, 2>(rp, g, v);
                     else decode64<SCHEME, 3>(rp, g, v);
+#ifdef RLXQ_TRACE
+                    tr_dec += clock64() - td0 + (long long)(v[0] & 0u);
+#endif
+#ifdef RLXQ_TRACE
+                    const long long tf0 = clock64();
+#endif
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
+#ifdef RLXQ_TRACE
+                    tr_wf += clock64() - tf0;
+                    const long long ts0 = clock64();
+#endif
                     tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * s, v);
                     tmem_st_wait();
+#ifdef RLXQ_TRACE
+                    tr_st += clock64() - ts0;
+#endif
+#ifdef RLXQ_TRACE
+                    if (!tr_first && warp == 4 && lane == 0) { GT(11); }
+                    tr_first = true;
+#endif
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[s]));
@@ -493,17 +786,53 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                 if (++r == kGemmRawStages) { r = 0; rph ^= 1u; }
             }
         }
+#ifdef RLXQ_TRACE
+        if (warp == 4 && lane == 0) { GTV(15, tr_wr); GTV(16, tr_wf); GTV(17, clock64() - tr_all0); GTV(23, tr_dec); GTV(24, tr_st); }
+#endif
     } else if (warp >= 4 + 4 * kGemmDecodeGroups) {
-        // ---------------- epilogue: accumulator -> y ----------------
+        // ---------------- epilogue: accumulator -> y (or -> a partial tile, completed by the last contributor) ----------------
         const uint32_t quarter = warp & 3u;
         const uint32_t lane_addr = (quarter * 32) << 16;
-        uint32_t dph = 0;
-        for (uint32_t t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
-            const uint32_t wt = t / P.xtiles, xt = t % P.xtiles;
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t epi_tid = (warp - (4 + 4 * kGemmDecodeGroups)) * 32 + lane;
+        uint32_t dph = 0, nseg = 0;
+        uint32_t cur, lim;
+        gemm_seg_init(P, cur, lim);
+        GemmSeg sg;
+        while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+            const uint32_t wt = sg.tile / P.xtiles, xt = sg.tile % P.xtiles;
             if (!mbar_wait(smem_u32(&bars->d_full), dph)) { give_up(17); break; }
             dph ^= 1u;
             tc_fence_after();
-            const uint32_t n_idx = wt * kGemmTileW + quarter * 32 + lane;
+#ifdef RLXQ_TRACE
+            if (epi_tid == 0) { if (nseg == 0) GT(6); GT(20); }
+#endif
+            const uint32_t n_idx = wt * kGemmTileW + row;
+            const bool whole = sg.g0 == 0 && sg.g1 == P.kgroups;
+            // a cut tile: this CTA's part goes to its head slot when its range begins inside the tile
+            // (only a first segment can), to its tail slot otherwise; layout [activation row][weight row]
+            const uint32_t u0 = sg.tile * P.kgroups;
+            uint32_t c_first = 0, c_last = 0;
+            float* slot = nullptr;
+            const float* other = nullptr;     // two contributors and the other one has already published
+            if (!whole) {
+                slot = P.partial + (size_t)(2 * blockIdx.x + ((nseg == 0 && sg.g0 != 0) ? 0u : 1u)) * (kGemmTileW * kGemmTileX);
+                c_first = gemm_owner(P, u0);
+                c_last = gemm_owner(P, u0 + P.kgroups - 1);
+                if (c_last - c_first == 1u) {
+                    // a + b == b + a: with two parts the sum does not depend on who adds, so the second one
+                    // to arrive adds the published part to its own registers and never publishes
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) (&bars->epi_prev)[nseg & 1u] = *reinterpret_cast<volatile uint32_t*>(&P.counters[sg.tile]);
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (reinterpret_cast<volatile uint32_t*>(&bars->epi_prev)[nseg & 1u] == 1u) {
+                        __threadfence();
+                        const uint32_t oc = blockIdx.x == c_first ? c_last : c_first;
+                        const uint32_t sid = 2 * oc + (gemm_range_start(P, oc) > u0 ? 0u : 1u);
+                        other = P.partial + (size_t)sid * (kGemmTileW * kGemmTileX);
+                    }
+                }
+            }
 #pragma unroll 1
             for (uint32_t c = 0; c < kGemmTileX / 32; ++c) {
                 uint32_t v[32];
@@ -513,8 +842,21 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->d_free));
+#ifdef RLXQ_TRACE
+                    if (epi_tid == 0) { if (nseg == 0) GT(7); GT(21); }
+#endif
                 }
-                if (n_idx < P.n) {
+                if (other) {
+                    gemm_add_store(epi_stage, epi_tid, row, v, reinterpret_cast<const uint4*>(other + (size_t)(32 * c) * kGemmTileW),
+                                   P, xt * kGemmTileX + 32 * c, wt * kGemmTileW);
+                } else if (!whole) {
+                    const GemmDst d{reinterpret_cast<uint8_t*>(slot), kGemmTileW, 0u, kGemmTileX, 0u, kGemmTileW};
+                    gemm_store_vec<true>(epi_stage, epi_tid, row, v, d, c);
+                } else if (P.y_vec) {
+                    const GemmDst d{reinterpret_cast<uint8_t*>(P.y), P.n, xt * kGemmTileX, P.m, wt * kGemmTileW, P.n};
+                    if (P.y_bf16) gemm_store_vec<false>(epi_stage, epi_tid, row, v, d, c);
+                    else gemm_store_vec<true>(epi_stage, epi_tid, row, v, d, c);
+                } else if (n_idx < P.n) {
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) {
                         const uint32_t m_idx = xt * kGemmTileX + 32 * c + j;
@@ -526,13 +868,38 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     }
                 }
             }
+            if (!whole && !other) {
+                // publish, count, and let the last contributor add all parts in contributor order (its own
+                // included, re-read from memory: the sum then never depends on who came last)
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (epi_tid == 0) (&bars->epi_prev)[nseg & 1u] = atomicAdd(&P.counters[sg.tile], 1u);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const uint32_t prev = reinterpret_cast<volatile uint32_t*>(&bars->epi_prev)[nseg & 1u];
+                if (prev == c_last - c_first) {
+                    __threadfence();
+                    gemm_reduce_parts(P, kGemmTileX, c_first, c_last, u0, xt * kGemmTileX, wt * kGemmTileW, epi_tid);
+                }
+            }
+#ifdef RLXQ_TRACE
+            if (epi_tid == 0) { if (nseg == 0) GT(8); GT(22); }
+#endif
+            ++nseg;
         }
     }
     // everybody meets here, also after a timeout, so the tensor memory is always returned
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
+#ifdef RLXQ_TRACE
+    if (tid == 0) GT(9);
+#endif
 }
+#ifdef RLXQ_TRACE
+extern "C" __attribute__((visibility("default"))) int rlxq_debug_gemm_trace(void* dst) {
+    return (int)cudaMemcpyFromSymbol(dst, g_gemm_trace, sizeof(g_gemm_trace));
+}
+#endif
 
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
@@ -543,9 +910,37 @@ bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
     return true;
 }
 
+// The k split ("stream-K") evens the work out over the SMs, at the price of exchanging partial tiles through
+// memory, which costs about as much as 36 steps of one 256-wide k group.  It is chosen when it saves at
+// least that many steps on the busiest SM against whole tiles (of the width they would be given): few
+// tiles and a long k, e.g. the down projection of a tensor-parallel shard at a small batch.
+static bool gemm_wants_streamk(uint32_t m, uint32_t k, uint32_t n) {
+    const int64_t opt = options().gemm_streamk.load();
+    if (opt == 1) return false;
+    if (opt == 2) return true;
+    const uint64_t sms = (uint64_t)sm_count(), wt = (n + kGemmTileW - 1) / kGemmTileW, kgroups = k / 256;
+    const uint64_t ntiles256 = wt * ((m + 255) / 256), ntiles128 = wt * ((m + 127) / 128);
+    const uint64_t whole_tiles = ntiles256 * 4 < sms * 3 ? ntiles128 : ntiles256;
+    const uint64_t steps_whole = (whole_tiles + sms - 1) / sms * kgroups;
+    const uint64_t steps_split = (ntiles256 * kgroups + sms - 1) / sms;
+    return steps_whole >= steps_split + 36;
+}
+static size_t gemm_streamk_bytes(uint32_t ntiles, size_t* off_partial) {
+    const size_t counters = ((size_t)ntiles * 4 + 255) / 256 * 256;
+    if (off_partial) *off_partial = counters;
+    return counters + 2 * (size_t)sm_count() * kGemmTileW * 256 * 4;     // two partial tiles per CTA
+}
+
+// Scratch the GEMM would use for this shape (0 when whole tiles fill the SMs well enough).
+size_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k, uint32_t n) {
+    if (m <= 8 || k == 0 || k % 256) return 0;
+    const uint32_t ntiles = ((n + kGemmTileW - 1) / kGemmTileW) * ((m + 255) / 256);
+    return gemm_wants_streamk(m, k, n) ? gemm_streamk_bytes(ntiles, nullptr) : 0;
+}
+
 template <uint32_t SCHEME, uint32_t TX>
 static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
-                         uint32_t k, uint32_t n) {
+                         uint32_t k, uint32_t n, void* ws, bool streamk) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
     constexpr uint32_t RAW_STRIDE = (kGemmTileW * RAW_ROW + 127) / 128 * 128;
     Geometry g;
@@ -556,12 +951,14 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     rc = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, RAW_ROW / 8, kGemmTileW);
     if (rc) return rc;
     P.y = y; P.m = m; P.n = n; P.k = k; P.y_bf16 = ybf;
+    P.y_vec = (((uintptr_t)y & 15u) == 0 && n % (ybf ? 8u : 4u) == 0) ? 1u : 0u;
     P.wtiles = (n + kGemmTileW - 1) / kGemmTileW;
     P.xtiles = (m + TX - 1) / TX;
+    P.kgroups = k / 256;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     const size_t smem = 1024 + (size_t)GemmRaw<SCHEME>::STAGES * TX * kGemmBK * 2 + (size_t)kGemmRawStages * RAW_STRIDE +
-                        sizeof(GemmBars) + 64;
+                        sizeof(GemmBars) + 64 + kGemmEpiStage;
     static std::atomic<uint32_t> attr_set[64];
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
@@ -571,31 +968,50 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     }
     uint32_t grid = (uint32_t)sm_count();
     const uint32_t ntiles = P.wtiles * P.xtiles;
-    if (grid > ntiles) grid = ntiles;
+    if (streamk) {
+        const uint64_t units = (uint64_t)ntiles * P.kgroups;
+        if (units > 0xFFFFFFFFull) return fail(RLXQ_E_LIMIT, "GEMM too large for the stream-K split");
+        if (grid > units) grid = (uint32_t)units;
+        size_t off_partial = 0;
+        gemm_streamk_bytes(ntiles, &off_partial);
+        P.streamk = 1;
+        P.units_q = (uint32_t)(units / grid);
+        P.units_r = (uint32_t)(units % grid);
+        P.counters = reinterpret_cast<uint32_t*>(ws);
+        P.partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + off_partial);
+        RLXQ_CUDA_TRY(cudaMemsetAsync(P.counters, 0, (size_t)ntiles * 4, stream));
+    } else if (grid > ntiles) {
+        grid = ntiles;
+    }
     gemm_tcgen05_kernel<SCHEME, TX><<<grid, (4 + 4 * GemmRaw<SCHEME>::GROUPS + 4) * 32, smem, stream>>>(P);
     count_launch();
     return check_launch("gemm_tcgen05_kernel");
 }
 
-// 256-row activation tiles halve the activation traffic per FLOP; 128-row tiles are used when the
-// wider ones would leave more than a quarter of the SMs without a tile.
+// 256-row activation tiles halve the activation traffic per FLOP.  When whole tiles would fill the SMs
+// badly the k dimension is split as well (stream-K, needs the workspace); without a workspace, 128-row
+// tiles are used when the wider ones would leave more than a quarter of the SMs without a tile.
 template <uint32_t SCHEME>
 static int launch_gemm_s(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
-                         uint32_t k, uint32_t n) {
+                         uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
     const uint32_t wt = (n + kGemmTileW - 1) / kGemmTileW, sms = (uint32_t)sm_count();
     const int64_t force = options().gemm_tile_x.load();
-    const bool narrow = force ? force == 128 : (wt * ((m + 255) / 256) * 4 < sms * 3);
-    if (narrow) return launch_gemm_t<SCHEME, 128>(stream, x, w, y, ybf, m, k, n);
-    return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n);
+    const uint32_t ntiles256 = wt * ((m + 255) / 256);
+    if (force != 128 && gemm_wants_streamk(m, k, n) && ws && !((uintptr_t)ws & 15u) &&
+        ws_bytes >= gemm_streamk_bytes(ntiles256, nullptr))
+        return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n, ws, true);
+    const bool narrow = force ? force == 128 : (ntiles256 * 4 < sms * 3);
+    if (narrow) return launch_gemm_t<SCHEME, 128>(stream, x, w, y, ybf, m, k, n, nullptr, false);
+    return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n, nullptr, false);
 }
 
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
-                   uint32_t m, uint32_t k, uint32_t n) {
+                   uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
     switch (scheme) {
-        case RLXQ_Q4_0: return launch_gemm_s<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q8_0: return launch_gemm_s<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n);
-        case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n);
+        case RLXQ_Q4_0: return launch_gemm_s<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q8_0: return launch_gemm_s<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }
 }

@@ -25,8 +25,9 @@ int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
 
 // tcgen05 / tensor-memory GEMM (m > 8, bf16 activations).
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf);
+size_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k, uint32_t n);
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
-                   uint32_t m, uint32_t k, uint32_t n);
+                   uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
 
 // One MoE decode row: the slab of the weight stack is chosen by *expert_sel on the device.
 bool int_expert_supported(uint32_t scheme, uint32_t k, uint32_t n, const void* w, const void* x);

@@ -20,6 +20,7 @@ def _reset_options():
     yield
     R.set_option("gemm_kernel", 0)
     R.set_option("gemm_tile_x", 0)
+    R.set_option("gemm_streamk", 0)
 
 
 def _tol(k):
@@ -66,6 +67,35 @@ def test_both_activation_tile_widths_match_oracle(sch, m, k, n, tile_x):
     y = _run(s, w, xb, n, kernel=2)
     ref = O.matmul_bt_mt(x, w, m, k, n, s)
     assert_within_tolerance(y, ref, bound(s, w, x, n), tol=_tol(k), what=f"gemm {sch} tile_x={tile_x}")
+
+
+@pytest.mark.parametrize("sch,m,k,n,y_bf16", [("q4_k", 300, 4096, 384, False), ("q8_0", 64, 8192, 130, True),
+                                              ("q4_0", 520, 1024, 2000, False), ("q6_k", 129, 6144, 200, True),
+                                              ("q4_k", 512, 4096, 14336, True), ("q4_k", 256, 3584, 8192, False)])
+def test_stream_k_split_matches_oracle_and_is_deterministic(sch, m, k, n, y_bf16):
+    """With gemm_streamk = 2 the (tile, k group) units are dealt evenly to the SMs and cut tiles are completed by
+    their last contributor: few tiles with a long k (one tile shared by many CTAs), many tiles (two contributors
+    per cut), and the two benchmark shapes whose whole tiles fill 148 SMs badly."""
+    s = O.SCHEMES[sch]
+    w, xb, x = _case(s, m, k, n, seed=90 + m)
+    R.set_option("gemm_streamk", 2)
+    a = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)
+    b = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)
+    assert np.array_equal(a, b)                                   # contributor order, not arrival order
+    rows = np.arange(m) if m * n <= 600_000 else np.random.default_rng(1).choice(m, 24, replace=False)
+    ref = O.matmul_bt_mt(np.ascontiguousarray(x[rows]), w, len(rows), k, n, s)
+    tol = max(_tol(k), 4e-3 if y_bf16 else 0.0)                   # bf16 output rounding on top
+    bnd = bound(s, w, np.ascontiguousarray(x[rows]), n)
+    if y_bf16:
+        assert np.all(np.abs(a[rows] - ref) <= _tol(k) * bnd + np.abs(ref) * 2.0 ** -8)
+    else:
+        assert_within_tolerance(a[rows], ref, bnd, tol=tol, what=f"stream-K {sch} {m}x{k}x{n}")
+    R.set_option("gemm_streamk", 1)
+    c = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)                # whole tiles: same values up to summation order
+    if y_bf16:
+        assert np.all(np.abs(a[rows] - c[rows]) <= 2 * _tol(k) * bnd + np.abs(ref) * 2.0 ** -7)
+    else:
+        assert_within_tolerance(a[rows], c[rows], bnd, tol=2 * _tol(k), what="stream-K vs whole tiles")
 
 
 def test_generic_kernel_for_large_m_matches_oracle():
