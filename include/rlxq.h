@@ -85,9 +85,9 @@ RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t
 /* Replaces dequant_gguf_scratch_bytes (rlx-cuda/src/gguf_gpu.rs:35-59) at plan time: the
  * scratch rlxq_matmul needs for this shape.  For m <= 8 that is the converted activations
  * (a few bytes per element of x), the partial output tiles of CTAs that share a row tile and
- * their counters: tens to hundreds of KiB.  The tensor-core GEMM needs none when whole tiles fill
- * the SMs, else two partial 128 x 256 f32 tiles per SM (39 MB on a 148-SM part) for its stream-K split;
- * without them it runs whole tiles.  The reference reserves k*n*4 bytes. */
+ * their counters: tens to hundreds of KiB.  The tensor-core GEMM needs none for most shapes; for few
+ * output tiles and a long k it asks for two partial 128 x 256 f32 tiles per SM (39 MB on a 148-SM
+ * part) for its stream-K split; without them it runs whole tiles.  The reference reserves k*n*4 bytes. */
 RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
                          uint32_t x_dtype, uint32_t y_dtype, size_t* bytes);
 
@@ -155,8 +155,9 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
  *                  GEMV, 3 = force the staged integer GEMV (m <= 4; 2, 3: error if the shape does not allow it)
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
- *   "gemm_streamk": 0 = automatic (split the k dimension across SMs when whole tiles would fill them
- *                  badly and a workspace is given), 1 = never, 2 = whenever a workspace is given
+ *   "gemm_streamk": 0 = automatic (split the k dimension across SMs when that saves at least 36
+ *                  256-wide k steps on the busiest SM and a workspace is given), 1 = never,
+ *                  2 = whenever a workspace is given
  *   "gemm_tile_x": 0 = automatic, 128 or 256 = activation rows per tile of the tcgen05 GEMM
  *   "gemv_inline_q": 0 = automatic, 1 = the integer GEMV always runs its activation quantiser as a
  *                  kernel of its own, 2 = the streaming kernel quantises the activations itself
