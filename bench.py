@@ -183,14 +183,19 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     from oracle import oracle as O
     sid = O.SCHEMES[sch]
     m = args.batch
-    weights = [O.fill_weights(sid, 1000 + i, k, n) for i, (k, n) in enumerate(layers)]
+    # the same rotation of distinct weight copies as the GPU arm (same `config`), so no step finds its
+    # weights in a cache; the copies are byte copies of one generated set
+    w_step = sum(packed_bytes(sch, k, n) for k, n in layers)
+    rotation = max(2, -(-2 * L2_BYTES // w_step) + 1)
+    base = [O.fill_weights(sid, 1000 + i, k, n) for i, (k, n) in enumerate(layers)]
+    wsets = [base] + [[w.copy() for w in base] for _ in range(rotation - 1)]
     x = O.fill_normal(77, m * layers[0][0]).reshape(m, layers[0][0])
     cores = os.cpu_count() or 1
-    for _ in range(args.warmup):
-        cpu_step(O, sid, layers, weights, x, cores)
+    for i in range(args.warmup):
+        cpu_step(O, sid, layers, wsets[i % rotation], x, cores)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_step(O, sid, layers, weights, x, cores)
+    for i in range(args.steps):
+        cpu_step(O, sid, layers, wsets[(args.warmup + i) % rotation], x, cores)
     dt = (time.perf_counter() - t0) / args.steps
     total_bytes = sum(algorithmic_bytes(sch, layers, m, 4 if act == "f32" else 2))
     val = total_bytes / dt / 1e9
@@ -198,7 +203,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
         "impl": "reference", "metric": "gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, sch, layers, act, rotation=1),
+        "config": workload_config(args, sch, layers, act, rotation),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{args.steps} full steps, all {cores} host threads (rows split across threads)"},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
