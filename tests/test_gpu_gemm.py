@@ -117,6 +117,39 @@ def test_gemm_bf16_output_is_rne_of_f32_output():
     assert np.array_equal(yb, torch.from_numpy(yf).to(torch.bfloat16).float().numpy())
 
 
+@pytest.mark.parametrize("sch,m,k,n", [("q8_0", 300, 512, 200), ("q4_k", 129, 1024, 136), ("q4_0", 257, 512, 264),
+                                       ("q6_k", 70, 2048, 392)])
+def test_gemm_row_piece_stores_equal_single_value_stores(sch, m, k, n):
+    """y rows that are 16-byte aligned (n a multiple of 8) leave the epilogue as transposed 16-byte pieces; an
+    output of the same product with n + 1 columns (one more weight row) takes the single-value stores.  The
+    common columns must be bit-identical, for f32 and bf16 outputs, ragged activation tiles and a partly
+    filled last weight tile included."""
+    s = O.SCHEMES[sch]
+    w1 = O.fill_weights(s, 21, k, n + 1)                       # rows 0..n-1 are shared with the n-row matrix
+    row_bytes = len(w1) // (n + 1)
+    w0 = np.ascontiguousarray(w1[: n * row_bytes])
+    xb = O.f32_to_bf16_bits(O.fill_normal(22, m * k).reshape(m, k))
+    for y_bf16 in (False, True):
+        a = _run(s, w0, xb, n, y_bf16=y_bf16, kernel=2)
+        b = _run(s, w1, xb, n + 1, y_bf16=y_bf16, kernel=2)
+        assert np.array_equal(a.view(np.uint32), b[:, :n].view(np.uint32)), f"{sch} bf16={y_bf16}"
+
+
+@pytest.mark.parametrize("sch,k", [("q4_0", 256), ("q8_0", 512), ("q4_k", 512), ("q6_k", 2048)])
+def test_gemm_weight_operand_is_the_bf16_rounding_of_the_dequantised_weight(sch, k):
+    """With the identity as activations every output is a single product 1 * w, so y^T is exactly the operand
+    the decode warps hand to the tensor core: it must equal the oracle's dequantised weight rounded once to
+    bf16 (round to nearest even), exactly."""
+    import torch
+    s, n = O.SCHEMES[sch], 200
+    w = O.fill_weights(s, 31, k, n)
+    xb = O.f32_to_bf16_bits(np.eye(k, dtype=np.float32))
+    y = _run(s, w, xb, n, kernel=2)                                   # [k, n] f32
+    deq = O.dequant(s, w, k * n).reshape(n, k)
+    want = torch.from_numpy(deq).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(y.T, want)       # compared as values: a zero weight's sign is lost in the sum with 0 * w terms
+
+
 def test_gemm_is_deterministic_and_matches_generic_kernel():
     s, m, k, n = O.Q4_K, 512, 2048, 256
     w, xb, x = _case(s, m, k, n, seed=10)
