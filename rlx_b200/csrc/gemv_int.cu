@@ -332,6 +332,55 @@ template <int MM> struct QUnit<RLXQ_Q4_K, MM> : QUnitRowHalf<MM> {
     }
 };
 
+// ---- Q5_K: unit = one 176-byte super-block d | dmin | 12 scale bytes | qh[32] | qs[128]; as Q4_K, with bit
+// j of qh[l] adding 16 to weight l of sub-block j (rlx-gguf/src/lib.rs:1019-1068) ----
+template <int MM> struct QUnit<RLXQ_Q5_K, MM> : QUnitRowHalf<MM> {
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
+        const uint32_t p = L.row + u * 176;
+        const uint4 hd = lds128(p);                   // d, dmin, 12 scale bytes
+        const float d = f16_bits_to_f32(hd.x & 0xFFFFu), dmin = f16_bits_to_f32(hd.x >> 16);
+        uint32_t scb, mnb;                            // four 6-bit scales / mins, one per byte
+        if (L.half == 0) {
+            scb = hd.y & 0x3F3F3F3Fu;
+            mnb = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scb = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mnb = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+        }
+        const uint4 ha = lds128(p + 16), hb = lds128(p + 32);
+        // the four high bits this half needs, moved to bits 0..3 of every byte
+        const uint32_t hs = 4 * L.half;
+        const uint32_t qh[8] = {(ha.x >> hs) & 0x0F0F0F0Fu, (ha.y >> hs) & 0x0F0F0F0Fu, (ha.z >> hs) & 0x0F0F0F0Fu,
+                                (ha.w >> hs) & 0x0F0F0F0Fu, (hb.x >> hs) & 0x0F0F0F0Fu, (hb.y >> hs) & 0x0F0F0F0Fu,
+                                (hb.z >> hs) & 0x0F0F0F0Fu, (hb.w >> hs) & 0x0F0F0F0Fu};
+        const uint32_t xh = L.xh + kb, xl = L.xl + kb, sb = L.sb + (kb >> 3), sx = L.sx + (kb >> 3);
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {              // a pair of sub-blocks shares 32 bytes
+            const uint32_t qp = p + 48 + 64 * L.half + 32 * pp;
+            const uint4 a = lds128(qp), b = lds128(qp + 16);
+            const uint32_t raw[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int nib = 0; nib < 2; ++nib) {
+                const int js = 2 * pp + nib;          // sub-block index within this half
+                uint32_t q[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    q[i] = ((raw[i] >> (4 * nib)) & 0x0F0F0F0Fu) | (((qh[i] >> js) & 0x01010101u) << 4);
+                const float dsc = d * (float)((scb >> (8 * js)) & 0xFFu);
+                const float dmn = dmin * (float)((mnb >> (8 * js)) & 0xFFu);
+#pragma unroll
+                for (int m = 0; m < MM; ++m) {
+                    const uint32_t ox = m * L.xstride;
+                    const int c = dot_limbs<8>(q, xh + ox + 32 * js, xl + ox + 32 * js, 0);
+                    const float sbv = ldsf(sb + ox + 4 * js);
+                    const float sxf = sbv * (float)(int)lds32(sx + ox + 4 * js);
+                    tot[m] = fmaf(dsc * sbv, (float)c, fmaf(-dmn, sxf, tot[m]));
+                }
+            }
+        }
+    }
+};
+
 // ---- Q6_K: unit = one 210-byte super-block (only 2-byte aligned); a thread takes one half ----
 template <int MM> struct QUnit<RLXQ_Q6_K, MM> : QUnitRowHalf<MM> {
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM]) {
@@ -394,6 +443,7 @@ template <uint32_t SCHEME> struct SumBias;
 template <> struct SumBias<RLXQ_Q4_0> { static constexpr int value = -8; };
 template <> struct SumBias<RLXQ_Q8_0> { static constexpr int value = 0; };
 template <> struct SumBias<RLXQ_Q4_K> { static constexpr int value = 1; };
+template <> struct SumBias<RLXQ_Q5_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
 
 // ---------------------------------------------------------------------------------------------
@@ -1090,6 +1140,7 @@ bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const vo
         case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0>(m, k, n).ok;
         case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0>(m, k, n).ok;
         case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K>(m, k, n).ok;
+        case RLXQ_Q5_K: return plan_int<RLXQ_Q5_K>(m, k, n).ok;
         case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K>(m, k, n).ok;
         default: return false;
     }
@@ -1101,6 +1152,7 @@ size_t int_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) 
         case RLXQ_Q4_0: pl = plan_int<RLXQ_Q4_0>(m, k, n); break;
         case RLXQ_Q8_0: pl = plan_int<RLXQ_Q8_0>(m, k, n); break;
         case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K>(m, k, n); break;
+        case RLXQ_Q5_K: pl = plan_int<RLXQ_Q5_K>(m, k, n); break;
         case RLXQ_Q6_K: pl = plan_int<RLXQ_Q6_K>(m, k, n); break;
         default: break;
     }
@@ -1114,6 +1166,7 @@ static int launch_gemv_int_err(cudaStream_t stream, uint32_t scheme, const void*
         case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
         case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
         case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
+        case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
         case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err_word, pair);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }
@@ -1134,6 +1187,7 @@ bool int_expert_supported(uint32_t scheme, uint32_t k, uint32_t n, const void* w
         case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0>(1, k, n).two_way;
         case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0>(1, k, n).two_way;
         case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K>(1, k, n).two_way;
+        case RLXQ_Q5_K: return plan_int<RLXQ_Q5_K>(1, k, n).two_way;
         case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K>(1, k, n).two_way;
         default: return false;
     }
@@ -1147,6 +1201,7 @@ int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, 
         case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
         case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
         case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
+        case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
         case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w_stack, y, ybf, 1, k, n, ws, ws_bytes, err, false, expert_sel, num_experts);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }

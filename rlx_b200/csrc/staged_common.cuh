@@ -37,6 +37,12 @@ template <> struct StagedTraits<RLXQ_Q6_K> {
     static constexpr float BIAS = -1056.f;
 };
 
+// Q5_K only runs in the integer GEMV (batch 1-2), which reads UNIT_B, AG and SUB; the rest mirrors Q4_K.
+template <> struct StagedTraits<RLXQ_Q5_K> {
+    static constexpr uint32_t UNIT_B = 176, AG = 1, CU = 4, STRIDE = 800, STAGES = 4, SUB = 32;
+    static constexpr float BIAS = -1024.f;
+};
+
 constexpr uint32_t kConsumerWarps = 4;
 constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
 // A waiting thread is suspended by the hardware for up to kSuspendHintNs per attempt, so a wait

@@ -62,6 +62,8 @@ def _kernels_for(s, m, k):
         ks.append(2)
         if m <= 4:
             ks.append(3)
+    if s == O.Q5_K and k % 256 == 0 and m <= 4:      # integer kernel only
+        ks.append(3)
     return ks
 
 
@@ -143,6 +145,7 @@ INT_SHAPES = [
     ("q8_0", 1, 256, 16), ("q8_0", 2, 768, 33), ("q8_0", 1, 4096, 100),
     ("q4_k", 1, 256, 1), ("q4_k", 1, 512, 19), ("q4_k", 2, 1280, 40), ("q4_k", 1, 4096, 31),
     ("q6_k", 1, 2048, 9), ("q6_k", 2, 2048, 16), ("q6_k", 1, 6144, 37),
+    ("q5_k", 1, 256, 1), ("q5_k", 1, 768, 19), ("q5_k", 2, 1280, 40), ("q5_k", 1, 4096, 131), ("q5_k", 4, 2048, 50),
     # three and four rows: the four-row kernel (one CTA per SM, activations of a block in registers for Q4_0)
     ("q4_0", 4, 4096, 130), ("q4_0", 3, 2304, 50), ("q4_0", 4, 11008, 33), ("q8_0", 4, 1024, 77), ("q8_0", 3, 4096, 40),
     ("q4_k", 4, 4096, 31), ("q4_k", 3, 1280, 100), ("q6_k", 4, 2048, 16), ("q6_k", 3, 6144, 37),
