@@ -57,8 +57,8 @@ enum rlxq_status {
  * Q4_0 and Q8_0 have no id there (that function panics on them) and get 6 and 7.  Q4_K, Q6_K,
  * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; Q5_K, Q8_K, Q2_K and Q3_K (the
  * rest of QuantScheme::is_gguf, rlx-ir/src/quant.rs:170-182) decode through the general kernel
- * (Q5_K also through the streaming GEMV for m <= 2), so every GGUF scheme the reference lowers
- * runs on the GPU without its host fallback. */
+ * (Q5_K also through the streaming GEMV for m <= 2 and the tensor-core GEMM for m > 8), so every
+ * GGUF scheme the reference lowers runs on the GPU without its host fallback. */
 enum rlxq_scheme {
     RLXQ_Q4_K = 0, RLXQ_Q5_K = 1, RLXQ_Q6_K = 2, RLXQ_Q8_K = 3, RLXQ_Q2_K = 4, RLXQ_Q3_K = 5,
     RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7

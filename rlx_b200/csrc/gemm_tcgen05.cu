@@ -116,6 +116,7 @@ template <uint32_t SCHEME> struct GemmRaw;
 template <> struct GemmRaw<RLXQ_Q4_0> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 2; };
 template <> struct GemmRaw<RLXQ_Q8_0> { static constexpr uint32_t ROW = 272, STAGES = 4, GROUPS = 2; };
 template <> struct GemmRaw<RLXQ_Q4_K> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q5_K> { static constexpr uint32_t ROW = 176, STAGES = 4, GROUPS = 2; };
 // Q6_K super-blocks are 210 bytes: group g of a row starts at byte 210 g, which is only 2-byte aligned.
 // The box starts at the 16-byte boundary below it and is 240 bytes wide (15 chunks: conflict-free, and
 // 14 + 210 <= 240); the decoder is compiled for each of the eight possible offsets 2 (g mod 8).
@@ -269,16 +270,54 @@ template <int S> struct Decode64<RLXQ_Q4_K, S> {
         const uint64_t off = f32x2_splat(-8388608.0f);
         const uint64_t dl2 = f32x2_splat(dl), ml2 = f32x2_splat(-ml), dh2 = f32x2_splat(dh), mh2 = f32x2_splat(-mh);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {       // fma(scale, nibble, -min), the nibble exact in f32
+        for (int i = 0; i < 8; ++i) {       // scale * nibble - min, rounded after each step as the dequantiser does
             const uint32_t lo = qs[i] & 0x0F0F0F0Fu, hi = (qs[i] >> 4) & 0x0F0F0F0Fu;
-            v[2 * i] = bf16x2_of(fma_f32x2(dl2, add_f32x2(magic_pair<0>(lo), off), ml2));
-            v[2 * i + 1] = bf16x2_of(fma_f32x2(dl2, add_f32x2(magic_pair<1>(lo), off), ml2));
-            v[16 + 2 * i] = bf16x2_of(fma_f32x2(dh2, add_f32x2(magic_pair<0>(hi), off), mh2));
-            v[16 + 2 * i + 1] = bf16x2_of(fma_f32x2(dh2, add_f32x2(magic_pair<1>(hi), off), mh2));
+            v[2 * i] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<0>(lo), off)), ml2));
+            v[2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<1>(lo), off)), ml2));
+            v[16 + 2 * i] = bf16x2_of(add_f32x2(mul_f32x2(dh2, add_f32x2(magic_pair<0>(hi), off)), mh2));
+            v[16 + 2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(dh2, add_f32x2(magic_pair<1>(hi), off)), mh2));
         }
     }
 };
 
+// Q5_K: d | dmin | 12 scale bytes | qh[32] | qs[128] (rlx-gguf/src/lib.rs:1019-1068): Q4_K with bit j of
+// qh[l] adding 16 to weight l of sub-block j.
+template <int S> struct Decode64<RLXQ_Q5_K, S> {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        const uint4 hd = *reinterpret_cast<const uint4*>(row);
+        const float d = f16_bits_to_f32(hd.x & 0xFFFFu), dmin = f16_bits_to_f32(hd.x >> 16);
+        uint32_t sc[2], mn[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = 2 * S + i;
+            if (j < 4) {
+                sc[i] = (hd.y >> (8 * j)) & 63u;
+                mn[i] = (hd.z >> (8 * j)) & 63u;
+            } else {
+                sc[i] = ((hd.w >> (8 * (j - 4))) & 0x0Fu) | (((hd.y >> (8 * (j - 4) + 6)) & 3u) << 4);
+                mn[i] = ((hd.w >> (8 * (j - 4) + 4)) & 0x0Fu) | (((hd.z >> (8 * (j - 4) + 6)) & 3u) << 4);
+            }
+        }
+        const float dl = d * (float)sc[0], ml = dmin * (float)mn[0];
+        const float dh = d * (float)sc[1], mh = dmin * (float)mn[1];
+        const uint4 ha = *reinterpret_cast<const uint4*>(row + 16), hb = *reinterpret_cast<const uint4*>(row + 32);
+        const uint4 a = *reinterpret_cast<const uint4*>(row + 48 + 32 * S);
+        const uint4 b = *reinterpret_cast<const uint4*>(row + 64 + 32 * S);
+        const uint32_t qs[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint32_t qh[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+        const uint64_t off = f32x2_splat(-8388608.0f);
+        const uint64_t dl2 = f32x2_splat(dl), ml2 = f32x2_splat(-ml), dh2 = f32x2_splat(dh), mh2 = f32x2_splat(-mh);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lo = (qs[i] & 0x0F0F0F0Fu) | (((qh[i] >> (2 * S)) & 0x01010101u) << 4);
+            const uint32_t hi = ((qs[i] >> 4) & 0x0F0F0F0Fu) | (((qh[i] >> (2 * S + 1)) & 0x01010101u) << 4);
+            v[2 * i] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<0>(lo), off)), ml2));
+            v[2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<1>(lo), off)), ml2));
+            v[16 + 2 * i] = bf16x2_of(add_f32x2(mul_f32x2(dh2, add_f32x2(magic_pair<0>(hi), off)), mh2));
+            v[16 + 2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(dh2, add_f32x2(magic_pair<1>(hi), off)), mh2));
+        }
+    }
+};
 
 // Words of a row buffer at compile-time byte offsets: loads the 16-byte chunks covering [B0, B0 + LEN)
 // and hands out the 32-bit little-endian word at any even byte offset inside.
@@ -904,7 +943,7 @@ extern "C" __attribute__((visibility("default"))) int rlxq_debug_gemm_trace(void
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
-    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K) return false;
+    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K && scheme != RLXQ_Q5_K) return false;
     if (scheme == RLXQ_Q6_K && k % 2048) return false;   // rows must stay 16-byte aligned
     if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
     return true;
@@ -1011,6 +1050,7 @@ int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const ui
         case RLXQ_Q4_0: return launch_gemm_s<RLXQ_Q4_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q8_0: return launch_gemm_s<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q5_K: return launch_gemm_s<RLXQ_Q5_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }

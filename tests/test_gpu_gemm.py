@@ -45,7 +45,8 @@ def _run(s, w, xb, n, y_bf16=False, kernel=0):
 
 SHAPES = [("q4_0", 256, 256, 128), ("q4_0", 9, 512, 130), ("q8_0", 300, 512, 200), ("q8_0", 512, 1024, 256),
           ("q4_k", 512, 1024, 384), ("q4_k", 130, 2048, 77), ("q4_0", 1000, 4096, 640),
-          ("q6_k", 256, 2048, 128), ("q6_k", 300, 4096, 200), ("q6_k", 64, 6144, 131)]
+          ("q6_k", 256, 2048, 128), ("q6_k", 300, 4096, 200), ("q6_k", 64, 6144, 131),
+          ("q5_k", 256, 512, 128), ("q5_k", 300, 2048, 200), ("q5_k", 70, 4096, 77)]
 
 
 @pytest.mark.parametrize("sch,m,k,n", SHAPES)
@@ -71,7 +72,8 @@ def test_both_activation_tile_widths_match_oracle(sch, m, k, n, tile_x):
 
 @pytest.mark.parametrize("sch,m,k,n,y_bf16", [("q4_k", 300, 4096, 384, False), ("q8_0", 64, 8192, 130, True),
                                               ("q4_0", 520, 1024, 2000, False), ("q6_k", 129, 6144, 200, True),
-                                              ("q4_k", 512, 4096, 14336, True), ("q4_k", 256, 3584, 8192, False)])
+                                              ("q4_k", 512, 4096, 14336, True), ("q4_k", 256, 3584, 8192, False),
+                                              ("q5_k", 200, 4096, 264, True)])
 def test_stream_k_split_matches_oracle_and_is_deterministic(sch, m, k, n, y_bf16):
     """With gemm_streamk = 2 the (tile, k group) units are dealt evenly to the SMs and cut tiles are completed by
     their last contributor: few tiles with a long k (one tile shared by many CTAs), many tiles (two contributors
@@ -135,7 +137,7 @@ def test_gemm_row_piece_stores_equal_single_value_stores(sch, m, k, n):
         assert np.array_equal(a.view(np.uint32), b[:, :n].view(np.uint32)), f"{sch} bf16={y_bf16}"
 
 
-@pytest.mark.parametrize("sch,k", [("q4_0", 256), ("q8_0", 512), ("q4_k", 512), ("q6_k", 2048)])
+@pytest.mark.parametrize("sch,k", [("q4_0", 256), ("q8_0", 512), ("q4_k", 512), ("q5_k", 512), ("q6_k", 2048)])
 def test_gemm_weight_operand_is_the_bf16_rounding_of_the_dequantised_weight(sch, k):
     """With the identity as activations every output is a single product 1 * w, so y^T is exactly the operand
     the decode warps hand to the tensor core: it must equal the oracle's dequantised weight rounded once to
