@@ -14,7 +14,8 @@ size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t 
     if (m <= 8) {
         // large enough for whichever GEMV kernel the dispatcher (or a forced option) picks
         const size_t a = staged_workspace_bytes(scheme, m, k, n);
-        const size_t b = m <= 4 ? int_workspace_bytes(scheme, m, k, n) : 0;
+        // (batch 5-8 of a format that only has the integer kernel runs it twice, four rows at a time)
+        const size_t b = int_workspace_bytes(scheme, m <= 4 ? m : 4, k, n);
         return a > b ? a : b;
     }
     return gemm_tc_workspace_bytes(m, k, n);      // partial tiles of the stream-K split, when the shape wants it
@@ -46,6 +47,18 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
             return launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 2 || (force == 0 && can_tc))
             return launch_gemv_staged(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        // A format with the integer kernel but no tensor-mode kernel (Q5_K): batch 3-4 in one pass, batch 5-8 in
+        // two passes of four rows; streaming the weights twice still beats the warp-per-row kernel several times.
+        if (force == 0 && can_int) return launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        if (force == 0 && m > 4 && int_supported(scheme, 4, k, n, w, x) && int_supported(scheme, m - 4, k, n, w, x)) {
+            const size_t xrow = (size_t)k * (xbf ? 2 : 4), yrow = (size_t)n * (ybf ? 2 : 4);
+            if ((4 * xrow) % 16 == 0) {
+                int rc = launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, 4, k, n, ws, ws_bytes);
+                if (rc) return rc;
+                return launch_gemv_int(stream, scheme, static_cast<const uint8_t*>(x) + 4 * xrow, xbf, w,
+                                       static_cast<uint8_t*>(y) + 4 * yrow, ybf, m - 4, k, n, ws, ws_bytes);
+            }
+        }
         return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
     }
     // m > 8: tensor-memory GEMM for bf16 activations, the tiled generic kernel otherwise
