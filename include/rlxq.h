@@ -103,7 +103,8 @@ RLXQ_API int rlxq_dequant_f32(rlxq_stream_t stream, uint32_t scheme, const void*
  * run_dequant_matmul_gguf (rlx-cuda/src/gguf_host.rs:90-128): y = x . W^T with the blocks
  * decoded inside the kernel.  m <= 8 runs the streaming GEMV; larger m runs the tensor-core
  * GEMM when the shape allows it (rlxq_workspace_bytes tells what it needs), else a tiled kernel.
- * x: f32 or bf16 [m,k]; y: f32 or bf16 [m,n]; accumulation is f32.  x must be 16-byte aligned, y
+ * x: f32 or bf16 [m,k]; y: f32 or bf16 [m,n]; accumulation is f32, a bf16 y is its round-to-nearest-even
+ * narrowing (a NaN result of the GEMM is stored as the canonical quiet NaN).  x must be 16-byte aligned, y
  * aligned to its element size, w_blocks to 2 bytes (16 bytes enables the bulk-copy fast paths).
  * workspace: rlxq_workspace_bytes(...) bytes, 16-byte aligned, contents irrelevant on entry; it is
  * private to the call while the kernels run (two calls in flight must not share it). */

@@ -498,10 +498,18 @@ __device__ __forceinline__ void gemm_store_vec(uint8_t* stage, uint32_t epi_tid,
 #pragma unroll
     for (uint32_t h = 0; h < NPASS; ++h) {
         uint8_t* buf = stage + ((NPASS == 1u ? c : h) & 1u) * 8192u;
+        if (F32) {
 #pragma unroll
-        for (uint32_t j = 0; j < CP; ++j) {
-            if (F32) *reinterpret_cast<uint32_t*>(buf + (j * kGemmTileW + row) * 4u) = v[h * CP + j];
-            else *reinterpret_cast<uint16_t*>(buf + (j * kGemmTileW + row) * 2u) = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[h * CP + j]));
+            for (uint32_t j = 0; j < CP; ++j) *reinterpret_cast<uint32_t*>(buf + (j * kGemmTileW + row) * 4u) = v[h * CP + j];
+        } else {
+            // one conversion instruction per two values (round to nearest even; a NaN becomes the canonical
+            // quiet NaN), the halves stored to the two output rows they belong to
+#pragma unroll
+            for (uint32_t j = 0; j < CP; j += 2) {
+                const uint32_t pr = bf16x2_of(f32x2(v[h * CP + j], v[h * CP + j + 1]));
+                *reinterpret_cast<uint16_t*>(buf + (j * kGemmTileW + row) * 2u) = (uint16_t)pr;
+                *reinterpret_cast<uint16_t*>(buf + ((j + 1) * kGemmTileW + row) * 2u) = (uint16_t)(pr >> 16);
+            }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
@@ -523,8 +531,8 @@ __device__ __forceinline__ void gemm_store4(const GemmParams& P, uint32_t mi, ui
     if (P.y_vec) {                       // n is a multiple of 4 at least and the rows are aligned
         if (P.y_bf16) {
             uint2 t;
-            t.x = f32_to_bf16_bits(a.x) | (f32_to_bf16_bits(a.y) << 16);
-            t.y = f32_to_bf16_bits(a.z) | (f32_to_bf16_bits(a.w) << 16);
+            t.x = bf16x2_of(f32x2(__float_as_uint(a.x), __float_as_uint(a.y)));
+            t.y = bf16x2_of(f32x2(__float_as_uint(a.z), __float_as_uint(a.w)));
             *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(P.y) + o) = t;
         } else {
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(P.y) + o) = a;
@@ -535,7 +543,7 @@ __device__ __forceinline__ void gemm_store4(const GemmParams& P, uint32_t mi, ui
 #pragma unroll
     for (uint32_t i = 0; i < 4; ++i) {
         if (ni + i < P.n) {
-            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o + i] = (uint16_t)f32_to_bf16_bits(e[i]);
+            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o + i] = (uint16_t)bf16x2_of(f32x2(__float_as_uint(e[i]), 0u));
             else reinterpret_cast<float*>(P.y)[o + i] = e[i];
         }
     }
@@ -901,7 +909,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                         const uint32_t m_idx = xt * kGemmTileX + 32 * c + j;
                         if (m_idx < P.m) {
                             const size_t o = (size_t)m_idx * P.n + n_idx;
-                            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(__uint_as_float(v[j]));
+                            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)bf16x2_of(f32x2(v[j], 0u));
                             else reinterpret_cast<float*>(P.y)[o] = __uint_as_float(v[j]);
                         }
                     }
