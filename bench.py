@@ -71,8 +71,8 @@ def algorithmic_bytes(sch: str, layers, m: int, act_bytes: int) -> list[int]:
 
 def finish_ranks(dist, torch) -> None:
     """Ends a multi-rank run: all ranks meet, flush and leave.  Tearing the NCCL process group down
-    while captured graphs that hold its kernels are alive blocked for minutes on this software stack,
-    so the ranks exit directly once every rank has printed what it has to print."""
+    while captured graphs that hold its kernels are alive has been seen to block for minutes (CUDA 12.9,
+    NCCL 2.28), so the ranks exit directly once every rank has printed what it has to print."""
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
@@ -81,12 +81,57 @@ def finish_ranks(dist, torch) -> None:
     os._exit(0)
 
 
-def measured_peaks() -> tuple[float, str]:
+def all_peaks() -> dict:
+    """Roofline denominators: the measured copy bandwidth and cuBLAS bf16 rates in MEASURED_PEAKS.json
+    beside this file when it exists, else fixed fallback figures (and the line says which)."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         with open(p) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+            d = json.load(f)
+        return {"hbm": float(d["hbm_gbs"]), "tf_burst": float(d["bf16_tflops"]),
+                "tf_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured": True}
+    return {"hbm": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "measured": False}
+
+
+def measured_peaks() -> tuple[float, str]:
+    pk = all_peaks()
+    return pk["hbm"], ("measured (MEASURED_PEAKS.json hbm_gbs)" if pk["measured"]
+                       else "fallback (6.65 TB/s, an earlier B200 copy measurement)")
+
+
+def captured_traffic(workload: str, m: int):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
+    summary of this workload under profiles/ (a line `traffic: workload=<name> batch=<m> dram_bytes_per_launch=<N>`);
+    None when no capture of this workload and batch is on file."""
+    import glob
+    import re
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", "*.md"))):
+        with open(path) as f:
+            for ln in f:
+                mt = re.search(r"traffic:\s*workload=(\S+)\s+batch=(\d+)\s+dram_bytes_per_launch=(\d+)", ln)
+                if mt and mt.group(1) == workload and int(mt.group(2)) == m:
+                    return int(mt.group(3))
+    return None
+
+
+def time_graph(torch, step, steps: int, warmup: int) -> float:
+    """ms per step: `warmup` eager steps, then `steps` steps captured once in a CUDA graph, one untimed
+    replay, one replay timed with CUDA events on the launching stream."""
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(steps):
+            step(warmup + i)
+    graph.replay()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    graph.replay()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / steps
 
 
 class ClockSampler:
@@ -370,6 +415,11 @@ def tp_bytes(m: int) -> int:
     return 3 * packed_bytes("q4_k", TP_D_MODEL, TP_D_FFN) + m * TP_D_MODEL * 2 + m * TP_D_MODEL * 4
 
 
+def tp_flops(m: int) -> float:
+    """Multiply-adds x 2 of one FFN pass: three projections of d_model x d_ffn."""
+    return 2.0 * m * 3 * TP_D_MODEL * TP_D_FFN
+
+
 def tp_config(args, world, rotation, reduce_kind="nccl"):
     return {"all_reduce": reduce_kind if world > 1 else "none", "workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
             "parallelism": f"tp{world}: gate/up column-split, down row-split, all-reduce of f32 partials",
@@ -378,31 +428,46 @@ def tp_config(args, world, rotation, reduce_kind="nccl"):
 
 
 def run_tp_reference_arm(args, rank, world):
+    """The reference's CPU path for configuration 3 (the oracle port of it), all host threads.  A decode batch
+    runs whole FFN passes; a prefill batch runs a bounded sample of 8 of its token rows (rows are independent)
+    and ms_per_step is scaled to the full batch."""
     if rank != 0:
         return
     from oracle import oracle as O
     m, dm, df = args.batch, TP_D_MODEL, TP_D_FFN
     gate, up, down = (O.fill_weights(O.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
-    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, m * dm))).reshape(m, dm)
+    rows = min(m, 8)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, rows * dm))).reshape(rows, dm)
     cores = os.cpu_count() or 1
     steps = min(args.steps, 20)          # a bounded sample: one pass is ~0.7 G multiply-adds per token
     for _ in range(min(args.warmup, 3)):
-        O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, threads=cores)
+        O.ffn_swiglu(x, gate, up, down, rows, dm, df, O.Q4_K, O.Q4_K, threads=cores)
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, threads=cores)
+        O.ffn_swiglu(x, gate, up, down, rows, dm, df, O.Q4_K, O.Q4_K, threads=cores)
     dt = (time.perf_counter() - t0) / steps
-    val = tp_bytes(m) / dt / 1e9
+    if m <= 8:
+        val, unit, metric, ms = tp_bytes(m) / dt / 1e9, "GB/s", "gemv_hbm_gbs", dt * 1e3
+        sample = f"{steps} full FFN passes on all {cores} host threads"
+    else:
+        val, unit, metric, ms = tp_flops(rows) / dt / 1e12, "TFLOP/s", "gemm_tflops", dt * 1e3 * m / rows
+        sample = f"{steps} FFN passes over {rows} of the {m} token rows on all {cores} host threads; ms_per_step scaled to {m} rows"
+    g = max(1, args.gpus)
+    shard = 3 * packed_bytes("q4_k", dm, df) // g
+    rotation = max(2, -(-2 * L2_BYTES // shard) + 1)
+    cfg = tp_config(args, g, rotation, "rank-order sum on the host" if g > 1 else "none")
     print(json.dumps({
-        "impl": "reference", "metric": "gemv_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": tp_config(args, 1, 1),
-        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{steps} full FFN passes on all {cores} host threads"},
-        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
 
 
 def run_tp_workload(args, rank, world, local_rank):
+    """Configuration 3 on `world` GPUs.  The headline is the batch given by --batch (1 unless stated): HBM GB/s
+    for a decode batch, TFLOP/s for a prefill batch; unless --no-sweep is given the other batch of the
+    configuration (256 / 1) follows as a `configs` entry.  Rank 0 checks its summed result against the oracle FFN."""
     import torch
     import torch.distributed as dist
     if not torch.cuda.is_available():
@@ -414,13 +479,13 @@ def run_tp_workload(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    m, dm, df = args.batch, TP_D_MODEL, TP_D_FFN
+    dm, df = TP_D_MODEL, TP_D_FFN
     plan = tp.shard_plan(O.Q4_K, dm, df, world, rank)
     shard_bytes = 2 * plan.gate_up_bytes + plan.down_bytes
     rotation = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
     # every rank generates only its own shards: blocks are counter-based, so a shard of the seeded
     # full tensor is a sub-range of its block stream (gate/up) or a strided set of sub-ranges (down)
-    be, bb = 256, 144
+    be = 256
     ffns = []
     for r in range(rotation):
         seeds = [2000 + 10 * r + i for i in range(3)]
@@ -432,22 +497,15 @@ def run_tp_workload(args, rank, world, local_rank):
         f = tp.TensorParallelFFN(O.Q4_K, dm, df, rank=rank, world=world, device=dev)
         f.load_shards(gu, dn)
         ffns.append(f)
-    x_host = O.fill_normal(78, m * dm).reshape(m, dm)
-    x_dev = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
-    y = torch.empty((m, dm), dtype=torch.float32, device=dev)
     # decode-sized partials are summed by the one-shot peer-memory all-reduce; larger ones, or when the peer
     # mapping cannot be set up (or RLXQ_TP_ALLREDUCE=nccl), by the process group's
-    reduce_kind = "nccl"
+    pr = None
     if world > 1 and os.environ.get("RLXQ_TP_ALLREDUCE", "peer") == "peer":
         pr = tp.PeerAllReduce(rank, world)
         if pr.available:
             for f in ffns:
                 f.peer_reduce = pr
-            if pr.fits(y):
-                reduce_kind = "peer memory, one shot, rank order"
-
-    def step(i):
-        ffns[i % rotation].forward(x_dev, out=y)
+    full = None      # rank 0: the whole tensors of rotation set 0, for the oracle check
 
     def sync_all():
         torch.cuda.synchronize()
@@ -455,93 +513,340 @@ def run_tp_workload(args, rank, world, local_rank):
             dist.barrier()
             torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    sync_all()
-    launches0 = R.launch_count()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        for i in range(args.steps):
-            step(args.warmup + i)
-    launches = R.launch_count() - launches0
-    graph.replay()
-    sync_all()
-    sampler = ClockSampler(local_rank)
+    def measure(m: int, steps: int, warmup: int, want_e2e: bool) -> dict:
+        nonlocal full
+        x_host = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, m * dm))).reshape(m, dm)
+        x_dev = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
+        y = torch.empty((m, dm), dtype=torch.float32, device=dev)
+        reduce_kind = "none" if world == 1 else ("peer memory, one shot, rank order" if pr is not None and pr.fits(y) else "nccl")
+
+        def step(i):
+            ffns[i % rotation].forward(x_dev, out=y)
+
+        for i in range(warmup):
+            step(i)
+        sync_all()
+        launches0 = R.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(steps):
+                step(warmup + i)
+        launches = R.launch_count() - launches0
+        graph.replay()
+        sync_all()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sync_all()
+        ev0.record()
+        graph.replay()
+        ev1.record()
+        sync_all()
+        R.device_status()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            tt = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+            lt = torch.tensor([launches], dtype=torch.int64, device=dev)
+            dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+            launches = int(lt.item())
+        clocks = sampler.stop() if rank == 0 else None
+        res = {"m": m, "ms_per_step": ms / steps, "steps": steps, "launches": launches, "clocks": clocks,
+               "reduce_kind": reduce_kind, "parity_max": None}
+        # rank 0: the summed result of rotation set 0 against the oracle FFN on sampled token rows
+        step(0)
+        sync_all()
+        if rank == 0:
+            if full is None:
+                full = tuple(O.fill_weights(O.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
+            rows = np.arange(m) if m <= 8 else np.unique(np.linspace(0, m - 1, 4).astype(np.int64))
+            res["parity_max"] = tp_oracle_check(O, x_host, y.cpu().numpy(), *full, dm, df, rows)
+            res["parity_sample"] = "every output" if m <= 8 else f"{len(rows)} token rows, every output"
+        if want_e2e:
+            # end to end: x from pinned host memory every step, y back to pinned host memory
+            x_pin = torch.from_numpy(x_host).to(torch.bfloat16).pin_memory()
+            y_pin = torch.empty((m, dm), dtype=torch.float32).pin_memory()
+
+            def e2e_step(i):
+                x_dev.copy_(x_pin, non_blocking=True)
+                ffns[i % rotation].forward(x_dev, out=y)
+                y_pin.copy_(y, non_blocking=True)
+                torch.cuda.synchronize()
+
+            for i in range(warmup):
+                e2e_step(i)
+            sync_all()
+            t0 = time.perf_counter()
+            for i in range(steps):
+                e2e_step(warmup + i)
+            e2e_s = time.perf_counter() - t0
+            if world > 1:
+                tt = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                e2e_s = float(tt.item())
+            res["e2e_s_per_step"] = e2e_s / steps
+        return res
+
+    def rate(m: int, s_per_step: float) -> tuple[float, str, str]:
+        if m <= 8:
+            return tp_bytes(m) / s_per_step / 1e9, "GB/s", "gemv_hbm_gbs"
+        return tp_flops(m) / s_per_step / 1e12, "TFLOP/s", "gemm_tflops"
+
+    def roofline_of(m: int, ms_per_step: float, pk: dict) -> dict:
+        if m <= 8:
+            per_gpu = (shard_bytes + m * dm * 6) / (ms_per_step * 1e-3) / 1e9
+            return {"bound": "hbm", "achieved": per_gpu, "peak": pk["hbm"], "unit": "GB/s", "frac": per_gpu / pk["hbm"],
+                    "peak_source": "measured copy bandwidth (MEASURED_PEAKS.json)" if pk["measured"] else "fallback 6.65 TB/s",
+                    "frac_of_nominal_8TBs": per_gpu / 8000.0,
+                    "kernel": "the GEMV kernels of one FFN step (per GPU: its shard bytes / whole step time, all-reduce included)",
+                    "bytes_per_step_per_gpu": shard_bytes + m * dm * 6, "traffic": None}
+        per_gpu = tp_flops(m) / world / (ms_per_step * 1e-3) / 1e12
+        return {"bound": "tensor", "achieved": per_gpu, "peak": pk["tf_burst"], "unit": "TFLOP/s", "frac": per_gpu / pk["tf_burst"],
+                "peak_source": "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)" if pk["measured"] else "fallback 1.59 PFLOP/s",
+                "frac_of_sustained": per_gpu / pk["tf_sustained"],
+                "kernel": "gemm_tcgen05_kernel x 2 + the SwiGLU kernel (per GPU: its share of the FLOPs / whole step time, all-reduce included)",
+                "flops_per_step_per_gpu": tp_flops(m) / world, "traffic": None}
+
+    m = args.batch
+    head = measure(m, args.steps if m <= 8 else min(args.steps, 20), args.warmup, True)
+    other = None
+    if not args.no_sweep and m in (1, 256):
+        om = 256 if m == 1 else 1
+        other = measure(om, 20 if om > 8 else 100, 3, False)
     if rank == 0:
-        sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    ev0.record()
-    graph.replay()
-    ev1.record()
-    sync_all()
-    R.device_status()
-    ms = ev0.elapsed_time(ev1)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        lt = torch.tensor([launches], dtype=torch.int64, device=dev)
-        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
-        launches = int(lt.item())
-    clocks = sampler.stop() if rank == 0 else None
-    ms_per_step = ms / args.steps
-    value = tp_bytes(m) / (ms_per_step * 1e-3) / 1e9
-
-    # end to end: x from pinned host memory every step, y back to pinned host memory
-    x_pin = torch.from_numpy(x_host).to(torch.bfloat16).pin_memory()
-    y_pin = torch.empty((m, dm), dtype=torch.float32).pin_memory()
-
-    def e2e_step(i):
-        x_dev.copy_(x_pin, non_blocking=True)
-        ffns[i % rotation].forward(x_dev, out=y)
-        y_pin.copy_(y, non_blocking=True)
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        e2e_step(i)
-    sync_all()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(args.warmup + i)
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_val = tp_bytes(m) / (e2e_s / args.steps) / 1e9
-    if rank == 0:
-        peak, peak_src = measured_peaks()
-        per_gpu = (shard_bytes + m * dm * 6) / (ms_per_step * 1e-3) / 1e9
+        pk = all_peaks()
+        value, unit, metric = rate(m, head["ms_per_step"] * 1e-3)
+        e2e_val = rate(m, head["e2e_s_per_step"])[0]
         line = {
-            "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": tp_config(args, world, rotation, reduce_kind),
-            "clocks": clocks,
-            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": m * dm * 2, "d2h_bytes_per_step": m * dm * 4,
-                    "ms_per_step": e2e_s / args.steps * 1e3,
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": head["steps"],
+            "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32" if m <= 8 else "bf16", "data": "synthetic",
+            "config": tp_config(args, world, rotation, head["reduce_kind"]),
+            "clocks": head["clocks"],
+            "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": m * dm * 2, "d2h_bytes_per_step": m * dm * 4,
+                    "ms_per_step": head["e2e_s_per_step"] * 1e3,
                     "api": "TensorParallelFFN.forward: pinned x -> device, rlxq_tp_ffn_partial, all-reduce, y -> pinned host"},
-            "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_source": peak_src, "frac_of_nominal_8TBs": per_gpu / 8000.0,
-                         "kernel": "gemv_int_kernel (per GPU: its shard bytes / whole step time, all-reduce included)",
-                         "bytes_per_step_per_gpu": shard_bytes + m * dm * 6, "traffic": None},
+            "gpu_launches": head["launches"],
+            "roofline": roofline_of(m, head["ms_per_step"], pk),
+            "parity_max": head["parity_max"], "parity_sample": head.get("parity_sample"),
         }
+        if other is not None:
+            ov, ou, om_metric = rate(other["m"], other["ms_per_step"] * 1e-3)
+            line["configs"] = [{"name": f"cfg3 q4_k 70b ffn m={other['m']}, {world} gpu", "m": other["m"], "metric": om_metric,
+                                "value": ov, "unit": ou, "ms": other["ms_per_step"], "all_reduce": other["reduce_kind"],
+                                "roofline": roofline_of(other["m"], other["ms_per_step"], pk),
+                                "parity_max": other["parity_max"], "parity_sample": other.get("parity_sample")}]
         if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle as O2
             cores = os.cpu_count() or 1
-            gate, up, down = (O2.fill_weights(O2.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
-            xx = O2.bf16_bits_to_f32(O2.f32_to_bf16_bits(x_host)).reshape(m, dm)
-            O2.ffn_swiglu(xx, gate, up, down, m, dm, df, O2.Q4_K, O2.Q4_K, threads=cores)
+            gate, up, down = full
+            ms_rows = min(m, 8)                 # a bounded sample for a prefill batch: 8 of its token rows
+            xx = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, ms_rows * dm))).reshape(ms_rows, dm)
+            O.ffn_swiglu(xx, gate, up, down, ms_rows, dm, df, O.Q4_K, O.Q4_K, threads=cores)
             t0 = time.perf_counter(); reps = 0
             while time.perf_counter() - t0 < 8.0 and reps < 20:
-                O2.ffn_swiglu(xx, gate, up, down, m, dm, df, O2.Q4_K, O2.Q4_K, threads=cores); reps += 1
+                O.ffn_swiglu(xx, gate, up, down, ms_rows, dm, df, O.Q4_K, O.Q4_K, threads=cores); reps += 1
             dt = (time.perf_counter() - t0) / reps
-            line["cpu_baseline"] = {"value": tp_bytes(m) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                                    "sample": f"{reps} full FFN passes, all {cores} host threads", "ms_per_step": dt * 1e3}
+            line["cpu_baseline"] = {"value": rate(ms_rows, dt)[0] if m <= 8 else tp_flops(ms_rows) / dt / 1e12, "unit": unit,
+                                    "cores": cores, "kind": "port",
+                                    "sample": f"{reps} FFN passes over {ms_rows} token rows, all {cores} host threads",
+                                    "ms_per_step": dt * 1e3}
         print(json.dumps(line), flush=True)
     if world > 1:
         finish_ranks(dist, torch)
+
+# --------------------------------------------------------------------------------------------
+# Every configuration on one line: the default run appends a `configs` list to the headline, each entry
+# measured the same way (resident inputs, CUDA graph, CUDA events, weights rotated past L2 or larger than
+# it) and checked against an oracle sample taken in the same run.
+# --------------------------------------------------------------------------------------------
+def parity_ratio(y, ref, xn, wn) -> float:
+    """worst |y - y_ref| / (||x_row|| ||w_row||) over the sample."""
+    err = np.abs(np.asarray(y, np.float64) - np.asarray(ref, np.float64))
+    return float((err / np.maximum(xn[:, None] * wn[None, :], 1e-30)).max())
+
+
+def sweep_gemv(torch, R, O, dev, name, sch, layers, act, m, steps, warmup, pk) -> dict:
+    sid = O.SCHEMES[sch]
+    act_t = torch.float32 if act == "f32" else torch.bfloat16
+    w_host = [O.fill_weights(sid, 5000 + i, k, n) for i, (k, n) in enumerate(layers)]
+    w_step = sum(w.size for w in w_host)
+    rotation = max(2, -(-2 * L2_BYTES // w_step) + 1)
+    base = [torch.from_numpy(w).to(dev) for w in w_host]
+    wsets = [base] + [[b.clone() for b in base] for _ in range(rotation - 1)]    # same bytes at other addresses
+    x_host = O.fill_normal(81, m * layers[0][0]).reshape(m, layers[0][0])
+    if act != "f32":
+        x_host = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x_host)).reshape(m, -1)
+    x_dev = torch.from_numpy(x_host).to(dev).to(act_t)
+    outs = [torch.empty((m, n), dtype=torch.float32, device=dev) for _, n in layers]
+    need = max(R.workspace_bytes(sid, m, k, n, 0 if act == "f32" or i else 1, 0) for i, (k, n) in enumerate(layers))
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+
+    def step(i):
+        cur = x_dev
+        for li, (_, n) in enumerate(layers):
+            R.matmul(cur, wsets[i % rotation][li], sid, n, out=outs[li], workspace=ws)
+            cur = outs[li]
+
+    l0 = R.launch_count()
+    step(0)
+    per_step_launches = R.launch_count() - l0
+    ms = time_graph(torch, step, steps, warmup)
+    R.device_status()
+    step(0)
+    torch.cuda.synchronize()
+    worst, cur = 0.0, x_host
+    for li, (k, n) in enumerate(layers):            # every layer against the oracle on the input it really had
+        y = outs[li].cpu().numpy()
+        ref = O.matmul_bt_mt(cur, w_host[li], m, k, n, sid)
+        xn = np.sqrt((cur.astype(np.float64) ** 2).sum(axis=1))
+        worst = max(worst, parity_ratio(y, ref, xn, O.row_norms(sid, w_host[li], k, n)))
+        cur = y
+    by = sum(algorithmic_bytes(sch, layers, m, 4 if act == "f32" else 2))
+    ach = by / (ms * 1e-3) / 1e9
+    return {"name": name, "scheme": sch, "m": m, "layers_k_to_n": [[k, n] for k, n in layers], "activations": act,
+            "metric": "gemv_hbm_gbs", "value": ach, "unit": "GB/s", "ms": ms, "launches_per_step": per_step_launches,
+            "roofline": {"bound": "hbm", "frac": ach / pk["hbm"], "peak": pk["hbm"],
+                         "peak_kind": "measured copy bandwidth" if pk["measured"] else "fallback"},
+            "parity_max": worst, "parity_sample": "every output of every layer",
+            "l2": f"{rotation} weight copies in rotation"}
+
+
+def sweep_gemm(torch, R, O, dev, name, sch, m, k, n, steps, warmup, pk) -> dict:
+    sid = O.SCHEMES[sch]
+    w_host = O.fill_weights(sid, 5100, k, n)
+    wd = torch.from_numpy(w_host).to(dev)
+    x_host = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(82, m * k))).reshape(m, k)
+    xd = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    need = R.workspace_bytes(sid, m, k, n, 1, 1)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    small = packed_bytes(sch, k, n) + m * k * 2 + m * n * 2 < 2 * L2_BYTES
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev) if small else None
+
+    def step(i):
+        R.matmul(xd, wd, sid, n, out=y, workspace=ws)
+
+    if small:
+        # operands smaller than L2: time single launches, L2 flushed by a 252 MB fill in between
+        for i in range(warmup):
+            step(i)
+        torch.cuda.synchronize()
+        times = []
+        for i in range(steps):
+            flush.fill_(i & 0xFF)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(); step(i); ev1.record()
+            torch.cuda.synchronize()
+            times.append(ev0.elapsed_time(ev1))
+        ms = statistics.median(times)
+    else:
+        ms = time_graph(torch, step, steps, warmup)
+    R.device_status()
+    # oracle sample: 16 token rows spread over m against two slabs of 64 weight rows
+    rows = np.unique(np.linspace(0, m - 1, 16).astype(np.int64))
+    rb = packed_bytes(sch, k, 1)
+    worst = 0.0
+    yh = y.float().cpu().numpy()
+    xs = np.ascontiguousarray(x_host[rows])
+    xn = np.sqrt((xs.astype(np.float64) ** 2).sum(axis=1))
+    for r0 in (0, max(0, (n // 2) // 64 * 64), max(0, n - 64)):
+        r1 = min(n, r0 + 64)
+        wsub = w_host[r0 * rb:r1 * rb]
+        ref = O.matmul_bt_mt(xs, wsub, len(rows), k, r1 - r0, sid)
+        worst = max(worst, parity_ratio(yh[rows][:, r0:r1], ref, xn, O.row_norms(sid, wsub, k, r1 - r0)))
+    flops = 2.0 * m * k * n
+    ach = flops / (ms * 1e-3) / 1e12
+    return {"name": name, "scheme": sch, "m": m, "k": k, "n": n, "activations": "bf16", "output": "bf16",
+            "metric": "gemm_tflops", "value": ach, "unit": "TFLOP/s", "ms": ms,
+            "roofline": {"bound": "tensor", "frac": ach / pk["tf_burst"], "peak": pk["tf_burst"],
+                         "peak_kind": "measured cuBLAS bf16 burst" if pk["measured"] else "fallback",
+                         "frac_of_sustained": ach / pk["tf_sustained"]},
+            "parity_max": worst, "parity_sample": f"{len(rows)} token rows x 3 slabs of 64 weight rows",
+            "l2": "L2 flushed between single timed launches" if small else "operands larger than L2"}
+
+
+def tp_oracle_check(O, x_host_bf16_as_f32, y, gate, up, down, dm, df, rows) -> float:
+    """Rank 0's FFN result against the oracle FFN on the sampled token rows (rows are independent)."""
+    xs = np.ascontiguousarray(x_host_bf16_as_f32[rows])
+    ref, h = O.ffn_swiglu(xs, gate, up, down, len(rows), dm, df, O.Q4_K, O.Q4_K, want_h=True)
+    hn = np.sqrt((h.astype(np.float64) ** 2).sum(axis=1))
+    return parity_ratio(y[rows], ref, hn, O.row_norms(O.Q4_K, down, df, dm))
+
+
+def sweep_ffn_one_gpu(torch, R, O, dev, name, m, steps, warmup, pk) -> dict:
+    from rlx_b200 import tp
+    dm, df = TP_D_MODEL, TP_D_FFN
+    gate, up, down = (O.fill_weights(O.Q4_K, 2000 + i, *sh) for i, sh in enumerate(((dm, df), (dm, df), (df, dm))))
+    ffns = []
+    for r in range(2):                               # 2 x 396 MB > 2 x L2
+        f = tp.TensorParallelFFN(O.Q4_K, dm, df, rank=0, world=1, device=dev)
+        if r == 0:
+            f.load(gate, up, down)
+        else:
+            f.gate_up, f.down = ffns[0].gate_up.clone(), ffns[0].down.clone()
+        ffns.append(f)
+    x_host = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, m * dm))).reshape(m, dm)
+    x_dev = torch.from_numpy(x_host).to(dev).to(torch.bfloat16)
+    y = torch.empty((m, dm), dtype=torch.float32, device=dev)
+
+    def step(i):
+        ffns[i % 2].forward(x_dev, out=y)
+
+    l0 = R.launch_count()
+    step(0)
+    per_step_launches = R.launch_count() - l0
+    ms = time_graph(torch, step, steps, warmup)
+    R.device_status()
+    step(0)
+    torch.cuda.synchronize()
+    rows = np.arange(m) if m <= 8 else np.unique(np.linspace(0, m - 1, 4).astype(np.int64))
+    worst = tp_oracle_check(O, x_host, y.cpu().numpy(), gate, up, down, dm, df, rows)
+    out = {"name": name, "scheme": "q4_k", "m": m, "d_model": dm, "d_ffn": df, "activations": "bf16", "output": "f32",
+           "ms": ms, "launches_per_step": per_step_launches, "parity_max": worst,
+           "parity_sample": "every output" if m <= 8 else f"{len(rows)} token rows, every output",
+           "l2": "2 weight sets of 396 MB in rotation"}
+    if m <= 8:
+        ach = tp_bytes(m) / (ms * 1e-3) / 1e9
+        out.update({"metric": "gemv_hbm_gbs", "value": ach, "unit": "GB/s",
+                    "roofline": {"bound": "hbm", "frac": ach / pk["hbm"], "peak": pk["hbm"],
+                                 "peak_kind": "measured copy bandwidth" if pk["measured"] else "fallback"}})
+    else:
+        ach = tp_flops(m) / (ms * 1e-3) / 1e12
+        out.update({"metric": "gemm_tflops", "value": ach, "unit": "TFLOP/s",
+                    "roofline": {"bound": "tensor", "frac": ach / pk["tf_burst"], "peak": pk["tf_burst"],
+                                 "peak_kind": "measured cuBLAS bf16 burst" if pk["measured"] else "fallback",
+                                 "frac_of_sustained": ach / pk["tf_sustained"]}})
+    return out
+
+
+def sweep_all_configs(torch, R, O, dev, headline_entry: dict) -> list[dict]:
+    """The configurations beside the headline one, one entry each; a failure becomes an entry with `error`."""
+    pk = all_peaks()
+    jobs = [
+        lambda: sweep_gemv(torch, R, O, dev, "cfg0 q8_0 4096x4096 gemv m=1", "q8_0", [(4096, 4096)], "f32", 1, 200, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg1 q4_0 llama7b ffn gemv pair m=4", "q4_0", [(4096, 11008), (11008, 4096)], "f32", 4, 100, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg1 q4_0 llama7b ffn gemv pair m=8", "q4_0", [(4096, 11008), (11008, 4096)], "f32", 8, 100, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemv m=1", "q4_k", [(4096, 14336)], "bf16", 1, 200, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemv m=1", "q6_k", [(14336, 4096)], "bf16", 1, 200, 5, pk),
+        lambda: sweep_gemm(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemm m=512", "q4_k", 512, 4096, 14336, 20, 3, pk),
+        lambda: sweep_gemm(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemm m=512", "q6_k", 512, 14336, 4096, 20, 3, pk),
+        lambda: sweep_ffn_one_gpu(torch, R, O, dev, "cfg3 q4_k 70b ffn m=1, 1 gpu", 1, 50, 3, pk),
+        lambda: sweep_ffn_one_gpu(torch, R, O, dev, "cfg3 q4_k 70b ffn m=256, 1 gpu", 256, 10, 3, pk),
+        lambda: sweep_gemm(torch, R, O, dev, "cfg4 q8_0 8192->28672 gemm m=4096", "q8_0", 4096, 8192, 28672, 5, 3, pk),
+        lambda: sweep_gemm(torch, R, O, dev, "cfg4 q4_0 8192->28672 gemm m=4096", "q4_0", 4096, 8192, 28672, 5, 3, pk),
+    ]
+    out = [headline_entry]
+    for job in jobs:
+        try:
+            out.append(job())
+        except Exception as e:                      # one broken configuration must not hide the others
+            out.append({"error": f"{type(e).__name__}: {e}"})
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    return out
+
 
 # --------------------------------------------------------------------------------------------
 # GPU arm
@@ -581,9 +886,6 @@ def run_moe_workload(args, rank, world, local_rank):
 
     def step(i):
         R.grouped_matmul(x_dev, stacks[i % rotation], routes[i % 8], sid, n, E, out=y, workspace=wsb)
-
-    if os.environ.get("RLXQ_BENCH_GENERAL_GROUPED"):       # development switch: time the general grouped kernel
-        R.set_option("gemv_kernel", 1)
 
     for i in range(args.warmup):
         step(i)
@@ -845,6 +1147,8 @@ def main() -> None:
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="default workload only: skip the `configs` list (the other configurations, one entry each)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -999,6 +1303,18 @@ def main() -> None:
     step(args.warmup + args.steps - 1)
     torch.cuda.synchronize()
     e2e_matches = bool(torch.equal(outs[-1].cpu(), y_pin))
+    # the headline's own parity: both layers of the last weight set against the oracle, each on the input it had
+    headline_parity = None
+    if rank == 0:
+        wl = wsets[(args.warmup + args.steps - 1) % rotation]
+        headline_parity, cur_h = 0.0, x_host if act == "f32" else O.bf16_bits_to_f32(O.f32_to_bf16_bits(x_host)).reshape(m, -1)
+        for li, (k, n) in enumerate(layers):
+            wh = wl[li].cpu().numpy()
+            ref = O.matmul_bt_mt(cur_h, wh, m, k, n, O.SCHEMES[sch])
+            yh = outs[li].cpu().numpy()
+            xn = np.sqrt((cur_h.astype(np.float64) ** 2).sum(axis=1))
+            headline_parity = max(headline_parity, parity_ratio(yh, ref, xn, O.row_norms(O.SCHEMES[sch], wh, k, n)))
+            cur_h = yh
 
     if rank == 0:
         peak, peak_src = measured_peaks()
@@ -1021,13 +1337,17 @@ def main() -> None:
                          "kernel": "gemv_int_kernel (+ its activation quantiser)", "bytes_per_launch": bytes_per_launch,
                          "avg_launch_us": avg_launch_s * 1e6,
                          "timing": "CUDA events over the timed region / launches (includes inter-launch gaps)",
-                         # dram__bytes_read + write per launch from the ncu capture summarised in
-                         # profiles/gemv_int_q4_0_llama7b_ffn_m1.md (25.46 MB for 25.42 MB algorithmic);
-                         # other workloads were not captured
-                         "traffic": 25460000 if args.workload == "q4_0_llama7b_ffn_gemv" and m == 1 else None},
+                         "traffic": captured_traffic(args.workload, m)},
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)
+        if world == 1 and not args.no_sweep and args.workload == "q4_0_llama7b_ffn_gemv" and m == 1:
+            head = {"name": "cfg1 q4_0 llama7b ffn gemv pair m=1 (the headline)", "scheme": sch, "m": m,
+                    "layers_k_to_n": [[k, n] for k, n in layers], "activations": act, "metric": "gemv_hbm_gbs",
+                    "value": value, "unit": "GB/s", "ms": ms_per_step,
+                    "roofline": {"bound": "hbm", "frac": achieved / peak, "peak": peak, "peak_kind": peak_src},
+                    "parity_max": headline_parity, "parity_sample": "every output of both layers"}
+            line["configs"] = sweep_all_configs(torch, R, O, dev, head)
         print(json.dumps(line), flush=True)
     if world > 1:
         finish_ranks(dist, torch)

@@ -131,7 +131,11 @@ RLXQ_API int rlxq_matmul(rlxq_stream_t stream, uint32_t scheme,
  * All calls on a device share the one array, which keeps whatever the previous call left; each call
  * rewrites or zeroes what it depends on, so calls issued one after the other (same stream, or
  * ordered by events) are independent, but two calls whose kernels may overlap on the GPU race on it
- * and must not be issued. */
+ * and must not be issued.
+ * A bounded wait that runs out inside this entry point is recorded in the device's regular error
+ * word when the process already has one (rlxq_init_device at start-up creates it), otherwise in a
+ * word inside the library image; rlxq_device_status reads both, and allocates nothing when only
+ * allocation-free calls have been made on the device. */
 RLXQ_API int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme,
                                         const void* x, uint32_t x_dtype, const void* w_blocks,
                                         void* y, uint32_t y_dtype, uint32_t m, uint32_t k, uint32_t n);
@@ -145,7 +149,11 @@ RLXQ_API int rlxq_init_device(void);
  * bounded wait since the last call (RLXQ_E_TIMEOUT, *device_error = which wait).  Every spin in
  * the kernels has an iteration limit, so a lost copy or a missing signal ends as this error, not
  * as a hung GPU.  Not capture-safe (it synchronises); the reference's equivalent is the
- * stream.synchronize() + panic in CudaExecutable::run (rlx-cuda/src/backend.rs:6675-6693). */
+ * stream.synchronize() + panic in CudaExecutable::run (rlx-cuda/src/backend.rs:6675-6693).
+ * After RLXQ_E_TIMEOUT the outputs of the calls since the last check are undefined, and the
+ * workspace those calls used (or the built-in scratch of rlxq_matmul_static_scratch) may hold a
+ * half-finished tile exchange: zero it (cudaMemsetAsync) before the next call or graph replay that
+ * uses it (rlxq_compiled_clear_scratch for a compiled graph's arena). */
 RLXQ_API int rlxq_device_status(int* device_error);
 
 /* Number of kernels this library has launched in this process (all threads). */
@@ -165,10 +173,10 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  kernel of its own, 2 = the streaming kernel quantises the activations itself
  *                  whenever the shape allows it
  *   "gemv_kslices": 0 = automatic, n > 0 = split k over n CTAs per row tile in the staged GEMV
+ *   "tp_spin_limit": polls of a peer's flag before rlxq_tp_allreduce_sum's kernel gives up and reports
+ *          RLXQ_E_TIMEOUT (device_error = 40 + the peer's rank); default 2^24, a few seconds
  *   "pdl": 1 (default) = launch the GEMV kernels with programmatic stream serialization so a
  *          kernel's weight prefetch overlaps the tail of its predecessor, 0 = plain launches
- *   "gemv_debug": profiling aid, 0 in production; bit 0 skips the arithmetic of the staged GEMVs,
- *                 bit 1 the activation staging (outputs are then meaningless)
  * Returns RLXQ_E_ARG for an unknown key. */
 RLXQ_API int rlxq_set_option(const char* key, int64_t value);
 RLXQ_API int rlxq_get_option(const char* key, int64_t* value);

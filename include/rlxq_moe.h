@@ -27,7 +27,9 @@ RLXQ_API int rlxq_grouped_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t 
 
 /* x: [m,k] f32 or bf16; expert_idx: [m] f32-encoded expert ids, as the reference's graph input
  * (rlx-runtime/tests/dequant_grouped_matmul_gguf.rs:92-105); y: [m,n] f32 or bf16.  A row whose id
- * is not in [0, num_experts) gets zeros (the reference only debug-asserts the range).
+ * is read as the reference's `expert_idx[i] as usize` reads it (rlx-cpu/src/gguf_matmul.rs:187,198: a
+ * saturating cast, so NaN, negative values and fractions below 1 mean expert 0); a row whose id is
+ * num_experts or more, which indexes out of bounds in the reference, gets zeros.
  * k must be a multiple of the block size and k*n of it too (whole blocks per slab row). */
 RLXQ_API int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
                                  const void* w_blocks, const float* expert_idx, void* y, uint32_t y_dtype,

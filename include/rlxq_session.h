@@ -88,6 +88,12 @@ RLXQ_API int rlxq_compiled_run_typed(rlxq_compiled* c, uint32_t n_inputs, const 
 /* Bytes of device memory the compiled graph holds (arena incl. workspace). */
 RLXQ_API uint64_t rlxq_compiled_arena_bytes(const rlxq_compiled* c);
 
+/* Zeroes the kernels' scratch region of the arena (not the params, inputs or outputs) and waits for it.
+ * Call it after rlxq_device_status reported RLXQ_E_TIMEOUT and before the next run: a wait that ran out
+ * can leave a half-finished tile exchange behind.  The reference has no counterpart: its executable
+ * panics on a failed synchronize (rlx-cuda/src/backend.rs:6675-6693) and is rebuilt. */
+RLXQ_API int rlxq_compiled_clear_scratch(rlxq_compiled* c);
+
 #ifdef __cplusplus
 }
 #endif

@@ -190,16 +190,18 @@ def grouped_matmul_bt(x: np.ndarray, w: np.ndarray, expert_idx: np.ndarray, m: i
                       num_experts: int, scheme: int) -> np.ndarray:
     """gguf_grouped_matmul_bt (rlx-cpu/src/gguf_matmul.rs:102-139): counting-sort the rows by expert
     (grouped_moe_sort_plan, :178-205), one fused matmul per expert over its slab, unpermute (:207-218).
-    The arithmetic is the C oracle's matmul; only the routing is done here."""
+    The arithmetic is the C oracle's matmul; only the routing is done here.  Ids are read as `expert_idx[i] as
+    usize` reads them (:187,198): a saturating cast, so NaN, negative values and fractions go to expert 0.  An id of
+    num_experts or more indexes out of bounds in the reference (a panic); such rows stay zero here."""
     be, bb = GEOMETRY[scheme]
     slab = k * n // be * bb
     assert w.size == num_experts * slab and expert_idx.size == m
     x = np.ascontiguousarray(x, np.float32).reshape(m, k)
-    ids = expert_idx.astype(np.float32)
+    raw = expert_idx.astype(np.float32)
+    ids = np.where(raw >= 1.0, np.floor(np.minimum(raw, np.float32(2.0 ** 31))), 0.0).astype(np.int64)   # NaN compares false
     out = np.zeros((m, n), np.float32)
     for e in range(num_experts):
-        rows = np.flatnonzero(ids.astype(np.int64) == e) if m else np.array([], np.int64)
-        rows = rows[(ids[rows] >= 0)]
+        rows = np.flatnonzero(ids == e) if m else np.array([], np.int64)
         if rows.size == 0:
             continue
         out[rows] = matmul_bt_mt(np.ascontiguousarray(x[rows]), np.ascontiguousarray(w[e * slab:(e + 1) * slab]),

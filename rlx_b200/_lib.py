@@ -78,6 +78,7 @@ _SIGS = {
     "rlxq_compiled_run_typed": (C.c_int, [vp, u32, C.POINTER(cp), C.POINTER(vp), C.POINTER(u64),
                                           C.POINTER(u32), vp, u64, u32]),
     "rlxq_compiled_arena_bytes": (u64, [vp]),
+    "rlxq_compiled_clear_scratch": (C.c_int, [vp]),
 }
 
 

@@ -318,6 +318,10 @@ class CompiledGraph:
     def arena_bytes(self) -> int:
         return int(lib.rlxq_compiled_arena_bytes(self._h))
 
+    def clear_scratch(self) -> None:
+        """Zeroes the kernels' scratch region; the step to take after device_status() raised a timeout."""
+        check(lib.rlxq_compiled_clear_scratch(self._h))
+
 
 class Session:
     """Session::new(Device::Cuda) — rlx-runtime/src/session.rs:42-87."""

@@ -25,12 +25,12 @@ struct Options {
     std::atomic<int64_t> gemv_kernel{0};
     std::atomic<int64_t> gemm_kernel{0};
     std::atomic<int64_t> gemv_kslices{0};
-    std::atomic<int64_t> gemv_debug{0};
     std::atomic<int64_t> pdl{1};
     std::atomic<int64_t> gemm_tile_x{0};
     std::atomic<int64_t> gemm_streamk{0};
     std::atomic<int64_t> gemv_inline_q{0};
     std::atomic<int64_t> gemv_early{2};
+    std::atomic<int64_t> tp_spin_limit{1 << 24};
 };
 Options& options();
 

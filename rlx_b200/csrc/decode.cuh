@@ -12,6 +12,16 @@
 
 namespace rlxq {
 
+// Expert id of a row as the reference reads it, `expert_idx[i] as usize` (rlx-cpu/src/gguf_matmul.rs:187,198):
+// a saturating cast, so NaN and every value below 1 select expert 0.  An id of num_experts or more indexes
+// out of bounds in the reference; here such a row is in no group (false) and its output stays zero.
+__device__ __forceinline__ bool expert_of_row(float f, uint32_t num_experts, uint32_t* e) {
+    if (!(f >= 1.0f)) { *e = 0u; return true; }
+    if (f >= (float)num_experts) return false;
+    *e = (uint32_t)f;
+    return true;
+}
+
 __device__ __forceinline__ float f16_bits_to_f32(uint32_t bits) {
     // Exact for every fp16 value, subnormals included (rlx-gguf/src/lib.rs:569-571).
     return __half2float(__ushort_as_half((unsigned short)bits));

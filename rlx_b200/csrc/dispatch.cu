@@ -65,7 +65,7 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     const int64_t gforce = options().gemm_kernel.load();
     const bool can = gemm_tc_supported(scheme, m, k, n, w, x, xbf);
     if (gforce == 2 && !can)
-        return fail(RLXQ_E_SHAPE, "the tcgen05 GEMM needs bf16 activations, k %% 256 == 0, Q4_0/Q8_0/Q4_K and 16-byte alignment");
+        return fail(RLXQ_E_SHAPE, "the tcgen05 GEMM needs bf16 activations, k %% 256 == 0 (2048 for Q6_K), one of Q4_0/Q8_0/Q4_K/Q5_K/Q6_K and 16-byte alignment");
     if (can && gforce != 1) return launch_gemm_tc(stream, scheme, x, w, y, ybf, m, k, n, ws, ws_bytes);
     return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
 }

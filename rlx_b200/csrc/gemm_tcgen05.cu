@@ -433,20 +433,6 @@ struct GemmParams {
     uint32_t* counters;
 };
 
-#ifdef RLXQ_TRACE
-// Timeline instrumentation for development builds only (never compiled into the shipped library).
-__device__ unsigned long long g_gemm_trace[256][32];
-__device__ __forceinline__ unsigned long long gemm_gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define GT(i) do { if (blockIdx.x < 256) g_gemm_trace[blockIdx.x][i] = gemm_gtime(); } while (0)
-#define GTV(i, v) do { if (blockIdx.x < 256) g_gemm_trace[blockIdx.x][i] = (unsigned long long)(v); } while (0)
-#else
-#define GT(i) do {} while (0)
-#define GTV(i, v) do {} while (0)
-#endif
 
 struct GemmSeg { uint32_t tile, g0, g1; };     // k groups [g0, g1) of one tile
 
@@ -628,7 +614,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     volatile uint32_t* abort_flag = &bars->abort_flag;
 
     if (tid == 0) {
-        GT(0);
         for (uint32_t s = 0; s < kGemmStages; ++s) {
             mbar_init(smem_u32(&bars->b_full[s]), 1);
             mbar_init(smem_u32(&bars->a_full[s]), 4);
@@ -652,8 +637,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_d = tmem_base, tmem_a = tmem_base + 256;
-    if (tid == 0) GT(1);
-
     auto give_up = [&](int code) {
         if (lane == 0) { atomicExch(P.err, code); *abort_flag = 1u; }
     };
@@ -662,9 +645,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         // ---------------- activation tiles (B operand) ----------------
         if (lane == 0) {
             tma_prefetch_desc(&P.xmap);
-#ifdef RLXQ_TRACE
-            bool tr_first = false;
-#endif
             uint32_t s = 0, ph = 1;      // parity to wait for on stage_free (1 passes on a fresh barrier)
             uint32_t cur, lim;
             gemm_seg_init(P, cur, lim);
@@ -677,9 +657,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     const uint32_t full = smem_u32(&bars->b_full[s]);
                     mbar_arrive_expect_tx(full, B_BYTES);
                     tma_load_2d(smem_u32(b_stage + s * B_BYTES), &P.xmap, (int32_t)(kb * kGemmBK), (int32_t)(xt * kGemmTileX), full);
-#ifdef RLXQ_TRACE
-                    if (!tr_first) { tr_first = true; GT(2); }
-#endif
                     if (++s == kGemmStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -710,37 +687,17 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             uint32_t s = 0, ph = 0, dph = 1;   // dph: parity to wait for on d_free (1 passes the first time)
-#ifdef RLXQ_TRACE
-            long long tr_wb = 0, tr_wa = 0, tr_wd = 0; uint32_t tr_n = 0, tr_seg = 0;
-#endif
             uint32_t cur, lim;
             gemm_seg_init(P, cur, lim);
             GemmSeg sg;
             while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
-#ifdef RLXQ_TRACE
-                const long long td0 = clock64();
-#endif
                 if (!mbar_wait(smem_u32(&bars->d_free), dph)) { give_up(13); break; }
-#ifdef RLXQ_TRACE
-                tr_wd += clock64() - td0;
-#endif
                 dph ^= 1u;
                 tc_fence_after();
                 bool ok = true;
                 for (uint32_t kb = 0; kb < 4 * (sg.g1 - sg.g0); ++kb) {    // the first MMA of a segment overwrites the accumulator
-#ifdef RLXQ_TRACE
-                    const long long t0 = clock64();
-                    if (!mbar_wait(smem_u32(&bars->b_full[s]), ph)) { give_up(14); ok = false; break; }
-                    const long long t1 = clock64();
-                    if (tr_n == 0) GT(3);
-                    if (!mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(14); ok = false; break; }
-                    tr_wb += t1 - t0; tr_wa += clock64() - t1;
-                    if (tr_n == 0) GT(4);
-                    ++tr_n;
-#else
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->b_full[s]), ph) ||
                         !mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(14); ok = false; break; }
-#endif
                     tc_fence_after();
                     const uint64_t bdesc = kmajor_sw128_desc(smem_u32(b_stage + s * B_BYTES));
 #pragma unroll
@@ -751,15 +708,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&bars->d_full));
-#ifdef RLXQ_TRACE
-                if (tr_seg == 0) GT(5);
-                GT(18);
-                ++tr_seg;
-#endif
             }
-#ifdef RLXQ_TRACE
-            GTV(12, tr_wb); GTV(13, tr_wa); GTV(14, tr_n); GTV(19, tr_wd);
-#endif
         }
     } else if (warp >= 4 && warp < 4 + 4 * kGemmDecodeGroups) {
         // ---------------- decode: raw blocks -> bf16 rows in tensor memory ----------------
@@ -770,22 +719,12 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         const uint32_t lane_addr = (quarter * 32) << 16;
         uint32_t r = 0, rph = 0, kbg0 = 0;   // kbg0: k blocks this CTA has gone through before the current group
         bool ok = true;
-#ifdef RLXQ_TRACE
-        long long tr_wr = 0, tr_wf = 0, tr_dec = 0, tr_st = 0, tr_all0 = clock64(); bool tr_first = false;
-#endif
         uint32_t cur, lim;
         gemm_seg_init(P, cur, lim);
         GemmSeg sg;
         while (ok && !*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
             for (uint32_t g = sg.g0; g < sg.g1 && ok; ++g, kbg0 += 4) {
-#ifdef RLXQ_TRACE
-                const long long tq0 = clock64();
-#endif
                 if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_full[r]), rph)) { give_up(15); ok = false; break; }
-#ifdef RLXQ_TRACE
-                tr_wr += clock64() - tq0;
-                if (!tr_first && warp == 4 && lane == 0) GT(10);
-#endif
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
 #pragma unroll
                 for (uint32_t sub = 0; sub < 4; ++sub) {                 // which 64 weights of the group
@@ -795,34 +734,14 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     // decode into registers first: only the store needs the stage's tensor-memory columns,
                     // so the arithmetic stays off the free -> store -> MMA chain
                     uint32_t v[32];
-#ifdef RLXQ_TRACE
-                    const long long td0 = clock64();
-#endif
                     if (sub == 0) decode64<SCHEME, 0>(rp, g, v);
                     else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
                     else if (sub == 2) decode64<SCHEME, 2>(rp, g, v);
                     else decode64<SCHEME, 3>(rp, g, v);
-#ifdef RLXQ_TRACE
-                    tr_dec += clock64() - td0 + (long long)(v[0] & 0u);
-#endif
-#ifdef RLXQ_TRACE
-                    const long long tf0 = clock64();
-#endif
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), fph)) { give_up(16); ok = false; break; }
-#ifdef RLXQ_TRACE
-                    tr_wf += clock64() - tf0;
-                    const long long ts0 = clock64();
-#endif
                     tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * s, v);
                     tmem_st_wait();
-#ifdef RLXQ_TRACE
-                    tr_st += clock64() - ts0;
-#endif
-#ifdef RLXQ_TRACE
-                    if (!tr_first && warp == 4 && lane == 0) { GT(11); }
-                    tr_first = true;
-#endif
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->a_full[s]));
@@ -833,9 +752,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                 if (++r == kGemmRawStages) { r = 0; rph ^= 1u; }
             }
         }
-#ifdef RLXQ_TRACE
-        if (warp == 4 && lane == 0) { GTV(15, tr_wr); GTV(16, tr_wf); GTV(17, clock64() - tr_all0); GTV(23, tr_dec); GTV(24, tr_st); }
-#endif
     } else if (warp >= 4 + 4 * kGemmDecodeGroups) {
         // ---------------- epilogue: accumulator -> y (or -> a partial tile, completed by the last contributor) ----------------
         const uint32_t quarter = warp & 3u;
@@ -851,9 +767,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
             if (!mbar_wait(smem_u32(&bars->d_full), dph)) { give_up(17); break; }
             dph ^= 1u;
             tc_fence_after();
-#ifdef RLXQ_TRACE
-            if (epi_tid == 0) { if (nseg == 0) GT(6); GT(20); }
-#endif
             const uint32_t n_idx = wt * kGemmTileW + row;
             const bool whole = sg.g0 == 0 && sg.g1 == P.kgroups;
             // a cut tile: this CTA's part goes to its head slot when its range begins inside the tile
@@ -889,9 +802,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->d_free));
-#ifdef RLXQ_TRACE
-                    if (epi_tid == 0) { if (nseg == 0) GT(7); GT(21); }
-#endif
                 }
                 if (other) {
                     gemm_add_store(epi_stage, epi_tid, row, v, reinterpret_cast<const uint4*>(other + (size_t)(32 * c) * kGemmTileW),
@@ -928,9 +838,6 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     gemm_reduce_parts(P, kGemmTileX, c_first, c_last, u0, xt * kGemmTileX, wt * kGemmTileW, epi_tid);
                 }
             }
-#ifdef RLXQ_TRACE
-            if (epi_tid == 0) { if (nseg == 0) GT(8); GT(22); }
-#endif
             ++nseg;
         }
     }
@@ -938,15 +845,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
-#ifdef RLXQ_TRACE
-    if (tid == 0) GT(9);
-#endif
 }
-#ifdef RLXQ_TRACE
-extern "C" __attribute__((visibility("default"))) int rlxq_debug_gemm_trace(void* dst) {
-    return (int)cudaMemcpyFromSymbol(dst, g_gemm_trace, sizeof(g_gemm_trace));
-}
-#endif
 
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {

@@ -82,7 +82,6 @@ struct IntParams {
     uint32_t nstages;
     uint32_t xq_row_bytes; // bytes of one row of xq
     uint32_t off_stage, off_red, off_bar;
-    uint32_t debug;
     // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
     // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
     uint32_t inline_q;
@@ -92,11 +91,10 @@ struct IntParams {
     unsigned long long token;    // odd, unique to this call
     uint32_t early;              // single-kernel mode: stages requested before the dependency wait
     // Expert-indirect mode (MoE decode): W is a stack of [n, k] slabs and this launch multiplies by slab
-    // (uint32_t)*expert_sel, read on the device after the dependency wait; ids outside [0, num_experts)
-    // make the kernel return at once (the caller has zeroed y).
+    // *expert_sel read as the reference's `as usize` cast does (expert_of_row), on the device after the
+    // dependency wait; an id of num_experts or more makes the kernel return at once (the caller has zeroed y).
     const float* expert_sel;
     uint32_t num_experts;
-    uint32_t tslot;              // development builds: which trace slot this launch writes
 };
 
 // Per-thread view for the integer kernel.  Everything is a 32-bit shared-memory byte address: the
@@ -112,19 +110,6 @@ struct QLane {
     uint32_t row_pitch; // bytes between tile rows inside a stage
 };
 
-#ifdef RLXQ_TRACE
-// Timeline instrumentation for development builds only (never compiled into the shipped library).
-__device__ unsigned long long g_trace[4][512][16];
-__device__ unsigned long long g_trace_q[4][4];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define RLXQ_T(slot, ev) do { if (blockIdx.x < 512) g_trace[(slot) & 3][blockIdx.x][ev] = gtime(); } while (0)
-#else
-#define RLXQ_T(slot, ev) do { } while (0)
-#endif
 
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
     uint4 v;
@@ -555,17 +540,9 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
                                                          uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
                                                          uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count,
                                                          uint32_t swiglu_pair) {
-#ifdef RLXQ_TRACE
-    const uint32_t tslot = swiglu_pair >> 8;
-    swiglu_pair &= 0xFFu;
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][0] = gtime();
-#endif
     griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
     const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
     griddep_wait();                // x (and the counters) may still be in use by the previous kernel
-#ifdef RLXQ_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][1] = gtime();
-#endif
     for (uint32_t i = gtid; i < ntiles; i += gridDim.x * blockDim.x) counters[i] = 0u;
     for (uint32_t i = gtid; i < y_count; i += gridDim.x * blockDim.x) y_zero[i] = 0.f;   // two-contributor add mode
     const uint32_t groups_per_row = k / 8;
@@ -576,9 +553,6 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
     if (swiglu_pair) load_group8_swiglu(x, k, r, c, f);
     else load_group8(x, x_bf16, k, r, c, f);
     quantise_store8<SUB>(f, k, bias, c, xq + (size_t)r * xq_row_bytes, lane);
-#ifdef RLXQ_TRACE
-    if (blockIdx.x == 0 && threadIdx.x == 0) g_trace_q[tslot & 3][2] = gtime();
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -655,10 +629,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     griddep_launch_dependents();
-    if (tid == 0) { RLXQ_T(P.tslot, 0); tma_prefetch_desc(&P.wmap); }
-#ifdef RLXQ_TRACE
-    const long long c_entry = clock64();
-#endif
+    if (tid == 0) tma_prefetch_desc(&P.wmap);
 
     const uint32_t G = gridDim.x, me = blockIdx.x;
     const Range rg = make_range(P, me);
@@ -679,7 +650,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid == 0) RLXQ_T(P.tslot, 1);
     // The first fill of the ring is spread over the warps, one stage each: a TMA request occupies its
     // issuing thread for a few hundred cycles, and one thread issuing them all delays the stream's start.
     const uint32_t pre = min(min(NS, kIntWarps), rg.len);
@@ -690,9 +660,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         row_off = 0u;
         if (!P.expert_sel) return true;
         griddep_wait();
-        const float f = *P.expert_sel;
-        if (!(f >= 0.f && f < (float)P.num_experts)) return false;
-        row_off = (uint32_t)f * P.n;
+        uint32_t e;
+        if (!expert_of_row(*P.expert_sel, P.num_experts, &e)) return false;
+        row_off = e * P.n;
         return true;
     };
 
@@ -719,13 +689,11 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 if (issued == NS && !waited) {
                     // the ring is full of (immutable) weights: only now wait for the previous kernel
                     waited = true;
-                    if (lane == 0) RLXQ_T(P.tslot, 2);
                     griddep_wait();
-                    if (lane == 0) RLXQ_T(P.tslot, 3);
                     const uint32_t xbar = smem_u32(&bars[2 * NS]);
-                    if (lane == 0 && !(P.debug & 4u) && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+                    if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
                     __syncwarp();
-                    if (lane < (uint32_t)MM && !(P.debug & 4u) && !P.inline_q)
+                    if (lane < (uint32_t)MM && !P.inline_q)
                         bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
                 }
                 if (issued >= NS) {
@@ -740,13 +708,11 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             }
         }
         if (!waited) {   // fewer chunks than stages: everything is in flight, now fetch the activations
-            if (lane == 0) RLXQ_T(P.tslot, 2);
             griddep_wait();
-            if (lane == 0) RLXQ_T(P.tslot, 3);
             const uint32_t xbar = smem_u32(&bars[2 * NS]);
-            if (lane == 0 && !(P.debug & 4u) && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+            if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
             __syncwarp();
-            if (lane < (uint32_t)MM && !(P.debug & 4u) && !P.inline_q)
+            if (lane < (uint32_t)MM && !P.inline_q)
                 bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
         }
         return;
@@ -788,7 +754,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&rbars[kIntRB + r]));
             if (++r == kIntRB) { r = 0; rph ^= 1u; }
-            if (P.debug & 8u) continue;
             const uint32_t orow = tile * 16 + rrow;
             bool store = mine == P.nchunks;
             if (!store && P.inline_q) {
@@ -862,7 +827,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 }
             }
         }
-        if (lane == 0) RLXQ_T(P.tslot, 9);
         return;
     }
 
@@ -888,7 +852,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     const uint32_t early = P.inline_q ? P.early : pre;   // stages requested before the dependency wait
     request_first_stage(0, early);
     griddep_wait();
-    if (tid == 0) RLXQ_T(P.tslot, 4);
     QLane L;
     L.half = lane >> 4;
     L.xstride = P.xq_row_bytes;
@@ -903,7 +866,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     const uint32_t trow = QU::first_row(lane), stages_u32 = smem_u32(stages);
     bool dead = false;
     if (P.inline_q) {
-        if (!(P.debug & 4u)) {
+        {
             // every load is issued before the first value is used: one trip to L2, not one per group
             const uint32_t gpr = P.k / 8, total = gpr * P.m_real;   // whole warps stay together: gpr % 32 == 0
             constexpr uint32_t kInlineGroups = inline_groups(MM);
@@ -929,45 +892,28 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 }
             }
         }
-        else request_first_stage(early, pre);
         consumer_bar_n<kIntWarps * 32>();
-    } else if (!(P.debug & 4u) && !mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+    } else if (!mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
         dead = true;
         if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
     }
     uint32_t s = 0, ph = 0, rr = 0, rrph = 1;   // rrph: a fresh 'empty' barrier passes a wait on parity 1
-    if (tid == 0) RLXQ_T(P.tslot, 5);
-#ifdef RLXQ_TRACE
-    bool first_stage = true;
-    long long t_wait = 0, t_math = 0;
-#endif
     for (uint32_t si = 0; si < nseg; ++si) {
         const Segment sg = segment_at(P, rg, si);
         float tot[QU::NT * MM];
 #pragma unroll
         for (int m = 0; m < QU::NT * MM; ++m) tot[m] = 0.f;
         for (uint32_t chunk = sg.c0; chunk < sg.c1; ++chunk) {
-#ifdef RLXQ_TRACE
-            const long long tw0 = clock64();
-#endif
             if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
                 dead = true;
                 if (lane == 0) { atomicExch(P.err, 4); *abort_flag = 1u; }
             }
-#ifdef RLXQ_TRACE
-            const long long tw1 = clock64();
-            t_wait += tw1 - tw0;
-            if (tid == 0 && first_stage) { RLXQ_T(P.tslot, 6); first_stage = false; }
-#endif
             if (!dead) {
                 const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
                 L.row = stages_u32 + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
-                if (warp < cu && !(P.debug & kDebugSkipMath))
+                if (warp < cu)
                     QU::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
                 __syncwarp();
-#ifdef RLXQ_TRACE
-                t_math += clock64() - tw1;
-#endif
                 if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
             }
             if (++s == NS) { s = 0; ph ^= 1u; }
@@ -987,10 +933,6 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         }
         if (++rr == kIntRB) { rr = 0; rrph ^= 1u; }
     }
-    if (tid == 0) RLXQ_T(P.tslot, 8);
-#ifdef RLXQ_TRACE
-    if (tid == 0 && blockIdx.x < 512) { g_trace[P.tslot & 3][blockIdx.x][10] = (unsigned long long)t_wait; g_trace[P.tslot & 3][blockIdx.x][11] = (unsigned long long)t_math; g_trace[P.tslot & 3][blockIdx.x][12] = rg.len; g_trace[P.tslot & 3][blockIdx.x][13] = (unsigned long long)(clock64() - c_entry); }
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1081,7 +1023,6 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.chunks_q = pl.total_chunks / pl.grid; P.chunks_r = pl.total_chunks % pl.grid;
     P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes;
     P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
-    P.debug = (uint32_t)options().gemv_debug.load();
     // One kernel instead of two when every shared tile has exactly two contributors and re-quantising
     // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
     // dependent-launch hop and a copy on the critical path of a call that lasts only microseconds.
@@ -1095,7 +1036,6 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.flags = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(ws) + pl.ws_xq + pl.ws_partial + pl.ws_counters);
     P.token = next_call_token();
     P.early = expert_sel ? 0u : (uint32_t)options().gemv_early.load();   // an indirect launch cannot prefetch before it knows its slab
-    P.tslot = (uint32_t)(P.token >> 2) & 3u;
     P.err = err_word;
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     static std::atomic<uint32_t> attr_set[64];
@@ -1108,12 +1048,9 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     const uint32_t groups = (k / 8) * m_real;
     int rc = RLXQ_OK;
     const uint32_t qgrid = (groups + 255) / 256;
-    if (!(P.debug & 16u) && !P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
+    if (!P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
                         m_real, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
                         P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? m_real * n : 0u,
-#ifdef RLXQ_TRACE
-                        (P.tslot << 8) |
-#endif
                         (pair ? 1u : 0u));
     if (rc) return rc;
     if (!P.inline_q) count_launch();
@@ -1237,9 +1174,17 @@ struct StaticScratch { uint8_t* scratch; int* err; };
 
 // First call on a device: resolve the two symbols.  No allocation; must happen outside stream
 // capture (symbol lookup may initialise the module on this device).
+static std::atomic<uint8_t*> scratch_ptr[64];
+static std::atomic<int*> err_ptr[64];
+
+// The built-in error word of the current device if an allocation-free call has resolved it, else null.
+int* static_error_word_if_resolved() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return err_ptr[dev].load();
+}
+
 static int static_scratch_for_current_device(StaticScratch* out) {
-    static std::atomic<uint8_t*> scratch_ptr[64];
-    static std::atomic<int*> err_ptr[64];
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(RLXQ_E_ARG, "device ordinal %d out of range", dev);
@@ -1265,14 +1210,6 @@ static int static_scratch_for_current_device(StaticScratch* out) {
 
 using namespace rlxq;
 
-#ifdef RLXQ_TRACE
-extern "C" RLXQ_API int rlxq_debug_trace(unsigned long long* main_events, unsigned long long* q_events) {
-    RLXQ_CUDA_TRY(cudaDeviceSynchronize());
-    RLXQ_CUDA_TRY(cudaMemcpyFromSymbol(main_events, g_trace, sizeof(g_trace)));
-    RLXQ_CUDA_TRY(cudaMemcpyFromSymbol(q_events, g_trace_q, sizeof(g_trace_q)));
-    return RLXQ_OK;
-}
-#endif
 
 extern "C" int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme, const void* x, uint32_t x_dtype,
                                           const void* w_blocks, void* y, uint32_t y_dtype, uint32_t m, uint32_t k,
@@ -1296,8 +1233,8 @@ extern "C" int rlxq_matmul_static_scratch(rlxq_stream_t stream, uint32_t scheme,
     StaticScratch ss;
     int rc = static_scratch_for_current_device(&ss);
     if (rc) return rc;
-    // Timeouts of bounded waits go to the device's regular error word when it already exists (so
-    // rlxq_device_status sees them); otherwise to a word in this library's image.
+    // Timeouts of bounded waits go to the device's regular error word when it already exists, otherwise
+    // to a word in this library's image; rlxq_device_status reads both and allocates neither.
     int* err = device_error_word_if_ready();
     if (!err) err = ss.err;
     // Nothing an earlier call left in the scratch is ever consumed: partial tiles are written before

@@ -439,9 +439,8 @@ __global__ void __launch_bounds__(kThreads) gemv_staged_kernel(const __grid_cons
             L.stage = stages + s * stage_bytes;
             L.row_lo = L.stage + g * T::STRIDE;
             L.row_hi = L.row_lo + 8 * T::STRIDE;
-            if (!(P.debug & kDebugSkipMath))
-                for (uint32_t u = warp; u < cu; u += kConsumerWarps)
-                    Unit<SCHEME>::run(L, u * T::UNIT_B, (chunk * T::CU + u) * 256, scratch, lane, tot);
+            for (uint32_t u = warp; u < cu; u += kConsumerWarps)
+                Unit<SCHEME>::run(L, u * T::UNIT_B, (chunk * T::CU + u) * 256, scratch, lane, tot);
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
         }
@@ -596,7 +595,6 @@ static int launch_staged_t(cudaStream_t stream, const void* x, bool xbf, const u
     P.xs_stride = pl.xs_stride; P.mp = pl.mp;
     P.off_sxb = pl.off_sxb; P.off_stage = pl.off_stage; P.off_scratch = pl.off_scratch;
     P.off_red = pl.off_red; P.off_bar = pl.off_bar;
-    P.debug = (uint32_t)options().gemv_debug.load();
     P.nstages = pl.nstages;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
@@ -655,12 +653,30 @@ int* device_error_word_if_ready() {
     return g_error_words[dev].load();
 }
 
+// Reads (and clears) the error words kernels on this device may have written: the allocated one, and the
+// one inside the library image that rlxq_matmul_static_scratch uses while the device has no allocated
+// word.  A process that has only ever made allocation-free calls has just the second, and this function
+// then allocates nothing either; with neither present nothing can have been recorded, and the regular
+// word is created so that later launches have one.
 int staged_device_error(int* value) {
-    int* p = device_error_word();
-    if (!p) return fail(RLXQ_E_CUDA, "device error word unavailable");
+    int* p = device_error_word_if_ready();
+    int* sp = static_error_word_if_resolved();
+    if (!p && !sp) {
+        p = device_error_word();
+        if (!p) return fail(RLXQ_E_CUDA, "device error word unavailable");
+    }
     RLXQ_CUDA_TRY(cudaDeviceSynchronize());
-    RLXQ_CUDA_TRY(cudaMemcpy(value, p, sizeof(int), cudaMemcpyDeviceToHost));
-    if (*value) RLXQ_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
+    *value = 0;
+    int* words[2] = {p, sp};
+    for (int* w : words) {
+        if (!w) continue;
+        int v = 0;
+        RLXQ_CUDA_TRY(cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost));
+        if (v) {
+            RLXQ_CUDA_TRY(cudaMemset(w, 0, sizeof(int)));
+            if (!*value) *value = v;
+        }
+    }
     return RLXQ_OK;
 }
 

@@ -152,8 +152,9 @@ extern "C" int rlxq_gguf_open(const char* path, rlxq_gguf** out) {
                     if (l > r.size - r.pos) r.ok = false; else r.pos += l;
                 }
             } else {
-                const uint64_t bytes = n * kScalarSize[inner];
-                if (bytes > r.size - r.pos) r.ok = false; else r.pos += bytes;
+                uint64_t bytes = 0;      // a count that wraps the product is a malformed header, not a short array
+                if (__builtin_mul_overflow(n, (uint64_t)kScalarSize[inner], &bytes) || bytes > r.size - r.pos) r.ok = false;
+                else r.pos += bytes;
             }
         } else {
             MetaScalar v;
@@ -175,14 +176,25 @@ extern "C" int rlxq_gguf_open(const char* path, rlxq_gguf** out) {
         t.n_dims = r.get<uint32_t>();
         if (!r.ok || t.n_dims > 4) { delete f; return fail(RLXQ_E_ARG, "tensor '%s': %u dimensions", name.c_str(), t.n_dims); }
         uint64_t elems = 1;
-        for (uint32_t d = 0; d < t.n_dims; ++d) { t.dims[d] = r.len(f->version); elems *= t.dims[d]; }
+        bool wraps = false;
+        for (uint32_t d = 0; d < t.n_dims; ++d) {
+            t.dims[d] = r.len(f->version);
+            wraps = __builtin_mul_overflow(elems, t.dims[d], &elems) || wraps;
+        }
         t.ggml_type = r.get<uint32_t>();
         t.offset = r.get<uint64_t>();
         if (!r.ok) break;
         if (!ggml_type_known(t.ggml_type)) { delete f; return fail(RLXQ_E_ARG, "tensor '%s': unknown ggml type %u", name.c_str(), t.ggml_type); }
+        if (wraps) { delete f; return fail(RLXQ_E_ARG, "tensor '%s': element count overflows 64 bits (malformed GGUF header)", name.c_str()); }
         uint32_t be = 0, bb = 0;
-        if (ggml_block(t.ggml_type, &be, &bb, &t.scheme) && elems % be == 0) t.bytes = elems / be * bb;
-        f->names.push_back(name);
+        if (ggml_block(t.ggml_type, &be, &bb, &t.scheme) && elems % be == 0 &&
+            __builtin_mul_overflow(elems / be, (uint64_t)bb, &t.bytes)) {
+            delete f;
+            return fail(RLXQ_E_ARG, "tensor '%s': byte size overflows 64 bits (malformed GGUF header)", name.c_str());
+        }
+        // a repeated name replaces the earlier entry, as inserting into the reference's map does
+        // (rlx-gguf/src/lib.rs:246-318); it is listed once
+        if (f->tensors.find(name) == f->tensors.end()) f->names.push_back(name);
         f->tensors[name] = t;
     }
     if (!r.ok) { delete f; return fail(RLXQ_E_ARG, "%s: truncated or malformed GGUF header", path); }

@@ -175,10 +175,13 @@ int Session::compile(const Graph& g, ExecMode mode, CompiledGraph** out) {
                     if (nd.bytes && !rc) rc = launch_copy_bytes(c->stream_, c->arena_ + c->offsets_[i], (uint8_t*)c->pinned_ + so, nd.bytes);
                     so += align_up(nd.bytes, 256);
                 }
+            const uint64_t launches_before = g_launches.load(std::memory_order_relaxed);
             if (!rc) rc = c->enqueue_steps(c->stream_);
             const Node& on = c->nodes_[c->output_];
             if (c->io_in_graph_ && on.bytes && !rc)
                 rc = launch_copy_bytes(c->stream_, (uint8_t*)c->pinned_ + so, c->arena_ + c->offsets_[c->output_], on.bytes);
+            // what one replay of the captured graph launches (the I/O copy kernels are counted below)
+            c->captured_launches_ = g_launches.load(std::memory_order_relaxed) - launches_before;
             cudaError_t e2 = cudaStreamEndCapture(c->stream_, &graph);
             if (e == cudaSuccess) e = e2;
             if (rc) { if (graph) cudaGraphDestroy(graph); delete c; return rc; }
@@ -240,6 +243,13 @@ int CompiledGraph::set_param_typed(const std::string& name, const void* data, ui
     return fail(RLXQ_E_ARG, "set_param_typed: no param named '%s'", name.c_str());
 }
 
+int CompiledGraph::clear_scratch() {
+    RLXQ_CUDA_TRY(cudaSetDevice(device_));
+    if (ws_bytes_) RLXQ_CUDA_TRY(cudaMemsetAsync(arena_ + ws_off_, 0, arena_bytes_ - ws_off_, stream_));
+    RLXQ_CUDA_TRY(cudaStreamSynchronize(stream_));
+    return RLXQ_OK;
+}
+
 static bool is_pinned(const void* p) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { (void)cudaGetLastError(); return false; }
@@ -287,14 +297,7 @@ int CompiledGraph::run_typed(uint32_t n_inputs, const char* const* names, const 
     if (mode_ == ExecMode::Graph) {
         RLXQ_CUDA_TRY(cudaGraphLaunch(graph_exec_, stream_));
         // the captured launches were counted at capture time; count the replays too
-        uint64_t launches = 0;
-        for (const Node& nd : nodes_) {
-            if (nd.op == OpKind::DequantMatMul || nd.op == OpKind::SwigluMul) ++launches;
-            if (nd.op == OpKind::DequantGroupedMatMul) launches += 2;
-            if (io_in_graph_ && nd.op == OpKind::Input && nd.bytes) ++launches;
-        }
-        if (io_in_graph_ && nodes_[output_].bytes) ++launches;
-        count_launch(launches);
+        count_launch(captured_launches_);
     } else {
         int rc = enqueue_steps(stream_);
         if (rc) return rc;
@@ -391,5 +394,10 @@ int rlxq_compiled_run_typed(rlxq_compiled* c, uint32_t n_inputs, const char* con
 }
 
 uint64_t rlxq_compiled_arena_bytes(const rlxq_compiled* c) { return c ? c->c->arena_bytes() : 0; }
+
+int rlxq_compiled_clear_scratch(rlxq_compiled* c) {
+    if (!c) return fail(RLXQ_E_NULL, "null argument");
+    return c->c->clear_scratch();
+}
 
 }  // extern "C"

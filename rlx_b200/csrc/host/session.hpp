@@ -58,6 +58,7 @@ public:
                   const uint64_t* bytes, const uint32_t* dtypes, void* out, uint64_t out_bytes,
                   uint32_t out_dtype);
     uint64_t arena_bytes() const { return arena_bytes_; }
+    int clear_scratch();
 
 private:
     friend class Session;
@@ -76,6 +77,7 @@ private:
     cudaGraphExec_t graph_exec_ = nullptr;
     void* pinned_ = nullptr;          // staging for pageable host buffers
     uint64_t pinned_bytes_ = 0;
+    uint64_t captured_launches_ = 0;  // Graph mode: kernels one replay of the captured graph launches
     bool io_in_graph_ = false;        // Graph mode, small I/O: the captured graph copies to and from pinned_
 };
 

@@ -39,6 +39,7 @@ int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu
                            uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
 
 int staged_device_error(int* value);   // synchronises the device
+int* static_error_word_if_resolved();  // error word inside the library image, once an allocation-free call resolved it
 int staged_prepare_device();           // allocates the per-device error word (call outside capture)
 
 // Shape-based selection used by rlxq_matmul / rlxq_workspace_bytes.

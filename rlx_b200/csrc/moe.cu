@@ -34,8 +34,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
     for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0u;
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const float f = expert_idx[i];
-        if (f >= 0.f && f < (float)E) atomicAdd(&cnt[(uint32_t)f], 1u);
+        uint32_t e;
+        if (expert_of_row(expert_idx[i], E, &e)) atomicAdd(&cnt[e], 1u);
     }
     __syncthreads();
     if (threadIdx.x == 0) {                    // E is small (tens to hundreds): a serial scan is enough
@@ -51,8 +51,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
     __threadfence_block();
     // cursor lives in global memory (this CTA is its only user); atomics hand out the slots
     for (uint32_t i = threadIdx.x; i < m; i += blockDim.x) {
-        const float f = expert_idx[i];
-        if (f >= 0.f && f < (float)E) perm[atomicAdd(&cursor[(uint32_t)f], 1u)] = i;
+        uint32_t e;
+        if (expert_of_row(expert_idx[i], E, &e)) perm[atomicAdd(&cursor[e], 1u)] = i;
     }
 }
 
@@ -183,7 +183,7 @@ extern "C" int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const 
     uint32_t* cursor = reinterpret_cast<uint32_t*>(ws + off_cursor);
     uint32_t* perm = reinterpret_cast<uint32_t*>(ws + off_perm);
     const bool xbf = x_dtype == RLXQ_BF16, ybf = y_dtype == RLXQ_BF16;
-    // rows with an id outside [0, num_experts) are in no group: their outputs stay zero
+    // rows with an id of num_experts or more are in no group: their outputs stay zero
     RLXQ_CUDA_TRY(cudaMemsetAsync(y, 0, (size_t)m * n * (ybf ? 2 : 4), s));
     const uint8_t* wst = (const uint8_t*)w_blocks;
     const size_t xes = xbf ? 2 : 4, yes = ybf ? 2 : 4;

@@ -49,8 +49,6 @@ constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
 // costs a handful of instructions however long it lasts; kWaitLimit attempts bound it (seconds).
 constexpr uint32_t kSuspendHintNs = 1000000u;
 constexpr uint32_t kWaitLimit = 1u << 12;
-// Debug switches (StagedParams::debug): measure the streaming pipeline without the arithmetic.
-constexpr uint32_t kDebugSkipMath = 1u, kDebugSkipActivations = 2u;
 
 struct StagedParams {
     const void* x;
@@ -69,7 +67,6 @@ struct StagedParams {
     uint32_t xs_stride;   // halfs between activation rows in shared memory
     uint32_t mp;          // m rounded up to even
     uint32_t off_sxb, off_stage, off_scratch, off_red, off_bar;  // shared-memory layout
-    uint32_t debug;       // kDebug* bits, 0 in production
     uint32_t nstages;     // ring depth (runtime: whatever shared memory is left)
     const __half* xh_ws;  // [m][k] activations as fp16 after the row rescale (written by the converter kernel)
     const float* sxb_ws;  // [k / SUB][mp] block sums * BIAS

@@ -19,7 +19,7 @@ namespace rlxq {
 
 constexpr uint32_t kCommMaxWorld = 8;
 constexpr uint32_t kCommHeader = 256;
-constexpr uint32_t kCommSpinLimit = 1u << 24;      // ~ a few seconds of polling a peer-written flag
+// Polls of a peer-written flag before a rank gives up: option "tp_spin_limit", default 2^24 (a few seconds).
 
 struct CommParams {
     uint8_t* buf[kCommMaxWorld];     // buf[r]: rank r's buffer as mapped in this process (buf[rank] is local)
@@ -27,6 +27,7 @@ struct CommParams {
     float* dst;
     int* err;
     uint32_t rank, world, elems, max_elems;
+    uint32_t spin_limit;
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(1024) tp_allreduce_kernel(const CommParams P) 
         const uint32_t p = threadIdx.x;
         st_release_sys(reinterpret_cast<unsigned long long*>(P.buf[p]) + 1 + P.rank, epoch);
         bool ok = false;
-        for (uint32_t it = 0; it < kCommSpinLimit; ++it) {
+        for (uint32_t it = 0; it < P.spin_limit; ++it) {
             if (ld_acquire_sys(hdr + 1 + p) >= epoch) { ok = true; break; }
         }
         if (!ok) { s_fail = 1; atomicExch(P.err, 40 + (int)p); }
@@ -148,6 +149,7 @@ extern "C" int rlxq_tp_allreduce_sum(rlxq_stream_t stream, uint32_t rank, uint32
         P.buf[r] = reinterpret_cast<uint8_t*>(bufs[r]);
     }
     P.src = src; P.dst = dst; P.rank = rank; P.world = world; P.elems = elems; P.max_elems = max_elems;
+    P.spin_limit = (uint32_t)options().tp_spin_limit.load();
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
     int rc = launch_pdl(tp_allreduce_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, P);

@@ -44,3 +44,14 @@ def assert_within_tolerance(y: np.ndarray, y_ref: np.ndarray, bnd: np.ndarray, t
     assert np.isfinite(y).all(), f"{what}: non-finite output"
     assert worst <= tol, f"{what}: max |y-y_ref|/(|x||w|) = {worst:.3e} > {tol:.1e}"
     return worst
+
+
+def copy_to_device(dst_ptr: int, host: np.ndarray) -> None:
+    """cudaMemcpy of a numpy array to a raw device address (for buffers the library allocated itself)."""
+    import ctypes as C
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    rt.cudaMemcpy.restype = C.c_int
+    host = np.ascontiguousarray(host)
+    rc = rt.cudaMemcpy(dst_ptr, host.ctypes.data, host.nbytes, 1)
+    assert rc == 0, f"cudaMemcpy failed with {rc}"

@@ -159,6 +159,31 @@ def test_malformed_files_are_rejected(tmp_path):
         R.GgufFile(good).tensor_bytes("missing")
 
 
+def test_header_sizes_that_wrap_64_bits_are_rejected(tmp_path):
+    """A crafted count must not wrap the size arithmetic: 2^61 u64 elements are 2^64 bytes = 0 mod 2^64, and
+    dimensions whose product wraps would record a small tensor.  Both are malformed headers."""
+    w = O.fill_weights(O.Q4_K, 1, 256, 2)
+    arr = tmp_path / "arr.gguf"
+    write_gguf(arr, [("w", [256, 2], Q4K, w.tobytes())],
+               meta=[("big", 9, struct.pack("<IQ", 10, 1 << 61))])                   # array of 2^61 u64
+    dims = tmp_path / "dims.gguf"
+    write_gguf(dims, [("w", [1 << 33, 1 << 33], Q4K, w.tobytes())])                  # 2^66 elements
+    for p in (arr, dims):
+        with pytest.raises(R.RlxqError) as e:
+            R.GgufFile(p)
+        assert e.value.status == -10, p.name
+
+
+def test_a_repeated_tensor_name_is_listed_once(tmp_path):
+    a = np.arange(4, dtype=np.float32)
+    b = np.arange(4, 8, dtype=np.float32)
+    p = tmp_path / "dup.gguf"
+    write_gguf(p, [("t", [4], F32, a.tobytes()), ("t", [4], F32, b.tobytes())])
+    f = R.GgufFile(p)
+    assert list(f.keys()) == ["t"] and int(R._lib.lib.rlxq_gguf_tensor_count(f._h)) == 1
+    assert np.array_equal(np.frombuffer(f.tensor_bytes("t"), np.float32), b)     # the later entry wins, as in a map insert
+
+
 @pytest.mark.gpu
 def test_upload_and_matmul_from_a_gguf_file(tmp_path):
     """File -> pinned staging -> device (several staging chunks), then the matmul on the uploaded bytes."""

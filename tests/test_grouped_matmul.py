@@ -37,6 +37,20 @@ def test_oracle_reproduces_the_reference_grouped_test():
     assert not _close(wrong, c)
 
 
+def test_oracle_reads_expert_ids_as_the_reference_cast_does():
+    """`expert_idx[i] as usize` (rlx-cpu/src/gguf_matmul.rs:187,198) saturates: NaN, negatives and fractions
+    below 1 select expert 0, 2.7 selects 2; ids of num_experts and above stay zero rows here."""
+    s, m, k, n, E = O.Q4_0, 6, 256, 5, 3
+    w = O.fill_weights(s, 13, k, n * E)
+    x = O.fill_normal(14, m * k).reshape(m, k)
+    idx = np.array([np.nan, -3.0, 0.9, 2.7, 3.0, 1e30], np.float32)
+    y = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    slab = w.size // E
+    for i, e in enumerate((0, 0, 0, 2)):
+        assert np.array_equal(y[i], O.matmul_bt(x[i:i + 1], w[e * slab:(e + 1) * slab], 1, k, n, s).ravel())
+    assert np.all(y[4:] == 0)
+
+
 def test_oracle_grouped_equals_per_row_matmul():
     s, m, k, n, E = O.Q4_K, 7, 512, 9, 4
     w = O.fill_weights(s, 3, k, n * E)          # E slabs of [n, k] back to back
@@ -137,7 +151,7 @@ def test_gpu_decode_rows_take_the_streaming_gemv(sch, m, k, n, E, x_bf16):
     before = R.launch_count()
     y = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16)
     assert R.launch_count() - before == m                  # one kernel per row, no sort kernel
-    ref = O.grouped_matmul_bt(x, w, np.where(idx < E, idx, -1).astype(np.float32), m, k, n, E, s)
+    ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
     slab = w.size // E
     wn = np.stack([O.row_norms(s, w[e * slab:(e + 1) * slab], k, n) for e in range(E)])
     xn = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
@@ -165,9 +179,15 @@ def test_gpu_grouped_routing_edges():
     y = _gpu(x, w, idx, s, n, E)
     ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
     assert np.allclose(y, ref, rtol=0, atol=2e-5 * np.abs(ref).max() + 1e-6)
-    idx[3], idx[7], idx[11] = 6.0, -1.0, np.nan
+    # the reference's `as usize` cast: negative, fractional and NaN ids mean expert 0; E and above is out of range
+    idx[3], idx[7], idx[11], idx[12], idx[13] = 6.0, -1.0, np.nan, 0.5, 5.9
     y = _gpu(x, w, idx, s, n, E)
-    assert np.all(y[[3, 7, 11]] == 0) and np.any(y[4] != 0)
+    ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    slab = w.size // E
+    for row, e in ((7, 0), (11, 0), (12, 0), (13, 5)):
+        assert np.array_equal(ref[row], O.matmul_bt(x[row:row + 1], w[e * slab:(e + 1) * slab], 1, k, n, s).ravel())
+    assert np.all(y[3] == 0) and np.all(ref[3] == 0) and np.any(y[4] != 0)
+    assert np.allclose(y, ref, rtol=0, atol=2e-5 * np.abs(ref).max() + 1e-6)
     # bf16 output is the rounding of the f32 output
     idx = (np.arange(m) % E).astype(np.float32)
     yf = _gpu(x, w, idx, s, n, E)

@@ -119,6 +119,55 @@ def test_per_rank_cuda_partials_sum_to_the_oracle_ffn(m, world):
     assert np.max(np.abs(y - y_ref) / bnd) < 1e-3        # the path's bound, both layers chained
 
 
+# ------------------------------------------------------------------ configuration 3 at its real shape
+_CFG3 = {}
+
+
+def _cfg3():
+    """The 70B-shaped FFN of configuration 3 (d_model 8192, d_ffn 28672, Q4_K), generated once per test run
+    with the oracle results the cases share: the full FFN for one token and for four sampled rows of a
+    256-token batch."""
+    if not _CFG3:
+        dm, df = 8192, 28672
+        gate, up, down = _weights(dm, df, seed=2000)
+        wn = O.row_norms(O.Q4_K, down, df, dm)
+        x256 = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(78, 256 * dm))).reshape(256, dm)
+        rows = np.array([0, 85, 170, 255])
+        ref = {}
+        for m, xs in ((1, x256[:1]), (256, x256[rows])):
+            y, h = O.ffn_swiglu(np.ascontiguousarray(xs), gate, up, down, xs.shape[0], dm, df, O.Q4_K, O.Q4_K, want_h=True)
+            ref[m] = (y, np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * wn[None, :])
+        _CFG3.update(dm=dm, df=df, gate=gate, up=up, down=down, x=x256, rows=rows, ref=ref)
+    return _CFG3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("m", [1, 256])
+def test_cfg3_real_shape_shards_sum_to_the_oracle_ffn(m, world):
+    """Q4_K, d_model 8192, d_ffn 28672, one token and 256 tokens, split 1 / 2 / 4 / 8 ways: every rank's shard
+    runs through rlxq_tp_ffn_partial on this GPU, the partials are summed in rank order
+    (rlx-driver/src/collective.rs:107-127) and compared with the oracle FFN -- every output for one token,
+    four sampled token rows (rows are independent) for 256.  The 8-way down projection has k = 3584."""
+    import torch
+    c = _cfg3()
+    dm, df = c["dm"], c["df"]
+    x = c["x"][:m]
+    xd = torch.from_numpy(np.ascontiguousarray(x)).cuda().to(torch.bfloat16)
+    parts = []
+    for r in range(world):
+        ffn = tp.TensorParallelFFN(O.Q4_K, dm, df, rank=r, world=world)
+        ffn.load(c["gate"], c["up"], c["down"])
+        parts.append(ffn.partial(xd).cpu().numpy())
+        del ffn
+    R.device_status()
+    y = O.allreduce_sum(np.stack(parts))
+    y_ref, bnd = c["ref"][m]
+    sel = np.arange(1) if m == 1 else c["rows"]
+    assert np.isfinite(y).all()
+    assert np.max(np.abs(y[sel].astype(np.float64) - y_ref) / bnd) < 1e-3   # the path's bound, both layers chained
+
+
 # ------------------------------------------------------------------ peer-memory all-reduce (needs two GPUs)
 def _peer_worker(rank, world, port, out_dir):
     import torch
@@ -191,3 +240,51 @@ def test_peer_memory_all_reduce_two_gpus(tmp_path):
     for rep in range(3):
         for r in range(world):
             assert np.array_equal(got[r][f"graph{rep}"], want), (rep, r)
+
+
+# ------------------------------------------------------------------ a bounded wait that runs out (one GPU)
+@pytest.mark.gpu
+def test_peer_all_reduce_wait_runs_out_and_the_context_stays_usable():
+    """rlxq_tp_allreduce_sum with world = 2 where the "peer" is a second buffer on the same GPU whose flag nobody
+    raises: with a short poll limit the kernel gives up, leaves dst alone and records 40 + peer rank;
+    rlxq_device_status turns that into RLXQ_E_TIMEOUT, and the next call (the peer's flag and data now written
+    by the host, as a live peer would) completes normally.  Nothing faults and nothing hangs: the wait is a
+    counted loop of plain loads."""
+    import ctypes as C
+    import torch
+    from rlx_b200._lib import lib
+    from tests.helpers import copy_to_device
+    n = 1024
+    bufs = []
+    for _ in range(2):
+        p = C.c_void_p()
+        assert lib.rlxq_tp_comm_alloc(n, C.byref(p)) == 0
+        bufs.append(p.value)
+    arr = (C.c_void_p * 2)(*bufs)
+    src = torch.from_numpy(O.fill_normal(1, n)).cuda()
+    dst = torch.full((n,), 7.0, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    code = C.c_int(0)
+    assert lib.rlxq_device_status(C.byref(code)) == 0          # clean before
+    R.set_option("tp_spin_limit", 1 << 12)
+    try:
+        assert lib.rlxq_tp_allreduce_sum(stream, 0, 2, arr, n, src.data_ptr(), dst.data_ptr(), n) == 0
+        st = lib.rlxq_device_status(C.byref(code))
+        assert st == -8 and code.value == 41, (st, code.value)  # RLXQ_E_TIMEOUT, waiting for rank 1
+        assert torch.all(dst == 7.0)                             # the sum never ran
+        assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0   # reported once, then clear
+        # now play the peer from the host: its partial in both data slots, its flag far ahead of any epoch
+        peer = O.fill_normal(2, n)
+        hdr = 256
+        raw = np.zeros(hdr + 2 * n * 4, np.uint8)
+        raw[hdr:] = np.concatenate([peer, peer]).view(np.uint8)
+        copy_to_device(bufs[1], raw)
+        copy_to_device(bufs[0] + 8 * (1 + 1), np.array([1 << 40], np.int64))
+        assert lib.rlxq_tp_allreduce_sum(stream, 0, 2, arr, n, src.data_ptr(), dst.data_ptr(), n) == 0
+        assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0
+        want = O.allreduce_sum(np.stack([src.cpu().numpy(), peer]))
+        assert np.array_equal(dst.cpu().numpy(), want)
+    finally:
+        R.set_option("tp_spin_limit", 1 << 24)
+        for b in bufs:
+            lib.rlxq_tp_comm_free(b)

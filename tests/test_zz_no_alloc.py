@@ -11,15 +11,18 @@ every other test.  The test calls the new entry point through the C ABI twice in
 call reuses the array with the first call's leftovers in it) and compares each result with what the
 existing entry point gives for the same inputs.  Both run the same two kernels with the same plan,
 so the results are expected to be identical; the assertion uses the tolerance of the other GEMV
-tests (2e-5 of |x| |w_row|) and additionally reports exact equality.
+tests (2e-5 of |x| |w_row|) and additionally reports exact equality.  Because a fault common to both
+entry points would pass that comparison, each result is also held against the CPU oracle.
 """
+import ctypes as C
+
 import numpy as np
 import pytest
 
 import rlx_b200 as R
 from rlx_b200._lib import lib
 from oracle import oracle as O
-from tests.helpers import bound, make_case
+from tests.helpers import assert_within_tolerance, bound, make_case
 
 pytestmark = pytest.mark.gpu
 
@@ -59,6 +62,20 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(sch, m, k, 
         err = np.abs(g.astype(np.float64) - wnt.astype(np.float64)) / bound(s, w, x, n)
         assert err.max() <= 2e-5, f"{sch}: static-scratch result differs from rlxq_matmul by {err.max():.2e}"
         assert np.array_equal(g, wnt), f"{sch}: same kernels, same plan: results should be identical"
+        ref = O.matmul_bt_mt(x, w, m, k, n, s)
+        assert_within_tolerance(g, ref, bound(s, w, x, n), tol=2e-5, what=f"static scratch vs oracle {sch}")
+
+
+def test_static_scratch_timeouts_are_visible_to_device_status():
+    """rlxq_device_status covers the error word this entry point uses, whichever it is: after a clean call it
+    reports no error, and it can be called by a process that has made allocation-free calls only."""
+    import torch
+    s, m, k, n = O.Q4_0, 1, 2048, 64
+    w, x = make_case(s, m, k, n, seed=5)
+    y = _static(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, n, torch.float32)
+    code = C.c_int(-1)
+    assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0
+    assert_within_tolerance(y.cpu().numpy(), O.matmul_bt_mt(x, w, m, k, n, s), bound(s, w, x, n), tol=2e-5)
 
 
 def test_static_scratch_bf16_in_and_out():
