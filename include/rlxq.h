@@ -86,7 +86,7 @@ RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t
 /* Replaces dequant_gguf_scratch_bytes (rlx-cuda/src/gguf_gpu.rs:35-59) at plan time: the
  * scratch rlxq_matmul needs for this shape.  For m <= 8 that is the converted activations
  * (a few bytes per element of x), the partial output tiles of CTAs that share a row tile and
- * their counters: tens to hundreds of KiB.  The tensor-core GEMM needs none for most shapes; for few
+ * their counters: tens to hundreds of KiB (up to 4.9 MB while the option gemv_kernel is 4).  The tensor-core GEMM needs none for most shapes; for few
  * output tiles and a long k it asks for two partial 128 x 256 f32 tiles per SM (39 MB on a 148-SM
  * part) for its stream-K split; without them it runs whole tiles.  The reference reserves k*n*4 bytes. */
 RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
@@ -163,7 +163,10 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  * RLX_CUDA_* environment keys (rlx-ir/src/env.rs:57-104).  Keys:
  *   "gemv_kernel": 0 = automatic (integer kernel for m <= 2, tensor-mode kernel for m <= 8),
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
- *                  GEMV, 3 = force the staged integer GEMV (m <= 4; 2, 3: error if the shape does not allow it)
+ *                  GEMV, 3 = force the staged integer GEMV (m <= 4), 4 = force the tcgen05 GEMV (m <= 8; Q4_0, Q8_0,
+ *                  Q4_K; k a multiple of 256).  2, 3, 4: error if the shape does not allow it.  The tcgen05 GEMV is
+ *                  correct but slower than the other two on the shapes measured so far, hence not automatic.
+ *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
  *   "gemm_streamk": 0 = automatic (split the k dimension across SMs when that saves at least 36
  *                  256-wide k steps on the busiest SM and a workspace is given), 1 = never,

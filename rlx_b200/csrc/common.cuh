@@ -31,6 +31,7 @@ struct Options {
     std::atomic<int64_t> gemv_inline_q{0};
     std::atomic<int64_t> gemv_early{2};
     std::atomic<int64_t> tp_spin_limit{1 << 24};
+    std::atomic<int64_t> gemv_tc_ctas{2};
 };
 Options& options();
 

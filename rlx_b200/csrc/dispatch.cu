@@ -16,7 +16,9 @@ size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t 
         const size_t a = staged_workspace_bytes(scheme, m, k, n);
         // (batch 5-8 of a format that only has the integer kernel runs it twice, four rows at a time)
         const size_t b = int_workspace_bytes(scheme, m <= 4 ? m : 4, k, n);
-        return a > b ? a : b;
+        // the tcgen05 GEMV (8-byte words for the parts of cut tiles) only runs when it is asked for
+        const size_t c = options().gemv_kernel.load() == 4 ? gemv_tc_workspace_bytes(scheme, m, k, n) : 0;
+        return a > b ? (a > c ? a : c) : (b > c ? b : c);
     }
     return gemm_tc_workspace_bytes(m, k, n);      // partial tiles of the stream-K split, when the shape wants it
 }
@@ -39,6 +41,11 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
         const int64_t force = options().gemv_kernel.load();
         const bool can_int = m <= 4 && int_supported(scheme, m, k, n, w, x);
         const bool can_tc = staged_supported(scheme, m, k, n, w, x, xbf);
+        const bool can_tcg = gemv_tc_supported(scheme, m, k, n, w, x, xbf);
+        if (force == 4) {
+            if (!can_tcg) return fail(RLXQ_E_SHAPE, "tensor-core GEMV does not support scheme %u m=%u k=%u n=%u (or 16-byte alignment)", scheme, m, k, n);
+            return launch_gemv_tc(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        }
         if (force == 3 && !can_int)
             return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
         if (force == 2 && !can_tc)

@@ -329,3 +329,54 @@ def test_launch_counter_counts_kernels():
     before = R.launch_count()
     R.matmul(x, wd, s, 16)
     assert R.launch_count() == before + 1      # integer GEMV, single-kernel mode
+
+
+# ------------------------------------------------------------------ the tcgen05 GEMV (opt-in, gemv_kernel = 4)
+TC_GEMV_SHAPES = [("q8_0", 1, 256, 128, False, False), ("q8_0", 1, 256, 100, False, False), ("q4_0", 2, 1024, 300, False, False),
+                  ("q4_k", 3, 2048, 1000, False, False), ("q4_0", 1, 4096, 11008, False, False),
+                  ("q4_0", 8, 11008, 4096, False, False), ("q8_0", 5, 4096, 4096, True, False),
+                  ("q4_k", 1, 4096, 14336, True, False), ("q4_k", 7, 8192, 3000, False, True),
+                  ("q4_0", 4, 4096, 11008, True, True)]
+
+
+@pytest.mark.parametrize("ctas", [2, 1])
+@pytest.mark.parametrize("sch,m,k,n,x_bf16,y_bf16", TC_GEMV_SHAPES)
+def test_tensor_core_gemv_matches_oracle(sch, m, k, n, x_bf16, y_bf16, ctas):
+    """The tcgen05 decode GEMV: weights as fp16(d * q) in tensor memory (one rounding of 2^-12 per weight),
+    activations as two fp16 limbs.  Held to min(1e-3, 4e-3 / sqrt(k)) of ||x|| ||w_row|| (1e-3 with a bf16
+    output); both CTA counts per SM, so short ranges (direct activation loads) and long ones (staging ring)
+    and tiles cut between two and many contributors are all exercised, twice in a row on the same scratch."""
+    import torch
+    s = O.SCHEMES[sch]
+    w, x = make_case(s, m, k, n, seed=900 + n + m, x_bf16=x_bf16)
+    R.set_option("gemv_kernel", 4)
+    R.set_option("gemv_tc_ctas", ctas)
+    try:
+        wd = torch.from_numpy(w).cuda()
+        xd = torch.from_numpy(x).cuda()
+        if x_bf16:
+            xd = xd.to(torch.bfloat16)
+        ws = torch.empty(R.workspace_bytes(s, m, k, n, 1 if x_bf16 else 0, 1 if y_bf16 else 0) + 16, dtype=torch.uint8, device="cuda")
+        outs = []
+        for _ in range(2):
+            before = R.launch_count()
+            y = R.matmul(xd, wd, s, n, out_dtype=torch.bfloat16 if y_bf16 else torch.float32, workspace=ws)
+            assert R.launch_count() - before == 1                 # one kernel, no prepass
+            outs.append(y.float().cpu().numpy())
+        R.device_status()
+    finally:
+        R.set_option("gemv_tc_ctas", 2)
+    assert np.array_equal(outs[0], outs[1])                       # same bits from run to run
+    ref = reference(s, w, x, n)
+    tol = 1e-3 if y_bf16 else min(1e-3, 4e-3 / np.sqrt(k))       # a bf16 output carries its own rounding of |y| * 2^-9
+    assert_within_tolerance(outs[0], ref, bound(s, w, x, n), tol=tol, what=f"tcgen05 gemv {sch} m={m} k={k} n={n}")
+
+
+def test_tensor_core_gemv_refuses_what_it_cannot_run():
+    import torch
+    R.set_option("gemv_kernel", 4)
+    s = O.Q6_K                                                   # no decoder for this format in this kernel
+    w, x = make_case(s, 1, 2048, 16, seed=3)
+    with pytest.raises(R.RlxqError) as e:
+        R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
+    assert e.value.status == -2
