@@ -178,6 +178,8 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *   "gemv_kslices": 0 = automatic, n > 0 = split k over n CTAs per row tile in the staged GEMV
  *   "tp_spin_limit": polls of a peer's flag before rlxq_tp_allreduce_sum's kernel gives up and reports
  *          RLXQ_E_TIMEOUT (device_error = 40 + the peer's rank); default 2^24, a few seconds
+ *   "graph_fuse_ffn": 1 (default) = the Session mirror lowers a SwiGLU FFN pattern to the fused form (rlxq_session.h),
+ *          0 = every node runs as its own kernels
  *   "pdl": 1 (default) = launch the GEMV kernels with programmatic stream serialization so a
  *          kernel's weight prefetch overlaps the tail of its predecessor, 0 = plain launches
  * Returns RLXQ_E_ARG for an unknown key. */

@@ -88,6 +88,14 @@ RLXQ_API int rlxq_compiled_run_typed(rlxq_compiled* c, uint32_t n_inputs, const 
 /* Bytes of device memory the compiled graph holds (arena incl. workspace). */
 RLXQ_API uint64_t rlxq_compiled_arena_bytes(const rlxq_compiled* c);
 
+/* How many SwiGLU FFNs the compiler recognised and fused in this graph: gate = dequant_matmul(x, Wg),
+ * up = dequant_matmul(x, Wu), h = swiglu_mul(gate, up), y = dequant_matmul(h, Wd), all f32, with the three
+ * intermediate values used nowhere else.  Such a group runs as one matmul over the stacked [Wg ; Wu] (their arena
+ * slots are placed back to back), the product up * silu(gate) formed inside the down projection's activation
+ * step, and the down projection: what rlxq_tp_ffn_partial does for one rank.  The reference's CUDA backend
+ * fuses the product as FusedSwiGLU (rlx-cuda/src/unfuse.rs:254-293).  Option "graph_fuse_ffn" = 0 turns it off. */
+RLXQ_API uint32_t rlxq_compiled_fused_ffn_count(const rlxq_compiled* c);
+
 /* Zeroes the kernels' scratch region of the arena (not the params, inputs or outputs) and waits for it.
  * Call it after rlxq_device_status reported RLXQ_E_TIMEOUT and before the next run: a wait that ran out
  * can leave a half-finished tile exchange behind.  The reference has no counterpart: its executable

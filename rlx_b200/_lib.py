@@ -79,6 +79,7 @@ _SIGS = {
                                           C.POINTER(u32), vp, u64, u32]),
     "rlxq_compiled_arena_bytes": (u64, [vp]),
     "rlxq_compiled_clear_scratch": (C.c_int, [vp]),
+    "rlxq_compiled_fused_ffn_count": (u32, [vp]),
 }
 
 

@@ -318,6 +318,10 @@ class CompiledGraph:
     def arena_bytes(self) -> int:
         return int(lib.rlxq_compiled_arena_bytes(self._h))
 
+    def fused_ffn_count(self) -> int:
+        """SwiGLU FFN groups the compiler fused (stacked gate / up matmul + down projection with the product inside)."""
+        return int(lib.rlxq_compiled_fused_ffn_count(self._h))
+
     def clear_scratch(self) -> None:
         """Zeroes the kernels' scratch region; the step to take after device_status() raised a timeout."""
         check(lib.rlxq_compiled_clear_scratch(self._h))

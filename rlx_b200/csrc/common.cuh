@@ -32,6 +32,7 @@ struct Options {
     std::atomic<int64_t> gemv_early{2};
     std::atomic<int64_t> tp_spin_limit{1 << 24};
     std::atomic<int64_t> gemv_tc_ctas{2};
+    std::atomic<int64_t> graph_fuse_ffn{1};
 };
 Options& options();
 

@@ -6,6 +6,7 @@
 
 #include "../../../include/rlxq_session.h"
 #include "../../../include/rlxq_moe.h"
+#include "../../../include/rlxq_tp.h"
 #include "../common.cuh"
 #include "../kernels.h"
 
@@ -106,6 +107,41 @@ int Graph::set_output(int node) {
     return RLXQ_OK;
 }
 
+// The SwiGLU FFN pattern (rlx-flow/src/blocks/swiglu.rs:48-52; the reference's CUDA backend fuses the product as
+// `FusedSwiGLU`, rlx-cuda/src/unfuse.rs:254-293): gate = dequant_matmul(x, Wg), up = dequant_matmul(x, Wu) on the same x
+// with the same scheme and width, h = swiglu_mul(gate, up), y = dequant_matmul(h, Wd), all f32, none of the three
+// intermediate values read by anything else or returned.
+void CompiledGraph::find_fused_ffns() {
+    const int nn = (int)nodes_.size();
+    fused_role_.assign(nn, -1);
+    fused_index_.assign(nn, -1);
+    if (!options().graph_fuse_ffn.load()) return;
+    std::vector<int> uses(nn, 0);
+    for (const Node& nd : nodes_)
+        for (int in : {nd.in0, nd.in1, nd.in2})
+            if (in >= 0) ++uses[in];
+    if (output_ >= 0) ++uses[output_];
+    for (int d = 0; d < nn; ++d) {
+        const Node& dn = nodes_[d];
+        if (dn.op != OpKind::DequantMatMul || dn.dtype != RLXQ_F32 || dn.in0 < 0) continue;
+        const int s = dn.in0;
+        const Node& sn = nodes_[s];
+        if (sn.op != OpKind::SwigluMul || uses[s] != 1 || fused_role_[s] != -1) continue;
+        const int gm = sn.in0, um = sn.in1;
+        const Node& gn = nodes_[gm];
+        const Node& un = nodes_[um];
+        if (gm == um || gn.op != OpKind::DequantMatMul || un.op != OpKind::DequantMatMul) continue;
+        if (uses[gm] != 1 || uses[um] != 1 || fused_role_[gm] != -1 || fused_role_[um] != -1) continue;
+        if (gn.in0 != un.in0 || gn.scheme != un.scheme || gn.cols != un.cols || gn.dtype != RLXQ_F32 || un.dtype != RLXQ_F32) continue;
+        if (gn.in1 == un.in1 || uses[gn.in1] != 1 || uses[un.in1] != 1) continue;     // the two weights become one stacked slot
+        if (nodes_[gn.in1].bytes % 256) continue;                                      // up must start where gate ends, aligned
+        fused_index_[d] = (int)fused_.size();
+        fused_.push_back({gm, um, s, d});
+        fused_role_[gm] = fused_role_[um] = fused_role_[s] = 0;
+        fused_role_[d] = 1;
+    }
+}
+
 // ------------------------------------------------------------------ Session::compile
 int Session::compile(const Graph& g, ExecMode mode, CompiledGraph** out) {
     if (!out) return fail(RLXQ_E_NULL, "out is null");
@@ -128,11 +164,40 @@ int Session::compile(const Graph& g, ExecMode mode, CompiledGraph** out) {
     c->mode_ = mode;
     c->nodes_ = g.nodes();
     c->output_ = g.output();
+    c->find_fused_ffns();
+    // a fused FFN reads [gate rows ; up rows] as one weight: the up param's slot follows the gate param's directly
+    std::vector<int> follows(c->nodes_.size(), -1);       // node -> the node whose slot it must follow
+    std::vector<char> deferred(c->nodes_.size(), 0);
+    for (const auto& f : c->fused_) {
+        const int wg = c->nodes_[f.gate_mm].in1, wu = c->nodes_[f.up_mm].in1;
+        follows[wu] = wg;
+        deferred[wu] = 1;
+    }
     uint64_t off = 0, ws = 0, stage = 0;
-    for (const Node& nd : c->nodes_) {
-        c->offsets_.push_back(off);
+    c->offsets_.assign(c->nodes_.size(), 0);
+    for (size_t ni = 0; ni < c->nodes_.size(); ++ni) {
+        const Node& nd = c->nodes_[ni];
+        if (deferred[ni]) continue;                        // placed right behind its gate param below
+        c->offsets_[ni] = off;
         off += align_up(nd.bytes ? nd.bytes : 1, 256);
-        if (nd.op == OpKind::DequantMatMul) {
+        for (size_t nj = 0; nj < c->nodes_.size(); ++nj)
+            if (follows[nj] == (int)ni) {
+                c->offsets_[nj] = c->offsets_[ni] + nd.bytes;      // nd.bytes is a multiple of 256 (checked when fusing)
+                off = c->offsets_[nj] + align_up(c->nodes_[nj].bytes ? c->nodes_[nj].bytes : 1, 256);
+            }
+    }
+    for (size_t ni = 0; ni < c->nodes_.size(); ++ni) {
+        const Node& nd = c->nodes_[ni];
+        if (c->fused_role_[ni] == 1) {
+            const auto& f = c->fused_[c->fused_index_[ni]];
+            const Node& gn = c->nodes_[f.gate_mm];
+            const Node& xn = c->nodes_[gn.in0];
+            size_t need = 0;
+            rc = rlxq_tp_ffn_workspace_bytes(gn.scheme, nd.scheme, nd.rows, xn.cols, gn.cols, xn.dtype, &need);
+            if (rc) { delete c; return rc; }
+            if (need > ws) ws = need;
+        }
+        if (nd.op == OpKind::DequantMatMul && c->fused_role_[ni] == -1) {
             size_t need = 0;
             const Node& xn = c->nodes_[nd.in0];
             rc = rlxq_workspace_bytes(nd.scheme, nd.rows, xn.cols, nd.cols, xn.dtype, nd.dtype, &need);
@@ -204,6 +269,17 @@ CompiledGraph::~CompiledGraph() {
 int CompiledGraph::enqueue_steps(cudaStream_t s) {
     for (size_t i = 0; i < nodes_.size(); ++i) {
         const Node& nd = nodes_[i];
+        if (fused_role_[i] == 0) continue;          // computed inside the fused FFN below
+        if (fused_role_[i] == 1) {
+            const FusedFfn& f = fused_[fused_index_[i]];
+            const Node& gn = nodes_[f.gate_mm];
+            const Node& xn = nodes_[gn.in0];
+            int rc = rlxq_tp_ffn_partial((rlxq_stream_t)s, gn.scheme, nd.scheme, arena_ + offsets_[gn.in0], xn.dtype,
+                                         arena_ + offsets_[gn.in1], arena_ + offsets_[nd.in1], (float*)(arena_ + offsets_[i]),
+                                         nd.rows, xn.cols, gn.cols, arena_ + ws_off_, ws_bytes_);
+            if (rc) return rc;
+            continue;
+        }
         if (nd.op == OpKind::DequantMatMul) {
             const Node& xn = nodes_[nd.in0];
             int rc = rlxq_matmul((rlxq_stream_t)s, nd.scheme, arena_ + offsets_[nd.in0], xn.dtype,
@@ -394,6 +470,8 @@ int rlxq_compiled_run_typed(rlxq_compiled* c, uint32_t n_inputs, const char* con
 }
 
 uint64_t rlxq_compiled_arena_bytes(const rlxq_compiled* c) { return c ? c->c->arena_bytes() : 0; }
+
+uint32_t rlxq_compiled_fused_ffn_count(const rlxq_compiled* c) { return c ? c->c->fused_ffn_count() : 0; }
 
 int rlxq_compiled_clear_scratch(rlxq_compiled* c) {
     if (!c) return fail(RLXQ_E_NULL, "null argument");

@@ -59,11 +59,20 @@ public:
                   uint32_t out_dtype);
     uint64_t arena_bytes() const { return arena_bytes_; }
     int clear_scratch();
+    uint32_t fused_ffn_count() const { return (uint32_t)fused_.size(); }
 
 private:
     friend class Session;
     CompiledGraph() = default;
     int enqueue_steps(cudaStream_t s);
+    void find_fused_ffns();
+
+    // down(up(x) * silu(gate(x))) recognised at compile time and lowered to one stacked gate / up matmul, the
+    // SwiGLU product formed inside the down projection's activation step, and the down projection.
+    struct FusedFfn { int gate_mm, up_mm, swiglu, down_mm; };
+    std::vector<FusedFfn> fused_;
+    std::vector<int> fused_role_;     // per node: -1 not fused, 0 absorbed (nothing to launch), 1 the down matmul of fused_[idx]
+    std::vector<int> fused_index_;
 
     int device_ = 0;
     ExecMode mode_ = ExecMode::Stream;

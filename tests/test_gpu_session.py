@@ -113,6 +113,66 @@ def test_swiglu_ffn_graph_matches_oracle():
     assert_within_tolerance(y, y_ref, bnd, what="ffn")
 
 
+@pytest.mark.parametrize("m,dm,df,x_bf16", [(1, 8192, 28672, True), (2, 1024, 4096, False), (1, 512, 1024, False), (16, 1024, 2048, True)])
+def test_swiglu_ffn_graph_is_fused_and_matches_the_unfused_graph(m, dm, df, x_bf16):
+    """The five-node FFN is lowered to the fused form: fewer kernels per run, and both lowerings agree with the
+    oracle FFN to the path's tolerance; the 70B-shaped layer of the tensor-parallel configuration included."""
+    gw = O.fill_weights(O.Q4_K, 11, dm, df)
+    uw = O.fill_weights(O.Q4_K, 12, dm, df)
+    dw = O.fill_weights(O.Q4_K, 13, df, dm)
+    x = O.fill_normal(14, m * dm).reshape(m, dm)
+    if x_bf16:
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)).reshape(m, dm)
+
+    def build():
+        g = Graph("ffn")
+        xi = g.input("x", [m, dm], DType.BF16 if x_bf16 else DType.F32)
+        pg, pu, pd = g.param("gate", [len(gw)]), g.param("up", [len(uw)]), g.param("down", [len(dw)])
+        gate = g.dequant_matmul_packed(xi, pg, QuantScheme.GgufQ4K, df)
+        up = g.dequant_matmul_packed(xi, pu, QuantScheme.GgufQ4K, df)
+        g.set_outputs([g.dequant_matmul_packed(g.swiglu_mul(gate, up), pd, QuantScheme.GgufQ4K, dm)])
+        c = Session(Device.Cuda, exec_mode="graph").compile(g)
+        for nm, arr in (("gate", gw), ("up", uw), ("down", dw)):
+            c.set_param_typed(nm, arr, DType.U8)
+        return c
+
+    def run(c):
+        xin = O.f32_to_bf16_bits(x) if x_bf16 else x
+        before = R.launch_count()
+        y = c.run_typed([("x", xin, DType.BF16 if x_bf16 else DType.F32)], (m, dm), DType.F32)
+        return y, R.launch_count() - before
+
+    fused = build()
+    assert fused.fused_ffn_count() == 1
+    y_f, launches_f = run(fused)
+    R.set_option("graph_fuse_ffn", 0)
+    try:
+        plain = build()
+    finally:
+        R.set_option("graph_fuse_ffn", 1)
+    assert plain.fused_ffn_count() == 0
+    y_p, launches_p = run(plain)
+    R.device_status()
+    assert launches_f < launches_p, (launches_f, launches_p)
+    y_ref, h_ref = O.ffn_swiglu(x, gw, uw, dw, m, dm, df, O.Q4_K, O.Q4_K, want_h=True)
+    bnd = bound(O.Q4_K, dw, h_ref, dm)
+    assert_within_tolerance(y_f, y_ref, bnd, what="fused ffn")
+    assert_within_tolerance(y_p, y_ref, bnd, what="unfused ffn")
+
+
+def test_ffn_pattern_is_not_fused_when_an_intermediate_value_is_used_elsewhere():
+    dm, df, m = 512, 1024, 1
+    g = Graph("ffn2")
+    xi = g.input("x", [m, dm])
+    pg, pu = g.param("gate", [R.packed_bytes(0, dm, df)]), g.param("up", [R.packed_bytes(0, dm, df)])
+    gate = g.dequant_matmul_packed(xi, pg, QuantScheme.GgufQ4K, df)
+    up = g.dequant_matmul_packed(xi, pu, QuantScheme.GgufQ4K, df)
+    h = g.swiglu_mul(gate, up)
+    g.set_outputs([h])                       # the product itself is the output: nothing to fuse into
+    c = Session(Device.Cuda).compile(g)
+    assert c.fused_ffn_count() == 0
+
+
 def test_run_errors():
     s, m, k, n = O.Q8_0, 1, 256, 8
     w, x = make_case(s, m, k, n, seed=2)
