@@ -83,6 +83,36 @@ RLXQ_API int rlxq_tp_ipc_close(void* buf);
 RLXQ_API int rlxq_tp_allreduce_sum(rlxq_stream_t stream, uint32_t rank, uint32_t world, void* const* bufs,
                                    uint32_t max_elems, const float* src, float* dst, uint32_t elems);
 
+/* ---- the whole layer from one host thread: create / load / run / destroy ----
+ *
+ * For a host that drives all GPUs of a node from one process (the reference's CudaExecutable lives in one
+ * process; rlx-cuda/src/device.rs:44-60 is what would grow a device list).  No counterpart in the reference.
+ * The library owns what it creates here: one stream per device, the shards, scratch that grows with the largest
+ * batch seen, the peer buffers of the decode-sized all-reduce, and (created on the first prefill-sized step) one
+ * NCCL communicator per device; libnccl.so.2 is loaded at run time, so the library has no link-time dependency
+ * on it and a host that only ever runs decode batches never touches it.
+ *
+ * rlxq_tp_create: devs = ndev device ordinals (null: 0 .. ndev-1), 1 <= ndev <= 8.  Enables peer access between
+ *   them where the hardware allows it.
+ * rlxq_tp_ffn_load: gate, up [d_ffn, d_model] and down [d_model, d_ffn] as packed blocks in HOST memory; every
+ *   device receives its shard (rlxq_tp_shard_plan) with one upload per tensor.  May be called again to replace
+ *   the weights.
+ * rlxq_tp_ffn_run: x [m, d_model] (f32 or bf16) and y [m, d_model] (f32) in HOST memory.  Per device: copy of x,
+ *   rlxq_tp_ffn_partial, then the sum of the partials -- rlxq_tp_allreduce_sum when m * d_model <= 65536 and every
+ *   device can read its peers, NCCL's all-reduce otherwise -- and device 0's result back to y.  Returns after all
+ *   devices have finished.  RLXQ_E_NCCL when NCCL is needed and cannot be loaded or fails.  Allocates on the first
+ *   call for a batch size (and for any larger one later): not for use inside a stream capture.
+ * rlxq_tp_status: rlxq_device_status on every device of the group.
+ * One thread at a time per handle. */
+typedef struct rlxq_tp rlxq_tp;
+RLXQ_API int rlxq_tp_create(int ndev, const int* devs, rlxq_tp** out);
+RLXQ_API int rlxq_tp_world(const rlxq_tp* t);
+RLXQ_API int rlxq_tp_ffn_load(rlxq_tp* t, uint32_t scheme, const void* gate, const void* up, const void* down,
+                              uint32_t d_model, uint32_t d_ffn);
+RLXQ_API int rlxq_tp_ffn_run(rlxq_tp* t, const void* x_host, uint32_t x_dtype, uint32_t m, float* y_host);
+RLXQ_API int rlxq_tp_status(rlxq_tp* t, int* device_error);
+RLXQ_API int rlxq_tp_destroy(rlxq_tp* t);
+
 #ifdef __cplusplus
 }
 #endif

@@ -142,6 +142,44 @@ class PeerAllReduce:
         self.available = False
 
 
+class TensorParallelGroup:
+    """The whole layer driven from this process: rlxq_tp_create / rlxq_tp_ffn_load / rlxq_tp_ffn_run / rlxq_tp_destroy.
+    Host buffers in, host buffers out; the library owns streams, shards, scratch and communicators."""
+
+    def __init__(self, devices=None, ndev: int | None = None):
+        devs = list(devices) if devices is not None else list(range(ndev or 1))
+        arr = (C.c_int * len(devs))(*devs)
+        h = C.c_void_p()
+        check(lib.rlxq_tp_create(len(devs), arr, C.byref(h)))
+        self._h = h.value
+        self.world = int(lib.rlxq_tp_world(self._h))
+        self.d_model = self.d_ffn = 0
+
+    def load(self, scheme: int, gate: np.ndarray, up: np.ndarray, down: np.ndarray, d_model: int, d_ffn: int) -> None:
+        g, u, d = (np.ascontiguousarray(a, np.uint8) for a in (gate, up, down))
+        check(lib.rlxq_tp_ffn_load(self._h, int(scheme), g.ctypes.data, u.ctypes.data, d.ctypes.data, d_model, d_ffn))
+        self.d_model, self.d_ffn = d_model, d_ffn
+
+    def run(self, x: np.ndarray, bf16: bool = False) -> np.ndarray:
+        """x: [m, d_model] float32, or uint16 bf16 bit patterns with bf16=True; returns [m, d_model] float32."""
+        x = np.ascontiguousarray(x, np.uint16 if bf16 else np.float32)
+        m = x.shape[0]
+        y = np.empty((m, self.d_model), np.float32)
+        check(lib.rlxq_tp_ffn_run(self._h, x.ctypes.data, 1 if bf16 else 0, m, y.ctypes.data))
+        return y
+
+    def status(self) -> None:
+        code = C.c_int(0)
+        check(lib.rlxq_tp_status(self._h, C.byref(code)))
+
+    def close(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib.rlxq_tp_destroy(h)
+
+    __del__ = close
+
+
 class TensorParallelFFN:
     def __init__(self, scheme: int, d_model: int, d_ffn: int, rank: int = 0, world: int = 1, device=None,
                  group=None):

@@ -288,3 +288,52 @@ def test_peer_all_reduce_wait_runs_out_and_the_context_stays_usable():
         R.set_option("tp_spin_limit", 1 << 24)
         for b in bufs:
             lib.rlxq_tp_comm_free(b)
+
+
+# ------------------------------------------------------------------ the C-ABI lifecycle: create / load / run / destroy
+def test_tp_create_without_a_device_fails_loudly():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    with pytest.raises(R.RlxqError) as e:
+        tp.TensorParallelGroup(ndev=1)
+    assert e.value.status == -6                      # RLXQ_E_CUDA: there is no CPU path behind this entry point
+    with pytest.raises(R.RlxqError) as e:
+        tp.TensorParallelGroup(ndev=9)
+    assert e.value.status == -10
+
+
+def _group_case(world, dm, df, ms):
+    gate, up, down = _weights(dm, df, seed=40)
+    g = tp.TensorParallelGroup(ndev=world)
+    assert g.world == world
+    g.load(O.Q4_K, gate, up, down, dm, df)
+    wn = O.row_norms(O.Q4_K, down, df, dm)
+    for m in ms:
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(50 + m, m * dm))).reshape(m, dm)
+        for bf16 in (False, True):
+            y = g.run(O.f32_to_bf16_bits(x).reshape(m, dm) if bf16 else x, bf16=bf16)
+            g.status()
+            y_ref, h = O.ffn_swiglu(x, gate, up, down, m, dm, df, O.Q4_K, O.Q4_K, want_h=True)
+            bnd = np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * wn[None, :]
+            assert np.isfinite(y).all()
+            assert np.max(np.abs(y - y_ref) / bnd) < 1e-3, (world, m, bf16)
+        y2 = g.run(x)                                 # the same bits from run to run
+        assert np.array_equal(y2, g.run(x))
+    g.close()
+
+
+@pytest.mark.gpu
+def test_tp_lifecycle_one_device():
+    """rlxq_tp_create / ffn_load / ffn_run / destroy with a single device: host buffers in and out, no collective."""
+    _group_case(1, 1024, 4096, (1, 2, 16))
+
+
+@pytest.mark.gpu
+def test_tp_lifecycle_two_devices():
+    """Two GPUs driven from this process: one token and 64 tokens take the peer-memory all-reduce (m * d_model up to
+    65536 values), 128 tokens NCCL's."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _group_case(2, 1024, 4096, (1, 64, 128))
