@@ -257,7 +257,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 
 
 def workload_config(args, sch, layers, act, rotation):
-    return {"workload": args.workload, "scheme": sch, "batch": args.batch,
+    return {"workload": args.workload, "scheme": sch, "batch": args.batch, "gemv_kernel": getattr(args, "gemv_kernel", 0),
             "layers_k_to_n": [[k, n] for k, n in layers], "activations": act, "output": "f32",
             "l2": f"rotating {rotation} distinct weight copies per rank "
                   f"({rotation * sum(packed_bytes(sch, k, n) for k, n in layers) / 1e6:.0f} MB) > 2 x 126 MB L2"}
@@ -1147,6 +1147,9 @@ def main() -> None:
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemv-kernel", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="force a GEMV kernel for the decode workloads (the library's gemv_kernel option): 0 automatic, "
+                         "1 generic, 2 mma.sync tensor mode, 3 integer dp4a, 4 tcgen05")
     ap.add_argument("--no-sweep", action="store_true",
                     help="default workload only: skip the `configs` list (the other configurations, one entry each)")
     args = ap.parse_args()
@@ -1156,7 +1159,7 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload is None:
-        args.workload = "q4_0_llama7b_ffn_gemv" if world == 1 else TP_WORKLOAD
+        args.workload = "q4_0_llama7b_ffn_gemv" if (world == 1 and args.gpus <= 1) else TP_WORKLOAD
     if args.workload in GEMM_WORKLOADS:
         run_gemm_workload(args, rank, world, local_rank)
         return
@@ -1194,6 +1197,11 @@ def main() -> None:
     sch, layers, act = WORKLOADS[args.workload]
     sid = SCHEME_IDS[sch]
     m = args.batch
+    if args.gemv_kernel:
+        R.set_option("gemv_kernel", args.gemv_kernel)
+    kernel_name = {0: ("gemv_int_kernel (+ its activation quantiser)" if m <= 2 else "gemv_staged_kernel (+ its activation converter)"),
+                   1: "gemv_generic_kernel", 2: "gemv_staged_kernel (+ its activation converter)",
+                   3: "gemv_int_kernel (+ its activation quantiser)", 4: "gemv_tc_kernel"}[args.gemv_kernel]
     act_t = torch.float32 if act == "f32" else torch.bfloat16
     act_bytes = 4 if act == "f32" else 2
     per_launch = algorithmic_bytes(sch, layers, m, act_bytes)
@@ -1334,14 +1342,14 @@ def main() -> None:
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "kernel": "gemv_int_kernel (+ its activation quantiser)", "bytes_per_launch": bytes_per_launch,
+                         "kernel": kernel_name, "bytes_per_launch": bytes_per_launch,
                          "avg_launch_us": avg_launch_s * 1e6,
                          "timing": "CUDA events over the timed region / launches (includes inter-launch gaps)",
                          "traffic": captured_traffic(args.workload, m)},
         }
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(sch, layers, m, act)
-        if world == 1 and not args.no_sweep and args.workload == "q4_0_llama7b_ffn_gemv" and m == 1:
+        if world == 1 and not args.no_sweep and args.workload == "q4_0_llama7b_ffn_gemv" and m == 1 and not args.gemv_kernel:
             head = {"name": "cfg1 q4_0 llama7b ffn gemv pair m=1 (the headline)", "scheme": sch, "m": m,
                     "layers_k_to_n": [[k, n] for k, n in layers], "activations": act, "metric": "gemv_hbm_gbs",
                     "value": value, "unit": "GB/s", "ms": ms_per_step,
