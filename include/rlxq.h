@@ -58,10 +58,13 @@ enum rlxq_status {
  * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; Q5_K, Q8_K, Q2_K and Q3_K (the
  * rest of QuantScheme::is_gguf, rlx-ir/src/quant.rs:170-182) decode through the general kernel
  * (Q5_K also through the streaming GEMV for m <= 2 and the tensor-core GEMM for m > 8), so every
- * GGUF scheme the reference lowers runs on the GPU without its host fallback. */
+ * GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
+ * are container types the reference only decodes to f32 when a file is loaded (GgufFile::tensor_f32,
+ * rlx-gguf/src/lib.rs:323-353, decoders :635-729) and no QuantScheme names; here they dequantise bit-exactly
+ * and multiply through the general kernel, so such a tensor can stay packed on the device as well. */
 enum rlxq_scheme {
     RLXQ_Q4_K = 0, RLXQ_Q5_K = 1, RLXQ_Q6_K = 2, RLXQ_Q8_K = 3, RLXQ_Q2_K = 4, RLXQ_Q3_K = 5,
-    RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7
+    RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7, RLXQ_Q4_1 = 8, RLXQ_Q5_0 = 9, RLXQ_Q5_1 = 10
 };
 
 /* Activation / output element types: the two the reference's typed I/O carries on this

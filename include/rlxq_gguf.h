@@ -23,7 +23,7 @@ typedef struct rlxq_gguf rlxq_gguf;
 /* One entry of the tensor table (GgufTensor, rlx-gguf/src/lib.rs:179-194). */
 typedef struct rlxq_gguf_tensor {
     uint32_t ggml_type;   /* GgmlType as stored in the file (rlx-gguf/src/lib.rs:55-99) */
-    int32_t scheme;       /* rlxq_scheme of that type, or -1 (F32, F16, BF16, formats this path does not decode) */
+    int32_t scheme;       /* rlxq_scheme of that type, or -1 (F32, F16, BF16: not block formats) */
     uint32_t n_dims;
     uint64_t dims[4];     /* GGML order, innermost first, verbatim; a weight W[n,k] is stored as {k, n} */
     uint64_t offset;      /* within the data segment */

@@ -16,11 +16,11 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "librlxq_oracle.so")
 
-Q4_K, Q5_K, Q6_K, Q8_K, Q2_K, Q3_K, Q4_0, Q8_0 = 0, 1, 2, 3, 4, 5, 6, 7
+Q4_K, Q5_K, Q6_K, Q8_K, Q2_K, Q3_K, Q4_0, Q8_0, Q4_1, Q5_0, Q5_1 = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10
 SCHEMES = {"q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "q8_k": Q8_K, "q2_k": Q2_K, "q3_k": Q3_K,
-           "q4_0": Q4_0, "q8_0": Q8_0}
+           "q4_0": Q4_0, "q8_0": Q8_0, "q4_1": Q4_1, "q5_0": Q5_0, "q5_1": Q5_1}
 GEOMETRY = {Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), Q8_K: (256, 292), Q2_K: (256, 84),
-            Q3_K: (256, 110), Q4_0: (32, 18), Q8_0: (32, 34)}
+            Q3_K: (256, 110), Q4_0: (32, 18), Q8_0: (32, 34), Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24)}
 
 
 def build(force: bool = False) -> str:

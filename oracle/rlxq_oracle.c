@@ -23,6 +23,9 @@ int rlxo_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32_t* block
         case RLXO_Q8_K: e = 256; b = 292; break; /* f32 d, 256 i8, 16 i16 block sums */
         case RLXO_Q2_K: e = 256; b = 84;  break; /* as the reference reads it: f16 d, f16 dmin, 16 scale bytes, 64 quant bytes */
         case RLXO_Q3_K: e = 256; b = 110; break; /* as the reference reads it: f16 d, 12 scale bytes, 32 high-mask bytes, 64 quant bytes */
+        case RLXO_Q4_1: e = 32;  b = 20;  break; /* f16 d, f16 m, 16 nibble bytes (rlx-gguf/src/lib.rs:405) */
+        case RLXO_Q5_0: e = 32;  b = 22;  break; /* f16 d, u32 fifth bits, 16 nibble bytes (:406) */
+        case RLXO_Q5_1: e = 32;  b = 24;  break; /* f16 d, f16 m, u32 fifth bits, 16 nibble bytes (:407) */
         default: return -1;
     }
     if (block_elems) *block_elems = e;
@@ -298,6 +301,50 @@ static void dequant_q3_k_block(const uint8_t* block, float* out) {
     }
 }
 
+/* rlx-gguf/src/lib.rs:635-660: d * q + m, product and sum rounded separately. */
+static void dequant_q4_1_block(const uint8_t* b, float* out) {
+    float d = rlxo_f16_to_f32((uint16_t)(b[0] | (b[1] << 8))), m = rlxo_f16_to_f32((uint16_t)(b[2] | (b[3] << 8)));
+    const uint8_t* qs = b + 4;
+    for (int j = 0; j < 16; j++) { float v0 = (float)(qs[j] & 0x0F); float p = d * v0; out[j] = p + m; }
+    for (int j = 0; j < 16; j++) { float v1 = (float)(qs[j] >> 4); float p = d * v1; out[16 + j] = p + m; }
+}
+
+/* rlx-gguf/src/lib.rs:662-694: bit j of qh (j + 16 for the high nibbles) is the fifth bit; d * (q - 16). */
+static void dequant_q5_0_block(const uint8_t* b, float* out) {
+    float d = rlxo_f16_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+    uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    const uint8_t* qs = b + 6;
+    for (int j = 0; j < 16; j++) {
+        uint8_t xh0 = (uint8_t)(((qh >> j) & 1u) << 4);
+        int v0 = (int)((qs[j] & 0x0F) | xh0) - 16;
+        out[j] = d * (float)v0;
+    }
+    for (int j = 0; j < 16; j++) {
+        uint8_t xh1 = (uint8_t)(((qh >> (j + 16)) & 1u) << 4);
+        int v1 = (int)((qs[j] >> 4) | xh1) - 16;
+        out[16 + j] = d * (float)v1;
+    }
+}
+
+/* rlx-gguf/src/lib.rs:696-729: d * q + m with the five-bit q. */
+static void dequant_q5_1_block(const uint8_t* b, float* out) {
+    float d = rlxo_f16_to_f32((uint16_t)(b[0] | (b[1] << 8))), m = rlxo_f16_to_f32((uint16_t)(b[2] | (b[3] << 8)));
+    uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+    const uint8_t* qs = b + 8;
+    for (int j = 0; j < 16; j++) {
+        uint8_t xh0 = (uint8_t)(((qh >> j) & 1u) << 4);
+        float v0 = (float)((qs[j] & 0x0F) | xh0);
+        float p = d * v0;
+        out[j] = p + m;
+    }
+    for (int j = 0; j < 16; j++) {
+        uint8_t xh1 = (uint8_t)(((qh >> (j + 16)) & 1u) << 4);
+        float v1 = (float)((qs[j] >> 4) | xh1);
+        float p = d * v1;
+        out[16 + j] = p + m;
+    }
+}
+
 /* rlx-cpu/src/gguf_matmul.rs:25-37 with the Q6_K arm taken from the signed full-tensor
  * decoder (the per-block decoder the reference calls there reads the scales unsigned). */
 static void dequant_block(uint32_t scheme, const uint8_t* block, float* out) {
@@ -310,6 +357,9 @@ static void dequant_block(uint32_t scheme, const uint8_t* block, float* out) {
         case RLXO_Q8_K: dequant_q8_k_block(block, out); break;
         case RLXO_Q2_K: dequant_q2_k_block(block, out); break;
         case RLXO_Q3_K: dequant_q3_k_block(block, out); break;
+        case RLXO_Q4_1: dequant_q4_1_block(block, out); break;
+        case RLXO_Q5_0: dequant_q5_0_block(block, out); break;
+        case RLXO_Q5_1: dequant_q5_1_block(block, out); break;
         default: break;
     }
 }
@@ -528,6 +578,20 @@ int rlxo_fill_blocks(uint32_t scheme, uint64_t seed, uint64_t first_block, uint6
             case RLXO_Q3_K:
                 put_u16(b, gen_scale_f16(&s));
                 gen_bytes(&s, b + 2, 12 + 32 + 64);
+                break;
+            case RLXO_Q4_1:          /* d and m like the other scales, quants uniform */
+                put_u16(b, gen_scale_f16(&s));
+                put_u16(b + 2, gen_scale_f16(&s));
+                gen_bytes(&s, b + 4, 16);
+                break;
+            case RLXO_Q5_0:
+                put_u16(b, gen_scale_f16(&s));
+                gen_bytes(&s, b + 2, 4 + 16);
+                break;
+            case RLXO_Q5_1:
+                put_u16(b, gen_scale_f16(&s));
+                put_u16(b + 2, gen_scale_f16(&s));
+                gen_bytes(&s, b + 4, 4 + 16);
                 break;
             default: return -1;
         }

@@ -32,7 +32,8 @@ extern "C" {
  * rlx-cuda/src/gguf_host.rs:24-34; 6 = Q4_0 and 7 = Q8_0 are new (the reference's
  * CUDA backend has no id for them). */
 /* 0..5 are the ids of gguf_scheme_id (rlx-cuda/src/gguf_host.rs:24-34) */
-enum { RLXO_Q4_K = 0, RLXO_Q5_K = 1, RLXO_Q6_K = 2, RLXO_Q8_K = 3, RLXO_Q2_K = 4, RLXO_Q3_K = 5, RLXO_Q4_0 = 6, RLXO_Q8_0 = 7 };
+enum { RLXO_Q4_K = 0, RLXO_Q5_K = 1, RLXO_Q6_K = 2, RLXO_Q8_K = 3, RLXO_Q2_K = 4, RLXO_Q3_K = 5, RLXO_Q4_0 = 6, RLXO_Q8_0 = 7,
+       RLXO_Q4_1 = 8, RLXO_Q5_0 = 9, RLXO_Q5_1 = 10 };
 
 /* rlx-ir/src/quant.rs:138-164 — block geometry. Returns 0, or -1 for an unknown scheme. */
 int rlxo_scheme_geometry(uint32_t scheme, uint32_t* block_elems, uint32_t* block_bytes);

@@ -31,6 +31,10 @@ class QuantScheme(enum.IntEnum):
     GgufQ3K = 5
     GgufQ4_0 = 6
     GgufQ8_0 = 7
+    # container types the reference decodes at load time only (no QuantScheme of its own names them)
+    GgufQ4_1 = 8
+    GgufQ5_0 = 9
+    GgufQ5_1 = 10
 
     def gguf_block_size(self) -> int:
         return scheme_geometry(self)[0]

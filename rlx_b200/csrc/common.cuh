@@ -47,6 +47,9 @@ inline bool geometry(uint32_t scheme, Geometry* g) {
         case RLXQ_Q8_K: *g = {256, 292}; return true;
         case RLXQ_Q2_K: *g = {256, 84}; return true;
         case RLXQ_Q3_K: *g = {256, 110}; return true;
+        case RLXQ_Q4_1: *g = {32, 20}; return true;
+        case RLXQ_Q5_0: *g = {32, 22}; return true;
+        case RLXQ_Q5_1: *g = {32, 24}; return true;
         default: return false;
     }
 }

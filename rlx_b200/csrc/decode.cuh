@@ -191,7 +191,53 @@ __device__ __forceinline__ float4 decode4_exact<RLXQ_Q3_K>(const uint8_t* b, uin
     return r;
 }
 
+// Q4_1 (rlx-gguf/src/lib.rs:635-660): f16 d | f16 m | 16 bytes; weight j = low nibble of byte j, 16 + j = high nibble;
+// value d * q + m, the product rounded before the sum as in the reference's `d * v0 + m`.
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q4_1>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b)), mn = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t w = ld_u32_2(b + 4 + (t & 15u)) >> (4 * (t >> 4));
+    float4 r;
+    r.x = __fadd_rn(__fmul_rn(d, (float)(w & 0xFu)), mn);
+    r.y = __fadd_rn(__fmul_rn(d, (float)((w >> 8) & 0xFu)), mn);
+    r.z = __fadd_rn(__fmul_rn(d, (float)((w >> 16) & 0xFu)), mn);
+    r.w = __fadd_rn(__fmul_rn(d, (float)((w >> 24) & 0xFu)), mn);
+    return r;
+}
+
+// Q5_0 (rlx-gguf/src/lib.rs:662-694): f16 d | u32 qh | 16 bytes; bit j (+16 for the high nibbles) of qh is the
+// fifth bit of the quant; value d * (q - 16).
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q5_0>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b));
+    const uint32_t qh = ld_u32_2(b + 2) >> t;                       // bit i: fifth bit of weight t + i
+    const uint32_t w = ld_u32_2(b + 6 + (t & 15u)) >> (4 * (t >> 4));
+    float4 r;
+    r.x = __fmul_rn(d, (float)((int)((w & 0xFu) | ((qh & 1u) << 4)) - 16));
+    r.y = __fmul_rn(d, (float)((int)(((w >> 8) & 0xFu) | (((qh >> 1) & 1u) << 4)) - 16));
+    r.z = __fmul_rn(d, (float)((int)(((w >> 16) & 0xFu) | (((qh >> 2) & 1u) << 4)) - 16));
+    r.w = __fmul_rn(d, (float)((int)(((w >> 24) & 0xFu) | (((qh >> 3) & 1u) << 4)) - 16));
+    return r;
+}
+
+// Q5_1 (rlx-gguf/src/lib.rs:696-729): f16 d | f16 m | u32 qh | 16 bytes; value d * q + m with the five-bit q.
+template <>
+__device__ __forceinline__ float4 decode4_exact<RLXQ_Q5_1>(const uint8_t* b, uint32_t t) {
+    const float d = f16_bits_to_f32(ld_u16(b)), mn = f16_bits_to_f32(ld_u16(b + 2));
+    const uint32_t qh = ld_u32_2(b + 4) >> t;
+    const uint32_t w = ld_u32_2(b + 8 + (t & 15u)) >> (4 * (t >> 4));
+    float4 r;
+    r.x = __fadd_rn(__fmul_rn(d, (float)((w & 0xFu) | ((qh & 1u) << 4))), mn);
+    r.y = __fadd_rn(__fmul_rn(d, (float)(((w >> 8) & 0xFu) | (((qh >> 1) & 1u) << 4))), mn);
+    r.z = __fadd_rn(__fmul_rn(d, (float)(((w >> 16) & 0xFu) | (((qh >> 2) & 1u) << 4))), mn);
+    r.w = __fadd_rn(__fmul_rn(d, (float)(((w >> 24) & 0xFu) | (((qh >> 3) & 1u) << 4))), mn);
+    return r;
+}
+
 template <uint32_t SCHEME> struct SchemeTraits;
+template <> struct SchemeTraits<RLXQ_Q4_1> { static constexpr uint32_t kElems = 32, kBytes = 20; };
+template <> struct SchemeTraits<RLXQ_Q5_0> { static constexpr uint32_t kElems = 32, kBytes = 22; };
+template <> struct SchemeTraits<RLXQ_Q5_1> { static constexpr uint32_t kElems = 32, kBytes = 24; };
 template <> struct SchemeTraits<RLXQ_Q5_K> { static constexpr uint32_t kElems = 256, kBytes = 176; };
 template <> struct SchemeTraits<RLXQ_Q8_K> { static constexpr uint32_t kElems = 256, kBytes = 292; };
 template <> struct SchemeTraits<RLXQ_Q2_K> { static constexpr uint32_t kElems = 256, kBytes = 84; };

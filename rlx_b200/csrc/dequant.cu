@@ -41,6 +41,9 @@ int launch_dequant_f32(cudaStream_t stream, uint32_t scheme, const uint8_t* w, u
         case RLXQ_Q8_K: dequant_f32_kernel<RLXQ_Q8_K><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
         case RLXQ_Q2_K: dequant_f32_kernel<RLXQ_Q2_K><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
         case RLXQ_Q3_K: dequant_f32_kernel<RLXQ_Q3_K><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
+        case RLXQ_Q4_1: dequant_f32_kernel<RLXQ_Q4_1><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
+        case RLXQ_Q5_0: dequant_f32_kernel<RLXQ_Q5_0><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
+        case RLXQ_Q5_1: dequant_f32_kernel<RLXQ_Q5_1><<<(unsigned)blocks, threads, 0, stream>>>(w, n_quads, o); break;
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }
     count_launch();

@@ -113,6 +113,9 @@ int launch_matmul_generic(cudaStream_t stream, uint32_t scheme, const void* x, b
         case RLXQ_Q8_K: return launch_generic_s<RLXQ_Q8_K>(stream, x, xbf, w, y, ybf, m, k, n);
         case RLXQ_Q2_K: return launch_generic_s<RLXQ_Q2_K>(stream, x, xbf, w, y, ybf, m, k, n);
         case RLXQ_Q3_K: return launch_generic_s<RLXQ_Q3_K>(stream, x, xbf, w, y, ybf, m, k, n);
+        case RLXQ_Q4_1: return launch_generic_s<RLXQ_Q4_1>(stream, x, xbf, w, y, ybf, m, k, n);
+        case RLXQ_Q5_0: return launch_generic_s<RLXQ_Q5_0>(stream, x, xbf, w, y, ybf, m, k, n);
+        case RLXQ_Q5_1: return launch_generic_s<RLXQ_Q5_1>(stream, x, xbf, w, y, ybf, m, k, n);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);
     }
 }

@@ -35,9 +35,9 @@ static bool ggml_block(uint32_t t, uint32_t* elems, uint32_t* bytes, int32_t* sc
         case 0: *elems = 1; *bytes = 4; return true;                       // F32
         case 1: case 30: *elems = 1; *bytes = 2; return true;              // F16, BF16
         case 2: *elems = 32; *bytes = 18; *scheme = RLXQ_Q4_0; return true;
-        case 3: *elems = 32; *bytes = 20; return true;                     // Q4_1
-        case 6: *elems = 32; *bytes = 22; return true;                     // Q5_0
-        case 7: *elems = 32; *bytes = 24; return true;                     // Q5_1
+        case 3: *elems = 32; *bytes = 20; *scheme = RLXQ_Q4_1; return true;
+        case 6: *elems = 32; *bytes = 22; *scheme = RLXQ_Q5_0; return true;
+        case 7: *elems = 32; *bytes = 24; *scheme = RLXQ_Q5_1; return true;
         case 8: *elems = 32; *bytes = 34; *scheme = RLXQ_Q8_0; return true;
         case 10: *elems = 256; *bytes = 84; *scheme = RLXQ_Q2_K; return true;
         case 11: *elems = 256; *bytes = 110; *scheme = RLXQ_Q3_K; return true;

@@ -303,6 +303,9 @@ static int lm_run(cudaStream_t stream, uint32_t scheme, const void* hidden, uint
             case RLXQ_Q8_K: launch_exact<RLXQ_Q8_K>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
             case RLXQ_Q2_K: launch_exact<RLXQ_Q2_K>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
             case RLXQ_Q3_K: launch_exact<RLXQ_Q3_K>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
+            case RLXQ_Q4_1: launch_exact<RLXQ_Q4_1>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
+            case RLXQ_Q5_0: launch_exact<RLXQ_Q5_0>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
+            case RLXQ_Q5_1: launch_exact<RLXQ_Q5_1>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
             case RLXQ_Q4_0: launch_exact<RLXQ_Q4_0>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
             case RLXQ_Q8_0: launch_exact<RLXQ_Q8_0>(stream, C, hidden, hbf, w, n_embd, si, ev); break;
             default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);

@@ -212,6 +212,9 @@ extern "C" int rlxq_grouped_matmul(rlxq_stream_t stream, uint32_t scheme, const 
         case RLXQ_Q8_K: launch_grouped_s<RLXQ_Q8_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
         case RLXQ_Q2_K: launch_grouped_s<RLXQ_Q2_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
         case RLXQ_Q3_K: launch_grouped_s<RLXQ_Q3_K>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q4_1: launch_grouped_s<RLXQ_Q4_1>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q5_0: launch_grouped_s<RLXQ_Q5_0>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
+        case RLXQ_Q5_1: launch_grouped_s<RLXQ_Q5_1>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
         case RLXQ_Q4_0: launch_grouped_s<RLXQ_Q4_0>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
         case RLXQ_Q8_0: launch_grouped_s<RLXQ_Q8_0>(s, grid, xbf, ybf, x, w, y, offsets, perm, k, n); break;
         default: return fail(RLXQ_E_SCHEME, "unknown scheme %u", scheme);

@@ -44,7 +44,8 @@ def test_geometry_matches_reference_table():
     assert R.scheme_geometry(R.QuantScheme.GgufQ8K) == (256, 292)
     assert R.scheme_geometry(R.QuantScheme.GgufQ2K) == (256, 84)
     assert R.scheme_geometry(R.QuantScheme.GgufQ3K) == (256, 110)
-    for bad in (8, 9, 100):
+    assert R.scheme_geometry(8) == (32, 20) and R.scheme_geometry(9) == (32, 22) and R.scheme_geometry(10) == (32, 24)
+    for bad in (11, 12, 100):
         with pytest.raises(R.RlxqError) as e:
             R.scheme_geometry(bad)
         assert e.value.status == -1

@@ -91,6 +91,9 @@ def test_tensor_table_metadata_kinds_and_alignment(tmp_path, version):
         "a.q8k": (Q8K, O.fill_weights(O.Q8_K, 6, k, n)),
         "a.q2": (Q2K, O.fill_weights(O.Q2_K, 7, k, n)),
         "a.q3": (Q3K, O.fill_weights(O.Q3_K, 8, k, n)),
+        "a.q41": (3, O.fill_weights(O.Q4_1, 9, k, n)),
+        "a.q50": (6, O.fill_weights(O.Q5_0, 10, k, n)),
+        "a.q51": (7, O.fill_weights(O.Q5_1, 11, k, n)),
     }
     tensors = [(nm, [k, n], ty, w.tobytes()) for nm, (ty, w) in blobs.items()]
     tensors.append(("output_norm.weight", [k], F32, np.arange(k, dtype=np.float32).tobytes()))
@@ -116,7 +119,8 @@ def test_tensor_table_metadata_kinds_and_alignment(tmp_path, version):
         with pytest.raises(R.RlxqError):
             f.meta_u64(key)                                     # negative, float, or a skipped array
     want = {"blk.0.ffn_up.weight": 0, "blk.0.ffn_down.weight": 2, "blk.0.attn_q.weight": 7, "blk.0.attn_k.weight": 6,
-            "a.q5": 1, "a.q8k": 3, "a.q2": 4, "a.q3": 5, "output_norm.weight": -1, "half.weight": -1}
+            "a.q5": 1, "a.q8k": 3, "a.q2": 4, "a.q3": 5, "a.q41": 8, "a.q50": 9, "a.q51": 10, "output_norm.weight": -1,
+            "half.weight": -1}
     for nm, (ty, w) in blobs.items():
         t = f.get(nm)
         assert t.shape == (k, n) and t.ggml_type == ty and t.scheme == want[nm] and t.nbytes == w.size

@@ -1,4 +1,5 @@
-"""GPU parity for the GGUF schemes beyond the four benchmark formats: Q5_K, Q8_K, Q2_K, Q3_K.
+"""GPU parity for the GGUF schemes beyond the four benchmark formats: Q5_K, Q8_K, Q2_K, Q3_K, and the 32-weight
+container types Q4_1, Q5_0, Q5_1 that the reference decodes only when a file is loaded (rlx-gguf/src/lib.rs:635-729).
 
 They complete QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182): with them every scheme the reference's
 `Op::DequantMatMul` accepts runs on the GPU (the reference sends all of them to a host fallback or to its
@@ -18,7 +19,7 @@ from tests.helpers import assert_within_tolerance, bound, make_case, reference
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
-NEW = ["q5_k", "q8_k", "q2_k", "q3_k"]
+NEW = ["q5_k", "q8_k", "q2_k", "q3_k", "q4_1", "q5_0", "q5_1"]
 
 
 def _gpu_dequant(scheme, w, n_elems):
@@ -43,8 +44,9 @@ def _gpu_matmul(scheme, w, x, n, x_bf16=False):
 def test_dequant_bit_exact_seeded(sch, nblk):
     s = O.SCHEMES[sch]
     w = O.fill_blocks(s, 200 + nblk, nblk)
-    got = _gpu_dequant(s, w, nblk * 256)
-    exp = O.dequant(s, w, nblk * 256)
+    be = O.GEOMETRY[s][0]
+    got = _gpu_dequant(s, w, nblk * be)
+    exp = O.dequant(s, w, nblk * be)
     assert np.array_equal(got.view(np.uint32), exp.view(np.uint32))
 
 
@@ -65,8 +67,9 @@ def test_dequant_arbitrary_bytes_and_special_scales(sch):
             w[i, 0], w[i, 1] = v & 0xFF, v >> 8
     # random d bytes can be NaN / Inf: compare bit patterns, NaN payloads included
     w = w.ravel()
-    got = _gpu_dequant(s, w, 96 * 256)
-    exp = O.dequant(s, w, 96 * 256)
+    be = O.GEOMETRY[s][0]
+    got = _gpu_dequant(s, w, 96 * be)
+    exp = O.dequant(s, w, 96 * be)
     same = got.view(np.uint32) == exp.view(np.uint32)
     both_nan = np.isnan(got) & np.isnan(exp)
     assert np.all(same | both_nan)
@@ -75,7 +78,7 @@ def test_dequant_arbitrary_bytes_and_special_scales(sch):
 def test_reference_known_answers_on_the_gpu():
     with open(os.path.join(GOLDEN, "known_answers.json")) as f:
         cases = [c for c in json.load(f) if c["scheme"] in NEW]
-    assert len(cases) >= 5
+    assert len(cases) >= 5          # the reference holds none for Q4_1 / Q5_0 / Q5_1 (cross-checked decoders only)
     for case in cases:
         s = O.SCHEMES[case["scheme"]]
         w = np.frombuffer(bytes.fromhex(case["bytes"]), np.uint8).copy()

@@ -149,10 +149,29 @@ def formula_decode(scheme, blocks, n_elems):
         val = (two - 4 * (1 - bit)).astype(f)                                # [nb, 2, 4, 2, 16]
         dl = (d[:, :, None, None] * sc.reshape(nb, 2, 4, 2).astype(f))[..., None]
         return (dl * val).astype(f).ravel()
+    if scheme in (O.Q4_1, O.Q5_0, O.Q5_1):
+        # 32-weight blocks: f16 d [, f16 m] [, u32 of fifth bits], 16 bytes of nibbles; weight j is the low nibble of
+        # byte j, weight 16 + j the high nibble, bit j (16 + j) of the u32 its fifth bit.
+        d = B[:, 0:2].copy().view("<f2").astype(f)
+        off = 2
+        mn = None
+        if scheme != O.Q5_0:
+            mn = B[:, 2:4].copy().view("<f2").astype(f)
+            off = 4
+        fifth = np.zeros((nb, 32), np.uint32)
+        if scheme != O.Q4_1:
+            qh = B[:, off:off + 4].copy().view("<u4")                          # [nb, 1]
+            fifth = ((qh >> np.arange(32, dtype=np.uint32)[None, :]) & 1) << 4
+            off += 4
+        qs = B[:, off:off + 16].astype(np.uint32)
+        q = np.concatenate([qs & 15, qs >> 4], axis=1) | fifth                # [nb, 32]
+        if scheme == O.Q5_0:
+            return (d * (q.astype(np.int32) - 16).astype(f)).astype(f).ravel()
+        return ((d * q.astype(f)).astype(f) + mn).astype(f).ravel()
     raise ValueError(scheme)
 
 
-@pytest.mark.parametrize("sch", ["q8_0", "q4_0", "q4_k", "q6_k", "q5_k", "q8_k", "q2_k", "q3_k"])
+@pytest.mark.parametrize("sch", ["q8_0", "q4_0", "q4_k", "q6_k", "q5_k", "q8_k", "q2_k", "q3_k", "q4_1", "q5_0", "q5_1"])
 def test_oracle_matches_formula_decoder_bit_exact(sch):
     s = O.SCHEMES[sch]
     be, _ = O.GEOMETRY[s]
