@@ -1147,9 +1147,9 @@ def main() -> None:
     ap.add_argument("--impl", default="rlxq", choices=["rlxq", "reference"])
     ap.add_argument("--gemm-shape", default=None, help="m,k,n override for a GEMM workload (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gemv-kernel", type=int, default=0, choices=[0, 1, 2, 3, 4],
+    ap.add_argument("--gemv-kernel", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="force a GEMV kernel for the decode workloads (the library's gemv_kernel option): 0 automatic, "
-                         "1 generic, 2 mma.sync tensor mode, 3 integer dp4a, 4 tcgen05")
+                         "1 generic, 2 mma.sync tensor mode, 3 integer dp4a, 4 tcgen05, 5 integer MMA")
     ap.add_argument("--no-sweep", action="store_true",
                     help="default workload only: skip the `configs` list (the other configurations, one entry each)")
     args = ap.parse_args()
@@ -1199,9 +1199,11 @@ def main() -> None:
     m = args.batch
     if args.gemv_kernel:
         R.set_option("gemv_kernel", args.gemv_kernel)
-    kernel_name = {0: ("gemv_int_kernel (+ its activation quantiser)" if m <= 2 else "gemv_staged_kernel (+ its activation converter)"),
+    kernel_name = {0: ("gemv_int_kernel, dp4a units (+ its activation quantiser)" if m == 1
+                       else "gemv_int_kernel, integer-MMA units (+ its activation quantiser) where the shape allows, else gemv_staged_kernel"),
                    1: "gemv_generic_kernel", 2: "gemv_staged_kernel (+ its activation converter)",
-                   3: "gemv_int_kernel (+ its activation quantiser)", 4: "gemv_tc_kernel"}[args.gemv_kernel]
+                   3: "gemv_int_kernel, dp4a units (+ its activation quantiser)", 4: "gemv_tc_kernel",
+                   5: "gemv_int_kernel, integer-MMA units (+ its activation quantiser)"}[args.gemv_kernel]
     act_t = torch.float32 if act == "f32" else torch.bfloat16
     act_bytes = 4 if act == "f32" else 2
     per_launch = algorithmic_bytes(sch, layers, m, act_bytes)

@@ -18,7 +18,9 @@ size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t 
         const size_t b = int_workspace_bytes(scheme, m <= 4 ? m : 4, k, n);
         // the tcgen05 GEMV (8-byte words for the parts of cut tiles) only runs when it is asked for
         const size_t c = options().gemv_kernel.load() == 4 ? gemv_tc_workspace_bytes(scheme, m, k, n) : 0;
-        return a > b ? (a > c ? a : c) : (b > c ? b : c);
+        const size_t d = int_mma_workspace_bytes(scheme, m, k, n);
+        const size_t ab = a > b ? a : b, cd = c > d ? c : d;
+        return ab > cd ? ab : cd;
     }
     return gemm_tc_workspace_bytes(m, k, n);      // partial tiles of the stream-K split, when the shape wants it
 }
@@ -35,9 +37,9 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     if ((uintptr_t)x & 15u) return fail(RLXQ_E_ALIGN, "x must be 16-byte aligned");
     if ((uintptr_t)y & (ybf ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
     if (m <= 8) {
-        // 0 = automatic: integer kernel for batch 1-2, tensor-mode kernel for 3-8, generic otherwise.  The integer
-        // kernel also runs batch 3-4 (one CTA per SM, 18 us against the tensor-mode kernel's 15 us on the 4096 ->
-        // 11008 Q4_0 shape), but only when asked for with gemv_kernel = 3.
+        // 0 = automatic: the integer kernel with its dp4a units for batch 1-2, with its integer-MMA units for batch
+        // 3-8 (and batch 2 of the formats with 32-weight blocks, where it already wins), then the staged tensor-mode
+        // kernel, then the generic one.  The dp4a units also run batch 3-4, but only when asked for with gemv_kernel = 3.
         const int64_t force = options().gemv_kernel.load();
         const bool can_int = m <= 4 && int_supported(scheme, m, k, n, w, x);
         const bool can_tc = staged_supported(scheme, m, k, n, w, x, xbf);
@@ -46,10 +48,17 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
             if (!can_tcg) return fail(RLXQ_E_SHAPE, "tensor-core GEMV does not support scheme %u m=%u k=%u n=%u (or 16-byte alignment)", scheme, m, k, n);
             return launch_gemv_tc(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         }
+        if (force == 5) {
+            if (!int_mma_supported(scheme, m, k, n, w, x)) return fail(RLXQ_E_SHAPE, "integer-MMA GEMV does not support scheme %u m=%u k=%u n=%u (or 16-byte alignment)", scheme, m, k, n);
+            return launch_gemv_int_mma(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
+        }
         if (force == 3 && !can_int)
             return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
         if (force == 2 && !can_tc)
             return fail(RLXQ_E_SHAPE, "staged GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
+        const bool mma_first = m >= 3 || (m == 2 && (scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0));
+        if (force == 0 && mma_first && int_mma_supported(scheme, m, k, n, w, x))
+            return launch_gemv_int_mma(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 3 || (force == 0 && can_int && m <= 2))
             return launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 2 || (force == 0 && can_tc))

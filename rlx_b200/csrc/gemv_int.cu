@@ -1,21 +1,30 @@
-// Streaming decode GEMV for batch 1-2: integer dot products (dp4a) on raw block quants.
+// Streaming decode GEMV for batch 1-8: integer dot products on raw block quants.
 //
 // The activations are quantised once to two int8 limbs per value, X = round(x / s_b) in
 // [-16256, 16256] = 128*h + l, one f32 scale s_b per 32 values, with the integer block sums the
 // formats' offsets need.  Weights are never converted: four 4-bit (or 8-, 6-bit) quants are masked
-// into one register and multiplied against four activations by one dp4a, exact in int32; one
-// int->float conversion and one FMA per 32-weight block apply d_block * s_block (f32 from there on).
+// into one register and multiplied against activations in int32, exactly; one int->float
+// conversion and one FMA per 32-weight block apply d_block * s_block (f32 from there on).
+// Two kinds of unit do the multiplying:
+//  * dp4a units (batch 1-2, on request 3-4): one dp4a per four weights, limb and activation row;
+//  * integer-MMA units (batch 3-8; Q4_0, Q8_0, Q4_K): one m16n8k32 MMA per 32-weight block of all
+//    16 tile rows against four activation rows x two limbs.  mma.sync with 8-bit integers runs at
+//    one m16n8k32 per 8 cycles per sub-core here, far more than the stream needs; what the units
+//    save is instruction issue, which is what bounds the dp4a units from batch 3 on.
 //
-// gemv_int_kernel (the streaming kernel).  Persistent CTAs, two per SM.  All CTAs together walk one
+// gemv_int_kernel (the streaming kernel).  Persistent CTAs, two per SM (one with the integer-MMA
+// units or more than two rows).  All CTAs together walk one
 // global list of work items, (16-row weight tile, 2048-weight chunk), split into equal contiguous
 // ranges ("stream-K"), so every SM streams the same number of bytes whatever n and k are.  Per CTA
 // a producer warp keeps a ring of shared-memory stages full, one 2-D TMA box (16 rows x one chunk)
 // and one mbarrier per stage; the ring takes all the shared memory the CTA has.  Eight consumer
-// warps take one 256-weight unit of the stage each; a finisher warp adds their partial sums and
+// warps take one 256-weight unit of the stage each (sixteen, half a unit each, with the integer-MMA
+// units); a finisher warp adds their partial sums and
 // writes the tile, so the consumers never wait on global memory.
 //
 // Two ways to run it:
-//  * single-kernel mode (m*k <= 12288, tiles shared by at most two CTAs): the consumer warps
+//  * single-kernel mode (m*k <= 12288, 16384 with the integer-MMA units; tiles shared by at most
+//    two CTAs): the consumer warps
 //    quantise the activations themselves into shared memory.  Two ring stages are requested before
 //    the dependency wait (weights are immutable, so they overlap the previous kernel's tail), then
 //    the activation loads, then the rest of the ring: a load issued behind a full ring of weight
@@ -30,10 +39,9 @@
 //
 // Error: the activation quantisation only; |y - y_exact| <= 2^-15 * sqrt(32) * |x| * |w_row|
 // = 1.7e-4 * |x| * |w_row| in the worst case, about 1e-6 typically, plus f32 accumulation over
-// blocks.  (The legacy HMMA pipe of this GPU sustains one m16n8k16 per 32 cycles per sub-core,
-// which alone would cap a tensor-mode Q4_0 GEMV below the HBM roofline; dp4a does not.)
+// blocks.
 //
-// Replaces, for m <= 2, the reference's dequantise-everything + cublasSgemm
+// Replaces, for m <= 8, the reference's dequantise-everything + cublasSgemm
 // (rlx-cuda/src/gguf_gpu.rs:62-134).
 #include <chrono>
 
@@ -45,11 +53,16 @@
 
 namespace rlxq {
 
-constexpr uint32_t kIntWarps = 8;                      // consumer warps
-constexpr uint32_t kIntThreads = (kIntWarps + 2) * 32; // + one producer warp + one finisher warp
+constexpr uint32_t kIntWarps = 8;                      // consumer warps of the dp4a units
+// Consumer warps: one per 256-weight unit of a stage for the dp4a units, two (four blocks of the unit each)
+// for the integer-MMA units, whose chain load -> mask -> MMA -> convert -> FMA wants more warps to hide under.
+constexpr uint32_t int_warps(bool mma) { return mma ? 16u : kIntWarps; }
+constexpr uint32_t int_threads(bool mma) { return (int_warps(mma) + 2) * 32; }   // + one producer warp + one finisher warp
+// lanes of a consumer warp that hand partial sums to the finisher
+constexpr uint32_t int_red_lanes(bool mma) { return mma ? 16u : 32u; }
 constexpr uint32_t kIntRB = 4;                         // ring of reduction buffers between consumers and finisher
 // single-kernel mode: groups of 8 activations a consumer thread quantises (8 for the four-row kernel)
-constexpr uint32_t inline_groups(int mm) { return mm > 2 ? 8u : 6u; }
+constexpr uint32_t inline_groups(int mm, bool mma = false) { return mma ? 4u : (mm > 2 ? 8u : 6u); }
 constexpr uint32_t kIntCU = 8;                         // 256-weight units per stage = one per warp
 
 // A stage is NB boxes of 16 rows x UB units, each box fetched by ONE 2-D TMA request (a request
@@ -58,10 +71,11 @@ constexpr uint32_t kIntCU = 8;                         // 256-weight units per s
 // row pitch of 8 words mod 32), read from the next units or zero past the row end, so that rows do
 // not all start on the same shared-memory bank; Q6_K's 1680-byte rows already do not.  TMA boxes
 // are at most 256 eight-byte elements wide, hence two for Q8_0.
-template <uint32_t SCHEME> struct IntBox {
+// (The integer-MMA unit of Q4_0 reads word t of rows g and g + 8, lane = 4 g + t: a pitch of 4 words mod 32.)
+template <uint32_t SCHEME, bool MMA = false> struct IntBox {
     static constexpr uint32_t NB = (SCHEME == RLXQ_Q8_0) ? 2u : 1u;
     static constexpr uint32_t UB = kIntCU / NB;                               // units per box
-    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : SCHEME == RLXQ_Q4_0 ? 32u : 16u);
+    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : (SCHEME == RLXQ_Q4_0 && !MMA) ? 32u : 16u);
     static constexpr uint32_t BOX_BYTES = 16 * ROW;
     static constexpr uint32_t STAGE_BYTES = NB * BOX_BYTES;
 };
@@ -80,7 +94,8 @@ struct IntParams {
     uint32_t row_bytes, ntiles, nchunks, total_chunks, slots;
     uint32_t chunks_q, chunks_r;   // total_chunks = grid * chunks_q + chunks_r: the first chunks_r CTAs take one more
     uint32_t nstages;
-    uint32_t xq_row_bytes; // bytes of one row of xq
+    uint32_t xq_row_bytes; // bytes of one row of xq (integer-MMA units: of one of the equal pieces it is fetched in)
+    uint32_t xq_pieces;    // bulk copies that fetch xq: one per activation row (integer-MMA units: 8)
     uint32_t off_stage, off_red, off_bar;
     // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
     // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
@@ -151,6 +166,8 @@ template <uint32_t SCHEME, int MM> struct QUnit;
 // and keeps one accumulator per activation row.
 template <int MM> struct QUnitRowHalf {
     static constexpr int NT = 1;                                           // accumulators per activation row
+    static constexpr int NACC = MM;
+    static constexpr bool HALF_OFFSETS = true;                             // the activation views start at the lane's half
     static constexpr uint32_t STRIDE_ROWS = 1;
     __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane & 15u; }
     __device__ static __forceinline__ void finalize(float (&)[MM], uint32_t) {}
@@ -163,6 +180,8 @@ template <int MM> struct QUnitRowHalf {
 // weight reads of a warp fall on 32 different banks.  The eight block sums of a row meet in finalize().
 template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
     static constexpr int NT = 4;
+    static constexpr int NACC = 4 * MM;
+    static constexpr bool HALF_OFFSETS = false;
     __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 3; }
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[NT * MM]) {
         const uint32_t b = L.lane & 7u, odd = b & 1u;
@@ -423,6 +442,207 @@ template <int MM> struct QUnit<RLXQ_Q6_K, MM> : QUnitRowHalf<MM> {
     }
 };
 
+// ---------------------------------------------------------------------------------------------
+// Integer-MMA units (batch 3-8).  A dp4a unit pays two instructions per four weights and activation
+// row.  Here one integer MMA (m16n8k32, u8 x s8 -> s32; 8 cycles per sub-core on this GPU) multiplies
+// a 32-weight block of all 16 tile rows by eight columns = four activation rows x two limbs.  The
+// weights are still never converted (the nibbles are masked into the A fragment straight from the
+// block), the products are exact in int32, and both limb sums of an (output row, activation row)
+// pair land in one lane: for lane = 4 g + t, c0 = sum q h and c1 = sum q l of (tile row g, activation
+// row t), c2 and c3 the same for tile row g + 8.  The activations sit in shared memory in fragment
+// order: [block][group of four rows][lane]{b0, b1}, then [block][row]{scale, bias * block sum}.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    // c = a * b (a zero accumulator comes in as the zero register, not as four moves)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Bytes of the fragment-ordered activations of mmg groups of four rows, and where their scales start.
+__host__ __device__ constexpr uint32_t frag_scale_offset(uint32_t k, uint32_t mmg) { return (k / 32) * mmg * 256; }
+__host__ __device__ constexpr uint32_t frag_total_bytes(uint32_t k, uint32_t mmg) { return (k / 32) * mmg * (256 + 32); }
+
+template <uint32_t SCHEME, int MM> struct QUnitMma;
+
+// Hands lane l < 16 the totals of tile row l in tot[0 .. MM) (zero to lanes 16..31), from the MMA's
+// accumulator layout: lane 4 g + t holds (tile row g, activation row 4 q + t) in tot[2 q] and
+// (tile row g + 8, the same activation row) in tot[2 q + 1].
+template <int MM>
+__device__ __forceinline__ void mma_rows_to_lanes(float (&tot)[MM], uint32_t lane) {
+    float out[MM];
+#pragma unroll
+    for (int c = 0; c < MM; ++c) {
+        const uint32_t src = 4u * (lane & 7u) + (uint32_t)(c & 3);
+        const float v0 = __shfl_sync(0xFFFFFFFFu, tot[2 * (c >> 2)], src);
+        const float v1 = __shfl_sync(0xFFFFFFFFu, tot[2 * (c >> 2) + 1], src);
+        out[c] = lane < 16u ? ((lane >> 3) ? v1 : v0) : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < MM; ++c) tot[c] = out[c];
+}
+
+// ---- Q4_0: quant word t of a block holds weights 4t .. 4t+3 in its low nibbles (the MMA's k = 4t ..)
+// and weights 16+4t .. in its high nibbles (k = 16+4t ..): one load and three logic instructions per
+// tile row and block.
+template <int MM> struct QUnitMma<RLXQ_Q4_0, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    // part: which four blocks of the unit this warp takes (two warps share a unit)
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * 144 + 72 * part, p8 = p0 + 8 * L.row_pitch;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            // the word that holds d: an even block starts on a word (d, then the quants from byte 2), an
+            // odd one two bytes into a word (d in its upper half, the quants aligned behind it)
+            const uint32_t o = 36 * (b >> 1) + 16 * (b & 1);
+            uint32_t q0, q8, dw0, dw8;
+            if (b & 1) {
+                dw0 = lds32(p0 + o) >> 16;
+                dw8 = lds32(p8 + o) >> 16;
+                q0 = lds32(p0 + o + 4 + 4 * t);
+                q8 = lds32(p8 + o + 4 + 4 * t);
+            } else {
+                dw0 = lds32(p0 + o) & 0xFFFFu;
+                dw8 = lds32(p8 + o) & 0xFFFFu;
+                q0 = __funnelshift_r(lds32(p0 + o + 4 * t), lds32(p0 + o + 4 * t + 4), 16);
+                q8 = __funnelshift_r(lds32(p8 + o + 4 * t), lds32(p8 + o + 4 * t + 4), 16);
+            }
+            const float d0 = f16_bits_to_f32(dw0), d8 = f16_bits_to_f32(dw8);
+            const uint32_t a0 = q0 & 0x0F0F0F0Fu, a2 = (q0 >> 4) & 0x0F0F0F0Fu;
+            const uint32_t a1 = q8 & 0x0F0F0F0Fu, a3 = (q8 >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int gq = 0; gq < MMG; ++gq) {
+                const uint2 bb = lds64(fb + (b * MMG + gq) * 256);
+                const uint2 sc = lds64(sb + (b * MMG + gq) * 32);
+                int c[4];
+                imma_u8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                const float s = __uint_as_float(sc.x);
+                const int sx = (int)sc.y;                          // -8 * sum(X): the format's offset
+                tot[2 * gq] = fmaf(d0 * s, (float)(c[0] * 128 + c[1] + sx), tot[2 * gq]);
+                tot[2 * gq + 1] = fmaf(d8 * s, (float)(c[2] * 128 + c[3] + sx), tot[2 * gq + 1]);
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
+// ---- Q8_0: the quants are the A fragment as they are (s8 x s8).  Blocks are 34 bytes: an even block of
+// the unit starts on a word (d, then the quants from byte 2: two words funnel-shifted per fragment
+// register), an odd one two bytes into a word (quants aligned).
+template <int MM> struct QUnitMma<RLXQ_Q8_0, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * 272 + 136 * part, p8 = p0 + 8 * L.row_pitch;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t o = 68 * (b >> 1) + 32 * (b & 1);       // the word that holds d
+            uint32_t a0, a1, a2, a3, dw0, dw8;
+            if (b & 1) {
+                dw0 = lds32(p0 + o) >> 16;
+                dw8 = lds32(p8 + o) >> 16;
+                a0 = lds32(p0 + o + 4 + 4 * t);  a2 = lds32(p0 + o + 20 + 4 * t);
+                a1 = lds32(p8 + o + 4 + 4 * t);  a3 = lds32(p8 + o + 20 + 4 * t);
+            } else {
+                dw0 = lds32(p0 + o) & 0xFFFFu;
+                dw8 = lds32(p8 + o) & 0xFFFFu;
+                a0 = __funnelshift_r(lds32(p0 + o + 4 * t), lds32(p0 + o + 4 * t + 4), 16);
+                a2 = __funnelshift_r(lds32(p0 + o + 16 + 4 * t), lds32(p0 + o + 20 + 4 * t), 16);
+                a1 = __funnelshift_r(lds32(p8 + o + 4 * t), lds32(p8 + o + 4 * t + 4), 16);
+                a3 = __funnelshift_r(lds32(p8 + o + 16 + 4 * t), lds32(p8 + o + 20 + 4 * t), 16);
+            }
+            const float d0 = f16_bits_to_f32(dw0), d8 = f16_bits_to_f32(dw8);
+#pragma unroll
+            for (int gq = 0; gq < MMG; ++gq) {
+                const uint2 bb = lds64(fb + (b * MMG + gq) * 256);
+                const float s = ldsf(sb + (b * MMG + gq) * 32);
+                int c[4];
+                imma_s8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                tot[2 * gq] = fmaf(d0 * s, (float)(c[0] * 128 + c[1]), tot[2 * gq]);
+                tot[2 * gq + 1] = fmaf(d8 * s, (float)(c[2] * 128 + c[3]), tot[2 * gq + 1]);
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
+// ---- Q4_K: a pair of sub-blocks shares 32 bytes (low nibbles: the first, high: the second); words t and
+// 4 + t of the pair are the two k-halves of lane t's fragment for both.  The warp's part of the unit is
+// four sub-blocks = one word of 6-bit scales and one of mins per tile row.  The second entry of an
+// activation block's pair is the float s_b * sum(X): the min term is dmin * m * that.
+template <int MM> struct QUnitMma<RLXQ_Q4_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void header(uint32_t p, uint32_t part, float& d, float& dmin, uint32_t& scb, uint32_t& mnb) {
+        const uint4 hd = lds128(p);                   // d, dmin, 12 scale bytes
+        d = f16_bits_to_f32(hd.x & 0xFFFFu);
+        dmin = f16_bits_to_f32(hd.x >> 16);
+        if (part == 0) {
+            scb = hd.y & 0x3F3F3F3Fu;
+            mnb = hd.z & 0x3F3F3F3Fu;
+        } else {
+            scb = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mnb = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+        }
+    }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * 144, p8 = p0 + 8 * L.row_pitch;
+        float d0, m0, d8, m8;
+        uint32_t sc0, mn0, sc8, mn8;
+        header(p0, part, d0, m0, sc0, mn0);
+        header(p8, part, d8, m8, sc8, mn8);
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+            const uint32_t qo = 16 + 64 * part + 32 * pp + 4 * t;
+            const uint32_t w0 = lds32(p0 + qo), w0b = lds32(p0 + qo + 16);
+            const uint32_t w8 = lds32(p8 + qo), w8b = lds32(p8 + qo + 16);
+#pragma unroll
+            for (int nib = 0; nib < 2; ++nib) {
+                const int js = 2 * pp + nib;          // sub-block inside the warp's part
+                const uint32_t a0 = (w0 >> (4 * nib)) & 0x0F0F0F0Fu, a2 = (w0b >> (4 * nib)) & 0x0F0F0F0Fu;
+                const uint32_t a1 = (w8 >> (4 * nib)) & 0x0F0F0F0Fu, a3 = (w8b >> (4 * nib)) & 0x0F0F0F0Fu;
+                const float dsc0 = d0 * (float)((sc0 >> (8 * js)) & 0xFFu), dmn0 = m0 * (float)((mn0 >> (8 * js)) & 0xFFu);
+                const float dsc8 = d8 * (float)((sc8 >> (8 * js)) & 0xFFu), dmn8 = m8 * (float)((mn8 >> (8 * js)) & 0xFFu);
+#pragma unroll
+                for (int gq = 0; gq < MMG; ++gq) {
+                    const uint2 bb = lds64(fb + (js * MMG + gq) * 256);
+                    const uint2 sc = lds64(sb + (js * MMG + gq) * 32);
+                    int c[4];
+                    imma_u8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                    const float s = __uint_as_float(sc.x), sxf = __uint_as_float(sc.y);
+                    tot[2 * gq] = fmaf(dsc0 * s, (float)(c[0] * 128 + c[1]), fmaf(-dmn0, sxf, tot[2 * gq]));
+                    tot[2 * gq + 1] = fmaf(dsc8 * s, (float)(c[2] * 128 + c[3]), fmaf(-dmn8, sxf, tot[2 * gq + 1]));
+                }
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
 // What the per-block integer sums are multiplied by before they are stored.
 template <uint32_t SCHEME> struct SumBias;
 template <> struct SumBias<RLXQ_Q4_0> { static constexpr int value = -8; };
@@ -430,6 +650,9 @@ template <> struct SumBias<RLXQ_Q8_0> { static constexpr int value = 0; };
 template <> struct SumBias<RLXQ_Q4_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q5_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
+// Whether the fragment-ordered activations carry the block sum as the float s_b * bias * sum(X) (formats
+// with a min term) or as the integer bias * sum(X) (added to the dot product before it is converted).
+constexpr bool frag_sum_is_float(uint32_t scheme) { return scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K; }
 
 // ---------------------------------------------------------------------------------------------
 // Kernel 1: activations -> two int8 limbs + per-32 scale + per-SUB integer sums (workspace).
@@ -534,7 +757,47 @@ __device__ __forceinline__ void quantise_store8(const float (&f)[8], uint32_t k,
     if ((lane & (SUB / 8 - 1)) == 0) sx[c / SUB] = bias * sum;
 }
 
-template <uint32_t SUB>
+// The same quantisation, stored in the fragment order of the integer-MMA units: dst = [block][MMG groups
+// of four rows][lane]{b0, b1} and, from byte frag_scale_offset(k, MMG) on, [block][row]{scale, bias * sum}.
+// Column 2 (r & 3) + limb of the MMA's B operand is (activation row r, limb); lane 4 col + t holds k = 4t ..
+// 4t+3 in b0 and k = 16+4t .. in b1.
+template <int MMG, bool FSUM>
+__device__ __forceinline__ void quantise_store8_frag(const float (&f)[8], uint32_t k, int bias, uint32_t r, uint32_t c,
+                                                     uint8_t* dst, uint32_t lane) {
+    float amax = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) amax = fmaxf(amax, fabsf(f[q]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    const bool ok = amax > 0.f && amax < 3.0e38f;
+    const float inv = ok ? 16256.0f / amax : 0.f;
+    const float s = ok ? amax * (1.0f / 16256.0f) : 0.f;
+    int sum = 0;
+    uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const int X = max(-16256, min(16256, __float2int_rn(f[q] * inv)));
+        sum += X;
+        const int hq = (X + 64) >> 7;             // in [-127, 127]
+        const int lq = X - (hq << 7);             // in [-64, 63]
+        hw[q >> 2] |= ((uint32_t)hq & 0xFFu) << (8 * (q & 3));
+        lw[q >> 2] |= ((uint32_t)lq & 0xFFu) << (8 * (q & 3));
+    }
+    const uint32_t blk = c >> 5, j = (c >> 3) & 3u;                  // the block, and which eight of its 32 values
+    const uint32_t half = j >> 1, t0 = 2u * (j & 1u), col = 2u * (r & 3u);
+    uint32_t* fr = reinterpret_cast<uint32_t*>(dst + ((size_t)blk * MMG + (r >> 2)) * 256) + half;
+    fr[2 * (4 * col + t0)] = hw[0];
+    fr[2 * (4 * col + t0 + 1)] = hw[1];
+    fr[2 * (4 * (col + 1) + t0)] = lw[0];
+    fr[2 * (4 * (col + 1) + t0 + 1)] = lw[1];
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if ((lane & 3u) == 0)
+        *reinterpret_cast<uint2*>(dst + frag_scale_offset(k, MMG) + ((size_t)blk * MMG * 4 + r) * 8) =
+            make_uint2(__float_as_uint(s), FSUM ? __float_as_uint(s * (float)(bias * sum)) : (uint32_t)(bias * sum));
+}
+
+template <uint32_t SUB, int MMG = 0, bool FSUM = false>
 __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict__ x, uint32_t x_bf16, uint32_t m,
                                                          uint32_t k, int bias, uint8_t* __restrict__ xq,
                                                          uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
@@ -552,7 +815,8 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
     float f[8];
     if (swiglu_pair) load_group8_swiglu(x, k, r, c, f);
     else load_group8(x, x_bf16, k, r, c, f);
-    quantise_store8<SUB>(f, k, bias, c, xq + (size_t)r * xq_row_bytes, lane);
+    if constexpr (MMG > 0) quantise_store8_frag<MMG, FSUM>(f, k, bias, r, c, xq, lane);   // fragment order (integer-MMA units)
+    else quantise_store8<SUB>(f, k, bias, c, xq + (size_t)r * xq_row_bytes, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -609,11 +873,12 @@ __device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& r
 // ---------------------------------------------------------------------------------------------
 // Kernel 2: the streaming kernel
 // ---------------------------------------------------------------------------------------------
-template <uint32_t SCHEME, int MM>
-__global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_constant__ IntParams P) {
+template <uint32_t SCHEME, int MM, bool MMA = false>
+__global__ void __launch_bounds__(int_threads(MMA)) gemv_int_kernel(const __grid_constant__ IntParams P) {
+    constexpr uint32_t CW = int_warps(MMA), WPU = CW / kIntCU, RL = int_red_lanes(MMA);
     using T = StagedTraits<SCHEME>;
-    using B = IntBox<SCHEME>;
-    using QU = QUnit<SCHEME, MM>;
+    using B = IntBox<SCHEME, MMA>;
+    using QU = std::conditional_t<MMA, QUnitMma<SCHEME, MM>, QUnit<SCHEME, MM>>;
     constexpr uint32_t STRIDE = B::ROW;
     constexpr uint32_t stage_bytes = B::STAGE_BYTES;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -639,11 +904,11 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     if (tid == 0) {
         for (uint32_t s = 0; s < NS; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[NS + s]), kIntWarps);
+            mbar_init(smem_u32(&bars[NS + s]), CW);
         }
         mbar_init(smem_u32(&bars[2 * NS]), 1);
         for (uint32_t r = 0; r < kIntRB; ++r) {
-            mbar_init(smem_u32(&rbars[r]), kIntWarps);
+            mbar_init(smem_u32(&rbars[r]), CW);
             mbar_init(smem_u32(&rbars[kIntRB + r]), 1);
         }
         *abort_flag = 0u;
@@ -652,7 +917,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     __syncthreads();
     // The first fill of the ring is spread over the warps, one stage each: a TMA request occupies its
     // issuing thread for a few hundred cycles, and one thread issuing them all delays the stream's start.
-    const uint32_t pre = min(min(NS, kIntWarps), rg.len);
+    const uint32_t pre = min(min(NS, CW), rg.len);
 
     // expert-indirect mode: every role learns the slab after the dependency wait (nothing is requested
     // before it) and leaves at once when the id is out of range
@@ -666,7 +931,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         return true;
     };
 
-    if (warp == kIntWarps) {
+    if (warp == CW) {
         // ---------------- producer warp ----------------
         uint32_t row_off;
         if (!resolve_expert(row_off)) return;
@@ -691,9 +956,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                     waited = true;
                     griddep_wait();
                     const uint32_t xbar = smem_u32(&bars[2 * NS]);
-                    if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+                    if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
                     __syncwarp();
-                    if (lane < (uint32_t)MM && !P.inline_q)
+                    if (lane < P.xq_pieces && !P.inline_q)
                         bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
                 }
                 if (issued >= NS) {
@@ -710,15 +975,15 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
         if (!waited) {   // fewer chunks than stages: everything is in flight, now fetch the activations
             griddep_wait();
             const uint32_t xbar = smem_u32(&bars[2 * NS]);
-            if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * MM);
+            if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
             __syncwarp();
-            if (lane < (uint32_t)MM && !P.inline_q)
+            if (lane < P.xq_pieces && !P.inline_q)
                 bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
         }
         return;
     }
 
-    if (warp == kIntWarps + 1) {
+    if (warp == CW + 1) {
         // ---------------- finisher warp ----------------
         { uint32_t ro; if (!resolve_expert(ro)) return; }
         // Adds the 16 partials of every output (2 halves x 8 warps, fixed order) and writes the tile,
@@ -737,7 +1002,7 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 if (lane == 0) { atomicExch(P.err, 6); *abort_flag = 1u; }
                 break;
             }
-            const float* rbuf = red + r * (kIntWarps * 32 * MM);
+            const float* rbuf = red + r * (CW * RL * MM);
             float v[NC];
 #pragma unroll
             for (int cp = 0; cp < NC; ++cp) {
@@ -745,9 +1010,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
                 v[cp] = 0.f;
                 if (col < (uint32_t)MM) {
 #pragma unroll
-                    for (uint32_t wv = 0; wv < kIntWarps; ++wv) {
-                        v[cp] += rbuf[(wv * 32 + rrow) * MM + col];
-                        v[cp] += rbuf[(wv * 32 + 16 + rrow) * MM + col];
+                    for (uint32_t wv = 0; wv < CW; ++wv) {
+                        v[cp] += rbuf[(wv * RL + rrow) * MM + col];
+                        if (RL == 32) v[cp] += rbuf[(wv * RL + 16 + rrow) * MM + col];
                     }
                 }
             }
@@ -858,22 +1123,23 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     L.lane = lane;
     L.row_pitch = STRIDE;
     // formats mapped (row, half) read from their half's offset on; Q4_0 indexes by block instead
-    const uint32_t hoff = (QU::NT == 1) ? L.half : 0u;
+    const uint32_t hoff = QU::HALF_OFFSETS ? L.half : 0u;
     L.xh = smem_u32(xs) + 128 * hoff;
     L.xl = L.xh + P.k;
     L.sb = smem_u32(xs) + 2 * P.k + 16 * hoff;
     L.sx = smem_u32(xs) + 2 * P.k + (P.k / 32) * 4 + (32 / T::SUB) * 16 * hoff;
+    if constexpr (MMA) L.sb = smem_u32(xs) + frag_scale_offset(P.k, MM / 4);   // fragments at xh, {scale, sum} pairs here
     const uint32_t trow = QU::first_row(lane), stages_u32 = smem_u32(stages);
     bool dead = false;
     if (P.inline_q) {
         {
             // every load is issued before the first value is used: one trip to L2, not one per group
             const uint32_t gpr = P.k / 8, total = gpr * P.m_real;   // whole warps stay together: gpr % 32 == 0
-            constexpr uint32_t kInlineGroups = inline_groups(MM);
+            constexpr uint32_t kInlineGroups = inline_groups(MM, MMA);
             uint4 raw[kInlineGroups][2];
 #pragma unroll
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
-                const uint32_t g = tid + i * kIntWarps * 32;
+                const uint32_t g = tid + i * CW * 32;
                 if (g < total) {
                     const uint32_t r = MM > 1 ? g / gpr : 0u;
                     load_raw8(P.x, P.x_bf16, P.k, r, (g - r * gpr) * 8, raw[i]);
@@ -882,17 +1148,20 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             request_first_stage(early, pre);
 #pragma unroll
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
-                const uint32_t g = tid + i * kIntWarps * 32;
+                const uint32_t g = tid + i * CW * 32;
                 if (g < total) {
                     const uint32_t r = MM > 1 ? g / gpr : 0u;
                     float f[8];
                     raw8_to_f32(raw[i], P.x_bf16, f);
-                    quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
-                                            xs + r * P.xq_row_bytes, lane);
+                    if constexpr (MMA)
+                        quantise_store8_frag<MM / 4, frag_sum_is_float(SCHEME)>(f, P.k, (int)SumBias<SCHEME>::value, r, (g - r * gpr) * 8, xs, lane);
+                    else
+                        quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
+                                                xs + r * P.xq_row_bytes, lane);
                 }
             }
         }
-        consumer_bar_n<kIntWarps * 32>();
+        consumer_bar_n<CW * 32>();
     } else if (!mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
         dead = true;
         if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
@@ -900,9 +1169,9 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
     uint32_t s = 0, ph = 0, rr = 0, rrph = 1;   // rrph: a fresh 'empty' barrier passes a wait on parity 1
     for (uint32_t si = 0; si < nseg; ++si) {
         const Segment sg = segment_at(P, rg, si);
-        float tot[QU::NT * MM];
+        float tot[QU::NACC];
 #pragma unroll
-        for (int m = 0; m < QU::NT * MM; ++m) tot[m] = 0.f;
+        for (int m = 0; m < QU::NACC; ++m) tot[m] = 0.f;
         for (uint32_t chunk = sg.c0; chunk < sg.c1; ++chunk) {
             if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
                 dead = true;
@@ -910,9 +1179,12 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             }
             if (!dead) {
                 const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
-                L.row = stages_u32 + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
-                if (warp < cu)
-                    QU::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
+                const uint32_t uw = warp / WPU;                   // the unit of the stage this warp works on
+                L.row = stages_u32 + s * stage_bytes + (uw / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                if (uw < cu) {
+                    if constexpr (MMA) QU::run(L, uw % B::UB, (chunk * kIntCU + uw) * 256, tot, warp % WPU);
+                    else QU::run(L, uw % B::UB, (chunk * kIntCU + uw) * 256, tot);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
             }
@@ -924,10 +1196,12 @@ __global__ void __launch_bounds__(kIntThreads) gemv_int_kernel(const __grid_cons
             if (lane == 0) { atomicExch(P.err, 7); *abort_flag = 1u; }
         }
         if (!dead) {
-            float* rbuf = red + rr * (kIntWarps * 32 * MM);
+            float* rbuf = red + rr * (CW * RL * MM);
             QU::finalize(tot, lane);
+            if (lane < RL) {
 #pragma unroll
-            for (int m = 0; m < MM; ++m) rbuf[(warp * 32 + lane) * MM + m] = tot[m];
+                for (int m = 0; m < MM; ++m) rbuf[(warp * RL + lane) * MM + m] = tot[m];
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&rbars[rr]));
         }
@@ -942,26 +1216,37 @@ struct IntPlan {
     bool ok;
     uint32_t grid, ntiles, nchunks, total_chunks, slots, nstages;
     bool two_way;
-    uint32_t xq_row_bytes, off_stage, off_red, off_bar, smem_bytes;
+    uint32_t xq_row_bytes, xq_pieces, off_stage, off_red, off_bar, smem_bytes;
     size_t ws_xq, ws_partial, ws_counters, ws_bytes;
 };
 
-template <uint32_t SCHEME>
+// Formats that have a integer-MMA unit (QUnitMma).
+constexpr bool int_has_mma(uint32_t scheme) { return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K; }
+
+template <uint32_t SCHEME, bool MMA = false>
 static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     using T = StagedTraits<SCHEME>;
-    constexpr uint32_t stage_bytes = IntBox<SCHEME>::STAGE_BYTES;
+    constexpr uint32_t stage_bytes = IntBox<SCHEME, MMA>::STAGE_BYTES;
     IntPlan pl{};
     pl.ok = false;
-    if (m == 0 || m > 4 || n == 0 || k == 0 || k % (256 * T::AG)) return pl;
-    const uint32_t mm = m > 2 ? 4u : m;                                // rows the kernel template carries
+    if (m == 0 || m > (MMA ? 8u : 4u) || n == 0 || k == 0 || k % (256 * T::AG)) return pl;
+    if (MMA && !int_has_mma(SCHEME)) return pl;
+    const uint32_t mm = MMA ? (m > 4 ? 8u : 4u) : (m > 2 ? 4u : m);    // rows the kernel template carries
     const uint32_t sms = (uint32_t)sm_count();
     auto align = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
     pl.ntiles = (n + 15) / 16;
     pl.nchunks = (k / 256 + kIntCU - 1) / kIntCU;
     if ((uint64_t)pl.ntiles * pl.nchunks > 0xFFFFFFFFull / 2) return pl;
     pl.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;      // a multiple of 16: k % 256 == 0
-    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * mm, 128);
-    const uint32_t tail = kIntRB * kIntWarps * 32 * mm * 4 + 1024;     // reduction buffers, barriers, flags
+    pl.xq_pieces = mm;
+    if (MMA) {                                                       // fragment order, fetched in 8 equal pieces
+        if ((uint64_t)k * (mm / 4) * 9 > 220u * 1024u) return pl;
+        pl.xq_pieces = 8;
+        pl.xq_row_bytes = frag_total_bytes(k, mm / 4) / 8;           // 9 k MMG / 8: a multiple of 16
+    }
+    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * pl.xq_pieces, 128);
+    const uint32_t red_bytes = kIntRB * int_warps(MMA) * int_red_lanes(MMA) * mm * 4;
+    const uint32_t tail = red_bytes + 1024;                            // reduction buffers, barriers, flags
     // two CTAs per SM when that still leaves each a ring of >= 4 stages, else one
     const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     uint32_t per_sm = 2, budget = budget2;
@@ -972,7 +1257,7 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     if (pl.nstages > 24) pl.nstages = 24;
     pl.off_stage = fixed;
     pl.off_red = pl.off_stage + pl.nstages * stage_bytes;
-    pl.off_bar = pl.off_red + kIntRB * kIntWarps * 32 * mm * 4;
+    pl.off_bar = pl.off_red + red_bytes;
     pl.smem_bytes = pl.off_bar + (2 * pl.nstages + 1 + 2 * kIntRB) * 8 + 64;
     pl.total_chunks = pl.ntiles * pl.nchunks;
     pl.grid = sms * per_sm;
@@ -982,7 +1267,7 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     const uint32_t per_cta = pl.total_chunks / pl.grid;              // >= 1
     pl.two_way = per_cta >= pl.nchunks;                              // a tile is cut by at most one range boundary
     pl.slots = (pl.nchunks + per_cta - 1) / per_cta + 1;             // contributors a tile can have
-    pl.ws_xq = align((size_t)pl.xq_row_bytes * mm, 256);
+    pl.ws_xq = align((size_t)pl.xq_row_bytes * pl.xq_pieces, 256);
     pl.ws_partial = align((size_t)pl.ntiles * pl.slots * mm * 16 * 4, 256);
     pl.ws_counters = align((size_t)pl.ntiles * 4, 256);
     pl.ws_bytes = pl.ws_xq + pl.ws_partial + pl.ws_counters + align((size_t)pl.ntiles * 8, 256);   // + rendezvous words
@@ -998,7 +1283,7 @@ static unsigned long long next_call_token() {
     return (epoch.fetch_add(1) << 2) | 1ull;
 }
 
-template <uint32_t SCHEME, int MM>
+template <uint32_t SCHEME, int MM, bool MMA = false>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                         uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair,
                         const float* expert_sel = nullptr, uint32_t num_experts = 0, uint32_t m_real = (uint32_t)MM) {
@@ -1010,7 +1295,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     if ((uintptr_t)ws & 15u) return fail(RLXQ_E_ALIGN, "workspace must be 16-byte aligned");
     IntParams P{};
     int rcm = encode_weight_map(&P.wmap, w, expert_sel ? (uint64_t)n * num_experts : n, (uint64_t)k / g.elems * g.bytes,
-                                IntBox<SCHEME>::ROW / 8, 16);
+                                IntBox<SCHEME, MMA>::ROW / 8, 16);
     if (rcm) return rcm;
     P.w = w; P.y = y;
     P.xq = reinterpret_cast<const uint8_t*>(ws);
@@ -1021,13 +1306,13 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.row_bytes = k / g.elems * g.bytes;
     P.ntiles = pl.ntiles; P.nchunks = pl.nchunks; P.total_chunks = pl.total_chunks; P.slots = pl.slots;
     P.chunks_q = pl.total_chunks / pl.grid; P.chunks_r = pl.total_chunks % pl.grid;
-    P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes;
+    P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes; P.xq_pieces = pl.xq_pieces;
     P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
     // One kernel instead of two when every shared tile has exactly two contributors and re-quantising
     // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
     // dependent-launch hop and a copy on the critical path of a call that lasts only microseconds.
     const int64_t iq = options().gemv_inline_q.load();
-    P.inline_q = (!pair && pl.two_way && (uint64_t)k * m_real <= inline_groups(MM) * kIntWarps * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
+    P.inline_q = (!pair && pl.two_way && (uint64_t)k * m_real <= inline_groups(MM, MMA) * int_warps(MMA) * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
     P.expert_sel = expert_sel;
     P.num_experts = num_experts;
@@ -1042,19 +1327,19 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && attr_set[dev].load() == 0) {
-        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[dev].store(1);
     }
     const uint32_t groups = (k / 8) * m_real;
     int rc = RLXQ_OK;
     const uint32_t qgrid = (groups + 255) / 256;
-    if (!P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
+    if (!P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB, MMA ? MM / 4 : 0, MMA && frag_sum_is_float(SCHEME)>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
                         m_real, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
                         P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? m_real * n : 0u,
                         (pair ? 1u : 0u));
     if (rc) return rc;
     if (!P.inline_q) count_launch();
-    rc = launch_pdl(gemv_int_kernel<SCHEME, MM>, dim3(pl.grid), dim3(kIntThreads), pl.smem_bytes, stream, P);
+    rc = launch_pdl(gemv_int_kernel<SCHEME, MM, MMA>, dim3(pl.grid), dim3(int_threads(MMA)), pl.smem_bytes, stream, P);
     if (rc) return rc;
     count_launch();
     return check_launch("gemv_int_kernel");
@@ -1063,7 +1348,17 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
 template <uint32_t SCHEME>
 static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                         uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word, bool pair,
-                        const float* expert_sel = nullptr, uint32_t num_experts = 0) {
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0, bool mma = false) {
+    if (mma) {
+        if constexpr (int_has_mma(SCHEME)) {
+            const IntPlan plm = plan_int<SCHEME, true>(m, k, n);
+            if (!plm.ok) return fail(RLXQ_E_SHAPE, "integer-MMA GEMV does not support m=%u k=%u n=%u", m, k, n);
+            if (m <= 4) return launch_int_t<SCHEME, 4, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m);
+            return launch_int_t<SCHEME, 8, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m);
+        } else {
+            return fail(RLXQ_E_SHAPE, "no integer-MMA GEMV for scheme %u", (unsigned)SCHEME);
+        }
+    }
     const IntPlan pl = plan_int<SCHEME>(m, k, n);
     if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
     if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
@@ -1114,6 +1409,39 @@ int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     return launch_gemv_int_err(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word());
 }
 
+// The same kernel with its integer-MMA units: batch 1-8 (carried as 4 or 8 rows); Q4_0, Q8_0, Q4_K.
+bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
+    if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
+    switch (scheme) {
+        case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0, true>(m, k, n).ok;
+        case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0, true>(m, k, n).ok;
+        case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K, true>(m, k, n).ok;
+        default: return false;
+    }
+}
+
+size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) {
+    IntPlan pl{};
+    switch (scheme) {
+        case RLXQ_Q4_0: pl = plan_int<RLXQ_Q4_0, true>(m, k, n); break;
+        case RLXQ_Q8_0: pl = plan_int<RLXQ_Q8_0, true>(m, k, n); break;
+        case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K, true>(m, k, n); break;
+        default: break;
+    }
+    return pl.ok ? pl.ws_bytes : 0;
+}
+
+int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
+                        bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    int* err = device_error_word();
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
+    }
+}
+
 // One row of an MoE decode step: y[n] = x[k] . W_e^T where W is a stack of num_experts [n, k] slabs and
 // e = (uint32_t)*expert_sel is read on the device.  Needs the single-kernel mode (k <= 12288, tiles shared
 // by at most two CTAs); int_expert_supported tells.
@@ -1148,6 +1476,15 @@ int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, 
 // activation quantiser, so the row-parallel down projection of an FFN needs no kernel in between.
 int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
                            uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
+    if (m > 2) {   // batch 3-8: the integer-MMA units
+        int* err = device_error_word();
+        switch (scheme) {
+            case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
+        }
+    }
     return launch_gemv_int_err(stream, scheme, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word(), true);
 }
 

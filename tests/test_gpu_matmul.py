@@ -380,3 +380,76 @@ def test_tensor_core_gemv_refuses_what_it_cannot_run():
     with pytest.raises(R.RlxqError) as e:
         R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
     assert e.value.status == -2
+
+
+# ------------------------------------------------------------------ the integer-MMA units (batch 3-8 by default)
+IMMA_SHAPES = [("q4_0", 3, 256, 100, False, False), ("q4_0", 4, 4096, 11008, False, False), ("q4_0", 4, 11008, 4096, False, False),
+               ("q4_0", 8, 4096, 11008, False, False), ("q4_0", 7, 8192, 4096, True, False), ("q4_0", 1, 2048, 1000, False, False),
+               ("q8_0", 3, 256, 100, False, False), ("q8_0", 8, 4096, 4096, False, False), ("q8_0", 5, 4096, 4096, True, True),
+               ("q4_k", 3, 256, 100, False, False), ("q4_k", 4, 4096, 14336, False, False), ("q4_k", 8, 2048, 1000, False, False),
+               ("q4_k", 3, 14336, 4096, False, False), ("q4_k", 6, 8192, 3000, True, False), ("q4_k", 2, 1024, 300, False, True)]
+
+
+@pytest.mark.parametrize("inline_q", [0, 1])
+@pytest.mark.parametrize("sch,m,k,n,x_bf16,y_bf16", IMMA_SHAPES)
+def test_integer_mma_gemv_matches_oracle(sch, m, k, n, x_bf16, y_bf16, inline_q):
+    """The integer GEMV with its MMA units (gemv_kernel = 5): same integer products as the dp4a units, so the
+    same bound.  Both ways to quantise the activations (inside the streaming kernel where the shape allows it,
+    and as a kernel of its own), ragged n, whole and cut tiles, twice in a row on the same scratch."""
+    import torch
+    s = O.SCHEMES[sch]
+    w, x = make_case(s, m, k, n, seed=700 + n + m, x_bf16=x_bf16)
+    R.set_option("gemv_kernel", 5)
+    R.set_option("gemv_inline_q", inline_q)
+    try:
+        wd = torch.from_numpy(w).cuda()
+        xd = torch.from_numpy(x).cuda()
+        if x_bf16:
+            xd = xd.to(torch.bfloat16)
+        ws = torch.empty(R.workspace_bytes(s, m, k, n, 1 if x_bf16 else 0, 1 if y_bf16 else 0) + 16, dtype=torch.uint8, device="cuda")
+        outs = []
+        for _ in range(2):
+            y = R.matmul(xd, wd, s, n, out_dtype=torch.bfloat16 if y_bf16 else torch.float32, workspace=ws)
+            outs.append(y.float().cpu().numpy())
+        R.device_status()
+    finally:
+        R.set_option("gemv_inline_q", 0)
+        R.set_option("gemv_kernel", 0)
+    assert np.array_equal(outs[0], outs[1])                       # same bits from run to run
+    ref = reference(s, w, x, n)
+    assert_within_tolerance(outs[0], ref, bound(s, w, x, n), tol=1e-3 if y_bf16 else 2e-4,
+                            what=f"integer-MMA gemv {sch} m={m} k={k} n={n}")
+
+
+def test_integer_mma_gemv_is_the_default_for_batch_3_to_8():
+    """Automatic dispatch and the forced kernel give the same bits for a batch the MMA units take by default."""
+    import torch
+    s = O.Q4_0
+    w, x = make_case(s, 4, 4096, 512, seed=41)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    y_auto = R.matmul(xd, wd, s, 512).cpu().numpy()
+    R.set_option("gemv_kernel", 5)
+    try:
+        y_forced = R.matmul(xd, wd, s, 512).cpu().numpy()
+    finally:
+        R.set_option("gemv_kernel", 0)
+    R.device_status()
+    assert np.array_equal(y_auto, y_forced)
+
+
+def test_integer_mma_gemv_refuses_what_it_cannot_run():
+    import torch
+    R.set_option("gemv_kernel", 5)
+    try:
+        s = O.Q6_K                                               # no MMA unit for this format
+        w, x = make_case(s, 4, 2048, 16, seed=3)
+        with pytest.raises(R.RlxqError) as e:
+            R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
+        assert e.value.status == -2
+        s = O.Q4_0                                               # eight rows of 11008 activations do not fit in shared memory
+        w, x = make_case(s, 8, 11008, 16, seed=4)
+        with pytest.raises(R.RlxqError) as e:
+            R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
+        assert e.value.status == -2
+    finally:
+        R.set_option("gemv_kernel", 0)
