@@ -23,7 +23,7 @@
 // writes the tile, so the consumers never wait on global memory.
 //
 // Two ways to run it:
-//  * single-kernel mode (m*k <= 12288, 16384 with the integer-MMA units; tiles shared by at most
+//  * single-kernel mode (m*k <= 12288; k <= 4096 for three or four rows with the integer-MMA units; tiles shared by at most
 //    two CTAs): the consumer warps
 //    quantise the activations themselves into shared memory.  Two ring stages are requested before
 //    the dependency wait (weights are immutable, so they overlap the previous kernel's tail), then
@@ -62,6 +62,8 @@ constexpr uint32_t int_threads(bool mma) { return (int_warps(mma) + 2) * 32; }  
 constexpr uint32_t int_red_lanes(bool mma) { return mma ? 16u : 32u; }
 constexpr uint32_t kIntRB = 4;                         // ring of reduction buffers between consumers and finisher
 // single-kernel mode: groups of 8 activations a consumer thread quantises (8 for the four-row kernel)
+// integer-MMA units, single-kernel mode: log2 of the activation rows a warp quantises per round
+__host__ __device__ constexpr uint32_t inline_rows_log2(uint32_t m_real) { return m_real >= 3 ? 2u : (m_real == 2 ? 1u : 0u); }
 constexpr uint32_t inline_groups(int mm, bool mma = false) { return mma ? 4u : (mm > 2 ? 8u : 6u); }
 constexpr uint32_t kIntCU = 8;                         // 256-weight units per stage = one per warp
 
@@ -173,18 +175,19 @@ template <int MM> struct QUnitRowHalf {
     __device__ static __forceinline__ void finalize(float (&)[MM], uint32_t) {}
 };
 
-// ---- Q4_0: unit = 8 blocks of 18 bytes.  Lane = (block b = lane & 7, row group rq = lane >> 3): it
+// ---- Q4_0: unit = 8 blocks of 18 bytes.  Lane = (row group rq = lane & 3, block b = lane >> 2): it
 // takes block b of the four tile rows rq, rq + 4, rq + 8, rq + 12.  The 32 activations of block b stay
 // in registers for all four rows, so a weight costs a quarter of the shared-memory traffic a
 // (row, half-unit) mapping pays for re-reading activations; with a row pitch of 8 words mod 32 the
-// weight reads of a warp fall on 32 different banks.  The eight block sums of a row meet in finalize().
+// weight reads of a warp fall on 32 different banks, and the eight lanes that a 16-byte activation
+// load is served for together want two addresses only.  The eight block sums of a row meet in finalize().
 template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
     static constexpr int NT = 4;
     static constexpr int NACC = 4 * MM;
     static constexpr bool HALF_OFFSETS = false;
-    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 3; }
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane & 3u; }
     __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[NT * MM]) {
-        const uint32_t b = L.lane & 7u, odd = b & 1u;
+        const uint32_t b = L.lane >> 2, odd = b & 1u;
         const uint32_t sh = 16u + 16u * odd, dsh = 16u * odd;
         // an even block starts on a word (d, then the quants from byte 2); an odd one two bytes into a word
         const uint32_t p = L.row + u * 144 + 36 * (b >> 1) + 16 * odd;
@@ -235,12 +238,12 @@ template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
 #pragma unroll
         for (int t = 0; t < NT * MM; ++t) {
             float v = tot[t];
-            v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
-            v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
             v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+            v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
             tot[t] = v;
         }
-        // tile row l = rq + 4 i lives in lane group rq = l & 3 as accumulator i = l >> 2
+        // tile row l = rq + 4 i lives in the lanes rq = l & 3 (mod 4) as accumulator i = l >> 2
         float out[MM];
 #pragma unroll
         for (int m = 0; m < MM; ++m) out[m] = 0.f;
@@ -248,7 +251,7 @@ template <int MM> struct QUnit<RLXQ_Q4_0, MM> {
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int m = 0; m < MM; ++m) {
-                const float v = __shfl_sync(0xFFFFFFFFu, tot[i * MM + m], (lane & 3u) * 8u);
+                const float v = __shfl_sync(0xFFFFFFFFu, tot[i * MM + m], lane & 3u);
                 if (lane < 16u && (lane >> 2) == (uint32_t)i) out[m] = v;
             }
 #pragma unroll
@@ -1136,28 +1139,46 @@ __global__ void __launch_bounds__(int_threads(MMA)) gemv_int_kernel(const __grid
             // every load is issued before the first value is used: one trip to L2, not one per group
             const uint32_t gpr = P.k / 8, total = gpr * P.m_real;   // whole warps stay together: gpr % 32 == 0
             constexpr uint32_t kInlineGroups = inline_groups(MM, MMA);
+            // the i-th group of eight activations of this thread: row r, first column c (false: none)
+            auto group_of = [&](uint32_t i, uint32_t& r, uint32_t& c) -> bool {
+                if constexpr (MMA) {
+                    // A warp takes 1, 2 or 4 activation rows (m_real 1, 2, 3+) of 8, 4 or 2 blocks at a time,
+                    // lane = (block, row, which eight values of the block): the same eight values of the next
+                    // block lie 256 bytes further on in the fragment order, so blocks collide on a bank and
+                    // rows do not.
+                    const uint32_t lr = inline_rows_log2(P.m_real);
+                    const uint32_t item = warp + i * CW;             // (group of 8 >> lr blocks, group of four rows)
+                    if (item >= ((P.k / 256) << lr) * (MM / 4)) return false;
+                    const uint32_t bg = item / (MM / 4), rg = item % (MM / 4);
+                    r = 4 * rg + ((lane >> 2) & ((1u << lr) - 1u));
+                    c = (bg * (8u >> lr) + (lane >> (2 + lr))) * 32 + 8 * (lane & 3u);
+                    return true;
+                } else {
+                    const uint32_t g = tid + i * CW * 32;
+                    if (g >= total) return false;
+                    r = MM > 1 ? g / gpr : 0u;
+                    c = (g - r * gpr) * 8;
+                    return true;
+                }
+            };
             uint4 raw[kInlineGroups][2];
 #pragma unroll
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
-                const uint32_t g = tid + i * CW * 32;
-                if (g < total) {
-                    const uint32_t r = MM > 1 ? g / gpr : 0u;
-                    load_raw8(P.x, P.x_bf16, P.k, r, (g - r * gpr) * 8, raw[i]);
-                }
+                uint32_t r, c;
+                raw[i][0] = raw[i][1] = make_uint4(0u, 0u, 0u, 0u);   // rows past m_real (integer-MMA units): zeros
+                if (group_of(i, r, c) && r < P.m_real) load_raw8(P.x, P.x_bf16, P.k, r, c, raw[i]);
             }
             request_first_stage(early, pre);
 #pragma unroll
             for (uint32_t i = 0; i < kInlineGroups; ++i) {
-                const uint32_t g = tid + i * CW * 32;
-                if (g < total) {
-                    const uint32_t r = MM > 1 ? g / gpr : 0u;
+                uint32_t r, c;
+                if (group_of(i, r, c)) {
                     float f[8];
                     raw8_to_f32(raw[i], P.x_bf16, f);
                     if constexpr (MMA)
-                        quantise_store8_frag<MM / 4, frag_sum_is_float(SCHEME)>(f, P.k, (int)SumBias<SCHEME>::value, r, (g - r * gpr) * 8, xs, lane);
+                        quantise_store8_frag<MM / 4, frag_sum_is_float(SCHEME)>(f, P.k, (int)SumBias<SCHEME>::value, r, c, xs, lane);
                     else
-                        quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
-                                                xs + r * P.xq_row_bytes, lane);
+                        quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, c, xs + r * P.xq_row_bytes, lane);
                 }
             }
         }
@@ -1312,7 +1333,11 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
     // dependent-launch hop and a copy on the critical path of a call that lasts only microseconds.
     const int64_t iq = options().gemv_inline_q.load();
-    P.inline_q = (!pair && pl.two_way && (uint64_t)k * m_real <= inline_groups(MM, MMA) * int_warps(MMA) * 32u * 8u && (iq == 2 || iq == 0)) ? 1u : 0u;
+    // what the consumer threads can quantise: groups of eight values each (integer-MMA units: a warp takes
+    // eight blocks of one row, four of two or two of four per round)
+    const bool fits_inline = MMA ? ((uint64_t)k * (MM / 4) << inline_rows_log2(m_real)) <= inline_groups(MM, true) * int_warps(true) * 256u
+                                 : (uint64_t)k * m_real <= inline_groups(MM) * kIntWarps * 32u * 8u;
+    P.inline_q = (!pair && pl.two_way && fits_inline && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
     P.expert_sel = expert_sel;
     P.num_experts = num_experts;
