@@ -91,7 +91,10 @@ RLXQ_API int rlxq_packed_bytes(uint32_t scheme, uint64_t k, uint64_t n, uint64_t
  * (a few bytes per element of x), the partial output tiles of CTAs that share a row tile and
  * their counters: tens to hundreds of KiB (up to 4.9 MB while the option gemv_kernel is 4).  The tensor-core GEMM needs none for most shapes; for few
  * output tiles and a long k it asks for two partial 128 x 256 f32 tiles per SM (39 MB on a 148-SM
- * part) for its stream-K split; without them it runs whole tiles.  The reference reserves k*n*4 bytes. */
+ * part) for its stream-K split; without them it runs whole tiles.  With f32 activations and m > 8 the GEMM runs
+ * on their bf16 hi + lo halves, a chunk of rows at a time: the split rows and the two partial results need up to
+ * about 150 MB (256-byte aligned); without that workspace such a call runs the tiled generic kernel, some 40 times
+ * slower.  The reference reserves k*n*4 bytes. */
 RLXQ_API int rlxq_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n,
                          uint32_t x_dtype, uint32_t y_dtype, size_t* bytes);
 
@@ -105,7 +108,8 @@ RLXQ_API int rlxq_dequant_f32(rlxq_stream_t stream, uint32_t scheme, const void*
 /* Replaces run_dequant_matmul_gguf_gpu (rlx-cuda/src/gguf_gpu.rs:62-134) and the host fallback
  * run_dequant_matmul_gguf (rlx-cuda/src/gguf_host.rs:90-128): y = x . W^T with the blocks
  * decoded inside the kernel.  m <= 8 runs the streaming GEMV; larger m runs the tensor-core
- * GEMM when the shape allows it (rlxq_workspace_bytes tells what it needs), else a tiled kernel.
+ * GEMM when the shape allows it (rlxq_workspace_bytes tells what it needs; f32 activations enter it as two bf16
+ * halves whose results are added, so no activation bit is lost), else a tiled kernel.
  * x: f32 or bf16 [m,k]; y: f32 or bf16 [m,n]; accumulation is f32, a bf16 y is its round-to-nearest-even
  * narrowing (a NaN result of the GEMM is stored as the canonical quiet NaN).  x must be 16-byte aligned, y
  * aligned to its element size, w_blocks to 2 bytes (16 bytes enables the bulk-copy fast paths).

@@ -7,10 +7,36 @@
 
 namespace rlxq {
 
+// Prefill with f32 activations: the tensor-core GEMM takes bf16 operands, so x goes in as hi + lo bf16 halves
+// (twice the rows), `chunk` rows of x at a time, and the two partial results are added.  The scratch holds the
+// 2 * chunk split rows, the 2 * chunk x n f32 partial results (kept under 128 MiB) and the GEMM's own workspace.
+struct SplitPlan { bool ok; uint32_t chunk; size_t off_y2, off_gemm, bytes; };
+static SplitPlan plan_f32_split(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n) {
+    SplitPlan p{};
+    if (m <= 8 || options().gemm_kernel.load() == 1) return p;
+    uint64_t chunk = (128ull << 20) / (8ull * n) / 128 * 128;
+    if (chunk < 128) chunk = 128;
+    if (chunk > 2048) chunk = 2048;
+    if (chunk > m) chunk = m;
+    // the GEMM's own conditions, on an aligned stand-in for the pointers (dispatch checks the real ones)
+    if (!gemm_tc_supported(scheme, 2 * (uint32_t)chunk, k, n, (const void*)256, (const void*)256, true)) return p;
+    auto al = [](size_t v) { return (v + 255) / 256 * 256; };
+    p.chunk = (uint32_t)chunk;
+    p.off_y2 = al((size_t)2 * chunk * k * 2);
+    p.off_gemm = p.off_y2 + al((size_t)2 * chunk * n * 4);
+    p.bytes = p.off_gemm + al(gemm_tc_workspace_bytes(2 * (uint32_t)chunk, k, n));
+    p.ok = true;
+    return p;
+}
+
 size_t matmul_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t x_dtype,
                               uint32_t y_dtype) {
-    (void)x_dtype; (void)y_dtype;
+    (void)y_dtype;
     if (m == 0 || n == 0 || k == 0) return 0;
+    if (m > 8 && x_dtype == RLXQ_F32) {
+        const SplitPlan sp = plan_f32_split(scheme, m, k, n);
+        return sp.ok ? sp.bytes : 0;
+    }
     if (m <= 8) {
         // large enough for whichever GEMV kernel the dispatcher (or a forced option) picks
         const size_t a = staged_workspace_bytes(scheme, m, k, n);
@@ -77,8 +103,27 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
         }
         return launch_matmul_generic(stream, scheme, x, xbf, w, y, ybf, m, k, n);
     }
-    // m > 8: tensor-memory GEMM for bf16 activations, the tiled generic kernel otherwise
+    // m > 8: tensor-memory GEMM for bf16 activations; for f32 activations the same GEMM on their hi + lo bf16
+    // halves when the caller's workspace holds them; the tiled generic kernel otherwise
     const int64_t gforce = options().gemm_kernel.load();
+    if (!xbf && gforce != 1 && !((uintptr_t)w & 15u) && !((uintptr_t)ws & 255u)) {
+        const SplitPlan sp = plan_f32_split(scheme, m, k, n);
+        if (sp.ok && ws && ws_bytes >= sp.bytes) {
+            uint8_t* base = static_cast<uint8_t*>(ws);
+            for (uint32_t r0 = 0; r0 < m; r0 += sp.chunk) {
+                const uint32_t rows = m - r0 < sp.chunk ? m - r0 : sp.chunk;
+                int rc = launch_split_hi_lo(stream, static_cast<const float*>(x) + (size_t)r0 * k, base, rows, k);
+                if (rc) return rc;
+                rc = launch_gemm_tc(stream, scheme, base, w, base + sp.off_y2, false, 2 * rows, k, n, base + sp.off_gemm,
+                                    sp.bytes - sp.off_gemm);
+                if (rc) return rc;
+                rc = launch_add_halves(stream, reinterpret_cast<const float*>(base + sp.off_y2),
+                                       static_cast<uint8_t*>(y) + (size_t)r0 * n * (ybf ? 2 : 4), ybf, rows, n);
+                if (rc) return rc;
+            }
+            return RLXQ_OK;
+        }
+    }
     const bool can = gemm_tc_supported(scheme, m, k, n, w, x, xbf);
     if (gforce == 2 && !can)
         return fail(RLXQ_E_SHAPE, "the tcgen05 GEMM needs bf16 activations, k %% 256 == 0 (2048 for Q6_K), one of Q4_0/Q8_0/Q4_K/Q5_K/Q6_K and 16-byte alignment");

@@ -180,3 +180,46 @@ def test_prefill_configurations_sampled(sch, m, k, n):
         assert_within_tolerance(y[rows][:, c0:c0 + 64], ref, bound(s, wsub, xs, 64), tol=_tol(k), what=f"{sch} cols {c0}")
     # zero rows of x give zero rows of y wherever they are (linearity at full size)
     assert np.isfinite(y).all()
+
+
+# ------------------------------------------------------------------ f32 activations at m > 8
+@pytest.mark.parametrize("sch,m,k,n,y_bf16", [("q4_0", 64, 512, 136, False), ("q8_0", 300, 1024, 200, False),
+                                               ("q4_k", 130, 2048, 77, True), ("q6_k", 40, 2048, 128, False),
+                                               ("q5_k", 9, 512, 64, False)])
+def test_f32_activations_run_the_gemm_on_their_bf16_halves(sch, m, k, n, y_bf16):
+    """x = bf16(x) + bf16(x - bf16(x)) goes through the tensor-core GEMM as 2 m rows and the halves are added:
+    three launches per chunk of rows.  The error is the weight operand's bf16 rounding, as with bf16 activations
+    (simulated on the host for these seeds: up to 3.7e-4 at k = 512); held to min(1e-3, 12e-3 / sqrt(k))."""
+    import torch
+    s = O.SCHEMES[sch]
+    w = O.fill_weights(s, 60 + m, k, n)
+    x = O.fill_normal(61 + m, m * k).reshape(m, k)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    before = R.launch_count()
+    y = R.matmul(xd, wd, s, n, out_dtype=torch.bfloat16 if y_bf16 else torch.float32)
+    assert R.launch_count() - before == 3
+    R.device_status()
+    ref = O.matmul_bt_mt(x, w, m, k, n, s)
+    tol = 1e-3 if y_bf16 else min(1e-3, 1.5 * _tol(k))
+    assert_within_tolerance(y.float().cpu().numpy(), ref, bound(s, w, x, n), tol=tol, what=f"f32-x gemm {sch} {m}x{k}x{n}")
+    # the generic kernel stays available and is tighter (f32 weights)
+    R.set_option("gemm_kernel", 1)
+    yg = R.matmul(xd, wd, s, n).cpu().numpy()
+    assert_within_tolerance(yg, ref, bound(s, w, x, n), tol=2e-5, what="generic kernel")
+
+
+def test_f32_activations_in_row_chunks():
+    """A wide output makes the partial results large, so the rows go through in chunks (here 256 + 44)."""
+    import torch
+    s, m, k, n = O.Q4_0, 300, 256, 65536
+    w = O.fill_weights(s, 7, k, n)
+    x = O.fill_normal(8, m * k).reshape(m, k)
+    wd, xd = torch.from_numpy(w).cuda(), torch.from_numpy(x).cuda()
+    before = R.launch_count()
+    y = R.matmul(xd, wd, s, n).cpu().numpy()
+    assert R.launch_count() - before == 6
+    R.device_status()
+    rows = [0, 1, 255, 256, 257, 299]
+    xs = np.ascontiguousarray(x[rows])
+    ref = O.matmul_bt_mt(xs, w, len(rows), k, n, s)
+    assert_within_tolerance(y[rows], ref, bound(s, w, xs, n), tol=min(1e-3, 1.5 * _tol(k)), what="f32-x gemm in chunks")
