@@ -855,11 +855,14 @@ def sweep_all_configs(torch, R, O, dev, headline_entry: dict) -> list[dict]:
 MOE_WORKLOADS = {
     "q4_k_moe_8x_top2_decode": ("q4_k", 4096, 14336, 8, 2),
     "q4_k_moe_64x_top8_decode": ("q4_k", 2048, 1408, 64, 8),
+    # prefill-sized: 512 tokens x top-2 = 1024 rows over 8 experts (the grouped tensor-core GEMM)
+    "q4_k_moe_8x_top2_prefill": ("q4_k", 4096, 14336, 8, 1024),
 }
 
 
 def run_moe_workload(args, rank, world, local_rank):
-    """Op::DequantGroupedMatMul at decode sizes: `rows` tokens each routed to a different expert."""
+    """Op::DequantGroupedMatMul: `rows` token rows routed over the experts (decode sizes: each row to a different
+    expert, GB/s over the routed slabs; prefill sizes: TFLOP/s)."""
     import torch
     if world != 1:
         raise SystemExit("the MoE workload is single-GPU")
@@ -873,7 +876,10 @@ def run_moe_workload(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     slab = packed_bytes(sch, k, n)
-    step_bytes = rows * (slab + k * 4 + n * 4)              # the routed experts only: the others are never read
+    prefill = rows > 8
+    # decode: the routed experts only (the others are never read); prefill: every expert once
+    step_bytes = (E * slab + rows * (k * 4 + n * 4)) if prefill else rows * (slab + k * 4 + n * 4)
+    step_flops = 2.0 * rows * k * n
     rotation = max(2, -(-2 * L2_BYTES // (E * slab)) + 1)
     w_host = O.fill_weights(sid, 777, k, n * E)
     stacks = [torch.from_numpy(w_host).to(dev)] + [torch.from_numpy(O.fill_weights(sid, 778 + r, k, n * E)).to(dev)
@@ -882,7 +888,11 @@ def run_moe_workload(args, rank, world, local_rank):
     x_dev = torch.from_numpy(x_host).to(dev)
     routes = [torch.from_numpy(np.array([(7 * s + 3 * r) % E for r in range(rows)], np.float32)).to(dev) for s in range(8)]
     y = torch.empty((rows, n), dtype=torch.float32, device=dev)
-    wsb = torch.empty(1 << 22, dtype=torch.uint8, device=dev)
+    import ctypes as C
+    from rlx_b200._lib import lib
+    need = C.c_size_t()
+    assert lib.rlxq_grouped_workspace_bytes(sid, rows, k, n, E, C.byref(need)) == 0
+    wsb = torch.empty(max(need.value, 1 << 22), dtype=torch.uint8, device=dev)
 
     def step(i):
         R.grouped_matmul(x_dev, stacks[i % rotation], routes[i % 8], sid, n, E, out=y, workspace=wsb)
@@ -907,7 +917,21 @@ def run_moe_workload(args, rank, world, local_rank):
     R.device_status()
     clocks = sampler.stop()
     ms_per_step = ev0.elapsed_time(ev1) / args.steps
-    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    value = step_flops / (ms_per_step * 1e-3) / 1e12 if prefill else step_bytes / (ms_per_step * 1e-3) / 1e9
+    # parity of one more step against the oracle, on a sample of rows (rows are independent)
+    last = args.warmup + args.steps
+    step(last)
+    torch.cuda.synchronize()
+    sample = list(range(0, rows, max(1, rows // 8)))[:8]
+    idx_s = routes[last % 8].cpu().numpy()[sample]
+    w_last = w_host if last % rotation == 0 else O.fill_weights(sid, 778 + last % rotation - 1, k, n * E)
+    ref = O.grouped_matmul_bt(np.ascontiguousarray(x_host[sample]), w_last, idx_s, len(sample), k, n, E, sid)
+    got = y.cpu().numpy()[sample]
+    xn = np.sqrt((x_host[sample].astype(np.float64) ** 2).sum(axis=1))
+    wn = np.stack([O.row_norms(sid, w_last[int(e) * slab:(int(e) + 1) * slab], k, n) for e in idx_s])
+    parity_max = float((np.abs(got - ref) / (xn[:, None] * wn)).max())
+    if not parity_max <= 1e-3:
+        raise SystemExit(f"MoE result differs from the oracle: {parity_max:.3e} of |x||w|")
     # end to end: activations and routing from pinned host memory, outputs back to the host
     x_pin = torch.from_numpy(x_host).pin_memory()
     r_pin = routes[1].cpu().pin_memory()
@@ -929,32 +953,48 @@ def run_moe_workload(args, rank, world, local_rank):
         e2e_step(i)
     e2e_s = (time.perf_counter() - t0) / e2e_n
     peak, peak_src = measured_peaks()
+    if prefill:
+        pk = all_peaks()
+        peak = pk["tf_burst"]
+        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops, burst)" if pk["measured"] else "fallback (1.59 PFLOP/s)"
+    unit = "TFLOP/s" if prefill else "GB/s"
+    e2e_value = step_flops / e2e_s / 1e12 if prefill else step_bytes / e2e_s / 1e9
     line = {
-        "metric": "gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "metric": "gemm_tflops" if prefill else "gemv_hbm_gbs", "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": args.workload, "scheme": sch, "k": k, "n": n, "experts": E, "rows_per_step": rows,
-                   "routing": "each row to a different expert, changing every step",
+                   "routing": ("rows dealt evenly over the experts, changing every step" if prefill
+                               else "each row to a different expert, changing every step"),
+                   "parity_max": parity_max,
                    "l2": f"rotating {rotation} expert stacks of {E * slab // 10**6} MB > 2 x 126 MB L2"},
         "clocks": clocks,
-        "e2e": {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": rows * k * 4 + rows * 4,
+        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": rows * k * 4 + rows * 4,
                 "d2h_bytes_per_step": rows * n * 4, "ms_per_step": e2e_s * 1e3,
                 "api": "rlx_b200.grouped_matmul, pinned host buffers"},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
-                     "peak_source": peak_src, "kernel": "grouped matmul kernels of one step", "bytes_per_launch": step_bytes,
+        "roofline": {"bound": "tensor" if prefill else "hbm", "achieved": value, "peak": peak, "unit": unit, "frac": value / peak,
+                     "peak_source": peak_src,
+                     "kernel": ("gemm_tcgen05_kernel in grouped mode (+ sort, tile table, gather, scatter)" if prefill
+                                else "grouped matmul kernels of one step"),
+                     "bytes_per_launch": step_bytes, "flops_per_launch": step_flops,
                      "avg_launch_us": ms_per_step * 1e3, "traffic": None},
     }
     if not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
-        idx = routes[1].cpu().numpy()
-        O.grouped_matmul_bt(x_host, w_host, idx, rows, k, n, E, sid)
+        srows = min(rows, 16)                                 # prefill: a sample of the rows, scaled (rows are independent)
+        idx = routes[1].cpu().numpy()[:srows]
+        xs = np.ascontiguousarray(x_host[:srows])
+        O.grouped_matmul_bt(xs, w_host, idx, srows, k, n, E, sid)
         t0 = time.perf_counter(); reps = 0
         while time.perf_counter() - t0 < 6.0 and reps < 20:
-            O.grouped_matmul_bt(x_host, w_host, idx, rows, k, n, E, sid); reps += 1
-        dt = (time.perf_counter() - t0) / reps
-        line["cpu_baseline"] = {"value": step_bytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                                "sample": f"{reps} full steps, each expert's rows split over {cores} host threads "
+            O.grouped_matmul_bt(xs, w_host, idx, srows, k, n, E, sid); reps += 1
+        dt = (time.perf_counter() - t0) / reps * (rows / srows)
+        line["cpu_baseline"] = {"value": (step_flops / dt / 1e12) if prefill else (step_bytes / dt / 1e9), "unit": unit,
+                                "cores": cores, "kind": "port",
+                                "sample": (f"{reps} passes over {srows} of the {rows} rows, scaled to a full step; " if prefill
+                                           else f"{reps} full steps, ") +
+                                          f"each expert's rows split over {cores} host threads "
                                           "(the reference runs them on one thread)"}
     print(json.dumps(line), flush=True)
 

@@ -9,7 +9,11 @@
  * host, counting-sorts the rows there, runs dequantise + sgemm per expert and copies back; here the
  * counting sort (grouped_moe_sort_plan, gguf_matmul.rs:178-205) runs on the device and one kernel
  * walks every expert's rows, so nothing crosses PCIe and nothing synchronises.  Up to 8 rows (decode)
- * go row by row through the streaming GEMV, the expert picked on the device.
+ * go row by row through the streaming GEMV, the expert picked on the device.  From 32 rows on, for the
+ * formats and shapes the tensor-core GEMM takes (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K; k a multiple of 256, 2048 for
+ * Q6_K; 16-byte aligned stack), every expert's rows are gathered next to each other as bf16 (f32 activations
+ * as hi + lo halves) and one launch of the GEMM in its grouped form multiplies each 128- or 256-row tile by its
+ * expert's slab; the weight operand is bf16(d * q) there, as in rlxq_matmul for m > 8.
  */
 #ifndef RLXQ_MOE_H
 #define RLXQ_MOE_H
@@ -21,7 +25,9 @@ extern "C" {
 #endif
 
 /* Scratch for rlxq_grouped_matmul: expert offsets, the row permutation, per-expert cursors, or (decode
- * sizes) the streaming GEMV's own scratch. */
+ * sizes) the streaming GEMV's own scratch.  For the tensor-core path also the tile table, the gathered
+ * activations (2 m rows of k bf16) and their results (2 m rows of n f32): 2 m (2 k + 4 n) bytes, 256-byte
+ * aligned.  A call given less than that (but enough for the sort) runs the general kernel instead. */
 RLXQ_API int rlxq_grouped_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, uint32_t num_experts,
                                           size_t* bytes);
 

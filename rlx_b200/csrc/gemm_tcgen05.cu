@@ -374,7 +374,26 @@ struct GemmParams {
     uint32_t streamk, kgroups, units_q, units_r;
     float* partial;
     uint32_t* counters;
+    // Grouped mode (MoE expert stacks; null = one dense matrix): W is a stack of [n, k] slabs and activation
+    // tile xt is described by groups[xt] = {first row in x, rows (0 = no such tile), expert, -}: the tile
+    // multiplies those rows by slab `expert`.  The table is written on the device by the kernel in front, and
+    // xtiles is only an upper bound of the tiles in use.  Never combined with the k split.
+    const uint4* groups;
 };
+
+// Where tile `tile` reads and writes: activation rows [xrow0, xlim), weight rows from wrow0 (in the stack).
+struct GemmTileRows { uint32_t xrow0, xlim, wrow0; };
+template <uint32_t TX>
+__device__ __forceinline__ bool gemm_tile_rows(const GemmParams& P, uint32_t tile, GemmTileRows& t) {
+    const uint32_t wt = tile / P.xtiles, xt = tile % P.xtiles;
+    if (P.groups) {
+        const uint4 g = __ldg(&P.groups[xt]);
+        t.xrow0 = g.x; t.xlim = g.x + g.y; t.wrow0 = g.z * P.n + wt * kGemmTileW;
+        return g.y != 0u;
+    }
+    t.xrow0 = xt * TX; t.xlim = P.m; t.wrow0 = wt * kGemmTileW;
+    return true;
+}
 
 
 struct GemmSeg { uint32_t tile, g0, g1; };     // k groups [g0, g1) of one tile
@@ -593,13 +612,14 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
             gemm_seg_init(P, cur, lim);
             GemmSeg sg;
             while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
-                const uint32_t xt = sg.tile % P.xtiles;
+                GemmTileRows tr;
+                if (!gemm_tile_rows<kGemmTileX>(P, sg.tile, tr)) continue;
                 bool ok = true;
                 for (uint32_t kb = 4 * sg.g0; kb < 4 * sg.g1; ++kb) {
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), ph)) { give_up(11); ok = false; break; }
                     const uint32_t full = smem_u32(&bars->b_full[s]);
                     mbar_arrive_expect_tx(full, B_BYTES);
-                    tma_load_2d(smem_u32(b_stage + s * B_BYTES), &P.xmap, (int32_t)(kb * kGemmBK), (int32_t)(xt * kGemmTileX), full);
+                    tma_load_2d(smem_u32(b_stage + s * B_BYTES), &P.xmap, (int32_t)(kb * kGemmBK), (int32_t)tr.xrow0, full);
                     if (++s == kGemmStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -614,13 +634,14 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
             gemm_seg_init(P, cur, lim);
             GemmSeg sg;
             while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
-                const uint32_t wt = sg.tile / P.xtiles;
+                GemmTileRows tr;
+                if (!gemm_tile_rows<kGemmTileX>(P, sg.tile, tr)) continue;
                 bool ok = true;
                 for (uint32_t g = sg.g0; g < sg.g1; ++g) {
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_empty[r]), ph)) { give_up(12); ok = false; break; }
                     const uint32_t full = smem_u32(&bars->raw_full[r]);
                     mbar_arrive_expect_tx(full, RAW_BYTES);
-                    tma_load_2d(smem_u32(raw_stage + r * RAW_STRIDE), &P.wmap, (int32_t)gemm_raw_x<SCHEME>(g), (int32_t)(wt * kGemmTileW), full);
+                    tma_load_2d(smem_u32(raw_stage + r * RAW_STRIDE), &P.wmap, (int32_t)gemm_raw_x<SCHEME>(g), (int32_t)tr.wrow0, full);
                     if (++r == kGemmRawStages) { r = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -634,6 +655,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
             gemm_seg_init(P, cur, lim);
             GemmSeg sg;
             while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+                { GemmTileRows tr; if (!gemm_tile_rows<kGemmTileX>(P, sg.tile, tr)) continue; }
                 if (!mbar_wait(smem_u32(&bars->d_free), dph)) { give_up(13); break; }
                 dph ^= 1u;
                 tc_fence_after();
@@ -666,6 +688,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         gemm_seg_init(P, cur, lim);
         GemmSeg sg;
         while (ok && !*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
+            { GemmTileRows tr; if (!gemm_tile_rows<kGemmTileX>(P, sg.tile, tr)) continue; }
             for (uint32_t g = sg.g0; g < sg.g1 && ok; ++g, kbg0 += 4) {
                 if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_full[r]), rph)) { give_up(15); ok = false; break; }
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
@@ -707,6 +730,8 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
         GemmSeg sg;
         while (!*abort_flag && gemm_seg_next(P, cur, lim, sg)) {
             const uint32_t wt = sg.tile / P.xtiles, xt = sg.tile % P.xtiles;
+            GemmTileRows tr;
+            if (!gemm_tile_rows<kGemmTileX>(P, sg.tile, tr)) continue;
             if (!mbar_wait(smem_u32(&bars->d_full), dph)) { give_up(17); break; }
             dph ^= 1u;
             tc_fence_after();
@@ -753,14 +778,14 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
                     const GemmDst d{reinterpret_cast<uint8_t*>(slot), kGemmTileW, 0u, kGemmTileX, 0u, kGemmTileW};
                     gemm_store_vec<true>(epi_stage, epi_tid, row, v, d, c);
                 } else if (P.y_vec) {
-                    const GemmDst d{reinterpret_cast<uint8_t*>(P.y), P.n, xt * kGemmTileX, P.m, wt * kGemmTileW, P.n};
+                    const GemmDst d{reinterpret_cast<uint8_t*>(P.y), P.n, tr.xrow0, tr.xlim, wt * kGemmTileW, P.n};
                     if (P.y_bf16) gemm_store_vec<false>(epi_stage, epi_tid, row, v, d, c);
                     else gemm_store_vec<true>(epi_stage, epi_tid, row, v, d, c);
                 } else if (n_idx < P.n) {
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) {
-                        const uint32_t m_idx = xt * kGemmTileX + 32 * c + j;
-                        if (m_idx < P.m) {
+                        const uint32_t m_idx = tr.xrow0 + 32 * c + j;
+                        if (m_idx < tr.xlim) {
                             const size_t o = (size_t)m_idx * P.n + n_idx;
                             if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)bf16x2_of(f32x2(v[j], 0u));
                             else reinterpret_cast<float*>(P.y)[o] = __uint_as_float(v[j]);
@@ -829,7 +854,8 @@ size_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k, uint32_t n) {
 
 template <uint32_t SCHEME, uint32_t TX>
 static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
-                         uint32_t k, uint32_t n, void* ws, bool streamk) {
+                         uint32_t k, uint32_t n, void* ws, bool streamk, const uint4* groups = nullptr,
+                         uint32_t group_tiles = 0, uint32_t num_slabs = 1) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
     constexpr uint32_t RAW_STRIDE = (kGemmTileW * RAW_ROW + 127) / 128 * 128;
     Geometry g;
@@ -837,12 +863,13 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     GemmParams P{};
     int rc = encode_bf16_kmajor_map(&P.xmap, x, m, k, TX);
     if (rc) return rc;
-    rc = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, RAW_ROW / 8, kGemmTileW);
+    rc = encode_weight_map(&P.wmap, w, (uint64_t)n * num_slabs, (uint64_t)k / g.elems * g.bytes, RAW_ROW / 8, kGemmTileW);
     if (rc) return rc;
     P.y = y; P.m = m; P.n = n; P.k = k; P.y_bf16 = ybf;
+    P.groups = groups;
     P.y_vec = (((uintptr_t)y & 15u) == 0 && n % (ybf ? 8u : 4u) == 0) ? 1u : 0u;
     P.wtiles = (n + kGemmTileW - 1) / kGemmTileW;
-    P.xtiles = (m + TX - 1) / TX;
+    P.xtiles = groups ? group_tiles : (m + TX - 1) / TX;
     P.kgroups = k / 256;
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
@@ -892,6 +919,32 @@ static int launch_gemm_s(cudaStream_t stream, const void* x, const uint8_t* w, v
     const bool narrow = force ? force == 128 : (ntiles256 * 4 < sms * 3);
     if (narrow) return launch_gemm_t<SCHEME, 128>(stream, x, w, y, ybf, m, k, n, nullptr, false);
     return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n, nullptr, false);
+}
+
+// Grouped form for MoE expert stacks: x holds x_rows gathered bf16 activation rows, w a stack of num_slabs
+// [n, k] slabs, groups[0 .. group_tiles) the device-side table of activation tiles of tile_rows (128 or 256) rows
+// (GemmParams::groups), y2 the f32 result rows in the order of x.
+template <uint32_t SCHEME>
+static int launch_gemm_grouped_s(cudaStream_t stream, const void* x, uint32_t x_rows, const uint8_t* w, uint32_t num_slabs,
+                                 float* y2, uint32_t k, uint32_t n, const uint4* gt, uint32_t group_tiles, uint32_t tile_rows) {
+    if (tile_rows == 256) return launch_gemm_t<SCHEME, 256>(stream, x, w, y2, false, x_rows, k, n, nullptr, false, gt, group_tiles, num_slabs);
+    return launch_gemm_t<SCHEME, 128>(stream, x, w, y2, false, x_rows, k, n, nullptr, false, gt, group_tiles, num_slabs);
+}
+
+int launch_gemm_grouped(cudaStream_t stream, uint32_t scheme, const void* x, uint32_t x_rows, const uint8_t* w,
+                        uint32_t num_slabs, float* y2, uint32_t k, uint32_t n, const void* groups, uint32_t group_tiles,
+                        uint32_t tile_rows) {
+    const uint4* gt = static_cast<const uint4*>(groups);
+    if ((uint64_t)n * num_slabs > 0x7FFFFFFFull) return fail(RLXQ_E_LIMIT, "expert stack too tall for a tensor map");
+    if (tile_rows != 128 && tile_rows != 256) return fail(RLXQ_E_ARG, "activation tiles are 128 or 256 rows");
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_gemm_grouped_s<RLXQ_Q4_0>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q8_0: return launch_gemm_grouped_s<RLXQ_Q8_0>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q4_K: return launch_gemm_grouped_s<RLXQ_Q4_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q5_K: return launch_gemm_grouped_s<RLXQ_Q5_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q6_K: return launch_gemm_grouped_s<RLXQ_Q6_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        default: return fail(RLXQ_E_SCHEME, "unknown scheme");
+    }
 }
 
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,

@@ -38,6 +38,9 @@ int launch_gemv_tc(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf
 // tcgen05 / tensor-memory GEMM (m > 8, bf16 activations).
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf);
 size_t gemm_tc_workspace_bytes(uint32_t m, uint32_t k, uint32_t n);
+int launch_gemm_grouped(cudaStream_t stream, uint32_t scheme, const void* x, uint32_t x_rows, const uint8_t* w,
+                        uint32_t num_slabs, float* y2, uint32_t k, uint32_t n, const void* groups, uint32_t group_tiles,
+                        uint32_t tile_rows);
 int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const uint8_t* w, void* y, bool ybf,
                    uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
 

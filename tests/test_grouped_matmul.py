@@ -127,7 +127,53 @@ def test_gpu_grouped_matches_oracle(sch, m, k, n, E, x_bf16):
     wn = np.stack([O.row_norms(s, w[e * slab:(e + 1) * slab], k, n) for e in range(E)])    # [E, n]
     xn = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
     bnd = xn[:, None] * wn[idx.astype(np.int64)]
-    assert_within_tolerance(y, ref, bnd, tol=2e-5, what=f"grouped {sch} m={m} E={E}")
+    # 32 rows and more of a format and shape the tensor-core GEMM takes run there (weights rounded to bf16)
+    on_gemm = m >= 32 and sch in ("q4_0", "q8_0", "q4_k", "q5_k", "q6_k") and k % (2048 if sch == "q6_k" else 256) == 0
+    tol = min(1e-3, 12e-3 / np.sqrt(k)) if on_gemm else 2e-5
+    assert_within_tolerance(y, ref, bnd, tol=tol, what=f"grouped {sch} m={m} E={E}")
+    if on_gemm:
+        import rlx_b200 as R
+        R.set_option("gemm_kernel", 1)                        # the general kernel stays available, and is tighter
+        try:
+            y = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16)
+        finally:
+            R.set_option("gemm_kernel", 0)
+        assert_within_tolerance(y, ref, bnd, tol=2e-5, what=f"grouped, general kernel {sch} m={m} E={E}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sch,m,k,n,E,x_bf16,y_bf16", [("q4_k", 300, 1024, 200, 8, False, False), ("q4_0", 700, 512, 136, 3, True, False),
+                                                       ("q8_0", 96, 256, 64, 24, False, True), ("q6_k", 260, 2048, 130, 4, False, False),
+                                                       ("q5_k", 1000, 512, 128, 5, True, True)])
+def test_gpu_prefill_sized_batches_take_the_tensor_core_gemm(sch, m, k, n, E, x_bf16, y_bf16):
+    """Sort, tile table, gather (f32 rows as bf16 hi + lo), one grouped GEMM launch over all experts, scatter:
+    five launches.  Ragged groups: experts with no rows, with a few, with several 128-row tiles; ids out of range."""
+    import torch
+    import rlx_b200 as R
+    from tests.helpers import assert_within_tolerance
+    s = O.SCHEMES[sch]
+    w = O.fill_weights(s, 70 + m, k, n * E)
+    x = O.fill_normal(71 + m, m * k).reshape(m, k)
+    if x_bf16:
+        x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)).reshape(m, k)
+    rng = np.random.default_rng(m + E)
+    p = rng.random(E) ** 3
+    p[rng.integers(0, E)] = 0.0                                # at least one expert without rows
+    idx = rng.choice(E, size=m, p=p / p.sum()).astype(np.float32)
+    idx[5], idx[17] = float(E), float(E + 3)                   # in no group: zero rows
+    before = R.launch_count()
+    y = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16, y_bf16=y_bf16)
+    assert R.launch_count() - before == 5
+    y_again = _gpu(x, w, idx, s, n, E, x_bf16=x_bf16, y_bf16=y_bf16)
+    assert np.array_equal(y, y_again)
+    ref = O.grouped_matmul_bt(x, w, idx, m, k, n, E, s)
+    assert np.all(y[5] == 0) and np.all(y[17] == 0) and np.all(ref[5] == 0)
+    slab = w.size // E
+    wn = np.stack([O.row_norms(s, w[e * slab:(e + 1) * slab], k, n) for e in range(E)])
+    xn = np.sqrt((x.astype(np.float64) ** 2).sum(axis=1))
+    bnd = xn[:, None] * wn[np.minimum(idx.astype(np.int64), E - 1)]
+    tol = 1e-3 if y_bf16 else min(1e-3, 12e-3 / np.sqrt(k))
+    assert_within_tolerance(y, ref, bnd, tol=tol, what=f"grouped GEMM {sch} m={m} E={E}")
 
 
 @pytest.mark.gpu
