@@ -63,9 +63,10 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
     if ((uintptr_t)x & 15u) return fail(RLXQ_E_ALIGN, "x must be 16-byte aligned");
     if ((uintptr_t)y & (ybf ? 1u : 3u)) return fail(RLXQ_E_ALIGN, "y must be aligned to its element size");
     if (m <= 8) {
-        // 0 = automatic: the integer kernel with its dp4a units for batch 1-2, with its integer-MMA units for batch
-        // 3-8 (and batch 2 of the formats with 32-weight blocks, where it already wins), then the staged tensor-mode
-        // kernel, then the generic one.  The dp4a units also run batch 3-4, but only when asked for with gemv_kernel = 3.
+        // 0 = automatic: the integer kernel with its dp4a units for batch 1, with its integer-MMA units for batch
+        // 2-8 (measured at batch 2: level on Q4_K 4096 -> 14336, 5-15 % ahead elsewhere), then the dp4a units again
+        // (batch 2, formats without an MMA unit), the staged tensor-mode kernel, the generic one.  The dp4a units
+        // also run batch 3-4, but only when asked for with gemv_kernel = 3.
         const int64_t force = options().gemv_kernel.load();
         const bool can_int = m <= 4 && int_supported(scheme, m, k, n, w, x);
         const bool can_tc = staged_supported(scheme, m, k, n, w, x, xbf);
@@ -82,8 +83,7 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
             return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
         if (force == 2 && !can_tc)
             return fail(RLXQ_E_SHAPE, "staged GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
-        const bool mma_first = m >= 3 || (m == 2 && (scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0));
-        if (force == 0 && mma_first && int_mma_supported(scheme, m, k, n, w, x))
+        if (force == 0 && m >= 2 && int_mma_supported(scheme, m, k, n, w, x))
             return launch_gemv_int_mma(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 3 || (force == 0 && can_int && m <= 2))
             return launch_gemv_int(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);

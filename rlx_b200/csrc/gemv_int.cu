@@ -472,7 +472,12 @@ __device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1,
 
 // Bytes of the fragment-ordered activations of mmg groups of four rows, and where their scales start.
 __host__ __device__ constexpr uint32_t frag_scale_offset(uint32_t k, uint32_t mmg) { return (k / 32) * mmg * 256; }
-__host__ __device__ constexpr uint32_t frag_total_bytes(uint32_t k, uint32_t mmg) { return (k / 32) * mmg * (256 + 32); }
+// A scale entry is {scale, bias * sum} (8 bytes) or, for formats whose offsets need the sums of 16 values,
+// {scale, bias * sum of the first 16, bias * sum of the second 16, -} (16 bytes).
+__host__ __device__ constexpr uint32_t frag_entry_bytes(uint32_t sub) { return sub == 16 ? 16u : 8u; }
+__host__ __device__ constexpr uint32_t frag_total_bytes(uint32_t k, uint32_t mmg, uint32_t sub) {
+    return (k / 32) * mmg * (256 + 4 * frag_entry_bytes(sub));
+}
 
 template <uint32_t SCHEME, int MM> struct QUnitMma;
 
@@ -646,6 +651,89 @@ template <int MM> struct QUnitMma<RLXQ_Q4_K, MM> {
     __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
 };
 
+__device__ __forceinline__ void imma16_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+// ---- Q6_K: 16-weight sub-blocks with an int8 scale each, so the MMA is the k = 16 shape, two per 32-weight
+// group (the B fragment's b0 and b1 serve one each).  The warp's part of the unit is one half of the super-block:
+// ql words t, 4+t, 8+t, 12+t and qh words t, 4+t of the half hold lane t's bytes of all four groups (low / high
+// nibble of ql[l] and ql[l+32], two bits of qh[l] each).  The six-bit quants go in unsigned; the -32 comes from
+// the block sums of 16 activations.  Both sub-blocks of a group share d and the activation scale, so their int8
+// scales are applied in integers (|sum| < 2^31) and one conversion and one FMA finish the group.  A unit starts
+// 2 bytes off a word when its index is odd: words are read from the aligned address below and funnel-shifted.
+template <int MM> struct QUnitMma<RLXQ_Q6_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    // word i (0 .. n-1, 4 bytes apart from byte offset `off` of the unit) for this lane's row
+    template <int N>
+    __device__ static __forceinline__ void words(uint32_t pa, uint32_t off, uint32_t stride, uint32_t sh, bool odd, uint32_t (&w)[N]) {
+        if (odd) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) w[i] = __funnelshift_r(lds32(pa + off + stride * i), lds32(pa + off + stride * i + 4), sh);
+        } else {
+#pragma unroll
+            for (int i = 0; i < N; ++i) w[i] = lds32(pa + off + stride * i);
+        }
+    }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const bool odd = u & 1u;
+        const uint32_t sh = odd ? 16u : 0u;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 64) + t * 16;
+        uint32_t ql[2][4], qh[2][2], scw[2][2];
+        float d[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t pa = L.row + 8 * r * L.row_pitch + u * 210 - (odd ? 2u : 0u);
+            words<4>(pa, 64 * part + 4 * t, 16, sh, odd, ql[r]);
+            words<2>(pa, 128 + 32 * part + 4 * t, 16, sh, odd, qh[r]);
+            words<2>(pa, 192 + 8 * part, 4, sh, odd, scw[r]);
+            d[r] = f16_bits_to_f32((lds32(pa + 208) >> sh) & 0xFFFFu);
+        }
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {               // the four 32-weight groups of the half
+            uint32_t a[2][2];                          // [sub-block][row]
+#pragma unroll
+            for (int sbk = 0; sbk < 2; ++sbk)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint32_t lo = (ql[r][2 * (gq & 1) + sbk] >> (4 * (gq >> 1))) & 0x0F0F0F0Fu;
+                    const uint32_t hv = qh[r][sbk];
+                    const uint32_t hi = (gq < 2 ? (hv << (4 - 2 * gq)) : (hv >> (2 * gq - 4))) & 0x30303030u;
+                    a[sbk][r] = lo | hi;
+                }
+            int sc[2][2];                              // [sub-block][row]
+#pragma unroll
+            for (int sbk = 0; sbk < 2; ++sbk)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int si = 2 * gq + sbk;
+                    sc[sbk][r] = (int)(int8_t)((scw[r][si >> 2] >> (8 * (si & 3))) & 0xFFu);
+                }
+#pragma unroll
+            for (int g2 = 0; g2 < MMG; ++g2) {
+                const uint2 bb = lds64(fb + (gq * MMG + g2) * 256);
+                const uint4 se = lds128(sb + (gq * MMG + g2) * 64);      // scale, -32 * sum of 16, -32 * sum of the next 16
+                int c0[4], c1[4];
+                imma16_u8s8(c0, a[0][0], a[0][1], bb.x);
+                imma16_u8s8(c1, a[1][0], a[1][1], bb.y);
+                const float s = __uint_as_float(se.x);
+                const int v0 = (c0[0] * 128 + c0[1] + (int)se.y) * sc[0][0] + (c1[0] * 128 + c1[1] + (int)se.z) * sc[1][0];
+                const int v8 = (c0[2] * 128 + c0[3] + (int)se.y) * sc[0][1] + (c1[2] * 128 + c1[3] + (int)se.z) * sc[1][1];
+                tot[2 * g2] = fmaf(d[0] * s, (float)v0, tot[2 * g2]);
+                tot[2 * g2 + 1] = fmaf(d[1] * s, (float)v8, tot[2 * g2 + 1]);
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
 // What the per-block integer sums are multiplied by before they are stored.
 template <uint32_t SCHEME> struct SumBias;
 template <> struct SumBias<RLXQ_Q4_0> { static constexpr int value = -8; };
@@ -764,7 +852,7 @@ __device__ __forceinline__ void quantise_store8(const float (&f)[8], uint32_t k,
 // of four rows][lane]{b0, b1} and, from byte frag_scale_offset(k, MMG) on, [block][row]{scale, bias * sum}.
 // Column 2 (r & 3) + limb of the MMA's B operand is (activation row r, limb); lane 4 col + t holds k = 4t ..
 // 4t+3 in b0 and k = 16+4t .. in b1.
-template <int MMG, bool FSUM>
+template <int MMG, bool FSUM, uint32_t SUB>
 __device__ __forceinline__ void quantise_store8_frag(const float (&f)[8], uint32_t k, int bias, uint32_t r, uint32_t c,
                                                      uint8_t* dst, uint32_t lane) {
     float amax = 0.f;
@@ -794,10 +882,17 @@ __device__ __forceinline__ void quantise_store8_frag(const float (&f)[8], uint32
     fr[2 * (4 * (col + 1) + t0)] = lw[0];
     fr[2 * (4 * (col + 1) + t0 + 1)] = lw[1];
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-    if ((lane & 3u) == 0)
-        *reinterpret_cast<uint2*>(dst + frag_scale_offset(k, MMG) + ((size_t)blk * MMG * 4 + r) * 8) =
-            make_uint2(__float_as_uint(s), FSUM ? __float_as_uint(s * (float)(bias * sum)) : (uint32_t)(bias * sum));
+    if constexpr (SUB == 16) {
+        // lanes 0 and 2 of the block's four hold the sums of its two halves
+        uint32_t* e = reinterpret_cast<uint32_t*>(dst + frag_scale_offset(k, MMG) + ((size_t)blk * MMG * 4 + r) * 16);
+        if ((lane & 3u) == 0) { e[0] = __float_as_uint(s); e[1] = (uint32_t)(bias * sum); }
+        if ((lane & 3u) == 2) e[2] = (uint32_t)(bias * sum);
+    } else {
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if ((lane & 3u) == 0)
+            *reinterpret_cast<uint2*>(dst + frag_scale_offset(k, MMG) + ((size_t)blk * MMG * 4 + r) * 8) =
+                make_uint2(__float_as_uint(s), FSUM ? __float_as_uint(s * (float)(bias * sum)) : (uint32_t)(bias * sum));
+    }
 }
 
 template <uint32_t SUB, int MMG = 0, bool FSUM = false>
@@ -818,7 +913,7 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
     float f[8];
     if (swiglu_pair) load_group8_swiglu(x, k, r, c, f);
     else load_group8(x, x_bf16, k, r, c, f);
-    if constexpr (MMG > 0) quantise_store8_frag<MMG, FSUM>(f, k, bias, r, c, xq, lane);   // fragment order (integer-MMA units)
+    if constexpr (MMG > 0) quantise_store8_frag<MMG, FSUM, SUB>(f, k, bias, r, c, xq, lane);   // fragment order (integer-MMA units)
     else quantise_store8<SUB>(f, k, bias, c, xq + (size_t)r * xq_row_bytes, lane);
 }
 
@@ -877,7 +972,7 @@ __device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& r
 // Kernel 2: the streaming kernel
 // ---------------------------------------------------------------------------------------------
 template <uint32_t SCHEME, int MM, bool MMA = false>
-__global__ void __launch_bounds__(int_threads(MMA)) gemv_int_kernel(const __grid_constant__ IntParams P) {
+__global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gemv_int_kernel(const __grid_constant__ IntParams P) {
     constexpr uint32_t CW = int_warps(MMA), WPU = CW / kIntCU, RL = int_red_lanes(MMA);
     using T = StagedTraits<SCHEME>;
     using B = IntBox<SCHEME, MMA>;
@@ -1176,7 +1271,7 @@ __global__ void __launch_bounds__(int_threads(MMA)) gemv_int_kernel(const __grid
                     float f[8];
                     raw8_to_f32(raw[i], P.x_bf16, f);
                     if constexpr (MMA)
-                        quantise_store8_frag<MM / 4, frag_sum_is_float(SCHEME)>(f, P.k, (int)SumBias<SCHEME>::value, r, c, xs, lane);
+                        quantise_store8_frag<MM / 4, frag_sum_is_float(SCHEME), T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, r, c, xs, lane);
                     else
                         quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, c, xs + r * P.xq_row_bytes, lane);
                 }
@@ -1242,7 +1337,9 @@ struct IntPlan {
 };
 
 // Formats that have a integer-MMA unit (QUnitMma).
-constexpr bool int_has_mma(uint32_t scheme) { return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K; }
+constexpr bool int_has_mma(uint32_t scheme) {
+    return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q6_K;
+}
 
 template <uint32_t SCHEME, bool MMA = false>
 static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
@@ -1261,9 +1358,9 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     pl.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;      // a multiple of 16: k % 256 == 0
     pl.xq_pieces = mm;
     if (MMA) {                                                       // fragment order, fetched in 8 equal pieces
-        if ((uint64_t)k * (mm / 4) * 9 > 220u * 1024u) return pl;
+        if ((uint64_t)frag_total_bytes(k, mm / 4, T::SUB) > 220u * 1024u) return pl;
         pl.xq_pieces = 8;
-        pl.xq_row_bytes = frag_total_bytes(k, mm / 4) / 8;           // 9 k MMG / 8: a multiple of 16
+        pl.xq_row_bytes = frag_total_bytes(k, mm / 4, T::SUB) / 8;   // 9 (or 10) k MMG / 8: a multiple of 16
     }
     const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * pl.xq_pieces, 128);
     const uint32_t red_bytes = kIntRB * int_warps(MMA) * int_red_lanes(MMA) * mm * 4;
@@ -1441,6 +1538,7 @@ bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
         case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0, true>(m, k, n).ok;
         case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0, true>(m, k, n).ok;
         case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K, true>(m, k, n).ok;
+        case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K, true>(m, k, n).ok;
         default: return false;
     }
 }
@@ -1451,6 +1549,7 @@ size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t
         case RLXQ_Q4_0: pl = plan_int<RLXQ_Q4_0, true>(m, k, n); break;
         case RLXQ_Q8_0: pl = plan_int<RLXQ_Q8_0, true>(m, k, n); break;
         case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K, true>(m, k, n); break;
+        case RLXQ_Q6_K: pl = plan_int<RLXQ_Q6_K, true>(m, k, n); break;
         default: break;
     }
     return pl.ok ? pl.ws_bytes : 0;
@@ -1463,6 +1562,7 @@ int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, boo
         case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
     }
 }
@@ -1501,12 +1601,13 @@ int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, 
 // activation quantiser, so the row-parallel down projection of an FFN needs no kernel in between.
 int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
                            uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
-    if (m > 2) {   // batch 3-8: the integer-MMA units
+    if (m >= 2 && int_mma_supported(scheme, m, k, n, w, gu)) {   // batch 2-8: the integer-MMA units
         int* err = device_error_word();
         switch (scheme) {
             case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
         }
     }

@@ -116,7 +116,7 @@ int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t 
     // gu is [m, 2f] with gate in columns [0, f) and up in [f, 2f)
     if (options().gemv_kernel.load() == 0 &&
         ((m <= 2 && int_supported(scheme_down, m, ffn_local, d_model, down_blocks, gu)) ||
-         (m > 2 && m <= 8 && int_mma_supported(scheme_down, m, ffn_local, d_model, down_blocks, gu)))) {
+         (m >= 2 && m <= 8 && int_mma_supported(scheme_down, m, ffn_local, d_model, down_blocks, gu)))) {
         // decode: the down projection's activation quantiser forms up * silu(gate) itself
         return launch_gemv_int_swiglu((cudaStream_t)stream, scheme_down, gu, (const uint8_t*)down_blocks, y_partial, false, m,
                                       ffn_local, d_model, ws, mm);
