@@ -98,6 +98,10 @@ struct IntParams {
     uint32_t nstages;
     uint32_t xq_row_bytes; // bytes of one row of xq (integer-MMA units: of one of the equal pieces it is fetched in)
     uint32_t xq_pieces;    // bulk copies that fetch xq: one per activation row (integer-MMA units: 8)
+    // Integer-MMA units when the fragments of all rows do not fit in shared memory: nothing of xq is resident;
+    // every ring stage carries, behind its weights, the fragments and scale entries of its own 2048-weight
+    // chunk (two bulk copies from the workspace, out of L2).  stage_stride: bytes from one ring stage to the next.
+    uint32_t xstream, stage_stride;
     uint32_t off_stage, off_red, off_bar;
     // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
     // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
@@ -1015,7 +1019,7 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
     __syncthreads();
     // The first fill of the ring is spread over the warps, one stage each: a TMA request occupies its
     // issuing thread for a few hundred cycles, and one thread issuing them all delays the stream's start.
-    const uint32_t pre = min(min(NS, CW), rg.len);
+    const uint32_t pre = P.xstream ? 0u : min(min(NS, CW), rg.len);
 
     // expert-indirect mode: every role learns the slab after the dependency wait (nothing is requested
     // before it) and leaves at once when the id is out of range
@@ -1037,15 +1041,35 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
             // rows past n and bytes past the row end arrive as zeros (d = 0: they add nothing)
             const uint32_t full = smem_u32(&bars[s]);
             if (lane == 0) {
-                mbar_arrive_expect_tx(full, stage_bytes);
+                uint32_t xb_frag = 0, xb_scale = 0;
+                if constexpr (MMA) {
+                    if (P.xstream) {                  // this chunk's blocks of 32 activations: fragments and scale entries
+                        const uint32_t blocks = min(kIntCU, ku - chunk * kIntCU) * 8u;
+                        xb_frag = blocks * (MM / 4) * 256u;
+                        xb_scale = blocks * (MM / 4) * 4u * frag_entry_bytes(T::SUB);
+                    }
+                }
+                mbar_arrive_expect_tx(full, stage_bytes + xb_frag + xb_scale);
 #pragma unroll
                 for (uint32_t b = 0; b < B::NB; ++b)
-                    tma_load_2d(smem_u32(stages + s * stage_bytes + b * B::BOX_BYTES), &P.wmap,
+                    tma_load_2d(smem_u32(stages + s * P.stage_stride + b * B::BOX_BYTES), &P.wmap,
                                 (int32_t)(((chunk * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(row_off + tile * 16), full);
+                if constexpr (MMA) {
+                    if (P.xstream) {
+                        constexpr uint32_t FC = kIntCU * 8u * (MM / 4) * 256u, SC = kIntCU * 8u * (MM / 4) * 4u * frag_entry_bytes(T::SUB);
+                        const uint32_t dst = smem_u32(stages + s * P.stage_stride + stage_bytes);
+                        bulk_g2s(dst, P.xq + (size_t)chunk * FC, xb_frag, full);
+                        bulk_g2s(dst + FC, P.xq + frag_scale_offset(P.k, MM / 4) + (size_t)chunk * SC, xb_scale, full);
+                    }
+                }
             }
         };
         uint32_t s = 0, ph = 1, issued = 0;   // ph: parity to wait for on empty[s] (1 passes on a fresh barrier)
         bool waited = false, dead = false;
+        if (P.xstream) {     // every stage carries activations: nothing can be requested before they exist
+            waited = true;
+            griddep_wait();
+        }
         for (uint32_t si = 0; si < nseg && !dead; ++si) {
             const Segment sg = segment_at(P, rg, si);
             for (uint32_t c = sg.c0; c < sg.c1; ++c, ++issued) {
@@ -1054,9 +1078,9 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
                     waited = true;
                     griddep_wait();
                     const uint32_t xbar = smem_u32(&bars[2 * NS]);
-                    if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
+                    if (lane == 0 && !P.inline_q && !P.xstream) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
                     __syncwarp();
-                    if (lane < P.xq_pieces && !P.inline_q)
+                    if (lane < P.xq_pieces && !P.inline_q && !P.xstream)
                         bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
                 }
                 if (issued >= NS) {
@@ -1073,9 +1097,9 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
         if (!waited) {   // fewer chunks than stages: everything is in flight, now fetch the activations
             griddep_wait();
             const uint32_t xbar = smem_u32(&bars[2 * NS]);
-            if (lane == 0 && !P.inline_q) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
+            if (lane == 0 && !P.inline_q && !P.xstream) mbar_arrive_expect_tx(xbar, P.xq_row_bytes * P.xq_pieces);
             __syncwarp();
-            if (lane < P.xq_pieces && !P.inline_q)
+            if (lane < P.xq_pieces && !P.inline_q && !P.xstream)
                 bulk_g2s(smem_u32(xs + lane * P.xq_row_bytes), P.xq + (size_t)lane * P.xq_row_bytes, P.xq_row_bytes, xbar);
         }
         return;
@@ -1205,7 +1229,7 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
             mbar_arrive_expect_tx(full, stage_bytes);
 #pragma unroll
             for (uint32_t b = 0; b < B::NB; ++b)
-                tma_load_2d(smem_u32(stages + warp * stage_bytes + b * B::BOX_BYTES), &P.wmap,
+                tma_load_2d(smem_u32(stages + warp * P.stage_stride + b * B::BOX_BYTES), &P.wmap,
                             (int32_t)((((sg.c0 + i) * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(row_off + sg.tile * 16), full);
         }
     };
@@ -1278,7 +1302,7 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
             }
         }
         consumer_bar_n<CW * 32>();
-    } else if (!mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+    } else if (!P.xstream && !mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
         dead = true;
         if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
     }
@@ -1296,10 +1320,18 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
             if (!dead) {
                 const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
                 const uint32_t uw = warp / WPU;                   // the unit of the stage this warp works on
-                L.row = stages_u32 + s * stage_bytes + (uw / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                L.row = stages_u32 + s * P.stage_stride + (uw / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                uint32_t kb = (chunk * kIntCU + uw) * 256;
+                if constexpr (MMA) {
+                    if (P.xstream) {                  // the stage's own fragments and scale entries, indexed inside the chunk
+                        L.xh = stages_u32 + s * P.stage_stride + stage_bytes;
+                        L.sb = L.xh + kIntCU * 8u * (MM / 4) * 256u;
+                        kb = uw * 256;
+                    }
+                }
                 if (uw < cu) {
-                    if constexpr (MMA) QU::run(L, uw % B::UB, (chunk * kIntCU + uw) * 256, tot, warp % WPU);
-                    else QU::run(L, uw % B::UB, (chunk * kIntCU + uw) * 256, tot);
+                    if constexpr (MMA) QU::run(L, uw % B::UB, kb, tot, warp % WPU);
+                    else QU::run(L, uw % B::UB, kb, tot);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
@@ -1333,6 +1365,7 @@ struct IntPlan {
     uint32_t grid, ntiles, nchunks, total_chunks, slots, nstages;
     bool two_way;
     uint32_t xq_row_bytes, xq_pieces, off_stage, off_red, off_bar, smem_bytes;
+    uint32_t xstream, stage_stride;
     size_t ws_xq, ws_partial, ws_counters, ws_bytes;
 };
 
@@ -1357,24 +1390,32 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     if ((uint64_t)pl.ntiles * pl.nchunks > 0xFFFFFFFFull / 2) return pl;
     pl.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;      // a multiple of 16: k % 256 == 0
     pl.xq_pieces = mm;
+    uint32_t stage_stride = stage_bytes;
     if (MMA) {                                                       // fragment order, fetched in 8 equal pieces
-        if ((uint64_t)frag_total_bytes(k, mm / 4, T::SUB) > 220u * 1024u) return pl;
+        if ((uint64_t)k * (mm / 4) * 10 > 0x7FFFFFFFull) return pl;
         pl.xq_pieces = 8;
         pl.xq_row_bytes = frag_total_bytes(k, mm / 4, T::SUB) / 8;   // 9 (or 10) k MMG / 8: a multiple of 16
     }
-    const uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * pl.xq_pieces, 128);
+    uint32_t fixed = (uint32_t)align((size_t)pl.xq_row_bytes * pl.xq_pieces, 128);
     const uint32_t red_bytes = kIntRB * int_warps(MMA) * int_red_lanes(MMA) * mm * 4;
     const uint32_t tail = red_bytes + 1024;                            // reduction buffers, barriers, flags
+    if (MMA && (uint64_t)fixed + tail + 2 * stage_bytes > 226u * 1024u) {
+        // the fragments of all rows do not fit beside a ring: none stay resident, every stage carries its chunk's
+        pl.xstream = 1;
+        fixed = 0;
+        stage_stride = stage_bytes + kIntCU * 8u * (mm / 4) * (256u + 4u * frag_entry_bytes(T::SUB));
+    }
     // two CTAs per SM when that still leaves each a ring of >= 4 stages, else one
     const uint32_t budget2 = 113u * 1024u, budget1 = 226u * 1024u;
     uint32_t per_sm = 2, budget = budget2;
     // the four-row kernel keeps 64 activation words in registers: one CTA per SM
-    if (mm > 2 || fixed + tail + 4 * stage_bytes > budget2) { per_sm = 1; budget = budget1; }
-    if (fixed + tail + 2 * stage_bytes > budget) return pl;          // activations do not fit: not this kernel
-    pl.nstages = (budget - fixed - tail) / stage_bytes;
+    if (mm > 2 || fixed + tail + 4 * stage_stride > budget2) { per_sm = 1; budget = budget1; }
+    if (fixed + tail + 2 * stage_stride > budget) return pl;         // activations do not fit: not this kernel
+    pl.nstages = (budget - fixed - tail) / stage_stride;
     if (pl.nstages > 24) pl.nstages = 24;
+    pl.stage_stride = stage_stride;
     pl.off_stage = fixed;
-    pl.off_red = pl.off_stage + pl.nstages * stage_bytes;
+    pl.off_red = pl.off_stage + pl.nstages * stage_stride;
     pl.off_bar = pl.off_red + red_bytes;
     pl.smem_bytes = pl.off_bar + (2 * pl.nstages + 1 + 2 * kIntRB) * 8 + 64;
     pl.total_chunks = pl.ntiles * pl.nchunks;
@@ -1385,7 +1426,8 @@ static IntPlan plan_int(uint32_t m, uint32_t k, uint32_t n) {
     const uint32_t per_cta = pl.total_chunks / pl.grid;              // >= 1
     pl.two_way = per_cta >= pl.nchunks;                              // a tile is cut by at most one range boundary
     pl.slots = (pl.nchunks + per_cta - 1) / per_cta + 1;             // contributors a tile can have
-    pl.ws_xq = align((size_t)pl.xq_row_bytes * pl.xq_pieces, 256);
+    // (a streamed chunk is copied whole-sized entries at a time: 16 bytes of slack behind the last one)
+    pl.ws_xq = align((size_t)pl.xq_row_bytes * pl.xq_pieces + 16, 256);
     pl.ws_partial = align((size_t)pl.ntiles * pl.slots * mm * 16 * 4, 256);
     pl.ws_counters = align((size_t)pl.ntiles * 4, 256);
     pl.ws_bytes = pl.ws_xq + pl.ws_partial + pl.ws_counters + align((size_t)pl.ntiles * 8, 256);   // + rendezvous words
@@ -1425,6 +1467,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     P.ntiles = pl.ntiles; P.nchunks = pl.nchunks; P.total_chunks = pl.total_chunks; P.slots = pl.slots;
     P.chunks_q = pl.total_chunks / pl.grid; P.chunks_r = pl.total_chunks % pl.grid;
     P.nstages = pl.nstages; P.xq_row_bytes = pl.xq_row_bytes; P.xq_pieces = pl.xq_pieces;
+    P.xstream = pl.xstream; P.stage_stride = pl.stage_stride;
     P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
     // One kernel instead of two when every shared tile has exactly two contributors and re-quantising
     // the activations in every CTA is cheap (they come from L2): the quantiser kernel in front costs a
@@ -1434,7 +1477,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     // eight blocks of one row, four of two or two of four per round)
     const bool fits_inline = MMA ? ((uint64_t)k * (MM / 4) << inline_rows_log2(m_real)) <= inline_groups(MM, true) * int_warps(true) * 256u
                                  : (uint64_t)k * m_real <= inline_groups(MM) * kIntWarps * 32u * 8u;
-    P.inline_q = (!pair && pl.two_way && fits_inline && (iq == 2 || iq == 0)) ? 1u : 0u;
+    P.inline_q = (!pair && pl.two_way && fits_inline && !pl.xstream && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
     P.expert_sel = expert_sel;
     P.num_experts = num_experts;

@@ -5,7 +5,7 @@ They complete QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182): with them ever
 `Op::DequantMatMul` accepts runs on the GPU (the reference sends all of them to a host fallback or to its
 dequantise-everything kernel).  Dequantisation is bit-exact against the oracle; the matmul goes through the
 general kernel (f32 accumulation in a different order from the CPU's) and is held to 2e-5 * |x| * |w_row|.
-Q5_K also has the integer streaming GEMV (batch 1-2) and the tensor-core GEMM (batch > 8, bf16 activations).
+Q5_K also has the integer streaming GEMV (batch 1-2) and the tensor-core GEMM (batch > 8; f32 activations as two bf16 halves).
 """
 import json
 import os
@@ -106,8 +106,8 @@ def test_matmul_matches_oracle(sch, m, k, n, x_bf16):
     w, x = make_case(s, m, k, n, seed=2000 + m + n, x_bf16=x_bf16)
     y = _gpu_matmul(s, w, x, n, x_bf16=x_bf16)
     tol = 2e-5
-    if sch == "q5_k" and x_bf16 and m > 8:      # tensor-core GEMM: weights rounded once to bf16
-        tol = min(1e-3, 8e-3 / np.sqrt(k))
+    if sch == "q5_k" and m > 8:                 # tensor-core GEMM (f32 activations as two bf16 halves): weights rounded once to bf16
+        tol = min(1e-3, 12e-3 / np.sqrt(k))
     assert_within_tolerance(y, reference(s, w, x, n), bound(s, w, x, n), tol=tol, what=f"{sch} {m}x{k}x{n}")
 
 
