@@ -655,6 +655,56 @@ template <int MM> struct QUnitMma<RLXQ_Q4_K, MM> {
     __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
 };
 
+// ---- Q5_K: Q4_K with a fifth bit: the unit is d | dmin | 12 scale bytes | qh[32] | qs[128], and bit j of qh[l]
+// adds 16 to weight l of sub-block j.  Words t and 4 + t of qh hold lane t's bits for every sub-block.
+template <int MM> struct QUnitMma<RLXQ_Q5_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * 176, p8 = p0 + 8 * L.row_pitch;
+        float d0, m0, d8, m8;
+        uint32_t sc0, mn0, sc8, mn8;
+        QUnitMma<RLXQ_Q4_K, MM>::header(p0, part, d0, m0, sc0, mn0);
+        QUnitMma<RLXQ_Q4_K, MM>::header(p8, part, d8, m8, sc8, mn8);
+        // the four high bits this part needs, moved to bits 0..3 of every byte
+        const uint32_t hs = 4 * part;
+        const uint32_t h0 = (lds32(p0 + 16 + 4 * t) >> hs) & 0x0F0F0F0Fu, h0b = (lds32(p0 + 32 + 4 * t) >> hs) & 0x0F0F0F0Fu;
+        const uint32_t h8 = (lds32(p8 + 16 + 4 * t) >> hs) & 0x0F0F0F0Fu, h8b = (lds32(p8 + 32 + 4 * t) >> hs) & 0x0F0F0F0Fu;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int pp = 0; pp < 2; ++pp) {
+            const uint32_t qo = 48 + 64 * part + 32 * pp + 4 * t;
+            const uint32_t w0 = lds32(p0 + qo), w0b = lds32(p0 + qo + 16);
+            const uint32_t w8 = lds32(p8 + qo), w8b = lds32(p8 + qo + 16);
+#pragma unroll
+            for (int nib = 0; nib < 2; ++nib) {
+                const int js = 2 * pp + nib;          // sub-block inside the warp's part
+                const uint32_t a0 = ((w0 >> (4 * nib)) & 0x0F0F0F0Fu) | (((h0 >> js) & 0x01010101u) << 4);
+                const uint32_t a2 = ((w0b >> (4 * nib)) & 0x0F0F0F0Fu) | (((h0b >> js) & 0x01010101u) << 4);
+                const uint32_t a1 = ((w8 >> (4 * nib)) & 0x0F0F0F0Fu) | (((h8 >> js) & 0x01010101u) << 4);
+                const uint32_t a3 = ((w8b >> (4 * nib)) & 0x0F0F0F0Fu) | (((h8b >> js) & 0x01010101u) << 4);
+                const float dsc0 = d0 * (float)((sc0 >> (8 * js)) & 0xFFu), dmn0 = m0 * (float)((mn0 >> (8 * js)) & 0xFFu);
+                const float dsc8 = d8 * (float)((sc8 >> (8 * js)) & 0xFFu), dmn8 = m8 * (float)((mn8 >> (8 * js)) & 0xFFu);
+#pragma unroll
+                for (int gq = 0; gq < MMG; ++gq) {
+                    const uint2 bb = lds64(fb + (js * MMG + gq) * 256);
+                    const uint2 sc = lds64(sb + (js * MMG + gq) * 32);
+                    int c[4];
+                    imma_u8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                    const float s = __uint_as_float(sc.x), sxf = __uint_as_float(sc.y);
+                    tot[2 * gq] = fmaf(dsc0 * s, (float)(c[0] * 128 + c[1]), fmaf(-dmn0, sxf, tot[2 * gq]));
+                    tot[2 * gq + 1] = fmaf(dsc8 * s, (float)(c[2] * 128 + c[3]), fmaf(-dmn8, sxf, tot[2 * gq + 1]));
+                }
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
 __device__ __forceinline__ void imma16_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
         : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
@@ -1371,7 +1421,7 @@ struct IntPlan {
 
 // Formats that have a integer-MMA unit (QUnitMma).
 constexpr bool int_has_mma(uint32_t scheme) {
-    return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q6_K;
+    return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K;
 }
 
 template <uint32_t SCHEME, bool MMA = false>
@@ -1581,6 +1631,7 @@ bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
         case RLXQ_Q4_0: return plan_int<RLXQ_Q4_0, true>(m, k, n).ok;
         case RLXQ_Q8_0: return plan_int<RLXQ_Q8_0, true>(m, k, n).ok;
         case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K, true>(m, k, n).ok;
+        case RLXQ_Q5_K: return plan_int<RLXQ_Q5_K, true>(m, k, n).ok;
         case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K, true>(m, k, n).ok;
         default: return false;
     }
@@ -1592,6 +1643,7 @@ size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t
         case RLXQ_Q4_0: pl = plan_int<RLXQ_Q4_0, true>(m, k, n); break;
         case RLXQ_Q8_0: pl = plan_int<RLXQ_Q8_0, true>(m, k, n); break;
         case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K, true>(m, k, n); break;
+        case RLXQ_Q5_K: pl = plan_int<RLXQ_Q5_K, true>(m, k, n); break;
         case RLXQ_Q6_K: pl = plan_int<RLXQ_Q6_K, true>(m, k, n); break;
         default: break;
     }
@@ -1605,6 +1657,7 @@ int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, boo
         case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
     }
@@ -1650,6 +1703,7 @@ int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu
             case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
         }

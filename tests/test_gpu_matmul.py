@@ -390,6 +390,8 @@ IMMA_SHAPES = [("q4_0", 3, 256, 100, False, False), ("q4_0", 4, 4096, 11008, Fal
                ("q4_k", 3, 14336, 4096, False, False), ("q4_k", 6, 8192, 3000, True, False), ("q4_k", 2, 1024, 300, False, True),
                ("q6_k", 3, 2048, 100, False, False), ("q6_k", 4, 14336, 4096, False, False), ("q6_k", 8, 4096, 3000, False, False),
                ("q6_k", 5, 6144, 256, True, True), ("q6_k", 2, 4096, 14336, False, False),
+               ("q5_k", 3, 256, 100, False, False), ("q5_k", 4, 4096, 14336, False, False), ("q5_k", 8, 2048, 1000, True, False),
+               ("q5_k", 2, 14336, 520, False, True), ("q5_k", 6, 28672, 300, False, False),
                # fragments of all rows do not fit in shared memory: they stream through the ring beside the weights
                ("q4_0", 8, 11008, 4096, False, False), ("q6_k", 8, 8192, 1000, False, False), ("q4_k", 4, 28672, 2048, False, False),
                ("q8_0", 8, 14336, 777, True, True), ("q4_k", 7, 28672, 520, True, False)]
@@ -446,7 +448,7 @@ def test_integer_mma_gemv_refuses_what_it_cannot_run():
     import torch
     R.set_option("gemv_kernel", 5)
     try:
-        s = O.Q5_K                                               # no MMA unit for this format
+        s = O.Q8_K                                               # no MMA unit for this format
         w, x = make_case(s, 4, 2048, 16, seed=3)
         with pytest.raises(R.RlxqError) as e:
             R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
