@@ -173,8 +173,7 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
  *                  GEMV, 3 = force the integer GEMV with its dp4a units (m <= 4), 4 = force the tcgen05 GEMV (m <= 8;
  *                  Q4_0, Q8_0, Q4_K; k a multiple of 256), 5 = force the integer GEMV with its integer-MMA units
- *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q6_K; the activations of 4 or 8 rows must fit in shared memory: 9 or 18
- *                  bytes per element of a row, 10 or 20 for Q6_K).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
+ *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K; k a multiple of 256, 2048 for Q6_K).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
  *                  correct but slower than the others on the shapes measured so far, hence not automatic.
  *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
