@@ -120,6 +120,34 @@ RLXQ_API int rlxq_matmul(rlxq_stream_t stream, uint32_t scheme,
                 void* y, uint32_t y_dtype, uint32_t m, uint32_t k, uint32_t n,
                 void* workspace, size_t workspace_bytes);
 
+/* A chain of dependent matmuls behind one call: y_i[m, n_i] = in_i[m, k_i] . W_i^T with in_0 = x and in_i = y_(i-1),
+ * or, with swiglu != 0, in_i = up * silu(gate) of y_(i-1) = [gate | up] ([m, 2 k_i]; silu(g) = g / (1 + exp(-g)),
+ * rlx-cpu/src/naive.rs:54-56).  Two plain layers are the up / down pair of a decode step, a plain layer over the
+ * stacked [gate ; up] weight followed by a swiglu layer is a SwiGLU FFN (rlx-flow/src/blocks/swiglu.rs:48-52).
+ * The reference runs such a chain as consecutive steps of its compiled graph (rlx-cuda/src/backend.rs:5366-5405),
+ * the product as FusedSwiGLU (rlx-cuda/src/unfuse.rs:254-293).  By default the layers run one after the other
+ * through the kernels rlxq_matmul uses (the SwiGLU product in a kernel of its own).  With option "gemv_chain" = 1,
+ * m <= 2 and up to 3 layers of the streaming formats (k a multiple of 256, 2048 for Q6_K; 16-byte aligned x and
+ * weights; every layer's tiles cut at most once by the CTA ranges) the whole chain is ONE cooperative kernel: the
+ * weight stream never stops between layers and a layer waits only for a grid-wide barrier on its input (bounded:
+ * RLXQ_E_TIMEOUT code 8 through rlxq_device_status).  That needs every CTA of the grid resident at once, so
+ * nothing else may occupy the GPU's SMs meanwhile.  It is off by default because it is slower than the separate
+ * launches on the shapes measured (24 us against 16 us for the Q4_0 4096 -> 11008 -> 4096 pair): every CTA
+ * quantises the whole input of every layer behind the barrier, and programmatic dependent launch already hides
+ * most of a launch boundary.  Same results either way up to f32 summation order.  Intermediate outputs are f32
+ * and live in the workspace.  y: f32 or bf16 [m, n_last].
+ * workspace: rlxq_chain_workspace_bytes(...) bytes, 256-byte aligned, contents irrelevant on entry. */
+typedef struct rlxq_chain_layer {
+    const void* w_blocks;     /* packed W_i[n, k] */
+    uint32_t k, n;
+    uint32_t swiglu;          /* input is the SwiGLU product of the previous layer's output (never for layer 0) */
+} rlxq_chain_layer;
+RLXQ_API int rlxq_chain_workspace_bytes(uint32_t scheme, const rlxq_chain_layer* layers, uint32_t nlayers, uint32_t m,
+                                        uint32_t x_dtype, size_t* bytes);
+RLXQ_API int rlxq_matmul_chain(rlxq_stream_t stream, uint32_t scheme, const rlxq_chain_layer* layers, uint32_t nlayers,
+                               const void* x, uint32_t x_dtype, void* y, uint32_t y_dtype, uint32_t m,
+                               void* workspace, size_t workspace_bytes);
+
 /* y = x . W^T for batch 1 and 2 (the streaming decode GEMV) without any device allocation and
  * without a caller workspace.  This entry point has no counterpart in the reference.
  *
@@ -176,6 +204,8 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K; k a multiple of 256, 2048 for Q6_K).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
  *                  correct but slower than the others on the shapes measured so far, hence not automatic.
  *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1
+ *   "gemv_chain": 1 = rlxq_matmul_chain runs a chain as one cooperative kernel where it can, 0 (default) = always
+ *                  layer by layer
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM
  *   "gemm_streamk": 0 = automatic (split the k dimension across SMs when that saves at least 36
  *                  256-wide k steps on the busiest SM and a workspace is given), 1 = never,

@@ -30,6 +30,8 @@ _SIGS = {
     "rlxq_dequant_f32": (C.c_int, [vp, u32, vp, u64, vp]),
     "rlxq_matmul": (C.c_int, [vp, u32, vp, u32, vp, vp, u32, u32, u32, u32, vp, C.c_size_t]),
     "rlxq_matmul_static_scratch": (C.c_int, [vp, u32, vp, u32, vp, vp, u32, u32, u32, u32]),
+    "rlxq_chain_workspace_bytes": (C.c_int, [u32, vp, u32, u32, u32, C.POINTER(C.c_size_t)]),
+    "rlxq_matmul_chain": (C.c_int, [vp, u32, vp, u32, vp, u32, vp, u32, u32, vp, C.c_size_t]),
     "rlxq_init_device": (C.c_int, []),
     "rlxq_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "rlxq_launch_count": (u64, []),

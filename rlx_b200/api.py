@@ -141,6 +141,47 @@ def matmul(x, w_blocks, scheme: int, n: int, out=None, out_dtype=None, workspace
     return out
 
 
+class ChainLayer(C.Structure):
+    """rlxq_chain_layer: one layer of rlxq_matmul_chain."""
+    _fields_ = [("w_blocks", C.c_void_p), ("k", C.c_uint32), ("n", C.c_uint32), ("swiglu", C.c_uint32)]
+
+
+def matmul_chain(x, layers, scheme: int, out=None, out_dtype=None, workspace=None):
+    """rlxq_matmul_chain: `layers` is a list of (w_blocks, n) or (w_blocks, n, swiglu) in order; layer i takes the
+    previous layer's output (or, with swiglu, the product up * silu(gate) of its [gate | up] halves).  CUDA tensors."""
+    torch = _torch()
+    assert x.is_cuda and x.dim() == 2 and x.is_contiguous()
+    m, width = x.shape
+    arr = (ChainLayer * len(layers))()
+    for i, ly in enumerate(layers):
+        w, n = ly[0], int(ly[1])
+        sw = int(bool(ly[2])) if len(ly) > 2 else 0
+        assert w.is_cuda and w.dtype == torch.uint8 and w.is_contiguous()
+        k = width // 2 if sw else width
+        arr[i] = ChainLayer(w.data_ptr(), k, n, sw)
+        width = n
+    if out is None:
+        out = torch.empty((m, width), dtype=out_dtype or torch.float32, device=x.device)
+    need = C.c_size_t()
+    check(lib.rlxq_chain_workspace_bytes(int(scheme), C.cast(arr, C.c_void_p), len(layers), m, _dt(x, torch), C.byref(need)))
+    if workspace is None or workspace.numel() < need.value:
+        workspace = torch.empty(max(need.value, 256), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.rlxq_matmul_chain(_stream_ptr(torch), int(scheme), C.cast(arr, C.c_void_p), len(layers), x.data_ptr(),
+                                    _dt(x, torch), out.data_ptr(), _dt(out, torch), m, workspace.data_ptr(), workspace.numel()))
+    return out
+
+
+def chain_workspace_bytes(scheme: int, layers, m: int, x_dtype: int = 0) -> int:
+    """layers: list of (k, n, swiglu)."""
+    arr = (ChainLayer * len(layers))()
+    for i, (k, n, sw) in enumerate(layers):
+        arr[i] = ChainLayer(None, k, n, int(bool(sw)))
+    need = C.c_size_t()
+    check(lib.rlxq_chain_workspace_bytes(int(scheme), C.cast(arr, C.c_void_p), len(layers), m, int(x_dtype), C.byref(need)))
+    return need.value
+
+
 # ------------------------------------------------------------------ MoE expert stacks
 def grouped_matmul(x, w_blocks, expert_idx, scheme: int, n: int, num_experts: int, out=None, out_dtype=None,
                    workspace=None):
@@ -349,4 +390,5 @@ class Session:
 __all__ = ["QuantScheme", "DType", "Device", "Graph", "Session", "CompiledGraph", "RlxqError",
            "dequant_f32", "matmul", "scheme_geometry", "packed_bytes", "workspace_bytes",
            "set_option", "get_option", "launch_count", "device_status",
+           "matmul_chain", "chain_workspace_bytes", "ChainLayer",
            "grouped_matmul", "gguf_tied_lm_argmax", "gguf_tied_lm_topk", "lm_head_workspace_bytes", "LM_MAX_CAP"]

@@ -102,6 +102,9 @@ struct IntParams {
     // every ring stage carries, behind its weights, the fragments and scale entries of its own 2048-weight
     // chunk (two bulk copies from the workspace, out of L2).  stage_stride: bytes from one ring stage to the next.
     uint32_t xstream, stage_stride;
+    // Chain kernel only: CTAs that take part in this layer (the split chunks_q / chunks_r is over them), and
+    // whether the layer's input is the SwiGLU product of the previous layer's [gate | up] output.
+    uint32_t active, swiglu;
     uint32_t off_stage, off_red, off_bar;
     // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
     // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
@@ -1408,6 +1411,366 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
 }
 
 // ---------------------------------------------------------------------------------------------
+// Kernel 3: a chain of dependent GEMVs in one launch (batch 1-2, dp4a units)
+// ---------------------------------------------------------------------------------------------
+// A decode step is a chain of small GEMVs, each the input of the next (gate/up -> SwiGLU -> down), and at
+// 25-50 MB per matrix a launch is mostly hand-over: the next kernel cannot be resident before this one
+// leaves, its ring starts empty, its activations come from L2 behind its own weight requests.  Here one
+// cooperative grid runs the whole chain.  The producer warps never stop: weights are immutable, so the ring
+// refills with the next layer's stages while this layer is still being multiplied, and the only thing a
+// layer waits for is its input: a grid-wide barrier between layers (every CTA's finisher arrives after its
+// last store of the layer; the consumer warps poll, bounded), then the usual in-kernel quantisation.
+// The barrier words need no zeroed memory and survive graph replay: a word counts arrivals under the
+// call's tag ((tag << 32) | count; any other upper half reads as zero), and the CTA that arrives last at
+// the exit word, when nobody polls any more, zeroes them all.
+// Measured, it does not pay yet (Q4_0 4096 -> 11008 -> 4096 at batch 1: 24.3 us against 16.2 us for two
+// launches; Q4_K 8192 -> 2 x 14336 -> 8192 with SwiGLU: 60 us against 41 us): behind every barrier each CTA
+// loads and quantises the layer's whole input (1.5-3.5 us, three rounds of loads for k = 14336, the SwiGLU
+// exponentials included) while its ring sits full and HBM idles, and programmatic dependent launch already
+// hides most of a launch boundary.  It runs on request only (option "gemv_chain").
+constexpr uint32_t kChainMaxLayers = 3;
+
+struct ChainParams {
+    IntParams layer[kChainMaxLayers];
+    uint32_t nlayers;
+    uint32_t tag;                   // odd: never the upper half of a zeroed word
+    uint32_t spin_limit;            // polls of a barrier word before the kernel gives up (error 8)
+    unsigned long long* sync;       // [nlayers]: barrier after layer i (i < nlayers - 1), then the exit word
+};
+
+// Counts this CTA in and returns the count including it.  Once the word carries the call's tag it only ever
+// counts up until the last CTA out zeroes it, so a plain atomic add does (hundreds of CTAs retrying a
+// compare-and-swap on one word would take one memory round trip per success); only the first arrivals, which
+// find something else in the word, install the tag by compare-and-swap.
+__device__ __forceinline__ uint32_t chain_arrive(unsigned long long* word, uint32_t tag) {
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word);
+    for (;;) {
+        if ((uint32_t)(old >> 32) == tag) return (uint32_t)atomicAdd(word, 1ull) + 1u;
+        const unsigned long long nw = ((unsigned long long)tag << 32) | 1ull;
+        const unsigned long long prev = atomicCAS(word, old, nw);
+        if (prev == old) return 1u;
+        old = prev;
+    }
+}
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ldg128_cg(const void* p) {      // from L2: the line may be stale in this SM's L1
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// The raw bytes of eight activations x[r][c .. c+8) of a layer: f32 or bf16 input (raw[0..1]), or, for the SwiGLU
+// product of the previous layer's [gate | up] output (P.swiglu: x is [m][2k] f32), gate in raw[0..1] and up in
+// raw[2..3].  Loads only: the caller issues all of a round's loads before it touches a value.
+__device__ __forceinline__ void chain_load_raw(const IntParams& P, uint32_t r, uint32_t c, uint4 (&raw)[4]) {
+    if (P.swiglu) {
+        const float* row = reinterpret_cast<const float*>(P.x) + (size_t)r * 2 * P.k;
+        raw[0] = ldg128_cg(row + c); raw[1] = ldg128_cg(row + c + 4);
+        raw[2] = ldg128_cg(row + P.k + c); raw[3] = ldg128_cg(row + P.k + c + 4);
+    } else if (P.x_bf16) {
+        raw[0] = ldg128_cg(reinterpret_cast<const uint16_t*>(P.x) + (size_t)r * P.k + c);
+    } else {
+        const float* q = reinterpret_cast<const float*>(P.x) + (size_t)r * P.k + c;
+        raw[0] = ldg128_cg(q); raw[1] = ldg128_cg(q + 4);
+    }
+}
+__device__ __forceinline__ void chain_raw_to_f32(const IntParams& P, const uint4 (&raw)[4], float (&f)[8]) {
+    const uint4 a[2] = {raw[0], raw[1]};
+    if (P.swiglu) {
+        const uint4 b[2] = {raw[2], raw[3]};
+        float gf[8], uf[8];
+        raw8_to_f32(a, 0u, gf);
+        raw8_to_f32(b, 0u, uf);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f[q] = uf[q] * (gf[q] / (1.0f + expf(-gf[q])));
+    } else {
+        raw8_to_f32(a, P.x_bf16, f);
+    }
+}
+
+template <uint32_t SCHEME, int MM>
+__global__ void __launch_bounds__(int_threads(false), 2) gemv_chain_kernel(const __grid_constant__ ChainParams A) {
+    static_assert(MM == 1 || MM == 2, "the chain kernel carries one or two activation rows");
+    constexpr uint32_t CW = kIntWarps;
+    using T = StagedTraits<SCHEME>;
+    using B = IntBox<SCHEME, false>;
+    using QU = QUnit<SCHEME, MM>;
+    constexpr uint32_t STRIDE = B::ROW;
+    constexpr uint32_t stage_bytes = B::STAGE_BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    // one layout for all layers (the host sizes the activation area for the longest k)
+    const IntParams& P0 = A.layer[0];
+    uint8_t* xs = smem;
+    uint8_t* stages = smem + P0.off_stage;
+    float* red = reinterpret_cast<float*>(smem + P0.off_red);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P0.off_bar);   // full[NS], empty[NS], "first loads issued"
+    const uint32_t NS = P0.nstages;
+    uint64_t* rbars = bars + 2 * NS + 1;
+    uint32_t* misc = reinterpret_cast<uint32_t*>(rbars + 2 * kIntRB);
+    volatile uint32_t* abort_flag = misc;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t G = gridDim.x, me = blockIdx.x;
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[NS + s]), CW);
+        }
+        mbar_init(smem_u32(&bars[2 * NS]), CW);
+        for (uint32_t r = 0; r < kIntRB; ++r) {
+            mbar_init(smem_u32(&rbars[r]), CW);
+            mbar_init(smem_u32(&rbars[kIntRB + r]), 1);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+    // a layer may use fewer CTAs than the grid has (chunks_q / chunks_r split its chunks over `active` CTAs);
+    // the others have nothing to do in that layer
+    auto range_of = [&](const IntParams& P) -> Range {
+        if (me < P.active) return make_range(P, me);
+        Range rg{};
+        return rg;                                  // nseg = 0
+    };
+
+    if (warp == CW) {
+        // ---------------- producer warp: the ring never drains between layers ----------------
+        uint32_t s = 0, ph = 1, issued = 0;
+        bool dead = false;
+        for (uint32_t li = 0; li < A.nlayers && !dead; ++li) {
+            const IntParams& P = A.layer[li];
+            if (lane == 0) tma_prefetch_desc(&P.wmap);
+            const Range rg = range_of(P);
+            for (uint32_t si = 0; si < rg.nseg && !dead; ++si) {
+                const Segment sg = segment_at(P, rg, si);
+                for (uint32_t c = sg.c0; c < sg.c1; ++c, ++issued) {
+                    if (issued == 2 && li == 0) {
+                        // the first activation loads must not queue behind a ring of weight requests: two stages,
+                        // then wait until the consumer warps have issued theirs
+                        if (!mbar_wait(smem_u32(&bars[2 * NS]), 0)) {
+                            if (lane == 0) { atomicExch(P.err, 5); *abort_flag = 1u; }
+                            dead = true;
+                            break;
+                        }
+                    }
+                    if (issued >= NS) {
+                        if (*abort_flag || !mbar_wait(smem_u32(&bars[NS + s]), ph)) {
+                            if (lane == 0) { atomicExch(P.err, 3); *abort_flag = 1u; }
+                            dead = true;
+                            break;
+                        }
+                    }
+                    if (lane == 0) {
+                        const uint32_t full = smem_u32(&bars[s]);
+                        mbar_arrive_expect_tx(full, stage_bytes);
+#pragma unroll
+                        for (uint32_t b = 0; b < B::NB; ++b)
+                            tma_load_2d(smem_u32(stages + s * stage_bytes + b * B::BOX_BYTES), &P.wmap,
+                                        (int32_t)(((c * kIntCU + b * B::UB) * T::UNIT_B) / 8), (int32_t)(sg.tile * 16), full);
+                    }
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+        return;
+    }
+
+    if (warp == CW + 1) {
+        // ---------------- finisher warp ----------------
+        constexpr int NC = (MM + 1) / 2;
+        const uint32_t chalf = lane >> 4, rrow = lane & 15u;
+        uint32_t r = 0, rph = 0;
+        bool dead = false;
+        griddep_wait();      // the workspace (partial tiles, rendezvous and barrier words) may be the previous launch's
+        for (uint32_t li = 0; li < A.nlayers; ++li) {
+            const IntParams& P = A.layer[li];
+            const Range rg = range_of(P);
+            for (uint32_t si = 0; si < rg.nseg && !dead; ++si) {
+                const Segment sg = segment_at(P, rg, si);
+                const uint32_t tile = sg.tile, mine = sg.c1 - sg.c0;
+                if (*abort_flag || !mbar_wait(smem_u32(&rbars[r]), rph)) {
+                    if (lane == 0) { atomicExch(P.err, 6); *abort_flag = 1u; }
+                    dead = true;
+                    break;
+                }
+                const float* rbuf = red + r * (CW * 32 * MM);
+                float v[NC];
+#pragma unroll
+                for (int cp = 0; cp < NC; ++cp) {
+                    const uint32_t col = 2 * cp + chalf;
+                    v[cp] = 0.f;
+                    if (col < (uint32_t)MM) {
+#pragma unroll
+                        for (uint32_t wv = 0; wv < CW; ++wv) {
+                            v[cp] += rbuf[(wv * 32 + rrow) * MM + col];
+                            v[cp] += rbuf[(wv * 32 + 16 + rrow) * MM + col];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&rbars[kIntRB + r]));
+                if (++r == kIntRB) { r = 0; rph ^= 1u; }
+                const uint32_t orow = tile * 16 + rrow;
+                bool store = mine == P.nchunks;
+                if (!store) {
+                    // a tile cut between two CTAs: token exchange as in gemv_int_kernel's single-kernel mode
+                    const uint32_t role = sg.c0 ? 1u : 0u;
+                    float* pt = P.partial + (size_t)tile * 2 * (MM * 16);
+#pragma unroll
+                    for (int cp = 0; cp < NC; ++cp)
+                        if (2 * cp + chalf < (uint32_t)MM) pt[(role * MM + 2 * cp + chalf) * 16 + rrow] = v[cp];
+                    __threadfence();
+                    __syncwarp();
+                    unsigned long long old = 0ull;
+                    if (lane == 0) old = atomicExch(&P.flags[tile], P.token + 2ull * role);
+                    old = __shfl_sync(0xFFFFFFFFu, old, 0);
+                    if (old == P.token + 2ull * (1u - role)) {
+                        __threadfence();
+#pragma unroll
+                        for (int cp = 0; cp < NC; ++cp)
+                            if (2 * cp + chalf < (uint32_t)MM) v[cp] += __ldcg(&pt[((1u - role) * MM + 2 * cp + chalf) * 16 + rrow]);
+                        if (lane == 0) P.flags[tile] = 0ull;
+                        store = true;
+                    }
+                }
+                if (store) {
+#pragma unroll
+                    for (int cp = 0; cp < NC; ++cp) {
+                        const uint32_t col = 2 * cp + chalf;
+                        if (col < P.m_real && orow < P.n) {
+                            const size_t o = (size_t)col * P.n + orow;
+                            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v[cp]);
+                            else reinterpret_cast<float*>(P.y)[o] = v[cp];
+                        }
+                    }
+                }
+            }
+            // everything this CTA contributes to the layer is stored (or will be by the partner that completes a
+            // shared tile before its own arrival): count in; a dead CTA counts in too, the error word tells
+            __threadfence();
+            __syncwarp();
+            if (lane == 0 && li + 1 < A.nlayers) chain_arrive(A.sync + li, A.tag);
+        }
+        if (lane == 0) {
+            // nobody polls after its last layer: the last CTA out leaves every word at zero for the next replay
+            if (chain_arrive(A.sync + A.nlayers - 1, A.tag) == G)
+                for (uint32_t i = 0; i < A.nlayers; ++i) A.sync[i] = 0ull;
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    QLane L;
+    L.half = lane >> 4;
+    L.lane = lane;
+    L.row_pitch = STRIDE;
+    const uint32_t hoff = QU::HALF_OFFSETS ? L.half : 0u;
+    const uint32_t trow = QU::first_row(lane), stages_u32 = smem_u32(stages);
+    bool dead = false;
+    uint32_t s = 0, ph = 0, rr = 0, rrph = 1;
+    for (uint32_t li = 0; li < A.nlayers; ++li) {
+        const IntParams& P = A.layer[li];
+        if (li > 0) {
+            // the layer's input is the previous layer's output: every CTA must have stored its part
+            if (tid == 0) {
+                const unsigned long long want = ((unsigned long long)A.tag << 32) | G;
+                uint32_t ok = 0;
+                for (uint32_t i = 0; i < A.spin_limit && !*abort_flag; ++i) {
+                    if (ld_acquire_u64(A.sync + li - 1) == want) { ok = 1; break; }
+                    __nanosleep(40);
+                }
+                if (!ok) { atomicExch(P.err, 8); *abort_flag = 1u; }
+            }
+            consumer_bar_n<CW * 32>();
+            if (*abort_flag) dead = true;
+        }
+        L.xstride = P.xq_row_bytes;
+        L.xh = smem_u32(xs) + 128 * hoff;
+        L.xl = L.xh + P.k;
+        L.sb = smem_u32(xs) + 2 * P.k + 16 * hoff;
+        L.sx = smem_u32(xs) + 2 * P.k + (P.k / 32) * 4 + (32 / T::SUB) * 16 * hoff;
+        if (li == 0) griddep_wait();                                    // x may be the previous kernel's output
+        if (!dead) {
+            // quantise the layer's activations; a round's loads (three groups of eight per thread) are all issued
+            // before the first value is used
+            const uint32_t gpr = P.k / 8, total = gpr * P.m_real;       // gpr % 32 == 0: whole warps stay together
+            constexpr uint32_t kInFlight = 3;
+            bool told = li != 0;                                        // whether the producer has been told to go on
+            for (uint32_t g0 = tid; g0 < total; g0 += kInFlight * CW * 32) {
+                uint4 raw[kInFlight][4];
+#pragma unroll
+                for (uint32_t i = 0; i < kInFlight; ++i) {
+                    const uint32_t g = g0 + i * CW * 32;
+                    if (g < total) {
+                        const uint32_t r = MM > 1 ? g / gpr : 0u;
+                        chain_load_raw(P, r, (g - r * gpr) * 8, raw[i]);
+                    }
+                }
+                if (!told) {                                            // the producer may go on filling the ring
+                    told = true;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars[2 * NS]));
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < kInFlight; ++i) {
+                    const uint32_t g = g0 + i * CW * 32;
+                    if (g < total) {
+                        const uint32_t r = MM > 1 ? g / gpr : 0u;
+                        float f[8];
+                        chain_raw_to_f32(P, raw[i], f);
+                        quantise_store8<T::SUB>(f, P.k, (int)SumBias<SCHEME>::value, (g - r * gpr) * 8,
+                                                xs + r * P.xq_row_bytes, lane);
+                    }
+                }
+            }
+            if (!told && lane == 0) mbar_arrive(smem_u32(&bars[2 * NS]));   // a warp without a group to quantise
+        } else if (li == 0 && lane == 0) {
+            mbar_arrive(smem_u32(&bars[2 * NS]));
+        }
+        consumer_bar_n<CW * 32>();
+        const Range rg = range_of(P);
+        const uint32_t ku = P.k / 256;
+        for (uint32_t si = 0; si < rg.nseg; ++si) {
+            const Segment sg = segment_at(P, rg, si);
+            float tot[QU::NACC];
+#pragma unroll
+            for (int m = 0; m < QU::NACC; ++m) tot[m] = 0.f;
+            for (uint32_t chunk = sg.c0; chunk < sg.c1; ++chunk) {
+                if (!dead && (*abort_flag || !mbar_wait(smem_u32(&bars[s]), ph))) {
+                    dead = true;
+                    if (lane == 0) { atomicExch(P.err, 4); *abort_flag = 1u; }
+                }
+                if (!dead) {
+                    const uint32_t cu = min(kIntCU, ku - chunk * kIntCU);
+                    L.row = stages_u32 + s * stage_bytes + (warp / B::UB) * B::BOX_BYTES + trow * STRIDE;
+                    if (warp < cu) QU::run(L, warp % B::UB, (chunk * kIntCU + warp) * 256, tot);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars[NS + s]));
+                }
+                if (++s == NS) { s = 0; ph ^= 1u; }
+            }
+            if (!dead && (*abort_flag || !mbar_wait(smem_u32(&rbars[kIntRB + rr]), rrph))) {
+                dead = true;
+                if (lane == 0) { atomicExch(P.err, 7); *abort_flag = 1u; }
+            }
+            if (!dead) {
+                float* rbuf = red + rr * (CW * 32 * MM);
+                QU::finalize(tot, lane);
+#pragma unroll
+                for (int m = 0; m < MM; ++m) rbuf[(warp * 32 + lane) * MM + m] = tot[m];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&rbars[rr]));
+            }
+            if (++rr == kIntRB) { rr = 0; rrph ^= 1u; }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 struct IntPlan {
@@ -1709,6 +2072,186 @@ int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu
         }
     }
     return launch_gemv_int_err(stream, scheme, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word(), true);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The chain kernel's host side
+// ---------------------------------------------------------------------------------------------
+struct ChainPlan {
+    bool ok;
+    uint32_t grid, nstages, off_stage, off_red, off_bar, smem_bytes;
+    struct { uint32_t ntiles, nchunks, total_chunks, active, xq_row_bytes; size_t off_partial, off_flags, off_y; } l[kChainMaxLayers];
+    size_t off_sync, ws_bytes;
+};
+
+template <uint32_t SCHEME>
+static ChainPlan plan_chain(const ChainLayer* L, uint32_t nl, uint32_t m) {
+    using T = StagedTraits<SCHEME>;
+    constexpr uint32_t stage_bytes = IntBox<SCHEME, false>::STAGE_BYTES;
+    ChainPlan pl{};
+    if (nl < 2 || nl > kChainMaxLayers || m == 0 || m > 2) return pl;
+    auto align = [](size_t v, size_t a) { return (v + a - 1) / a * a; };
+    const uint32_t sms = (uint32_t)sm_count();
+    pl.grid = 2 * sms;
+    uint32_t xq_max = 0;
+    size_t off = 0;
+    for (uint32_t i = 0; i < nl; ++i) {
+        const uint32_t k = L[i].k, n = L[i].n;
+        if (n == 0 || k == 0 || k % (256 * T::AG)) return pl;
+        // a layer's input is the previous layer's output, or the SwiGLU product of its [gate | up] halves
+        if (i > 0 && L[i - 1].n != (L[i].swiglu ? 2 * k : k)) return pl;
+        if (i == 0 && L[i].swiglu) return pl;
+        auto& q = pl.l[i];
+        q.ntiles = (n + 15) / 16;
+        q.nchunks = (k / 256 + kIntCU - 1) / kIntCU;
+        if ((uint64_t)q.ntiles * q.nchunks > 0xFFFFFFFFull / 2) return pl;
+        q.total_chunks = q.ntiles * q.nchunks;
+        q.active = pl.grid;
+        if (q.ntiles < q.active && q.ntiles * 10 >= q.active * 7) q.active = q.ntiles;   // one whole tile per CTA
+        if (q.active > q.total_chunks) q.active = q.total_chunks;
+        if (q.total_chunks / q.active < q.nchunks) return pl;        // a tile would be cut more than once
+        q.xq_row_bytes = 2 * k + (k / 32) * 4 + (k / T::SUB) * 4;
+        xq_max = q.xq_row_bytes > xq_max ? q.xq_row_bytes : xq_max;
+        q.off_partial = off; off += align((size_t)q.ntiles * 2 * m * 16 * 4, 256);
+        q.off_flags = off;   off += align((size_t)q.ntiles * 8, 256);
+        q.off_y = off;       if (i + 1 < nl) off += align((size_t)m * n * 4, 256);   // intermediate outputs (f32)
+    }
+    pl.off_sync = off; off += 256;
+    pl.ws_bytes = off;
+    const uint32_t fixed = (uint32_t)align((size_t)xq_max * m, 128);
+    const uint32_t red_bytes = kIntRB * kIntWarps * 32 * m * 4;
+    const uint32_t budget = 113u * 1024u;
+    if (fixed + red_bytes + 1024 + 3 * stage_bytes > budget) return pl;   // too little ring left beside the activations
+    pl.nstages = (budget - fixed - red_bytes - 1024) / stage_bytes;
+    if (pl.nstages > 24) pl.nstages = 24;
+    pl.off_stage = fixed;
+    pl.off_red = pl.off_stage + pl.nstages * stage_bytes;
+    pl.off_bar = pl.off_red + red_bytes;
+    pl.smem_bytes = pl.off_bar + (2 * pl.nstages + 1 + 2 * kIntRB) * 8 + 64;
+    pl.ok = true;
+    return pl;
+}
+
+template <uint32_t SCHEME, int MM>
+static int launch_chain_t(cudaStream_t stream, const ChainLayer* L, uint32_t nl, const void* x, bool xbf, void* y, bool ybf,
+                          void* ws, size_t ws_bytes, const ChainPlan& pl) {
+    Geometry g;
+    geometry(SCHEME, &g);
+    if (!ws || ws_bytes < pl.ws_bytes)
+        return fail(RLXQ_E_WORKSPACE, "GEMV chain needs %zu workspace bytes, got %zu", pl.ws_bytes, ws_bytes);
+    if ((uintptr_t)ws & 255u) return fail(RLXQ_E_ALIGN, "chain workspace must be 256-byte aligned");
+    static std::atomic<int> coop_ok[64];        // 0 unknown, 1 usable, -1 not (the grid would not be co-resident)
+    int dev = 0;
+    RLXQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RLXQ_E_CUDA, "device index out of range");
+    if (coop_ok[dev].load() == 0) {
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_chain_kernel<SCHEME, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        int coop = 0, per_sm = 0;
+        RLXQ_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        RLXQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel<SCHEME, MM>, (int)int_threads(false),
+                                                                    pl.smem_bytes));
+        coop_ok[dev].store(coop && per_sm >= 2 ? 1 : -1);
+    }
+    if (coop_ok[dev].load() < 0) return fail(RLXQ_E_SHAPE, "the chain kernel's grid cannot be co-resident on this device");
+    ChainParams A{};
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    const unsigned long long token = next_call_token();
+    int* err = device_error_word();
+    if (!err) return fail(RLXQ_E_CUDA, "device error word unavailable");
+    for (uint32_t i = 0; i < nl; ++i) {
+        IntParams& P = A.layer[i];
+        const auto& q = pl.l[i];
+        int rc = encode_weight_map(&P.wmap, L[i].w, L[i].n, (uint64_t)L[i].k / g.elems * g.bytes, IntBox<SCHEME, false>::ROW / 8, 16);
+        if (rc) return rc;
+        P.w = L[i].w;
+        P.y = i + 1 < nl ? static_cast<void*>(base + q.off_y) : y;
+        P.y_bf16 = i + 1 < nl ? 0u : (ybf ? 1u : 0u);
+        P.x = i == 0 ? x : A.layer[i - 1].y;
+        P.x_bf16 = i == 0 && xbf ? 1u : 0u;
+        P.k = L[i].k; P.n = L[i].n; P.m_real = MM;
+        P.row_bytes = L[i].k / g.elems * g.bytes;
+        P.ntiles = q.ntiles; P.nchunks = q.nchunks; P.total_chunks = q.total_chunks; P.slots = 2;
+        P.active = q.active;
+        P.chunks_q = q.total_chunks / q.active; P.chunks_r = q.total_chunks % q.active;
+        P.nstages = pl.nstages; P.xq_row_bytes = q.xq_row_bytes; P.xq_pieces = MM;
+        P.stage_stride = IntBox<SCHEME, false>::STAGE_BYTES;
+        P.off_stage = pl.off_stage; P.off_red = pl.off_red; P.off_bar = pl.off_bar;
+        P.inline_q = 1u;
+        P.partial = reinterpret_cast<float*>(base + q.off_partial);
+        P.flags = reinterpret_cast<unsigned long long*>(base + q.off_flags);
+        P.token = token;
+        P.swiglu = L[i].swiglu ? 1u : 0u;
+        P.err = err;
+    }
+    A.nlayers = nl;
+    A.tag = (uint32_t)(token >> 8) | 1u;
+    A.spin_limit = 1u << 22;
+    A.sync = reinterpret_cast<unsigned long long*>(base + pl.off_sync);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3(int_threads(false));
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;      // the CTAs wait for one another: they must all be resident
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    // with programmatic serialization the ring fills while the predecessor drains; where the driver does not take
+    // both attributes together the launch is cooperative only
+    static std::atomic<int> both_ok[64];             // 0 untried, 1 accepted, -1 refused
+    cfg.numAttrs = (options().pdl.load() && both_ok[dev].load() >= 0) ? 2 : 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<SCHEME, MM>, A);
+    if (le != cudaSuccess && cfg.numAttrs == 2 && both_ok[dev].load() == 0) {
+        (void)cudaGetLastError();
+        both_ok[dev].store(-1);
+        cfg.numAttrs = 1;
+        le = cudaLaunchKernelEx(&cfg, gemv_chain_kernel<SCHEME, MM>, A);
+    } else if (le == cudaSuccess && cfg.numAttrs == 2) {
+        both_ok[dev].store(1);
+    }
+    RLXQ_CUDA_TRY(le);
+    count_launch();
+    return check_launch("gemv_chain_kernel");
+}
+
+template <uint32_t SCHEME>
+static int launch_chain_s(cudaStream_t stream, const ChainLayer* L, uint32_t nl, const void* x, bool xbf, void* y, bool ybf,
+                          uint32_t m, void* ws, size_t ws_bytes) {
+    const ChainPlan pl = plan_chain<SCHEME>(L, nl, m);
+    if (!pl.ok) return fail(RLXQ_E_SHAPE, "these layers cannot run as one chain kernel");
+    if (m == 1) return launch_chain_t<SCHEME, 1>(stream, L, nl, x, xbf, y, ybf, ws, ws_bytes, pl);
+    return launch_chain_t<SCHEME, 2>(stream, L, nl, x, xbf, y, ybf, ws, ws_bytes, pl);
+}
+
+// 0 when the layers cannot run as one chain kernel (then the caller runs them one by one).
+size_t chain_workspace_bytes(uint32_t scheme, const ChainLayer* L, uint32_t nl, uint32_t m) {
+    ChainPlan pl{};
+    switch (scheme) {
+        case RLXQ_Q4_0: pl = plan_chain<RLXQ_Q4_0>(L, nl, m); break;
+        case RLXQ_Q8_0: pl = plan_chain<RLXQ_Q8_0>(L, nl, m); break;
+        case RLXQ_Q4_K: pl = plan_chain<RLXQ_Q4_K>(L, nl, m); break;
+        case RLXQ_Q5_K: pl = plan_chain<RLXQ_Q5_K>(L, nl, m); break;
+        case RLXQ_Q6_K: pl = plan_chain<RLXQ_Q6_K>(L, nl, m); break;
+        default: break;
+    }
+    return pl.ok ? pl.ws_bytes : 0;
+}
+
+int launch_gemv_chain(cudaStream_t stream, uint32_t scheme, const ChainLayer* L, uint32_t nl, const void* x, bool xbf, void* y,
+                      bool ybf, uint32_t m, void* ws, size_t ws_bytes) {
+    for (uint32_t i = 0; i < nl; ++i)
+        if ((uintptr_t)L[i].w & 15u) return fail(RLXQ_E_ALIGN, "chain weights must be 16-byte aligned");
+    if ((uintptr_t)x & 15u) return fail(RLXQ_E_ALIGN, "x must be 16-byte aligned");
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_chain_s<RLXQ_Q4_0>(stream, L, nl, x, xbf, y, ybf, m, ws, ws_bytes);
+        case RLXQ_Q8_0: return launch_chain_s<RLXQ_Q8_0>(stream, L, nl, x, xbf, y, ybf, m, ws, ws_bytes);
+        case RLXQ_Q4_K: return launch_chain_s<RLXQ_Q4_K>(stream, L, nl, x, xbf, y, ybf, m, ws, ws_bytes);
+        case RLXQ_Q5_K: return launch_chain_s<RLXQ_Q5_K>(stream, L, nl, x, xbf, y, ybf, m, ws, ws_bytes);
+        case RLXQ_Q6_K: return launch_chain_s<RLXQ_Q6_K>(stream, L, nl, x, xbf, y, ybf, m, ws, ws_bytes);
+        default: return fail(RLXQ_E_SCHEME, "no chain kernel for scheme %u", scheme);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -26,6 +26,12 @@ int launch_gemv_int(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
 // tcgen05 / tensor-memory GEMV (m <= 8): weights decoded to fp16 in tensor memory, activations as bf16 high / low rows.
 int launch_split_hi_lo(cudaStream_t stream, const float* x, void* out, uint64_t rows, uint64_t k);
 int launch_add_halves(cudaStream_t stream, const float* y2, void* y, bool ybf, uint64_t rows, uint64_t n);
+int launch_swiglu_pair(cudaStream_t stream, const float* gu, void* h, uint32_t m, uint32_t f);
+// A chain of dependent batch-1/2 GEMVs in one cooperative launch (gemv_int.cu, gemv_chain_kernel).
+struct ChainLayer { const uint8_t* w; uint32_t k, n, swiglu; };
+size_t chain_workspace_bytes(uint32_t scheme, const ChainLayer* layers, uint32_t nlayers, uint32_t m);
+int launch_gemv_chain(cudaStream_t stream, uint32_t scheme, const ChainLayer* layers, uint32_t nlayers, const void* x, bool xbf,
+                      void* y, bool ybf, uint32_t m, void* ws, size_t ws_bytes);
 bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x);
 size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
 int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,

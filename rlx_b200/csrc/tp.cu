@@ -33,6 +33,18 @@ __global__ void __launch_bounds__(256) swiglu_pair_kernel(const float* __restric
     }
 }
 
+// h[m, f] (f32) = up * silu(gate) of gu[m, 2f].
+int launch_swiglu_pair(cudaStream_t stream, const float* gu, void* h, uint32_t m, uint32_t f) {
+    const uint64_t total = (uint64_t)m * f;
+    if (total == 0) return RLXQ_OK;
+    uint64_t blocks = (total + 255) / 256;
+    const uint64_t cap = (uint64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    swiglu_pair_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(gu, h, m, f);
+    count_launch();
+    return check_launch("swiglu_pair_kernel");
+}
+
 }  // namespace rlxq
 
 using namespace rlxq;

@@ -460,3 +460,66 @@ def test_integer_mma_gemv_refuses_what_it_cannot_run():
         assert e.value.status == -2
     finally:
         R.set_option("gemv_kernel", 0)
+
+
+# ------------------------------------------------------------------ rlxq_matmul_chain
+def _chain_reference(s, x, ws, spec):
+    cur = x.astype(np.float32)
+    for w, (k, n, sw) in zip(ws, spec):
+        if sw:
+            g, u = cur[:, :k].astype(np.float64), cur[:, k:].astype(np.float64)
+            cur = (u * (g / (1.0 + np.exp(-g)))).astype(np.float32)
+        cur = O.matmul_bt_mt(np.ascontiguousarray(cur), w, cur.shape[0], k, n, s).astype(np.float32)
+    return cur
+
+
+CHAIN_CASES = [("q4_0", 1, [(256, 512, 0), (512, 256, 0)]), ("q4_0", 1, [(4096, 11008, 0), (11008, 4096, 0)]),
+               ("q4_0", 2, [(4096, 11008, 0), (11008, 4096, 0)]), ("q4_k", 1, [(4096, 2 * 7168, 0), (7168, 8192, 1)]),
+               ("q6_k", 1, [(2048, 8192, 0), (8192, 6144, 0), (6144, 4800, 0)]), ("q8_0", 2, [(1024, 2 * 4096, 0), (4096, 5000, 1)]),
+               ("q4_k", 4, [(2048, 2 * 1024, 0), (1024, 512, 1)]), ("q5_k", 1, [(512, 300, 0)])]
+
+
+@pytest.mark.parametrize("fused", [0, 1])
+@pytest.mark.parametrize("sch,m,spec", CHAIN_CASES)
+def test_matmul_chain_matches_the_layers_run_on_the_oracle(sch, m, spec, fused):
+    """rlxq_matmul_chain layer by layer (the default) and as one cooperative kernel (option gemv_chain = 1, where
+    the shapes allow it; the call falls back by itself elsewhere): plain layers, SwiGLU layers, two and three
+    layers, twice in a row on the same workspace."""
+    import torch
+    s = O.SCHEMES[sch]
+    ws = [O.fill_weights(s, 300 + 7 * i + m, k, n) for i, (k, n, sw) in enumerate(spec)]
+    x = O.fill_normal(301 + m, m * spec[0][0]).reshape(m, -1)
+    wd = [torch.from_numpy(w).cuda() for w in ws]
+    xd = torch.from_numpy(x).cuda()
+    layers = [(w, n, sw) for w, (k, n, sw) in zip(wd, spec)]
+    need = R.chain_workspace_bytes(s, spec, m)
+    wsb = torch.full((need + 256,), 0xA5, dtype=torch.uint8, device="cuda")      # contents irrelevant on entry
+    R.set_option("gemv_chain", fused)
+    try:
+        before = R.launch_count()
+        y1 = R.matmul_chain(xd, layers, s, workspace=wsb).cpu().numpy()
+        launches = R.launch_count() - before
+        y2 = R.matmul_chain(xd, layers, s, workspace=wsb).cpu().numpy()
+        R.device_status()
+    finally:
+        R.set_option("gemv_chain", 0)
+    assert np.array_equal(y1, y2)
+    if fused and sch == "q4_0" and m <= 2:
+        assert launches == 1                                   # one kernel for the whole chain
+    ref = _chain_reference(s, x, ws, spec)
+    assert np.isfinite(y1).all()
+    assert np.abs(y1 - ref).max() <= 1e-3 * (np.abs(ref).max() + 1e-30)
+
+
+def test_matmul_chain_rejects_layers_that_do_not_fit_together():
+    s = O.Q4_0
+    with pytest.raises(R.RlxqError) as e:
+        R.chain_workspace_bytes(s, [(256, 64, 0), (256, 32, 0)], 1)      # layer 1 takes 256 values, layer 0 yields 64
+    assert e.value.status == -2
+    with pytest.raises(R.RlxqError) as e:
+        R.chain_workspace_bytes(s, [(256, 64, 1)], 1)                    # the first layer has nothing to combine
+    assert e.value.status == -2
+    with pytest.raises(R.RlxqError) as e:
+        R.chain_workspace_bytes(s, [(256, 64, 0), (32, 16, 0)], 1)       # SwiGLU flag missing: 64 != 32
+    assert e.value.status == -2
+    assert R.chain_workspace_bytes(s, [(256, 64, 0), (32, 16, 1)], 1) > 0
