@@ -523,3 +523,39 @@ def test_matmul_chain_rejects_layers_that_do_not_fit_together():
         R.chain_workspace_bytes(s, [(256, 64, 0), (32, 16, 0)], 1)       # SwiGLU flag missing: 64 != 32
     assert e.value.status == -2
     assert R.chain_workspace_bytes(s, [(256, 64, 0), (32, 16, 1)], 1) > 0
+
+
+# ------------------------------------------------------------------ seeded random shapes through the automatic dispatch
+def _random_gemv_cases(count=72, seed=20240611):
+    rng = np.random.default_rng(seed)
+    cases = []
+    while len(cases) < count:
+        sch = ["q4_0", "q8_0", "q4_k", "q5_k", "q6_k"][int(rng.integers(0, 5))]
+        unit = 2048 if sch == "q6_k" else 256
+        k = unit * int(rng.integers(1, 32768 // unit + 1))
+        m = int(rng.integers(1, 9))
+        nmax = max(1, min(6000, 24_000_000 // k))
+        n = int(rng.integers(1, nmax + 1))
+        cases.append((sch, m, k, n, bool(rng.integers(0, 2)), bool(rng.integers(0, 4) == 0), int(rng.integers(0, 2))))
+    return cases
+
+
+@pytest.mark.parametrize("sch,m,k,n,x_bf16,y_bf16,two_kernel", _random_gemv_cases())
+def test_decode_gemv_random_shapes(sch, m, k, n, x_bf16, y_bf16, two_kernel):
+    """Whatever the plan makes of a shape (ring depth, CTAs per SM, tiles cut once or many times, activations
+    resident or streamed, quantised in the kernel or in front of it), the result is the oracle's."""
+    import torch
+    s = O.SCHEMES[sch]
+    w, x = make_case(s, m, k, n, seed=31 * k + n + m, x_bf16=x_bf16)
+    R.set_option("gemv_inline_q", 1 if two_kernel else 0)
+    try:
+        wd = torch.from_numpy(w).cuda()
+        xd = torch.from_numpy(x).cuda()
+        if x_bf16:
+            xd = xd.to(torch.bfloat16)
+        y = R.matmul(xd, wd, s, n, out_dtype=torch.bfloat16 if y_bf16 else torch.float32).float().cpu().numpy()
+        R.device_status()
+    finally:
+        R.set_option("gemv_inline_q", 0)
+    assert_within_tolerance(y, reference(s, w, x, n), bound(s, w, x, n), tol=1e-3 if y_bf16 else 2e-4,
+                            what=f"random {sch} m={m} k={k} n={n}")
