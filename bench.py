@@ -830,6 +830,10 @@ def sweep_all_configs(torch, R, O, dev, headline_entry: dict) -> list[dict]:
         lambda: sweep_gemv(torch, R, O, dev, "cfg1 q4_0 llama7b ffn gemv pair m=8", "q4_0", [(4096, 11008), (11008, 4096)], "f32", 8, 100, 5, pk),
         lambda: sweep_gemv(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemv m=1", "q4_k", [(4096, 14336)], "bf16", 1, 200, 5, pk),
         lambda: sweep_gemv(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemv m=1", "q6_k", [(14336, 4096)], "bf16", 1, 200, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemv m=4", "q4_k", [(4096, 14336)], "bf16", 4, 100, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemv m=8", "q4_k", [(4096, 14336)], "bf16", 8, 100, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemv m=4", "q6_k", [(14336, 4096)], "bf16", 4, 100, 5, pk),
+        lambda: sweep_gemv(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemv m=8", "q6_k", [(14336, 4096)], "bf16", 8, 100, 5, pk),
         lambda: sweep_gemm(torch, R, O, dev, "cfg2 q4_k 4096->14336 gemm m=512", "q4_k", 512, 4096, 14336, 20, 3, pk),
         lambda: sweep_gemm(torch, R, O, dev, "cfg2 q6_k 14336->4096 gemm m=512", "q6_k", 512, 14336, 4096, 20, 3, pk),
         lambda: sweep_ffn_one_gpu(torch, R, O, dev, "cfg3 q4_k 70b ffn m=1, 1 gpu", 1, 50, 3, pk),
