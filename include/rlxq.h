@@ -201,7 +201,8 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
  *                  GEMV, 3 = force the integer GEMV with its dp4a units (m <= 4), 4 = force the tcgen05 GEMV (m <= 8;
  *                  Q4_0, Q8_0, Q4_K; k a multiple of 256), 5 = force the integer GEMV with its integer-MMA units
- *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K; k a multiple of 256, 2048 for Q6_K).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
+ *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K with k a multiple of 256, 2048 for Q6_K; Q8_K, Q2_K with k a
+ *                  multiple of 1024, Q3_K of 2048: whole 16-byte groups of super-blocks per row).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
  *                  correct but slower than the others on the shapes measured so far, hence not automatic.
  *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1
  *   "gemv_chain": 1 = rlxq_matmul_chain runs a chain as one cooperative kernel where it can, 0 (default) = always

@@ -74,10 +74,13 @@ constexpr uint32_t kIntCU = 8;                         // 256-weight units per s
 // not all start on the same shared-memory bank; Q6_K's 1680-byte rows already do not.  TMA boxes
 // are at most 256 eight-byte elements wide, hence two for Q8_0.
 // (The integer-MMA unit of Q4_0 reads word t of rows g and g + 8, lane = 4 g + t: a pitch of 4 words mod 32.)
+// (Q8_K: two boxes of four 292-byte units, 32 bytes of padding: a pitch of 12 words mod 32.  Q2_K: 8 x 84 + 16 bytes,
+// also 12 mod 32.  Q3_K: 8 x 110 bytes, 28 mod 32, no padding.)
 template <uint32_t SCHEME, bool MMA = false> struct IntBox {
-    static constexpr uint32_t NB = (SCHEME == RLXQ_Q8_0) ? 2u : 1u;
+    static constexpr uint32_t NB = (SCHEME == RLXQ_Q8_0 || SCHEME == RLXQ_Q8_K) ? 2u : 1u;
     static constexpr uint32_t UB = kIntCU / NB;                               // units per box
-    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B + (SCHEME == RLXQ_Q6_K ? 0u : (SCHEME == RLXQ_Q4_0 && !MMA) ? 32u : 16u);
+    static constexpr uint32_t ROW = UB * StagedTraits<SCHEME>::UNIT_B +
+        ((SCHEME == RLXQ_Q6_K || SCHEME == RLXQ_Q3_K) ? 0u : ((SCHEME == RLXQ_Q4_0 && !MMA) || SCHEME == RLXQ_Q8_K) ? 32u : 16u);
     static constexpr uint32_t BOX_BYTES = 16 * ROW;
     static constexpr uint32_t STAGE_BYTES = NB * BOX_BYTES;
 };
@@ -791,6 +794,169 @@ template <int MM> struct QUnitMma<RLXQ_Q6_K, MM> {
     __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
 };
 
+// ---- Q8_K: f32 d, then 256 int8 quants in order (the 16 block sums behind them are not read): the quants are the
+// A fragment as they are, word-aligned.
+template <int MM> struct QUnitMma<RLXQ_Q8_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * 292, p8 = p0 + 8 * L.row_pitch;
+        const float d0 = ldsf(p0), d8 = ldsf(p8);
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t o = 4 + 128 * part + 32 * b + 4 * t;
+            const uint32_t a0 = lds32(p0 + o), a2 = lds32(p0 + o + 16), a1 = lds32(p8 + o), a3 = lds32(p8 + o + 16);
+#pragma unroll
+            for (int gq = 0; gq < MMG; ++gq) {
+                const uint2 bb = lds64(fb + (b * MMG + gq) * 256);
+                const float s = ldsf(sb + (b * MMG + gq) * 32);
+                int c[4];
+                imma_s8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                tot[2 * gq] = fmaf(d0 * s, (float)(c[0] * 128 + c[1]), tot[2 * gq]);
+                tot[2 * gq + 1] = fmaf(d8 * s, (float)(c[2] * 128 + c[3]), tot[2 * gq + 1]);
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
+// ---- Q2_K as the reference reads it: d, dmin, 16 bytes of (scale | min << 4), 64 quant bytes.  A half of the
+// super-block is 32 bytes holding four 2-bit planes of 32 weights; every 16 weights have their own 4-bit scale and
+// min, so the MMA is the k = 16 shape.  Scales and mins multiply the integer sums (dot products, and the sums of
+// 16 activations that come with the fragments); d and dmin times the activation scale finish a group of 32.
+template <int MM> struct QUnitMma<RLXQ_Q2_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 64) + t * 16;
+        uint32_t q[2][2], scw[2][2];
+        float d[2], dm[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t p = L.row + 8 * r * L.row_pitch + u * 84;
+            const uint32_t hd = lds32(p);
+            d[r] = f16_bits_to_f32(hd & 0xFFFFu);
+            dm[r] = f16_bits_to_f32(hd >> 16);
+            scw[r][0] = lds32(p + 4 + 8 * part);
+            scw[r][1] = lds32(p + 8 + 8 * part);
+            q[r][0] = lds32(p + 20 + 32 * part + 4 * t);
+            q[r][1] = lds32(p + 36 + 32 * part + 4 * t);
+        }
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {               // the four 2-bit planes of the half
+            uint32_t a[2][2];                          // [sub-block][row]
+            int sc[2][2], mn[2][2];
+#pragma unroll
+            for (int sbk = 0; sbk < 2; ++sbk)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    a[sbk][r] = (q[r][sbk] >> (2 * gq)) & 0x03030303u;
+                    const int si = 2 * gq + sbk;
+                    const uint32_t byte = (scw[r][si >> 2] >> (8 * (si & 3))) & 0xFFu;
+                    sc[sbk][r] = (int)(byte & 0xFu);
+                    mn[sbk][r] = (int)(byte >> 4);
+                }
+#pragma unroll
+            for (int g2 = 0; g2 < MMG; ++g2) {
+                const uint2 bb = lds64(fb + (gq * MMG + g2) * 256);
+                const uint4 se = lds128(sb + (gq * MMG + g2) * 64);      // scale, sum of 16, sum of the next 16
+                int c0[4], c1[4];
+                imma16_u8s8(c0, a[0][0], a[0][1], bb.x);
+                imma16_u8s8(c1, a[1][0], a[1][1], bb.y);
+                const float s = __uint_as_float(se.x);
+                const int v0 = (c0[0] * 128 + c0[1]) * sc[0][0] + (c1[0] * 128 + c1[1]) * sc[1][0];
+                const int v8 = (c0[2] * 128 + c0[3]) * sc[0][1] + (c1[2] * 128 + c1[3]) * sc[1][1];
+                const int m0 = (int)se.y * mn[0][0] + (int)se.z * mn[1][0];
+                const int m8 = (int)se.y * mn[0][1] + (int)se.z * mn[1][1];
+                tot[2 * g2] = fmaf(d[0] * s, (float)v0, fmaf(-dm[0] * s, (float)m0, tot[2 * g2]));
+                tot[2 * g2 + 1] = fmaf(d[1] * s, (float)v8, fmaf(-dm[1] * s, (float)m8, tot[2 * g2 + 1]));
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
+// ---- Q3_K as the reference reads it: d, 12 bytes of sixteen 6-bit scales, 32 high-mask bytes, 64 quant bytes.  A
+// weight is its 2-bit plane value, minus 4 unless its mask bit is set, times d * (scale - 32): the quants go in as
+// 2 bits + 4 * mask bit (0 .. 7) and the -4 comes from the sums of 16 activations.  A unit starts 2 bytes off a
+// word when its index is odd.
+template <int MM> struct QUnitMma<RLXQ_Q3_K, MM> {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        using W = QUnitMma<RLXQ_Q6_K, MM>;             // its word loader: aligned words, funnel-shifted for odd units
+        const uint32_t t = L.lane & 3u;
+        const bool odd = u & 1u;
+        const uint32_t sh = odd ? 16u : 0u;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 64) + t * 16;
+        uint32_t q[2][2], hm[2][2], scw[2][2];
+        float d[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t pa = L.row + 8 * r * L.row_pitch + u * 110 - (odd ? 2u : 0u);
+            // bytes 0..15 of the unit: d, the 12 scale bytes, two mask bytes
+            uint32_t hd[4];
+            W::template words<4>(pa, 0, 4, sh, odd, hd);
+            d[r] = f16_bits_to_f32(hd[0] & 0xFFFFu);
+            const uint32_t aux0 = __funnelshift_r(hd[0], hd[1], 16), aux1 = __funnelshift_r(hd[1], hd[2], 16),
+                           tmp = __funnelshift_r(hd[2], hd[3], 16);
+            // the eight scales of this half, one per byte (rlx-gguf/src/lib.rs:897-911)
+            if (part == 0) {
+                scw[r][0] = (aux0 & 0x0F0F0F0Fu) | ((tmp & 0x03030303u) << 4);
+                scw[r][1] = (aux1 & 0x0F0F0F0Fu) | (((tmp >> 2) & 0x03030303u) << 4);
+            } else {
+                scw[r][0] = ((aux0 >> 4) & 0x0F0F0F0Fu) | (((tmp >> 4) & 0x03030303u) << 4);
+                scw[r][1] = ((aux1 >> 4) & 0x0F0F0F0Fu) | (((tmp >> 6) & 0x03030303u) << 4);
+            }
+            // the mask (byte 14) and the quants (byte 46) sit 2 mod 4 inside the unit: aligned in an odd unit,
+            // funnel-shifted from the word below in an even one
+            W::template words<2>(pa, (odd ? 16u : 12u) + 4 * t, 16, 16u, !odd, hm[r]);
+            W::template words<2>(pa, (odd ? 48u : 44u) + 32 * part + 4 * t, 16, 16u, !odd, q[r]);
+        }
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {
+            uint32_t a[2][2];
+            int sc[2][2];
+#pragma unroll
+            for (int sbk = 0; sbk < 2; ++sbk)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint32_t lo = (q[r][sbk] >> (2 * gq)) & 0x03030303u;
+                    const uint32_t hb = (hm[r][sbk] >> (4 * part + gq)) & 0x01010101u;
+                    a[sbk][r] = lo | (hb << 2);
+                    const int si = 2 * gq + sbk;
+                    sc[sbk][r] = (int)((scw[r][si >> 2] >> (8 * (si & 3))) & 0xFFu) - 32;
+                }
+#pragma unroll
+            for (int g2 = 0; g2 < MMG; ++g2) {
+                const uint2 bb = lds64(fb + (gq * MMG + g2) * 256);
+                const uint4 se = lds128(sb + (gq * MMG + g2) * 64);      // scale, -4 * sum of 16, -4 * sum of the next 16
+                int c0[4], c1[4];
+                imma16_u8s8(c0, a[0][0], a[0][1], bb.x);
+                imma16_u8s8(c1, a[1][0], a[1][1], bb.y);
+                const float s = __uint_as_float(se.x);
+                const int v0 = (c0[0] * 128 + c0[1] + (int)se.y) * sc[0][0] + (c1[0] * 128 + c1[1] + (int)se.z) * sc[1][0];
+                const int v8 = (c0[2] * 128 + c0[3] + (int)se.y) * sc[0][1] + (c1[2] * 128 + c1[3] + (int)se.z) * sc[1][1];
+                tot[2 * g2] = fmaf(d[0] * s, (float)v0, tot[2 * g2]);
+                tot[2 * g2 + 1] = fmaf(d[1] * s, (float)v8, tot[2 * g2 + 1]);
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+
 // What the per-block integer sums are multiplied by before they are stored.
 template <uint32_t SCHEME> struct SumBias;
 template <> struct SumBias<RLXQ_Q4_0> { static constexpr int value = -8; };
@@ -798,6 +964,9 @@ template <> struct SumBias<RLXQ_Q8_0> { static constexpr int value = 0; };
 template <> struct SumBias<RLXQ_Q4_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q5_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
+template <> struct SumBias<RLXQ_Q8_K> { static constexpr int value = 0; };
+template <> struct SumBias<RLXQ_Q2_K> { static constexpr int value = 1; };
+template <> struct SumBias<RLXQ_Q3_K> { static constexpr int value = -4; };
 // Whether the fragment-ordered activations carry the block sum as the float s_b * bias * sum(X) (formats
 // with a min term) or as the integer bias * sum(X) (added to the dot product before it is converted).
 constexpr bool frag_sum_is_float(uint32_t scheme) { return scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K; }
@@ -1784,6 +1953,11 @@ struct IntPlan {
 
 // Formats that have a integer-MMA unit (QUnitMma).
 constexpr bool int_has_mma(uint32_t scheme) {
+    return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K ||
+           scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K;
+}
+// Formats that have a dp4a unit (QUnit); the others run batch 1 on their integer-MMA unit as well.
+constexpr bool int_has_dp4a(uint32_t scheme) {
     return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K;
 }
 
@@ -1937,11 +2111,15 @@ static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint
             return fail(RLXQ_E_SHAPE, "no integer-MMA GEMV for scheme %u", (unsigned)SCHEME);
         }
     }
-    const IntPlan pl = plan_int<SCHEME>(m, k, n);
-    if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
-    if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
-    if (m == 2) return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
-    return launch_int_t<SCHEME, 4>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, m);
+    if constexpr (int_has_dp4a(SCHEME)) {
+        const IntPlan pl = plan_int<SCHEME>(m, k, n);
+        if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
+        if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
+        if (m == 2) return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+        return launch_int_t<SCHEME, 4>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, m);
+    } else {
+        return fail(RLXQ_E_SHAPE, "no dp4a unit for scheme %u", (unsigned)SCHEME);
+    }
 }
 
 bool int_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x) {
@@ -1996,6 +2174,9 @@ bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
         case RLXQ_Q4_K: return plan_int<RLXQ_Q4_K, true>(m, k, n).ok;
         case RLXQ_Q5_K: return plan_int<RLXQ_Q5_K, true>(m, k, n).ok;
         case RLXQ_Q6_K: return plan_int<RLXQ_Q6_K, true>(m, k, n).ok;
+        case RLXQ_Q8_K: return plan_int<RLXQ_Q8_K, true>(m, k, n).ok;
+        case RLXQ_Q2_K: return plan_int<RLXQ_Q2_K, true>(m, k, n).ok;
+        case RLXQ_Q3_K: return plan_int<RLXQ_Q3_K, true>(m, k, n).ok;
         default: return false;
     }
 }
@@ -2008,6 +2189,9 @@ size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t
         case RLXQ_Q4_K: pl = plan_int<RLXQ_Q4_K, true>(m, k, n); break;
         case RLXQ_Q5_K: pl = plan_int<RLXQ_Q5_K, true>(m, k, n); break;
         case RLXQ_Q6_K: pl = plan_int<RLXQ_Q6_K, true>(m, k, n); break;
+        case RLXQ_Q8_K: pl = plan_int<RLXQ_Q8_K, true>(m, k, n); break;
+        case RLXQ_Q2_K: pl = plan_int<RLXQ_Q2_K, true>(m, k, n); break;
+        case RLXQ_Q3_K: pl = plan_int<RLXQ_Q3_K, true>(m, k, n); break;
         default: break;
     }
     return pl.ok ? pl.ws_bytes : 0;
@@ -2022,6 +2206,9 @@ int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, boo
         case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
     }
 }
@@ -2068,6 +2255,9 @@ int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu
             case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
+            case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
             default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
         }
     }

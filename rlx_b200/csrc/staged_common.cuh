@@ -43,6 +43,21 @@ template <> struct StagedTraits<RLXQ_Q5_K> {
     static constexpr float BIAS = -1024.f;
 };
 
+// Q8_K, Q2_K, Q3_K only run in the integer GEMV with its integer-MMA units, which reads UNIT_B, AG and SUB
+// (rows of 292-, 84- and 110-byte super-blocks are 16-byte aligned every 4, 4 and 8 of them).
+template <> struct StagedTraits<RLXQ_Q8_K> {
+    static constexpr uint32_t UNIT_B = 292, AG = 4, CU = 4, STRIDE = 1200, STAGES = 4, SUB = 32;
+    static constexpr float BIAS = 0.f;
+};
+template <> struct StagedTraits<RLXQ_Q2_K> {
+    static constexpr uint32_t UNIT_B = 84, AG = 4, CU = 8, STRIDE = 688, STAGES = 4, SUB = 16;
+    static constexpr float BIAS = 0.f;
+};
+template <> struct StagedTraits<RLXQ_Q3_K> {
+    static constexpr uint32_t UNIT_B = 110, AG = 8, CU = 8, STRIDE = 880, STAGES = 4, SUB = 16;
+    static constexpr float BIAS = 0.f;
+};
+
 constexpr uint32_t kConsumerWarps = 4;
 constexpr uint32_t kThreads = (kConsumerWarps + 1) * 32;
 // A waiting thread is suspended by the hardware for up to kSuspendHintNs per attempt, so a wait

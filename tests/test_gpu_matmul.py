@@ -392,6 +392,12 @@ IMMA_SHAPES = [("q4_0", 3, 256, 100, False, False), ("q4_0", 4, 4096, 11008, Fal
                ("q6_k", 5, 6144, 256, True, True), ("q6_k", 2, 4096, 14336, False, False),
                ("q5_k", 3, 256, 100, False, False), ("q5_k", 4, 4096, 14336, False, False), ("q5_k", 8, 2048, 1000, True, False),
                ("q5_k", 2, 14336, 520, False, True), ("q5_k", 6, 28672, 300, False, False),
+               ("q8_k", 1, 1024, 100, False, False), ("q8_k", 4, 4096, 4096, False, False), ("q8_k", 8, 2048, 1000, True, False),
+               ("q8_k", 6, 28672, 300, False, True),
+               ("q2_k", 1, 1024, 100, False, False), ("q2_k", 3, 4096, 4096, False, False), ("q2_k", 8, 2048, 1000, True, False),
+               ("q2_k", 5, 28672, 300, False, False), ("q2_k", 2, 5120, 777, False, True),
+               ("q3_k", 1, 2048, 100, False, False), ("q3_k", 4, 4096, 4096, False, False), ("q3_k", 8, 2048, 1000, True, False),
+               ("q3_k", 7, 28672, 300, False, False), ("q3_k", 2, 6144, 777, False, True),
                # fragments of all rows do not fit in shared memory: they stream through the ring beside the weights
                ("q4_0", 8, 11008, 4096, False, False), ("q6_k", 8, 8192, 1000, False, False), ("q4_k", 4, 28672, 2048, False, False),
                ("q8_0", 8, 14336, 777, True, True), ("q4_k", 7, 28672, 520, True, False)]
@@ -448,7 +454,7 @@ def test_integer_mma_gemv_refuses_what_it_cannot_run():
     import torch
     R.set_option("gemv_kernel", 5)
     try:
-        s = O.Q8_K                                               # no MMA unit for this format
+        s = O.Q4_1                                               # no MMA unit for this format
         w, x = make_case(s, 4, 2048, 16, seed=3)
         with pytest.raises(R.RlxqError) as e:
             R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
@@ -526,12 +532,12 @@ def test_matmul_chain_rejects_layers_that_do_not_fit_together():
 
 
 # ------------------------------------------------------------------ seeded random shapes through the automatic dispatch
-def _random_gemv_cases(count=72, seed=20240611):
+def _random_gemv_cases(count=96, seed=20240611):
     rng = np.random.default_rng(seed)
     cases = []
     while len(cases) < count:
-        sch = ["q4_0", "q8_0", "q4_k", "q5_k", "q6_k"][int(rng.integers(0, 5))]
-        unit = 2048 if sch == "q6_k" else 256
+        sch = ["q4_0", "q8_0", "q4_k", "q5_k", "q6_k", "q8_k", "q2_k", "q3_k"][int(rng.integers(0, 8))]
+        unit = {"q6_k": 2048, "q3_k": 2048, "q8_k": 1024, "q2_k": 1024}.get(sch, 256)
         k = unit * int(rng.integers(1, 32768 // unit + 1))
         m = int(rng.integers(1, 9))
         nmax = max(1, min(6000, 24_000_000 // k))
