@@ -103,14 +103,25 @@ extern "C" int rlxq_matmul_chain(rlxq_stream_t stream, uint32_t scheme, const rl
     bool cur_bf = xbf;
     for (uint32_t i = 0; i < nlayers; ++i) {
         const rlxq_chain_layer& Li = layers[i];
+        const bool last = i + 1 == nlayers;
+        void* out = last ? y : static_cast<void*>(base + ((i & 1u) ? sp.off_b : sp.off_a));
         if (Li.swiglu) {
+            const uint8_t* w = static_cast<const uint8_t*>(Li.w_blocks);
+            // decode sizes: the integer GEMV's activation quantiser forms up * silu(gate) itself
+            if (options().gemv_kernel.load() == 0 &&
+                ((m <= 2 && int_supported(scheme, m, Li.k, Li.n, w, cur)) ||
+                 (m >= 2 && m <= 8 && int_mma_supported(scheme, m, Li.k, Li.n, w, cur)))) {
+                rc = launch_gemv_int_swiglu(s, scheme, static_cast<const float*>(cur), w, out, last && ybf, m, Li.k, Li.n, base, sp.mm);
+                if (rc) return rc;
+                cur = out;
+                cur_bf = false;
+                continue;
+            }
             rc = launch_swiglu_pair(s, static_cast<const float*>(cur), base + sp.off_h, m, Li.k);
             if (rc) return rc;
             cur = base + sp.off_h;
             cur_bf = false;
         }
-        const bool last = i + 1 == nlayers;
-        void* out = last ? y : static_cast<void*>(base + ((i & 1u) ? sp.off_b : sp.off_a));
         rc = dispatch_matmul(s, scheme, cur, cur_bf, static_cast<const uint8_t*>(Li.w_blocks), out, last && ybf, m, Li.k, Li.n, base, sp.mm);
         if (rc) return rc;
         cur = out;

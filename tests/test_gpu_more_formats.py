@@ -3,7 +3,7 @@ container types Q4_1, Q5_0, Q5_1 that the reference decodes only when a file is 
 
 They complete QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182): with them every scheme the reference's
 `Op::DequantMatMul` accepts runs on the GPU (the reference sends all of them to a host fallback or to its
-dequantise-everything kernel).  Dequantisation is bit-exact against the oracle; the matmul goes through the
+dequantise-everything kernel).  Dequantisation is bit-exact against the oracle; the matmul goes through the integer-MMA units where the shape allows (Q5_K, Q8_K, Q2_K, Q3_K), else the
 general kernel (f32 accumulation in a different order from the CPU's) and is held to 2e-5 * |x| * |w_row|.
 Q5_K also has the integer streaming GEMV (batch 1-2) and the tensor-core GEMM (batch > 8; f32 activations as two bf16 halves).
 """
