@@ -66,7 +66,10 @@ RLXQ_API int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, 
  * the summation order here is theirs: rank 0, 1, ... world-1).  One process per GPU.  Set-up, once:
  * every rank allocates a buffer with rlxq_tp_comm_alloc, exports its handle, the ranks exchange the
  * handles through whatever channel they share (torch.distributed, MPI, a file) and open each other's
- * with rlxq_tp_ipc_open.  Per step: rlxq_tp_allreduce_sum on every rank.  world <= 8. */
+ * with rlxq_tp_ipc_open.  Per step: rlxq_tp_allreduce_sum on every rank.  world <= 8.
+ * A buffer holds a 1 KiB header and, twice, one slot of max_elems floats per possible rank (64 * max_elems
+ * + 1024 bytes): every rank stores its partial into its slot of every peer's buffer, raises flags there, and
+ * adds the slots of its own buffer once all flags are in (eight CTAs, an eighth of the vector each). */
 RLXQ_API int rlxq_tp_comm_bytes(uint32_t max_elems, size_t* bytes);
 RLXQ_API int rlxq_tp_comm_alloc(uint32_t max_elems, void** buf);       /* cudaMalloc + zero; not capture-safe */
 RLXQ_API int rlxq_tp_comm_free(void* buf);

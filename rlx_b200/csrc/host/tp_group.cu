@@ -49,7 +49,7 @@ struct NcclApi {
 struct TpRank {
     int dev = 0;
     cudaStream_t stream = nullptr;
-    void* comm_buf = nullptr;             // rlxq_tp_comm_alloc: header + two data slots, read by the peers
+    void* comm_buf = nullptr;             // rlxq_tp_comm_alloc: header + two parities of one slot per rank, written by the peers
     uint8_t* gate_up = nullptr;
     uint8_t* down = nullptr;
     uint8_t* x = nullptr;                 // [m, d_model] staging for the activations

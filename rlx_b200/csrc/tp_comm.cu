@@ -1,16 +1,25 @@
 // One-shot sum all-reduce of a small f32 vector over NVLink peer memory, one rank per GPU.
 //
 // The decode step of the tensor-parallel FFN ends with a sum of world partial rows [m, d_model] (32 KiB
-// at m = 1).  For that size a library all-reduce is all latency (10-20 us); here every rank publishes its
-// partial in a buffer the others have mapped (CUDA IPC), raises a flag in every peer's header, waits for
-// the peers' flags, then reads all partials over NVLink and adds them in rank order -- the order of the
-// reference's host collective (rlx-driver/src/collective.rs:107-127), so the result is the same on every
-// rank and from run to run.  Plain peer loads and stores; no multimem, no TMA.
+// at m = 1).  For that size a library all-reduce is all latency (10-20 us).  Here every rank writes its
+// partial straight into every peer's buffer (posted stores over NVLink: nobody waits for a read to come
+// back), raises a flag in every peer's header behind them, waits for the peers' flags in its own header,
+// and then adds the world partials that now sit in its own memory, in rank order -- the order of the
+// reference's host collective (rlx-driver/src/collective.rs:107-127: put, barrier, fold from the identity),
+// so the result is the same on every rank and from run to run.  Plain peer stores; no multimem, no TMA.
+// (The first version pulled: publish locally, flag, then read every peer's partial.  Its sum loop over the
+// ranks was not unrolled, so each thread paid one NVLink round trip per peer, one after the other: 33 us
+// of a 53 us step on eight GPUs.)
 //
-// Buffer of a rank: [header 256 B: epoch, flags[8]] [data slot 0] [data slot 1].  The epoch lives on the
-// device and is advanced by the kernel, so a captured launch works on every replay; the two data slots
-// alternate with it, which is what lets a fast rank start the next step while a slow one still reads.
-// Every wait is bounded: a rank whose peer never arrives records an error word and returns.
+// The vector is cut into kCommParts parts, one CTA each, every part with its own epoch and flags, so the
+// parts never wait for one another: eight SMs push and add instead of one.
+//
+// Buffer of a rank: [header 1 KiB: epoch[part], flags[part][8]] [parity 0: world slots] [parity 1: world
+// slots], a slot max_elems floats.  The epochs live on the device and are advanced by the kernel, so a
+// captured launch works on every replay; the two parities alternate with them, which is what lets a fast
+// rank push the next step while a slow one still adds the previous one (a rank cannot be two steps ahead:
+// finishing a step takes every peer's flag of that step).  Every wait is bounded: a rank whose peer never
+// arrives records an error word and returns without touching (that part of) dst.
 #include "common.cuh"
 #include "rlxq_tp.h"
 #include "staged_common.cuh"
@@ -18,7 +27,8 @@
 namespace rlxq {
 
 constexpr uint32_t kCommMaxWorld = 8;
-constexpr uint32_t kCommHeader = 256;
+constexpr uint32_t kCommParts = 8;            // CTAs per all-reduce, each with its own epoch and flags
+constexpr uint32_t kCommHeader = 1024;        // epoch[kCommParts], then flags[kCommParts][kCommMaxWorld], 8 bytes each
 // Polls of a peer-written flag before a rank gives up: option "tp_spin_limit", default 2^24 (a few seconds).
 
 struct CommParams {
@@ -38,51 +48,66 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float4 ld_peer_f4(const float4* p) {       // no caching: another GPU wrote it
+__device__ __forceinline__ float4 ld_sys_f4(const float4* p) {        // no caching: another GPU wrote it
     float4 v;
     asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_sys_f4(float4* p, float4 v) {
+    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
 
-__global__ void __launch_bounds__(1024) tp_allreduce_kernel(const CommParams P) {
+__global__ void __launch_bounds__(512) tp_allreduce_kernel(const CommParams P) {
     __shared__ unsigned long long s_epoch;
     __shared__ int s_fail;
     griddep_launch_dependents();
     griddep_wait();                  // src comes from the kernel in front
-    unsigned long long* hdr = reinterpret_cast<unsigned long long*>(P.buf[P.rank]);   // [0] epoch, [1..8] flags
+    const uint32_t part = blockIdx.x;
+    unsigned long long* hdr = reinterpret_cast<unsigned long long*>(P.buf[P.rank]);
+    unsigned long long* my_flags = hdr + kCommParts + part * kCommMaxWorld;           // written by the peers
     if (threadIdx.x == 0) {
-        s_epoch = hdr[0] + 1ull;
-        hdr[0] = s_epoch;
+        s_epoch = hdr[part] + 1ull;
+        hdr[part] = s_epoch;
         s_fail = 0;
     }
     __syncthreads();
     const unsigned long long epoch = s_epoch;
-    const size_t slot = (size_t)(epoch & 1ull) * P.max_elems;
-    const uint32_t n4 = P.elems / 4;
-    // 1. publish this rank's partial
-    float4* mine = reinterpret_cast<float4*>(P.buf[P.rank] + kCommHeader) + slot / 4;
-    for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) mine[i] = reinterpret_cast<const float4*>(P.src)[i];
+    const size_t parity = (size_t)(epoch & 1ull) * kCommMaxWorld * P.max_elems;      // floats
+    // this CTA's share of the float4s
+    const uint32_t n4 = P.elems / 4, per = (n4 + kCommParts - 1) / kCommParts;
+    const uint32_t i0 = min(n4, part * per), i1 = min(n4, i0 + per);
+    // 1. this rank's partial into its slot of every rank's buffer (its own included)
+    for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        const float4 v = reinterpret_cast<const float4*>(P.src)[i];
+#pragma unroll
+        for (uint32_t r = 0; r < kCommMaxWorld; ++r)
+            if (r < P.world)
+                st_sys_f4(reinterpret_cast<float4*>(P.buf[r] + kCommHeader) + (parity + (size_t)P.rank * P.max_elems) / 4 + i, v);
+    }
     __syncthreads();                 // the release stores below, after this barrier, cover every thread's writes
     // 2. tell every peer, 3. wait for every peer (one thread per peer)
     if (threadIdx.x < P.world && threadIdx.x != P.rank) {
         const uint32_t p = threadIdx.x;
-        st_release_sys(reinterpret_cast<unsigned long long*>(P.buf[p]) + 1 + P.rank, epoch);
+        st_release_sys(reinterpret_cast<unsigned long long*>(P.buf[p]) + kCommParts + part * kCommMaxWorld + P.rank, epoch);
         bool ok = false;
         for (uint32_t it = 0; it < P.spin_limit; ++it) {
-            if (ld_acquire_sys(hdr + 1 + p) >= epoch) { ok = true; break; }
+            if (ld_acquire_sys(my_flags + p) >= epoch) { ok = true; break; }
         }
         if (!ok) { s_fail = 1; atomicExch(P.err, 40 + (int)p); }
     }
     __syncthreads();
     if (s_fail) return;
-    // 4. sum in rank order
-    for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) {
+    // 4. sum in rank order, out of this rank's own memory; all loads of an element are issued before the first add
+    const float4* mine = reinterpret_cast<const float4*>(P.buf[P.rank] + kCommHeader) + parity / 4;
+    for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        float4 v[kCommMaxWorld];
+#pragma unroll
+        for (uint32_t r = 0; r < kCommMaxWorld; ++r)
+            if (r < P.world) v[r] = ld_sys_f4(mine + (size_t)r * (P.max_elems / 4) + i);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t r = 0; r < P.world; ++r) {
-            const float4* q = reinterpret_cast<const float4*>(P.buf[r] + kCommHeader) + slot / 4 + i;
-            const float4 v = r == P.rank ? *q : ld_peer_f4(q);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+#pragma unroll
+        for (uint32_t r = 0; r < kCommMaxWorld; ++r)
+            if (r < P.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
         reinterpret_cast<float4*>(P.dst)[i] = acc;
     }
 }
@@ -94,7 +119,7 @@ using namespace rlxq;
 extern "C" int rlxq_tp_comm_bytes(uint32_t max_elems, size_t* bytes) {
     if (!bytes) return fail(RLXQ_E_NULL, "bytes is null");
     if (max_elems == 0 || max_elems % 4) return fail(RLXQ_E_SHAPE, "max_elems=%u must be a positive multiple of 4", max_elems);
-    *bytes = kCommHeader + 2 * (size_t)max_elems * 4;
+    *bytes = kCommHeader + 2 * (size_t)kCommMaxWorld * max_elems * 4;      // two parities of one slot per possible rank
     return RLXQ_OK;
 }
 
@@ -152,7 +177,7 @@ extern "C" int rlxq_tp_allreduce_sum(rlxq_stream_t stream, uint32_t rank, uint32
     P.spin_limit = (uint32_t)options().tp_spin_limit.load();
     P.err = device_error_word();
     if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
-    int rc = launch_pdl(tp_allreduce_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, P);
+    int rc = launch_pdl(tp_allreduce_kernel, dim3(kCommParts), dim3(512), 0, (cudaStream_t)stream, P);
     if (rc) return rc;
     count_launch();
     return check_launch("tp_allreduce_kernel");

@@ -273,13 +273,14 @@ def test_peer_all_reduce_wait_runs_out_and_the_context_stays_usable():
         assert st == -8 and code.value == 41, (st, code.value)  # RLXQ_E_TIMEOUT, waiting for rank 1
         assert torch.all(dst == 7.0)                             # the sum never ran
         assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0   # reported once, then clear
-        # now play the peer from the host: its partial in both data slots, its flag far ahead of any epoch
+        # now play the peer from the host, as a live peer would push: its partial into rank 1's slot of rank 0's
+        # buffer (both parities: [header][parity][rank slot of n floats, 8 of them]), its flags far ahead of any epoch
         peer = O.fill_normal(2, n)
-        hdr = 256
-        raw = np.zeros(hdr + 2 * n * 4, np.uint8)
-        raw[hdr:] = np.concatenate([peer, peer]).view(np.uint8)
-        copy_to_device(bufs[1], raw)
-        copy_to_device(bufs[0] + 8 * (1 + 1), np.array([1 << 40], np.int64))
+        hdr, parts = 1024, 8            # header: epoch[parts], flags[parts][8]
+        for parity in (0, 1):
+            copy_to_device(bufs[0] + hdr + (parity * 8 + 1) * n * 4, peer)
+        for part in range(parts):
+            copy_to_device(bufs[0] + 8 * (parts + part * 8 + 1), np.array([1 << 40], np.int64))
         assert lib.rlxq_tp_allreduce_sum(stream, 0, 2, arr, n, src.data_ptr(), dst.data_ptr(), n) == 0
         assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0
         want = O.allreduce_sum(np.stack([src.cpu().numpy(), peer]))
