@@ -421,7 +421,7 @@ def tp_flops(m: int) -> float:
 
 
 def tp_config(args, world, rotation, reduce_kind="nccl"):
-    return {"all_reduce": reduce_kind if world > 1 else "none", "workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
+    return {"all_reduce": reduce_kind if world > 1 else "none", "tp_fused": int(args.tp_fused), "workload": TP_WORKLOAD, "scheme": "q4_k", "batch": args.batch, "d_model": TP_D_MODEL, "d_ffn": TP_D_FFN,
             "parallelism": f"tp{world}: gate/up column-split, down row-split, all-reduce of f32 partials",
             "activations": "bf16", "output": "f32",
             "l2": f"rotating {rotation} distinct shard sets per rank > 2 x 126 MB L2"}
@@ -479,6 +479,7 @@ def run_tp_workload(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    R.set_option("tp_fused", args.tp_fused)
     dm, df = TP_D_MODEL, TP_D_FFN
     plan = tp.shard_plan(O.Q4_K, dm, df, world, rank)
     shard_bytes = 2 * plan.gate_up_bytes + plan.down_bytes
@@ -627,7 +628,7 @@ def run_tp_workload(args, rank, world, local_rank):
             "clocks": head["clocks"],
             "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": m * dm * 2, "d2h_bytes_per_step": m * dm * 4,
                     "ms_per_step": head["e2e_s_per_step"] * 1e3,
-                    "api": "TensorParallelFFN.forward: pinned x -> device, rlxq_tp_ffn_partial, all-reduce, y -> pinned host"},
+                    "api": "TensorParallelFFN.forward: pinned x -> device, rlxq_tp_ffn_step (partial + all-reduce), y -> pinned host"},
             "gpu_launches": head["launches"],
             "roofline": roofline_of(m, head["ms_per_step"], pk),
             "parity_max": head["parity_max"], "parity_sample": head.get("parity_sample"),
@@ -1194,6 +1195,9 @@ def main() -> None:
     ap.add_argument("--gemv-kernel", type=int, default=0, choices=[0, 1, 2, 3, 4, 5],
                     help="force a GEMV kernel for the decode workloads (the library's gemv_kernel option): 0 automatic, "
                          "1 generic, 2 mma.sync tensor mode, 3 integer dp4a, 4 tcgen05, 5 integer MMA")
+    ap.add_argument("--tp-fused", type=int, default=0, choices=[0, 1],
+                    help="tensor-parallel workload: 1 the down projection pushes and sums inside its own kernel (the library's "
+                         "tp_fused option), 0 a separate all-reduce launch follows it")
     ap.add_argument("--no-sweep", action="store_true",
                     help="default workload only: skip the `configs` list (the other configurations, one entry each)")
     args = ap.parse_args()

@@ -205,6 +205,10 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  multiple of 1024, Q3_K of 2048: whole 16-byte groups of super-blocks per row).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
  *                  correct but slower than the others on the shapes measured so far, hence not automatic.
  *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1
+ *   "tp_fused": 1 = rlxq_tp_ffn_step lets the down projection push its tiles to the peers and finish the sum
+ *                  itself (rlxq_tp.h), 0 (default) = partial, then the stand-alone all-reduce kernel.  The pushing
+ *                  form is one launch shorter but measured slower on NVLink (its CTAs hold their SMs while the
+ *                  exchange completes, so the next kernel cannot fetch its first weights meanwhile)
  *   "gemv_chain": 1 = rlxq_matmul_chain runs a chain as one cooperative kernel where it can, 0 (default) = always
  *                  layer by layer
  *   "gemm_kernel": 0 = automatic, 1 = force the tiled generic kernel, 2 = force the tcgen05 GEMM

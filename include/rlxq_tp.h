@@ -86,6 +86,23 @@ RLXQ_API int rlxq_tp_ipc_close(void* buf);
 RLXQ_API int rlxq_tp_allreduce_sum(rlxq_stream_t stream, uint32_t rank, uint32_t world, void* const* bufs,
                                    uint32_t max_elems, const float* src, float* dst, uint32_t elems);
 
+/* One step of the sharded FFN on this rank, exchange included: y[m, d_model] = sum over ranks of the partials of
+ * rlxq_tp_ffn_partial, in rank order, the same bits on every rank (every rank calls it with its own shard).  bufs,
+ * max_elems as for rlxq_tp_allreduce_sum; m * d_model <= max_elems and a multiple of 4.  By default this is
+ * rlxq_tp_ffn_partial followed by rlxq_tp_allreduce_sum.  With option "tp_fused" = 1, for batch 1-8 of Q4_0, Q8_0,
+ * Q4_K, Q5_K and Q6_K, the down projection is the collective: its finisher warps store every finished 16-row tile
+ * into this rank's slot of every rank's buffer (plain peer stores) while later tiles are still being multiplied,
+ * each CTA counts itself in on its own rank behind its stores, the CTA that completes the count tells every rank
+ * (one red.release.sys each), and a few CTAs wait, bounded, until all ranks are in and add the world slots out of
+ * their own rank's memory.  One launch fewer, no copy of the partial; measured slower than the default all the
+ * same (2 GPUs, 70B FFN shard, batch 1: 54 us against 47 us a step), because the stand-alone all-reduce leaves the
+ * SMs free for the next kernel to fetch its first weights while the exchange completes.  All ranks must make the
+ * same sequence of calls with the same shapes and the same option.  No counterpart in the reference (rlx-driver/src/collective.rs:79-128 is its host-side exchange). */
+RLXQ_API int rlxq_tp_ffn_step(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down, const void* x,
+                              uint32_t x_dtype, const void* gate_up_blocks, const void* down_blocks, float* y,
+                              uint32_t m, uint32_t d_model, uint32_t ffn_local, void* workspace, size_t workspace_bytes,
+                              uint32_t rank, uint32_t world, void* const* bufs, uint32_t max_elems);
+
 /* ---- the whole layer from one host thread: create / load / run / destroy ----
  *
  * For a host that drives all GPUs of a node from one process (the reference's CudaExecutable lives in one

@@ -48,6 +48,7 @@ _SIGS = {
     "rlxq_tp_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),
     "rlxq_tp_ipc_close": (C.c_int, [vp]),
     "rlxq_tp_allreduce_sum": (C.c_int, [vp, u32, u32, C.POINTER(vp), u32, vp, vp, u32]),
+    "rlxq_tp_ffn_step": (C.c_int, [vp, u32, u32, vp, u32, vp, vp, vp, u32, u32, u32, vp, C.c_size_t, u32, u32, C.POINTER(vp), u32]),
     "rlxq_tp_create": (C.c_int, [C.c_int, C.POINTER(C.c_int), C.POINTER(vp)]),
     "rlxq_tp_world": (C.c_int, [vp]),
     "rlxq_tp_ffn_load": (C.c_int, [vp, u32, vp, vp, vp, u32, u32]),

@@ -32,6 +32,7 @@ struct Options {
     std::atomic<int64_t> gemv_early{2};
     std::atomic<int64_t> tp_spin_limit{1 << 24};
     std::atomic<int64_t> gemv_tc_ctas{2};
+    std::atomic<int64_t> tp_fused{0};         // rlxq_tp_ffn_step: the down projection pushes its tiles and finishes the sum
     std::atomic<int64_t> gemv_chain{0};       // 1: rlxq_matmul_chain runs a chain as one cooperative kernel where it can
     std::atomic<int64_t> graph_fuse_ffn{1};
 };

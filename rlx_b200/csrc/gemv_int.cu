@@ -50,6 +50,7 @@
 #include "kernels.h"
 #include "staged_common.cuh"
 #include "tensormap.cuh"
+#include "tp_comm.cuh"
 
 namespace rlxq {
 
@@ -108,6 +109,12 @@ struct IntParams {
     // Chain kernel only: CTAs that take part in this layer (the split chunks_q / chunks_r is over them), and
     // whether the layer's input is the SwiGLU product of the previous layer's [gate | up] output.
     uint32_t active, swiglu;
+    // Tensor-parallel push (tp.world = 0: off).  The kernel is the row-parallel down projection of a sharded FFN:
+    // a finished tile goes into this rank's slot of every rank's exchange buffer instead of y; after its last
+    // tile a CTA counts itself in at every rank, waits until every rank's CTAs are all in, and writes its share
+    // of y = sum over ranks, in rank order, out of its own rank's buffer.  The quantiser kernel in front advances
+    // the step counter and the expected arrival count (tp_comm.cuh).
+    TpPush tp;
     uint32_t off_stage, off_red, off_bar;
     // Single-kernel mode: the consumer warps quantise the activations themselves (no quantiser kernel in
     // front), and a tile shared by two CTAs is completed through a token exchange that needs no zeroed memory.
@@ -1126,10 +1133,15 @@ __global__ void __launch_bounds__(256) quantise_x_kernel(const void* __restrict_
                                                          uint32_t k, int bias, uint8_t* __restrict__ xq,
                                                          uint32_t xq_row_bytes, uint32_t* __restrict__ counters,
                                                          uint32_t ntiles, float* __restrict__ y_zero, uint32_t y_count,
-                                                         uint32_t swiglu_pair) {
+                                                         uint32_t swiglu_pair, unsigned long long* __restrict__ tp_header,
+                                                         uint32_t tp_arrivals) {
     griddep_launch_dependents();   // the streaming kernel may become resident and prefetch weights
     const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, lane = threadIdx.x & 31u;
     griddep_wait();                // x (and the counters) may still be in use by the previous kernel
+    if (tp_header && gtid == 0) {  // tensor-parallel push: one more step, tp_arrivals more CTAs expected from every rank
+        tp_header[kCommWordEpoch] += 1ull;
+        tp_header[kCommWordExpected] += tp_arrivals;
+    }
     for (uint32_t i = gtid; i < ntiles; i += gridDim.x * blockDim.x) counters[i] = 0u;
     for (uint32_t i = gtid; i < y_count; i += gridDim.x * blockDim.x) y_zero[i] = 0.f;   // two-contributor add mode
     const uint32_t groups_per_row = k / 8;
@@ -1194,10 +1206,56 @@ __device__ __forceinline__ Segment segment_at(const IntParams& P, const Range& r
     return sg;
 }
 
+// Tail of a pushing down projection (one warp): wait, bounded, until every rank has counted all its CTAs in, then
+// write outputs e0 .. e1 as the sum over ranks, in rank order, out of this rank's own buffer.  Kept out of line: its
+// registers (eight outputs x eight ranks in flight) must not weigh on the kernel that calls it.
+static __device__ __noinline__ void tp_wait_and_sum(const TpPush& tp, unsigned long long tp_expected, size_t tp_parity,
+                                                    uint32_t e0, uint32_t e1, void* y, uint32_t y_bf16, int* err, uint32_t lane) {
+    bool ok = true;
+    if (lane < tp.world) {
+        const unsigned long long* arr = reinterpret_cast<const unsigned long long*>(tp.buf[tp.rank]) + kCommWordArrive + lane;
+        ok = false;
+        for (uint32_t it = 0; it < tp.spin_limit; ++it) {
+            unsigned long long seen;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(arr) : "memory");
+            if (seen >= tp_expected) { ok = true; break; }
+            __nanosleep(32);
+        }
+        if (!ok) atomicExch(err, 40 + (int)lane);
+    }
+    if (!__all_sync(0xFFFFFFFFu, ok)) return;
+    const float* slots = reinterpret_cast<const float*>(tp.buf[tp.rank] + kCommHeader) + tp_parity;
+    for (uint32_t c0 = e0; c0 < e1; c0 += 256u) {
+        float part[8][kCommMaxWorld];
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t e = c0 + j * 32 + lane;
+#pragma unroll
+            for (uint32_t pr = 0; pr < kCommMaxWorld; ++pr) {
+                part[j][pr] = 0.f;
+                if (pr < tp.world && e < e1)
+                    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(part[j][pr]) : "l"(slots + (size_t)pr * tp.max_elems + e) : "memory");
+            }
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t e = c0 + j * 32 + lane;
+            float acc = 0.f;
+#pragma unroll
+            for (uint32_t pr = 0; pr < kCommMaxWorld; ++pr)
+                if (pr < tp.world) acc += part[j][pr];
+            if (e < e1) {
+                if (y_bf16) reinterpret_cast<uint16_t*>(y)[e] = (uint16_t)f32_to_bf16_bits(acc);
+                else reinterpret_cast<float*>(y)[e] = acc;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel 2: the streaming kernel
 // ---------------------------------------------------------------------------------------------
-template <uint32_t SCHEME, int MM, bool MMA = false>
+template <uint32_t SCHEME, int MM, bool MMA = false, bool TP = false>
 __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gemv_int_kernel(const __grid_constant__ IntParams P) {
     constexpr uint32_t CW = int_warps(MMA), WPU = CW / kIntCU, RL = int_red_lanes(MMA);
     using T = StagedTraits<SCHEME>;
@@ -1335,6 +1393,15 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
         // sequence is a chain of three global round trips; here it delays nobody, because the
         // consumer warps only hand over a reduction buffer and go on.
         griddep_wait();
+        // tensor-parallel push: which set of slots this step uses, and where this rank's slot starts in a buffer
+        size_t tp_slot = 0, tp_parity = 0;
+        unsigned long long tp_expected = 0ull;
+        if constexpr (TP) {
+            const unsigned long long* hdr = reinterpret_cast<const unsigned long long*>(P.tp.buf[P.tp.rank]);
+            tp_parity = (size_t)(hdr[kCommWordEpoch] & 1ull) * kCommMaxWorld * P.tp.max_elems;
+            tp_slot = tp_parity + (size_t)P.tp.rank * P.tp.max_elems;
+            tp_expected = hdr[kCommWordExpected];
+        }
         // a lane finishes tile row rrow of activation rows col = 2 cp + (lane >> 4), cp = 0 .. NC-1
         constexpr int NC = (MM + 1) / 2;
         const uint32_t chalf = lane >> 4, rrow = lane & 15u;
@@ -1430,11 +1497,41 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
                     const uint32_t col = 2 * cp + chalf;
                     if (col < P.m_real && orow < P.n) {
                         const size_t o = (size_t)col * P.n + orow;
-                        if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v[cp]);
+                        if constexpr (TP) {
+#pragma unroll
+                            for (uint32_t pr = 0; pr < kCommMaxWorld; ++pr)
+                                if (pr < P.tp.world)
+                                    asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(P.tp.buf[pr] + kCommHeader) + tp_slot + o),
+                                                 "f"(v[cp]) : "memory");
+                        } else if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v[cp]);
                         else reinterpret_cast<float*>(P.y)[o] = v[cp];
                     }
                 }
             }
+        }
+        if constexpr (TP) {
+            // Everything this CTA pushes is out (a tile it shares is pushed by whoever completes it, before that
+            // CTA counts itself in).  CTAs count in on this rank's own word; the one that completes the count tells
+            // every rank, behind all of this rank's pushes, with one addition each.  (Every CTA adding at every rank
+            // would put grid x world same-address reductions on the links, which serialise at the far L2.)
+            __threadfence_system();
+            __syncwarp();
+            unsigned long long prev = 0ull;
+            if (lane == 0)
+                prev = atomicAdd(reinterpret_cast<unsigned long long*>(P.tp.buf[P.tp.rank]) + kCommWordLocal, 1ull);
+            prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+            if (prev + 1ull == tp_expected) {
+                __threadfence_system();
+                if (lane < P.tp.world)
+                    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long*>(P.tp.buf[lane]) + kCommWordArrive + P.tp.rank),
+                                 "l"((unsigned long long)G) : "memory");
+            }
+            // A few CTAs stay for the sum, 256 outputs each; the others leave now, so that the next kernel's CTAs can
+            // become resident and fetch their first weights while the exchange completes.
+            const uint32_t total = P.m_real * P.n, per = max(256u, ((total + G - 1) / G + 31u) & ~31u);
+            const uint32_t e0 = me * per, e1 = min(total, e0 + per);
+            if (e0 >= total) return;
+            tp_wait_and_sum(P.tp, tp_expected, tp_parity, e0, e1, P.y, P.y_bf16, P.err, lane);
         }
         return;
     }
@@ -1957,6 +2054,10 @@ constexpr bool int_has_mma(uint32_t scheme) {
            scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K;
 }
 // Formats that have a dp4a unit (QUnit); the others run batch 1 on their integer-MMA unit as well.
+// formats whose down projection also exists as a pushing kernel (tensor-parallel exchange inside the finisher)
+constexpr bool int_has_push(uint32_t scheme) {
+    return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K;
+}
 constexpr bool int_has_dp4a(uint32_t scheme) {
     return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K;
 }
@@ -2030,10 +2131,11 @@ static unsigned long long next_call_token() {
     return (epoch.fetch_add(1) << 2) | 1ull;
 }
 
-template <uint32_t SCHEME, int MM, bool MMA = false>
+template <uint32_t SCHEME, int MM, bool MMA = false, bool TP = false>
 static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                         uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const IntPlan& pl, int* err_word, bool pair,
-                        const float* expert_sel = nullptr, uint32_t num_experts = 0, uint32_t m_real = (uint32_t)MM) {
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0, uint32_t m_real = (uint32_t)MM,
+                        const TpPush* tp = nullptr) {
     using T = StagedTraits<SCHEME>;
     Geometry g;
     geometry(SCHEME, &g);
@@ -2064,8 +2166,14 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     // eight blocks of one row, four of two or two of four per round)
     const bool fits_inline = MMA ? ((uint64_t)k * (MM / 4) << inline_rows_log2(m_real)) <= inline_groups(MM, true) * int_warps(true) * 256u
                                  : (uint64_t)k * m_real <= inline_groups(MM) * kIntWarps * 32u * 8u;
-    P.inline_q = (!pair && pl.two_way && fits_inline && !pl.xstream && (iq == 2 || iq == 0)) ? 1u : 0u;
+    P.inline_q = (!pair && !tp && pl.two_way && fits_inline && !pl.xstream && (iq == 2 || iq == 0)) ? 1u : 0u;
     if (P.inline_q) P.use_red = 0u;
+    if (TP != (tp != nullptr)) return fail(RLXQ_E_SHAPE, "pushing and plain launches are different kernels");
+    if (tp) {                        // tiles go to the exchange buffers with plain stores, the quantiser kernel advances the step
+        if ((uint64_t)m_real * n > tp->max_elems) return fail(RLXQ_E_SHAPE, "the exchange buffers hold %u values, the output has %llu", tp->max_elems, (unsigned long long)m_real * n);
+        P.tp = *tp;
+        P.use_red = 0u;
+    }
     P.expert_sel = expert_sel;
     P.num_experts = num_experts;
     if (expert_sel && !P.inline_q) return fail(RLXQ_E_SHAPE, "expert-indirect GEMV needs the single-kernel mode");
@@ -2079,7 +2187,7 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     int dev = 0;
     RLXQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && attr_set[dev].load() == 0) {
-        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemv_int_kernel<SCHEME, MM, MMA, TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         attr_set[dev].store(1);
     }
     const uint32_t groups = (k / 8) * m_real;
@@ -2088,10 +2196,10 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
     if (!P.inline_q) rc = launch_pdl(quantise_x_kernel<T::SUB, MMA ? MM / 4 : 0, MMA && frag_sum_is_float(SCHEME)>, dim3(qgrid), dim3(256), 0, stream, x, (uint32_t)xbf,
                         m_real, k, (int)SumBias<SCHEME>::value, reinterpret_cast<uint8_t*>(ws), pl.xq_row_bytes,
                         P.counters, pl.ntiles, reinterpret_cast<float*>(y), P.use_red ? m_real * n : 0u,
-                        (pair ? 1u : 0u));
+                        (pair ? 1u : 0u), tp ? reinterpret_cast<unsigned long long*>(tp->buf[tp->rank]) : nullptr, tp ? pl.grid : 0u);
     if (rc) return rc;
     if (!P.inline_q) count_launch();
-    rc = launch_pdl(gemv_int_kernel<SCHEME, MM, MMA>, dim3(pl.grid), dim3(int_threads(MMA)), pl.smem_bytes, stream, P);
+    rc = launch_pdl(gemv_int_kernel<SCHEME, MM, MMA, TP>, dim3(pl.grid), dim3(int_threads(MMA)), pl.smem_bytes, stream, P);
     if (rc) return rc;
     count_launch();
     return check_launch("gemv_int_kernel");
@@ -2100,11 +2208,19 @@ static int launch_int_t(cudaStream_t stream, const void* x, bool xbf, const uint
 template <uint32_t SCHEME>
 static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint8_t* w, void* y, bool ybf,
                         uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, int* err_word, bool pair,
-                        const float* expert_sel = nullptr, uint32_t num_experts = 0, bool mma = false) {
+                        const float* expert_sel = nullptr, uint32_t num_experts = 0, bool mma = false, const TpPush* tp = nullptr) {
     if (mma) {
         if constexpr (int_has_mma(SCHEME)) {
             const IntPlan plm = plan_int<SCHEME, true>(m, k, n);
             if (!plm.ok) return fail(RLXQ_E_SHAPE, "integer-MMA GEMV does not support m=%u k=%u n=%u", m, k, n);
+            if (tp) {
+                if constexpr (int_has_push(SCHEME)) {
+                    if (m <= 4) return launch_int_t<SCHEME, 4, true, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m, tp);
+                    return launch_int_t<SCHEME, 8, true, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m, tp);
+                } else {
+                    return fail(RLXQ_E_SHAPE, "no pushing GEMV for scheme %u", (unsigned)SCHEME);
+                }
+            }
             if (m <= 4) return launch_int_t<SCHEME, 4, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m);
             return launch_int_t<SCHEME, 8, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, plm, err_word, pair, nullptr, 0, m);
         } else {
@@ -2114,8 +2230,15 @@ static int launch_int_s(cudaStream_t stream, const void* x, bool xbf, const uint
     if constexpr (int_has_dp4a(SCHEME)) {
         const IntPlan pl = plan_int<SCHEME>(m, k, n);
         if (!pl.ok) return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u", m, k, n);
-        if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts);
-        if (m == 2) return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair);
+        if (tp) {
+            if constexpr (int_has_push(SCHEME)) {
+                if (m == 1) return launch_int_t<SCHEME, 1, false, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, 1, tp);
+                if (m == 2) return launch_int_t<SCHEME, 2, false, true>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, 2, tp);
+            }
+            return fail(RLXQ_E_SHAPE, "no pushing dp4a GEMV for scheme %u at m=%u", (unsigned)SCHEME, m);
+        }
+        if (m == 1) return launch_int_t<SCHEME, 1>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, expert_sel, num_experts, 1);
+        if (m == 2) return launch_int_t<SCHEME, 2>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, 2);
         return launch_int_t<SCHEME, 4>(stream, x, xbf, w, y, ybf, k, n, ws, ws_bytes, pl, err_word, pair, nullptr, 0, m);
     } else {
         return fail(RLXQ_E_SHAPE, "no dp4a unit for scheme %u", (unsigned)SCHEME);
@@ -2245,23 +2368,23 @@ int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, 
 
 // y = (up * silu(gate)) . W^T with gu = [gate | up] ([m][2k] f32): the SwiGLU product is formed by the
 // activation quantiser, so the row-parallel down projection of an FFN needs no kernel in between.
+bool int_push_supported(uint32_t scheme) { return int_has_push(scheme); }
+
 int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
-                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes) {
-    if (m >= 2 && int_mma_supported(scheme, m, k, n, w, gu)) {   // batch 2-8: the integer-MMA units
-        int* err = device_error_word();
-        switch (scheme) {
-            case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true);
-            default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
-        }
+                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const TpPush* tp) {
+    int* err = device_error_word();
+    const bool mma = m >= 2 && int_mma_supported(scheme, m, k, n, w, gu);     // batch 2-8: the integer-MMA units
+    switch (scheme) {
+        case RLXQ_Q4_0: return launch_int_s<RLXQ_Q4_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, mma, tp);
+        case RLXQ_Q8_0: return launch_int_s<RLXQ_Q8_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, mma, tp);
+        case RLXQ_Q4_K: return launch_int_s<RLXQ_Q4_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, mma, tp);
+        case RLXQ_Q5_K: return launch_int_s<RLXQ_Q5_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, mma, tp);
+        case RLXQ_Q6_K: return launch_int_s<RLXQ_Q6_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, mma, tp);
+        case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        default: return fail(RLXQ_E_SCHEME, "no integer GEMV for scheme %u", scheme);
     }
-    return launch_gemv_int_err(stream, scheme, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, device_error_word(), true);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -223,24 +223,23 @@ extern "C" int rlxq_tp_ffn_run(rlxq_tp* t, const void* x_host, uint32_t x_dtype,
         if (rc) return rc;
     }
     const size_t xb = (size_t)elems * (x_dtype == RLXQ_BF16 ? 2 : 4);
-    for (TpRank& r : t->ranks) {
+    void* bufs[8] = {nullptr};
+    for (uint32_t i = 0; i < world; ++i) bufs[i] = t->ranks[i].comm_buf;
+    for (uint32_t i = 0; i < world; ++i) {
+        TpRank& r = t->ranks[i];
         RLXQ_CUDA_TRY(cudaSetDevice(r.dev));
         RLXQ_CUDA_TRY(cudaMemcpyAsync(r.x, x_host, xb, cudaMemcpyHostToDevice, r.stream));
         uint8_t* ws = reinterpret_cast<uint8_t*>(((uintptr_t)r.ws + 255) & ~(uintptr_t)255);
-        rc = rlxq_tp_ffn_partial((rlxq_stream_t)r.stream, t->scheme, t->scheme, r.x, x_dtype, r.gate_up, r.down, r.y, m,
-                                 t->d_model, f, ws, r.ws_bytes - (size_t)(ws - r.ws));
+        // decode sizes over peer memory: the step with the exchange inside (rlxq_tp_ffn_step); else the partial alone
+        if (peer)
+            rc = rlxq_tp_ffn_step((rlxq_stream_t)r.stream, t->scheme, t->scheme, r.x, x_dtype, r.gate_up, r.down, r.y, m,
+                                  t->d_model, f, ws, r.ws_bytes - (size_t)(ws - r.ws), i, world, bufs, kTpPeerElems);
+        else
+            rc = rlxq_tp_ffn_partial((rlxq_stream_t)r.stream, t->scheme, t->scheme, r.x, x_dtype, r.gate_up, r.down, r.y, m,
+                                     t->d_model, f, ws, r.ws_bytes - (size_t)(ws - r.ws));
         if (rc) return rc;
     }
-    if (peer) {
-        void* bufs[8];
-        for (uint32_t i = 0; i < world; ++i) bufs[i] = t->ranks[i].comm_buf;
-        for (uint32_t i = 0; i < world; ++i) {
-            TpRank& r = t->ranks[i];
-            RLXQ_CUDA_TRY(cudaSetDevice(r.dev));
-            rc = rlxq_tp_allreduce_sum((rlxq_stream_t)r.stream, i, world, bufs, kTpPeerElems, r.y, r.y, elems);
-            if (rc) return rc;
-        }
-    } else if (world > 1) {
+    if (!peer && world > 1) {
         RLXQ_NCCL_TRY(t, t->nccl.GroupStart());
         for (TpRank& r : t->ranks) {
             const ncclResult_t nr = t->nccl.AllReduce(r.y, r.y, elems, ncclFloat, ncclSum, r.nccl, r.stream);

@@ -33,6 +33,8 @@ size_t chain_workspace_bytes(uint32_t scheme, const ChainLayer* layers, uint32_t
 int launch_gemv_chain(cudaStream_t stream, uint32_t scheme, const ChainLayer* layers, uint32_t nlayers, const void* x, bool xbf,
                       void* y, bool ybf, uint32_t m, void* ws, size_t ws_bytes);
 bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x);
+// whether the format's down projection also exists as a kernel that pushes its tiles into peers' exchange buffers
+bool int_push_supported(uint32_t scheme);
 size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n);
 int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, bool xbf, const uint8_t* w, void* y,
                         bool ybf, uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
@@ -56,8 +58,9 @@ int launch_gemv_int_expert(cudaStream_t stream, uint32_t scheme, const void* x, 
                            bool ybf, uint32_t k, uint32_t n, uint32_t num_experts, const float* expert_sel, void* ws,
                            size_t ws_bytes);
 
+struct TpPush;   // tp_comm.cuh: the exchange buffers of a tensor-parallel group (null: plain output)
 int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu, const uint8_t* w, void* y, bool ybf,
-                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes);
+                           uint32_t m, uint32_t k, uint32_t n, void* ws, size_t ws_bytes, const TpPush* tp = nullptr);
 
 int staged_device_error(int* value);   // synchronises the device
 int* static_error_word_if_resolved();  // error word inside the library image, once an allocation-free call resolved it

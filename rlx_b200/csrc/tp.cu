@@ -14,6 +14,7 @@
 #include "decode.cuh"
 #include "host/session.hpp"
 #include "kernels.h"
+#include "tp_comm.cuh"
 #include "../../include/rlxq_tp.h"
 
 namespace rlxq {
@@ -103,9 +104,13 @@ int rlxq_tp_ffn_workspace_bytes(uint32_t scheme_gate_up, uint32_t scheme_down, u
     return RLXQ_OK;
 }
 
-int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down, const void* x,
-                        uint32_t x_dtype, const void* gate_up_blocks, const void* down_blocks, float* y_partial,
-                        uint32_t m, uint32_t d_model, uint32_t ffn_local, void* workspace, size_t workspace_bytes) {
+// The per-rank forward pass.  tp (may be null): the group's exchange buffers; when the down projection runs on the
+// integer GEMV it then pushes its tiles into them and finishes the sum itself, and *summed tells the caller so.
+static int ffn_partial_impl(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down, const void* x,
+                            uint32_t x_dtype, const void* gate_up_blocks, const void* down_blocks, float* y_partial,
+                            uint32_t m, uint32_t d_model, uint32_t ffn_local, void* workspace, size_t workspace_bytes,
+                            const TpPush* tp, bool* summed) {
+    if (summed) *summed = false;
     size_t need = 0;
     int rc = rlxq_tp_ffn_workspace_bytes(scheme_gate_up, scheme_down, m, d_model, ffn_local, x_dtype, &need);
     if (rc) return rc;
@@ -130,8 +135,11 @@ int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t 
         ((m <= 2 && int_supported(scheme_down, m, ffn_local, d_model, down_blocks, gu)) ||
          (m >= 2 && m <= 8 && int_mma_supported(scheme_down, m, ffn_local, d_model, down_blocks, gu)))) {
         // decode: the down projection's activation quantiser forms up * silu(gate) itself
-        return launch_gemv_int_swiglu((cudaStream_t)stream, scheme_down, gu, (const uint8_t*)down_blocks, y_partial, false, m,
-                                      ffn_local, d_model, ws, mm);
+        const bool push = tp && (uint64_t)m * d_model <= tp->max_elems && int_push_supported(scheme_down);
+        rc = launch_gemv_int_swiglu((cudaStream_t)stream, scheme_down, gu, (const uint8_t*)down_blocks, y_partial, false, m,
+                                    ffn_local, d_model, ws, mm, push ? tp : nullptr);
+        if (rc == RLXQ_OK && push && summed) *summed = true;
+        return rc;
     }
     {
         const uint64_t total = (uint64_t)m * ffn_local;
@@ -146,6 +154,35 @@ int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t 
     }
     return rlxq_matmul(stream, scheme_down, h, h_bf16 ? RLXQ_BF16 : RLXQ_F32, down_blocks, y_partial, RLXQ_F32, m,
                        ffn_local, d_model, ws, mm);
+}
+
+int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down, const void* x,
+                        uint32_t x_dtype, const void* gate_up_blocks, const void* down_blocks, float* y_partial,
+                        uint32_t m, uint32_t d_model, uint32_t ffn_local, void* workspace, size_t workspace_bytes) {
+    return ffn_partial_impl(stream, scheme_gate_up, scheme_down, x, x_dtype, gate_up_blocks, down_blocks, y_partial, m,
+                            d_model, ffn_local, workspace, workspace_bytes, nullptr, nullptr);
+}
+
+int rlxq_tp_ffn_step(rlxq_stream_t stream, uint32_t scheme_gate_up, uint32_t scheme_down, const void* x, uint32_t x_dtype,
+                     const void* gate_up_blocks, const void* down_blocks, float* y, uint32_t m, uint32_t d_model,
+                     uint32_t ffn_local, void* workspace, size_t workspace_bytes, uint32_t rank, uint32_t world,
+                     void* const* bufs, uint32_t max_elems) {
+    if (world < 1 || world > kCommMaxWorld || rank >= world) return fail(RLXQ_E_ARG, "bad rank %u of %u", rank, world);
+    if (!bufs) return fail(RLXQ_E_NULL, "bufs is null");
+    const uint64_t elems = (uint64_t)m * d_model;
+    if (elems > max_elems || elems % 4) return fail(RLXQ_E_SHAPE, "m * d_model = %llu must be a multiple of 4 and at most %u", (unsigned long long)elems, max_elems);
+    TpPush tp{};
+    for (uint32_t r = 0; r < world; ++r) {
+        if (!bufs[r]) return fail(RLXQ_E_NULL, "buffer of rank %u is null", r);
+        tp.buf[r] = static_cast<uint8_t*>(bufs[r]);
+    }
+    tp.world = world; tp.rank = rank; tp.max_elems = max_elems;
+    tp.spin_limit = (uint32_t)options().tp_spin_limit.load();
+    bool summed = false;
+    int rc = ffn_partial_impl(stream, scheme_gate_up, scheme_down, x, x_dtype, gate_up_blocks, down_blocks, y, m, d_model,
+                              ffn_local, workspace, workspace_bytes, options().tp_fused.load() ? &tp : nullptr, &summed);
+    if (rc || summed || m == 0 || d_model == 0) return rc;
+    return rlxq_tp_allreduce_sum(stream, rank, world, bufs, max_elems, y, y, (uint32_t)elems);
 }
 
 }  // extern "C"

@@ -23,12 +23,10 @@
 #include "common.cuh"
 #include "rlxq_tp.h"
 #include "staged_common.cuh"
+#include "tp_comm.cuh"
 
 namespace rlxq {
 
-constexpr uint32_t kCommMaxWorld = 8;
-constexpr uint32_t kCommParts = 8;            // CTAs per all-reduce, each with its own epoch and flags
-constexpr uint32_t kCommHeader = 1024;        // epoch[kCommParts], then flags[kCommParts][kCommMaxWorld], 8 bytes each
 // Polls of a peer-written flag before a rank gives up: option "tp_spin_limit", default 2^24 (a few seconds).
 
 struct CommParams {

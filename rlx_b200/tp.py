@@ -235,10 +235,29 @@ class TensorParallelFFN:
         return out
 
     def forward(self, x, out=None):
+        torch = self.torch
+        m = x.shape[0]
+        pr = self.peer_reduce
+        if self.world > 1 and pr is not None and pr.available and m * self.d_model <= pr.max_elems and (m * self.d_model) % 4 == 0:
+            # rlxq_tp_ffn_step: the partial and the peer-memory all-reduce behind one call (option tp_fused = 1: the down
+            # projection pushes its tiles to the peers and finishes the sum itself)
+            assert x.is_cuda and x.dim() == 2 and x.shape[1] == self.d_model and x.is_contiguous()
+            dt = 0 if x.dtype == torch.float32 else 1
+            if out is None:
+                out = torch.empty((m, self.d_model), dtype=torch.float32, device=x.device)
+            ws = self._workspace(m, dt)
+            base = (ws.data_ptr() + 255) // 256 * 256
+            with torch.cuda.device(x.device):
+                check(lib.rlxq_tp_ffn_step(torch.cuda.current_stream().cuda_stream, self.scheme, self.scheme,
+                                           x.data_ptr(), dt, self.gate_up.data_ptr(), self.down.data_ptr(),
+                                           out.data_ptr(), m, self.d_model, self.plan.ffn_local, base,
+                                           ws.numel() - (base - ws.data_ptr()), self.rank, self.world, pr._bufs,
+                                           pr.max_elems))
+            return out
         y = self.partial(x, out)
         if self.world > 1:
-            if self.peer_reduce is not None and self.peer_reduce.fits(y):
-                self.peer_reduce(y)
+            if pr is not None and pr.fits(y):
+                pr(y)
             else:
                 import torch.distributed as dist
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)

@@ -338,3 +338,51 @@ def test_tp_lifecycle_two_devices():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _group_case(2, 1024, 4096, (1, 64, 128))
+
+
+# ------------------------------------------------------------------ the step with the exchange inside the down projection
+@pytest.mark.gpu
+@pytest.mark.parametrize("dm,df,m", [(1024, 4096, 1), (1024, 4096, 2), (2048, 8192, 4), (4096, 14336, 8)])
+def test_ffn_step_pushes_and_sums_inside_the_down_projection(dm, df, m):
+    """rlxq_tp_ffn_step with world = 1 (the one rank is its own peer: it pushes its tiles into its own exchange buffer,
+    counts its CTAs in and sums one slot): the same bits as rlxq_tp_ffn_partial, one launch fewer than partial +
+    all-reduce, step after step on the same buffers (the two sets of slots alternate), fused and not."""
+    import ctypes as C
+    import torch
+    from rlx_b200._lib import lib
+    s = O.Q4_K
+    gate, up, down = _weights(dm, df, seed=70 + m)
+    f = tp.TensorParallelFFN(s, dm, df, rank=0, world=1, device=torch.device("cuda", 0))
+    f.load(gate, up, down)
+    x = O.bf16_bits_to_f32(O.f32_to_bf16_bits(O.fill_normal(71 + m, m * dm))).reshape(m, dm)
+    xd = torch.from_numpy(x).cuda()
+    want = f.partial(xd).cpu().numpy()
+    buf = C.c_void_p()
+    assert lib.rlxq_tp_comm_alloc(65536, C.byref(buf)) == 0
+    bufs = (C.c_void_p * 1)(buf.value)
+    ws = f._workspace(m, 0)
+    base = (ws.data_ptr() + 255) // 256 * 256
+    stream = torch.cuda.current_stream().cuda_stream
+    counts = {}
+    try:
+        for fused in (1, 0, 1):
+            R.set_option("tp_fused", fused)
+            for _ in range(3):
+                y = torch.full((m, dm), 9.0, device="cuda")
+                before = R.launch_count()
+                rc = lib.rlxq_tp_ffn_step(stream, s, s, xd.data_ptr(), 0, f.gate_up.data_ptr(), f.down.data_ptr(),
+                                          y.data_ptr(), m, dm, f.plan.ffn_local, base, ws.numel() - (base - ws.data_ptr()),
+                                          0, 1, bufs, 65536)
+                assert rc == 0
+                launches = R.launch_count() - before
+                R.device_status()
+                assert np.array_equal(y.cpu().numpy(), want), (fused, m)
+            counts[fused] = launches
+        assert counts[1] == counts[0] - 1          # the pushing down projection replaces GEMV + all-reduce
+    finally:
+        R.set_option("tp_fused", 0)
+        lib.rlxq_tp_comm_free(buf.value)
+    y_ref, h = O.ffn_swiglu(x, gate, up, down, m, dm, df, s, s, want_h=True)
+    wn = O.row_norms(s, down, df, dm)
+    bnd = np.sqrt((h.astype(np.float64) ** 2).sum(1))[:, None] * wn[None, :]
+    assert np.max(np.abs(want - y_ref) / bnd) < 1e-3
