@@ -215,6 +215,11 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *   "gemm_streamk": 0 = automatic (split the k dimension across SMs when that saves at least 36
  *                  256-wide k steps on the busiest SM and a workspace is given), 1 = never,
  *                  2 = whenever a workspace is given
+ *   "gemm_pair": the tcgen05 GEMM with two CTAs per MMA (a cluster of two SMs on 256 weight rows x 256 activation
+ *                  rows, each CTA loading half of the activation tile): 0 = automatic (n a multiple of 256, at
+ *                  least one tile pair per resident cluster, not Q6_K, no k split chosen), 1 = never, 2 = wherever
+ *                  n is a multiple of 256.  Same bits as the single-CTA kernel.  "gemm_pair_clusters" (read only):
+ *                  clusters the device keeps resident, 0 until the paired kernel has run
  *   "gemm_tile_x": 0 = automatic, 128 or 256 = activation rows per tile of the tcgen05 GEMM
  *   "gemv_inline_q": 0 = automatic, 1 = the integer GEMV always runs its activation quantiser as a
  *                  kernel of its own, 2 = the streaming kernel quantises the activations itself

@@ -149,6 +149,11 @@ int rlxq_set_option(const char* key, int64_t value) {
     if (!strcmp(key, "gemv_tc_ctas")) { options().gemv_tc_ctas = value < 1 ? 1 : (value > 2 ? 2 : value); return RLXQ_OK; }
     if (!strcmp(key, "gemv_chain")) { options().gemv_chain = value ? 1 : 0; return RLXQ_OK; }
     if (!strcmp(key, "tp_fused")) { options().tp_fused = value ? 1 : 0; return RLXQ_OK; }
+    if (!strcmp(key, "gemm_pair")) {
+        if (value < 0 || value > 2) return fail(RLXQ_E_ARG, "gemm_pair is 0, 1 or 2");
+        options().gemm_pair = value;
+        return RLXQ_OK;
+    }
     if (!strcmp(key, "tp_spin_limit")) {
         if (value < 1 || value > (1ll << 30)) return fail(RLXQ_E_ARG, "tp_spin_limit must be in [1, 2^30]");
         options().tp_spin_limit = value;
@@ -183,6 +188,8 @@ int rlxq_get_option(const char* key, int64_t* value) {
     if (!strcmp(key, "gemv_tc_ctas")) { *value = options().gemv_tc_ctas; return RLXQ_OK; }
     if (!strcmp(key, "gemv_chain")) { *value = options().gemv_chain; return RLXQ_OK; }
     if (!strcmp(key, "tp_fused")) { *value = options().tp_fused; return RLXQ_OK; }
+    if (!strcmp(key, "gemm_pair")) { *value = options().gemm_pair; return RLXQ_OK; }
+    if (!strcmp(key, "gemm_pair_clusters")) { *value = options().gemm_pair_clusters; return RLXQ_OK; }
     if (!strcmp(key, "tp_spin_limit")) { *value = options().tp_spin_limit; return RLXQ_OK; }
     if (!strcmp(key, "gemv_early")) { *value = options().gemv_early; return RLXQ_OK; }
     if (!strcmp(key, "gemv_inline_q")) { *value = options().gemv_inline_q; return RLXQ_OK; }

@@ -32,6 +32,8 @@ struct Options {
     std::atomic<int64_t> gemv_early{2};
     std::atomic<int64_t> tp_spin_limit{1 << 24};
     std::atomic<int64_t> gemv_tc_ctas{2};
+    std::atomic<int64_t> gemm_pair{0};        // tcgen05 GEMM, two CTAs per MMA (cta_group::2): 0 = where it pays, 1 = never, 2 = wherever the shape allows
+    std::atomic<int64_t> gemm_pair_clusters{0};   // read-only: clusters of two CTAs the device keeps resident (0 until the paired GEMM ran)
     std::atomic<int64_t> tp_fused{0};         // rlxq_tp_ffn_step: the down projection pushes its tiles and finishes the sum
     std::atomic<int64_t> gemv_chain{0};       // 1: rlxq_matmul_chain runs a chain as one cooperative kernel where it can
     std::atomic<int64_t> graph_fuse_ffn{1};

@@ -550,6 +550,16 @@ __device__ __noinline__ void gemm_reduce_parts(const GemmParams& P, uint32_t til
     }
 }
 
+// A whole warp waiting on one barrier: one lane polls (every try_wait is a serialised operation on the barrier's
+// word, and eight to twelve decode warps share the stage barriers), the warp barrier hands the result and the
+// memory ordering to the others.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t lane) {
+    uint32_t got = 1u;
+    if (lane == 0) got = mbar_wait(bar, parity) ? 1u : 0u;
+    got = __shfl_sync(0xFFFFFFFFu, got, 0);
+    return got != 0u;
+}
+
 struct GemmBars {
     uint64_t b_full[kGemmMaxStages], a_full[kGemmMaxStages], stage_free[kGemmMaxStages];
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
@@ -815,6 +825,246 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// ---- the same GEMM, two CTAs per MMA (cta_group::2) --------------------------------------------
+// A pair of CTAs (a cluster of two, on neighbouring SMs) works on 256 weight rows x 256 activation rows: each CTA
+// decodes its own 128 weight rows into its own tensor memory and owns their accumulators, exactly as above, but
+// loads only HALF of the activation tile (128 rows) into its shared memory; one tcgen05.mma.cta_group::2, issued by
+// the first CTA of the pair, reads both halves.  A CTA therefore takes 16 KB of activations per k block from L2
+// instead of 32 KB, so a stage of the same size holds a k block of 128 instead of 64: eight MMAs per round of
+// barrier hand-overs instead of four.  That is what the pair buys here: the hand-overs of one round (stage freed ->
+// refill and decode -> full -> issue -> commit) cost about 0.42 us whatever the ring depth and whatever else runs
+// (measured with everything but the barriers switched off), against 0.35 us of tensor time for four MMAs.
+//   barriers: the first CTA's b_full[s] collects its own TMA and the other CTA's (forwarded by a warp that waits
+//   on that CTA's own barrier), its a_full[s] the decode warps of both CTAs, its d_free the epilogue warps of
+//   both; one tcgen05.commit with a CTA mask signals stage_free[s] / d_full in both CTAs.
+// Whole tiles only, n a multiple of 256, no expert groups; everything else runs the single-CTA kernel.
+constexpr uint32_t kPairStages = 4;
+constexpr uint32_t kPairHalf = 128;                       // activation rows a CTA loads
+constexpr uint32_t kPairSubBytes = kPairHalf * kGemmBK * 2;   // one 64-wide swizzled box: 16 KB
+constexpr uint32_t kPairBBytes = 2 * kPairSubBytes;       // a stage: k block of 128 as two boxes
+constexpr uint32_t kPairIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
+
+struct PairBars {
+    uint64_t b_full[kPairStages], b_own[kPairStages], a_full[kPairStages], stage_free[kPairStages];
+    uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];
+    uint64_t d_full, d_free;
+    uint32_t tmem_base, abort_flag;
+};
+
+template <uint32_t SCHEME>
+__global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __grid_constant__ GemmParams P) {
+    constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
+    constexpr uint32_t kGemmDecodeGroups = GemmRaw<SCHEME>::GROUPS;
+    constexpr uint32_t RAW_BYTES = kGemmTileW * RAW_ROW;
+    constexpr uint32_t RAW_STRIDE = (RAW_BYTES + 127) / 128 * 128;
+    constexpr uint32_t TX = 256;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* b_stage = smem;                                          // kPairStages x 32 KB, 1024-aligned
+    uint8_t* raw_stage = smem + kPairStages * kPairBBytes;
+    PairBars* bars = reinterpret_cast<PairBars*>(raw_stage + kGemmRawStages * RAW_STRIDE);
+    uint8_t* epi_stage = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(bars + 1) + 15) & ~(uintptr_t)15);
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t rank = cluster_cta_rank();            // 0 issues the MMAs
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kPairStages; ++s) {
+            mbar_init(smem_u32(&bars->b_full[s]), 2);        // own TMA (with its bytes) + the other CTA's, forwarded
+            mbar_init(smem_u32(&bars->b_own[s]), 1);
+            mbar_init(smem_u32(&bars->a_full[s]), 16);       // two 64-wide halves x four decode warps, of each CTA
+            mbar_init(smem_u32(&bars->stage_free[s]), 1);
+        }
+        for (uint32_t r = 0; r < kGemmRawStages; ++r) {
+            mbar_init(smem_u32(&bars->raw_full[r]), 1);
+            mbar_init(smem_u32(&bars->raw_empty[r]), 4 * kGemmDecodeGroups);
+        }
+        mbar_init(smem_u32(&bars->d_full), 1);
+        mbar_init(smem_u32(&bars->d_free), 8);               // four epilogue warps of each CTA
+        bars->abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {               // the same warp of both CTAs: all 512 columns in each
+        tmem_alloc_pair(smem_u32(&bars->tmem_base), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // the other CTA's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    const uint32_t tmem_d = tmem_base, tmem_a = tmem_base + 256;
+    auto give_up = [&](int code) {
+        if (lane == 0) { atomicExch(P.err, code); *abort_flag = 1u; }
+    };
+    // the pair's tiles: 256 weight rows (pair index wp) x 256 activation rows (xt), xt fastest
+    const uint32_t pt0 = blockIdx.x >> 1, pstep = gridDim.x >> 1, plim = (P.wtiles >> 1) * P.xtiles;
+    const uint32_t rounds = 2 * P.kgroups;               // 128-wide k blocks of a tile
+
+    if (warp == 0) {
+        // ---------------- this CTA's half of the activation tile ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&P.xmap);
+            uint32_t s = 0, ph = 1;
+            bool ok = true;
+            for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
+                const uint32_t xrow = (pt % P.xtiles) * TX + rank * kPairHalf;
+                for (uint32_t kb = 0; kb < rounds; ++kb) {
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), ph)) { give_up(21); ok = false; break; }
+                    const uint32_t full = smem_u32(rank == 0 ? &bars->b_full[s] : &bars->b_own[s]);
+                    mbar_arrive_expect_tx(full, kPairBBytes);
+                    tma_load_2d(smem_u32(b_stage + s * kPairBBytes), &P.xmap, (int32_t)(kb * 2 * kGemmBK), (int32_t)xrow, full);
+                    tma_load_2d(smem_u32(b_stage + s * kPairBBytes + kPairSubBytes), &P.xmap, (int32_t)(kb * 2 * kGemmBK + kGemmBK), (int32_t)xrow, full);
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // ---------------- second CTA: tell the first that this half has landed ----------------
+        if (lane == 0 && rank == 1) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
+                for (uint32_t kb = 0; kb < rounds; ++kb) {
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars->b_own[s]), ph)) { give_up(22); ok = false; break; }
+                    mbar_arrive_cluster(cluster_map(smem_u32(&bars->b_full[s]), 0));
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- raw weight groups of this CTA's 128 rows ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&P.wmap);
+            uint32_t r = 0, ph = 1;
+            bool ok = true;
+            for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
+                const uint32_t wrow0 = (2 * (pt / P.xtiles) + rank) * kGemmTileW;
+                for (uint32_t g = 0; g < P.kgroups; ++g) {
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars->raw_empty[r]), ph)) { give_up(23); ok = false; break; }
+                    const uint32_t full = smem_u32(&bars->raw_full[r]);
+                    mbar_arrive_expect_tx(full, RAW_BYTES);
+                    tma_load_2d(smem_u32(raw_stage + r * RAW_STRIDE), &P.wmap, (int32_t)gemm_raw_x<SCHEME>(g), (int32_t)wrow0, full);
+                    if (++r == kGemmRawStages) { r = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the first CTA, for both ----------------
+        if (lane == 0 && rank == 0) {
+            uint32_t s = 0, ph = 0, dph = 1;
+            bool ok = true;
+            for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
+                if (!mbar_wait(smem_u32(&bars->d_free), dph)) { give_up(24); break; }
+                dph ^= 1u;
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < rounds; ++kb) {
+                    if (*abort_flag || !mbar_wait(smem_u32(&bars->b_full[s]), ph) ||
+                        !mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(25); ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t bdesc0 = kmajor_sw128_desc(smem_u32(b_stage + s * kPairBBytes));
+                    const uint64_t bdesc1 = kmajor_sw128_desc(smem_u32(b_stage + s * kPairBBytes + kPairSubBytes));
+#pragma unroll
+                    for (uint32_t j = 0; j < 2 * kGemmBK / 16; ++j)
+                        tc_mma_ts_pair(tmem_d, tmem_a + 64 * s + 8 * j, (j < 4 ? bdesc0 : bdesc1) + 2 * (j & 3u), kPairIdesc, (kb | j) ? 1u : 0u);
+                    tc_commit_pair_both(smem_u32(&bars->stage_free[s]), 3);     // frees the stage in both CTAs
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit_pair_both(smem_u32(&bars->d_full), 3);
+            }
+        }
+    } else if (warp >= 4 && warp < 4 + 4 * kGemmDecodeGroups) {
+        // ---------------- decode: raw blocks -> bf16 rows in this CTA's tensor memory ----------------
+        const uint32_t quarter = warp & 3u, grp = (warp - 4) >> 2;
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        uint32_t r = 0, rph = 0, kbg0 = 0;
+        bool ok = true;
+        for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
+            for (uint32_t g = 0; g < P.kgroups && ok; ++g, kbg0 += 4) {
+                if (*abort_flag || !mbar_wait_warp(smem_u32(&bars->raw_full[r]), rph, lane)) { give_up(26); ok = false; break; }
+                const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
+#pragma unroll
+                for (uint32_t sub = 0; sub < 4; ++sub) {
+                    const uint32_t kbg = kbg0 + sub;
+                    if (kbg % kGemmDecodeGroups != grp) continue;
+                    // 64-wide block kbg is half (kbg & 1) of round kbg / 2
+                    const uint32_t s = (kbg >> 1) % kPairStages, fph = (((kbg >> 1) / kPairStages) & 1u) ^ 1u;
+                    uint32_t v[32];
+                    if (sub == 0) decode64<SCHEME, 0>(rp, g, v);
+                    else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
+                    else if (sub == 2) decode64<SCHEME, 2>(rp, g, v);
+                    else decode64<SCHEME, 3>(rp, g, v);
+                    if (*abort_flag || !mbar_wait_warp(smem_u32(&bars->stage_free[s]), fph, lane)) { give_up(27); ok = false; break; }
+                    tc_fence_after();
+                    tmem_st32(tmem_a + lane_addr + 64 * s + 32 * (kbg & 1u), v);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank == 0) mbar_arrive(smem_u32(&bars->a_full[s]));
+                        else mbar_arrive_cluster(cluster_map(smem_u32(&bars->a_full[s]), 0));
+                    }
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->raw_empty[r]));
+                if (++r == kGemmRawStages) { r = 0; rph ^= 1u; }
+            }
+        }
+    } else if (warp >= 4 + 4 * kGemmDecodeGroups) {
+        // ---------------- epilogue: this CTA's 128 weight rows x 256 activation rows -> y ----------------
+        const uint32_t quarter = warp & 3u;
+        const uint32_t lane_addr = (quarter * 32) << 16;
+        const uint32_t row = quarter * 32 + lane;
+        const uint32_t epi_tid = (warp - (4 + 4 * kGemmDecodeGroups)) * 32 + lane;
+        uint32_t dph = 0;
+        for (uint32_t pt = pt0; pt < plim && !*abort_flag; pt += pstep) {
+            const uint32_t wt = 2 * (pt / P.xtiles) + rank, xrow0 = (pt % P.xtiles) * TX;
+            if (!mbar_wait_warp(smem_u32(&bars->d_full), dph, lane)) { give_up(28); break; }
+            dph ^= 1u;
+            tc_fence_after();
+            const uint32_t n_idx = wt * kGemmTileW + row;
+#pragma unroll 1
+            for (uint32_t c = 0; c < TX / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + lane_addr + 32 * c, v);
+                tmem_ld_wait();
+                if (c == TX / 32 - 1) {          // everything is in registers: the accumulator may be overwritten
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank == 0) mbar_arrive(smem_u32(&bars->d_free));
+                        else mbar_arrive_cluster(cluster_map(smem_u32(&bars->d_free), 0));
+                    }
+                }
+                if (P.y_vec) {
+                    const GemmDst d{reinterpret_cast<uint8_t*>(P.y), P.n, xrow0, P.m, wt * kGemmTileW, P.n};
+                    if (P.y_bf16) gemm_store_vec<false>(epi_stage, epi_tid, row, v, d, c);
+                    else gemm_store_vec<true>(epi_stage, epi_tid, row, v, d, c);
+                } else if (n_idx < P.n) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        const uint32_t m_idx = xrow0 + 32 * c + j;
+                        if (m_idx < P.m) {
+                            const size_t o = (size_t)m_idx * P.n + n_idx;
+                            if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)bf16x2_of(f32x2(v[j], 0u));
+                            else reinterpret_cast<float*>(P.y)[o] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // both CTAs meet here, also after a timeout: neither returns its tensor memory while the other may still use it
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
@@ -904,6 +1154,73 @@ static int launch_gemm_t(cudaStream_t stream, const void* x, const uint8_t* w, v
     return check_launch("gemm_tcgen05_kernel");
 }
 
+// The two-CTA form: whole 256 x 256 tile pairs dealt round-robin to as many clusters as are resident at once.
+static bool gemm_pair_fits(uint32_t m, uint32_t k, uint32_t n) {
+    return n % 256 == 0 && m >= 1 && k % 256 == 0;
+}
+// Chosen by itself where it measured faster: at least one 256 x 256 tile pair per resident cluster, and a format
+// whose decoder keeps pace with two groups of decode warps (Q6_K's three groups lose 12 % in the paired form).
+template <uint32_t SCHEME>
+static bool gemm_wants_pair(uint32_t m, uint32_t k, uint32_t n) {
+    const int64_t opt = options().gemm_pair.load();
+    if (opt == 1 || !gemm_pair_fits(m, k, n)) return false;
+    if (opt == 2) return true;
+    if (SCHEME == RLXQ_Q6_K) return false;
+    return (uint64_t)(n / 256) * ((m + 255) / 256) >= (uint64_t)sm_count() / 2;
+}
+template <uint32_t SCHEME>
+static int launch_gemm_pair_t(cudaStream_t stream, const void* x, const uint8_t* w, void* y, bool ybf, uint32_t m,
+                              uint32_t k, uint32_t n) {
+    constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
+    constexpr uint32_t RAW_STRIDE = (kGemmTileW * RAW_ROW + 127) / 128 * 128;
+    Geometry g;
+    geometry(SCHEME, &g);
+    GemmParams P{};
+    int rc = encode_bf16_kmajor_map(&P.xmap, x, m, k, kPairHalf);
+    if (rc) return rc;
+    rc = encode_weight_map(&P.wmap, w, n, (uint64_t)k / g.elems * g.bytes, RAW_ROW / 8, kGemmTileW);
+    if (rc) return rc;
+    P.y = y; P.m = m; P.n = n; P.k = k; P.y_bf16 = ybf;
+    P.y_vec = (((uintptr_t)y & 15u) == 0 && n % (ybf ? 8u : 4u) == 0) ? 1u : 0u;
+    P.wtiles = n / kGemmTileW;
+    P.xtiles = (m + 255) / 256;
+    P.kgroups = k / 256;
+    P.err = device_error_word();
+    if (!P.err) return fail(RLXQ_E_CUDA, "device error word unavailable");
+    const size_t smem = 1024 + (size_t)kPairStages * kPairBBytes + (size_t)kGemmRawStages * RAW_STRIDE + sizeof(PairBars) + 64 +
+                        kGemmEpiStage;
+    const uint32_t threads = (4 + 4 * GemmRaw<SCHEME>::GROUPS + 4) * 32;
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static std::atomic<int> clusters_of[64];        // resident clusters per device, found once (0 = not yet)
+    int dev = 0;
+    RLXQ_CUDA_TRY(cudaGetDevice(&dev));
+    int clusters = (dev >= 0 && dev < 64) ? clusters_of[dev].load() : 0;
+    if (clusters == 0) {
+        RLXQ_CUDA_TRY(cudaFuncSetAttribute(gemm_pair_kernel<SCHEME>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cfg.gridDim = dim3((unsigned)sm_count() & ~1u);
+        RLXQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<SCHEME>, &cfg));
+        if (clusters < 1) return fail(RLXQ_E_CUDA, "no cluster of two CTAs of the paired GEMM fits this device");
+        if (dev >= 0 && dev < 64) clusters_of[dev].store(clusters);
+        options().gemm_pair_clusters = clusters;
+    }
+    const uint32_t ptiles = (P.wtiles / 2) * P.xtiles;
+    uint32_t pairs = (uint32_t)clusters;
+    if (pairs > (uint32_t)sm_count() / 2) pairs = (uint32_t)sm_count() / 2;
+    if (pairs > ptiles) pairs = ptiles;
+    cfg.gridDim = dim3(2 * pairs);
+    RLXQ_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<SCHEME>, P));
+    count_launch();
+    return check_launch("gemm_pair_kernel");
+}
+
 // 256-row activation tiles halve the activation traffic per FLOP.  When whole tiles would fill the SMs
 // badly the k dimension is split as well (stream-K, needs the workspace); without a workspace, 128-row
 // tiles are used when the wider ones would leave more than a quarter of the SMs without a tile.
@@ -913,11 +1230,14 @@ static int launch_gemm_s(cudaStream_t stream, const void* x, const uint8_t* w, v
     const uint32_t wt = (n + kGemmTileW - 1) / kGemmTileW, sms = (uint32_t)sm_count();
     const int64_t force = options().gemm_tile_x.load();
     const uint32_t ntiles256 = wt * ((m + 255) / 256);
+    if (options().gemm_pair.load() == 2 && gemm_pair_fits(m, k, n))               // forced: two CTAs per MMA
+        return launch_gemm_pair_t<SCHEME>(stream, x, w, y, ybf, m, k, n);
     if (force != 128 && gemm_wants_streamk(m, k, n) && ws && !((uintptr_t)ws & 15u) &&
         ws_bytes >= gemm_streamk_bytes(ntiles256, nullptr))
         return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n, ws, true);
     const bool narrow = force ? force == 128 : (ntiles256 * 4 < sms * 3);
     if (narrow) return launch_gemm_t<SCHEME, 128>(stream, x, w, y, ybf, m, k, n, nullptr, false);
+    if (force == 0 && gemm_wants_pair<SCHEME>(m, k, n)) return launch_gemm_pair_t<SCHEME>(stream, x, w, y, ybf, m, k, n);
     return launch_gemm_t<SCHEME, 256>(stream, x, w, y, ybf, m, k, n, nullptr, false);
 }
 

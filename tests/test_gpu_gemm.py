@@ -21,6 +21,7 @@ def _reset_options():
     R.set_option("gemm_kernel", 0)
     R.set_option("gemm_tile_x", 0)
     R.set_option("gemm_streamk", 0)
+    R.set_option("gemm_pair", 0)
 
 
 def _tol(k):
@@ -98,6 +99,67 @@ def test_stream_k_split_matches_oracle_and_is_deterministic(sch, m, k, n, y_bf16
         assert np.all(np.abs(a[rows] - c[rows]) <= 2 * _tol(k) * bnd + np.abs(ref) * 2.0 ** -7)
     else:
         assert_within_tolerance(a[rows], c[rows], bnd, tol=2 * _tol(k), what="stream-K vs whole tiles")
+
+
+PAIR_SHAPES = [("q8_0", 256, 256, 256, False), ("q4_0", 300, 512, 512, True), ("q4_k", 1000, 2048, 1024, False),
+               ("q5_k", 777, 1024, 2560, True), ("q6_k", 512, 2048, 768, False), ("q8_0", 9, 768, 256, False),
+               ("q4_k", 2048, 1024, 5120, True), ("q4_0", 129, 4096, 1280, False)]
+
+
+@pytest.mark.parametrize("sch,m,k,n,y_bf16", PAIR_SHAPES)
+def test_two_cta_gemm_matches_oracle_and_the_single_cta_kernel(sch, m, k, n, y_bf16):
+    """gemm_pair = 2: two CTAs (a cluster) share one tcgen05.mma.cta_group::2 per 256 weight rows x 256 activation
+    rows, each loading half of the activation tile.  Same products summed in the same order as the single-CTA
+    kernel: identical bits, f32 and bf16 outputs, ragged activation tiles, one tile pair up to more pairs than
+    clusters; and held to the oracle like every other GEMM path."""
+    s = O.SCHEMES[sch]
+    w, xb, x = _case(s, m, k, n, seed=300 + m)
+    R.set_option("gemm_streamk", 1)
+    R.set_option("gemm_tile_x", 256)
+    R.set_option("gemm_pair", 1)
+    single = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)
+    R.set_option("gemm_tile_x", 0)
+    R.set_option("gemm_pair", 2)
+    before = R.launch_count()
+    pair = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)
+    assert R.launch_count() - before == 1
+    assert R.get_option("gemm_pair_clusters") >= 1            # the paired kernel ran (it records the resident clusters)
+    assert np.array_equal(pair, single)
+    again = _run(s, w, xb, n, y_bf16=y_bf16, kernel=2)
+    assert np.array_equal(pair, again)
+    rows = np.arange(m) if m * n <= 600_000 else np.random.default_rng(2).choice(m, 24, replace=False)
+    xs = np.ascontiguousarray(x[rows])
+    ref = O.matmul_bt_mt(xs, w, len(rows), k, n, s)
+    bnd = bound(s, w, xs, n)
+    if y_bf16:
+        assert np.all(np.abs(pair[rows] - ref) <= _tol(k) * bnd + np.abs(ref) * 2.0 ** -8)
+    else:
+        assert_within_tolerance(pair[rows], ref, bnd, tol=_tol(k), what=f"paired gemm {sch} {m}x{k}x{n}")
+
+
+def test_two_cta_gemm_is_chosen_by_itself_and_refused_where_it_cannot_run():
+    """Automatic choice: at least one tile pair per cluster and not Q6_K; n not a multiple of 256 always runs the
+    single-CTA kernel, also when the pair is forced."""
+    import torch
+    s = O.Q4_K
+    m, k, n = 2560, 512, 2048                                  # 8 x 10 = 80 tile pairs >= 74 clusters
+    w, xb, x = _case(s, m, k, n, seed=77)
+    auto = _run(s, w, xb, n, kernel=0)
+    R.set_option("gemm_pair", 1)
+    never = _run(s, w, xb, n, kernel=0)
+    assert np.array_equal(auto, never)
+    rows = np.arange(0, m, 107)
+    xs = np.ascontiguousarray(x[rows])
+    assert_within_tolerance(auto[rows], O.matmul_bt_mt(xs, w, len(rows), k, n, s), bound(s, w, xs, n), tol=_tol(k), what="auto pair")
+    R.set_option("gemm_pair", 2)
+    w2, xb2, x2 = _case(s, 300, 512, 384, seed=78)             # 384 = 1.5 pairs of weight tiles: single-CTA kernel
+    y2 = _run(s, w2, xb2, 384, kernel=2)
+    R.set_option("gemm_pair", 1)
+    assert np.array_equal(y2, _run(s, w2, xb2, 384, kernel=2))
+    # (one of 115 200 outputs of this case sits at 5.03 standard deviations of the bf16 weight rounding)
+    assert_within_tolerance(y2, O.matmul_bt_mt(x2, w2, 300, 512, 384, s), bound(s, w2, x2, 384), tol=1.25 * _tol(512), what="n=384")
+    with pytest.raises(R.RlxqError):
+        R.set_option("gemm_pair", 3)
 
 
 def test_generic_kernel_for_large_m_matches_oracle():
