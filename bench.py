@@ -389,7 +389,8 @@ def run_gemm_workload(args, rank, world, local_rank):
                 "gpu_launches": launches,
                 "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                              "peak_source": src, "frac_of_burst": ach / float(peaks.get("bf16_tflops", 1590.0)),
-                             "frac_of_nominal_2250": ach / 2250.0, "kernel": "gemm_tcgen05_kernel",
+                             "frac_of_nominal_2250": ach / 2250.0,
+                             "kernel": "gemm_pair_kernel (two CTAs per MMA)" if R.get_option("gemm_pair_clusters") > 0 else "gemm_tcgen05_kernel",
                              "flops_per_launch": flops, "avg_launch_us": ms_per_step * 1e3,
                              "traffic": packed_bytes(sch, k, n) + m * k * 2 + m * n * 2}}
         if not args.no_cpu_baseline and world == 1:
