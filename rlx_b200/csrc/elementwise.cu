@@ -4,6 +4,7 @@
 #include "decode.cuh"
 #include "host/session.hpp"
 #include "kernels.h"
+#include "staged_common.cuh"
 
 namespace rlxq {
 
@@ -30,8 +31,13 @@ int launch_swiglu_mul(cudaStream_t stream, const float* gate, const float* up, f
 // Byte copy between a pinned host staging buffer and device memory (either direction), both 16-byte
 // aligned.  A session in graph mode uses it for activations and outputs of a few KB: a kernel node
 // starts sooner than a copy-engine node, and the bytes cross PCIe as plain loads / posted stores.
+// Launched with programmatic stream serialization: the kernel behind an input copy becomes resident and
+// requests its first weights while the input crosses PCIe, and an output copy is resident, waiting, when
+// the kernel in front of it completes.
 __global__ void __launch_bounds__(256) copy_bytes_kernel(uint8_t* __restrict__ dst, const uint8_t* __restrict__ src,
                                                          uint64_t bytes) {
+    griddep_launch_dependents();
+    griddep_wait();                // every thread: whoever waits for this kernel has then waited for its predecessors
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t n16 = bytes / 16;
     for (uint64_t i = tid; i < n16; i += stride)
@@ -45,7 +51,8 @@ int launch_copy_bytes(cudaStream_t stream, void* dst, const void* src, uint64_t 
     uint64_t blocks = (bytes / 16 + 255) / 256;
     if (blocks == 0) blocks = 1;
     if (blocks > 64) blocks = 64;
-    copy_bytes_kernel<<<(unsigned)blocks, 256, 0, stream>>>((uint8_t*)dst, (const uint8_t*)src, bytes);
+    int rc = launch_pdl(copy_bytes_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (uint8_t*)dst, (const uint8_t*)src, bytes);
+    if (rc) return rc;
     count_launch();
     return check_launch("copy_bytes_kernel");
 }

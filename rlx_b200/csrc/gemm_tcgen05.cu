@@ -550,16 +550,6 @@ __device__ __noinline__ void gemm_reduce_parts(const GemmParams& P, uint32_t til
     }
 }
 
-// A whole warp waiting on one barrier: one lane polls (every try_wait is a serialised operation on the barrier's
-// word, and eight to twelve decode warps share the stage barriers), the warp barrier hands the result and the
-// memory ordering to the others.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t lane) {
-    uint32_t got = 1u;
-    if (lane == 0) got = mbar_wait(bar, parity) ? 1u : 0u;
-    got = __shfl_sync(0xFFFFFFFFu, got, 0);
-    return got != 0u;
-}
-
 struct GemmBars {
     uint64_t b_full[kGemmMaxStages], a_full[kGemmMaxStages], stage_free[kGemmMaxStages];
     uint64_t raw_full[kGemmRawStages], raw_empty[kGemmRawStages];

@@ -118,6 +118,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// A whole warp waiting on one barrier: one lane polls (every try_wait is a serialised operation on the barrier's
+// word, and many warps share a stage barrier), the warp barrier hands the result and the memory ordering to the others.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t lane) {
+    uint32_t got = 1u;
+    if (lane == 0) got = mbar_wait(bar, parity) ? 1u : 0u;
+    __syncwarp();
+    return __shfl_sync(0xFFFFFFFFu, got, 0) != 0u;
+}
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
