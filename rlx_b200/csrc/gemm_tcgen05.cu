@@ -828,10 +828,11 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_tcgen05_kernel(const __
 //   on that CTA's own barrier), its a_full[s] the decode warps of both CTAs, its d_free the epilogue warps of
 //   both; one tcgen05.commit with a CTA mask signals stage_free[s] / d_full in both CTAs.
 // Whole tiles only, n a multiple of 256, no expert groups; everything else runs the single-CTA kernel.
-constexpr uint32_t kPairStages = 4;
+constexpr uint32_t kPairRound = 2;                        // 64-wide k blocks per stage (per round of hand-overs); 4 with two stages measured the same
+constexpr uint32_t kPairStages = 8 / kPairRound;          // 8 x 32 tensor-memory columns of A, 8 x 16 KB of B, whatever the round
 constexpr uint32_t kPairHalf = 128;                       // activation rows a CTA loads
 constexpr uint32_t kPairSubBytes = kPairHalf * kGemmBK * 2;   // one 64-wide swizzled box: 16 KB
-constexpr uint32_t kPairBBytes = 2 * kPairSubBytes;       // a stage: k block of 128 as two boxes
+constexpr uint32_t kPairBBytes = kPairRound * kPairSubBytes;  // a stage: kPairRound boxes
 constexpr uint32_t kPairIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((256u >> 4) << 24);
 
 struct PairBars {
@@ -863,7 +864,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
         for (uint32_t s = 0; s < kPairStages; ++s) {
             mbar_init(smem_u32(&bars->b_full[s]), 2);        // own TMA (with its bytes) + the other CTA's, forwarded
             mbar_init(smem_u32(&bars->b_own[s]), 1);
-            mbar_init(smem_u32(&bars->a_full[s]), 16);       // two 64-wide halves x four decode warps, of each CTA
+            mbar_init(smem_u32(&bars->a_full[s]), 8 * kPairRound);   // per 64-wide block four decode warps, of each CTA
             mbar_init(smem_u32(&bars->stage_free[s]), 1);
         }
         for (uint32_t r = 0; r < kGemmRawStages; ++r) {
@@ -890,7 +891,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
     };
     // the pair's tiles: 256 weight rows (pair index wp) x 256 activation rows (xt), xt fastest
     const uint32_t pt0 = blockIdx.x >> 1, pstep = gridDim.x >> 1, plim = (P.wtiles >> 1) * P.xtiles;
-    const uint32_t rounds = 2 * P.kgroups;               // 128-wide k blocks of a tile
+    const uint32_t rounds = 4 * P.kgroups / kPairRound;  // rounds of a tile
 
     if (warp == 0) {
         // ---------------- this CTA's half of the activation tile ----------------
@@ -904,8 +905,10 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->stage_free[s]), ph)) { give_up(21); ok = false; break; }
                     const uint32_t full = smem_u32(rank == 0 ? &bars->b_full[s] : &bars->b_own[s]);
                     mbar_arrive_expect_tx(full, kPairBBytes);
-                    tma_load_2d(smem_u32(b_stage + s * kPairBBytes), &P.xmap, (int32_t)(kb * 2 * kGemmBK), (int32_t)xrow, full);
-                    tma_load_2d(smem_u32(b_stage + s * kPairBBytes + kPairSubBytes), &P.xmap, (int32_t)(kb * 2 * kGemmBK + kGemmBK), (int32_t)xrow, full);
+#pragma unroll
+                    for (uint32_t q = 0; q < kPairRound; ++q)
+                        tma_load_2d(smem_u32(b_stage + s * kPairBBytes + q * kPairSubBytes), &P.xmap,
+                                    (int32_t)((kb * kPairRound + q) * kGemmBK), (int32_t)xrow, full);
                     if (++s == kPairStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -953,11 +956,11 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
                     if (*abort_flag || !mbar_wait(smem_u32(&bars->b_full[s]), ph) ||
                         !mbar_wait(smem_u32(&bars->a_full[s]), ph)) { give_up(25); ok = false; break; }
                     tc_fence_after();
-                    const uint64_t bdesc0 = kmajor_sw128_desc(smem_u32(b_stage + s * kPairBBytes));
-                    const uint64_t bdesc1 = kmajor_sw128_desc(smem_u32(b_stage + s * kPairBBytes + kPairSubBytes));
 #pragma unroll
-                    for (uint32_t j = 0; j < 2 * kGemmBK / 16; ++j)
-                        tc_mma_ts_pair(tmem_d, tmem_a + 64 * s + 8 * j, (j < 4 ? bdesc0 : bdesc1) + 2 * (j & 3u), kPairIdesc, (kb | j) ? 1u : 0u);
+                    for (uint32_t j = 0; j < kPairRound * kGemmBK / 16; ++j) {
+                        const uint64_t bdesc = kmajor_sw128_desc(smem_u32(b_stage + s * kPairBBytes + (j >> 2) * kPairSubBytes));
+                        tc_mma_ts_pair(tmem_d, tmem_a + 32 * kPairRound * s + 8 * j, bdesc + 2 * (j & 3u), kPairIdesc, (kb | j) ? 1u : 0u);
+                    }
                     tc_commit_pair_both(smem_u32(&bars->stage_free[s]), 3);     // frees the stage in both CTAs
                     if (++s == kPairStages) { s = 0; ph ^= 1u; }
                 }
@@ -980,8 +983,8 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
                 for (uint32_t sub = 0; sub < 4; ++sub) {
                     const uint32_t kbg = kbg0 + sub;
                     if (kbg % kGemmDecodeGroups != grp) continue;
-                    // 64-wide block kbg is half (kbg & 1) of round kbg / 2
-                    const uint32_t s = (kbg >> 1) % kPairStages, fph = (((kbg >> 1) / kPairStages) & 1u) ^ 1u;
+                    // 64-wide block kbg is part kbg % kPairRound of round kbg / kPairRound
+                    const uint32_t rd = kbg / kPairRound, s = rd % kPairStages, fph = ((rd / kPairStages) & 1u) ^ 1u;
                     uint32_t v[32];
                     if (sub == 0) decode64<SCHEME, 0>(rp, g, v);
                     else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
@@ -989,7 +992,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
                     else decode64<SCHEME, 3>(rp, g, v);
                     if (*abort_flag || !mbar_wait_warp(smem_u32(&bars->stage_free[s]), fph, lane)) { give_up(27); ok = false; break; }
                     tc_fence_after();
-                    tmem_st32(tmem_a + lane_addr + 64 * s + 32 * (kbg & 1u), v);
+                    tmem_st32(tmem_a + lane_addr + 32 * (kPairRound * s + kbg % kPairRound), v);
                     tmem_st_wait();
                     tc_fence_before();
                     __syncwarp();
