@@ -842,6 +842,15 @@ struct PairBars {
     uint32_t tmem_base, abort_flag;
 };
 
+// How a decode warp waits.  Where the decoders keep pace with the MMA they spend their time waiting, and one polling
+// lane per warp keeps the barrier word free (every lane polling serialises on it).  Q6_K's decoders are the pacing
+// part and hardly ever find a barrier closed: there the single instruction of an all-lane poll is the cheaper form.
+template <uint32_t SCHEME>
+__device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, uint32_t lane) {
+    if constexpr (SCHEME == RLXQ_Q6_K) return mbar_wait(bar, parity);
+    else return mbar_wait_warp(bar, parity, lane);
+}
+
 template <uint32_t SCHEME>
 __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __grid_constant__ GemmParams P) {
     constexpr uint32_t RAW_ROW = GemmRaw<SCHEME>::ROW;
@@ -977,7 +986,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
         bool ok = true;
         for (uint32_t pt = pt0; ok && pt < plim && !*abort_flag; pt += pstep) {
             for (uint32_t g = 0; g < P.kgroups && ok; ++g, kbg0 += 4) {
-                if (*abort_flag || !mbar_wait_warp(smem_u32(&bars->raw_full[r]), rph, lane)) { give_up(26); ok = false; break; }
+                if (*abort_flag || !pair_wait<SCHEME>(smem_u32(&bars->raw_full[r]), rph, lane)) { give_up(26); ok = false; break; }
                 const uint8_t* rp = raw_stage + r * RAW_STRIDE + row * RAW_ROW;
 #pragma unroll
                 for (uint32_t sub = 0; sub < 4; ++sub) {
@@ -990,7 +999,7 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
                     else if (sub == 1) decode64<SCHEME, 1>(rp, g, v);
                     else if (sub == 2) decode64<SCHEME, 2>(rp, g, v);
                     else decode64<SCHEME, 3>(rp, g, v);
-                    if (*abort_flag || !mbar_wait_warp(smem_u32(&bars->stage_free[s]), fph, lane)) { give_up(27); ok = false; break; }
+                    if (*abort_flag || !pair_wait<SCHEME>(smem_u32(&bars->stage_free[s]), fph, lane)) { give_up(27); ok = false; break; }
                     tc_fence_after();
                     tmem_st32(tmem_a + lane_addr + 32 * (kPairRound * s + kbg % kPairRound), v);
                     tmem_st_wait();
