@@ -55,10 +55,10 @@ enum rlxq_status {
 
 /* Scheme ids.  0..5 keep the values of gguf_scheme_id (rlx-cuda/src/gguf_host.rs:24-34);
  * Q4_0 and Q8_0 have no id there (that function panics on them) and get 6 and 7.  Q4_K, Q6_K,
- * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; Q5_K, Q8_K, Q2_K and Q3_K (the
- * rest of QuantScheme::is_gguf, rlx-ir/src/quant.rs:170-182) decode through the general kernel
- * (Q5_K also through the streaming GEMV for m <= 2 and the tensor-core GEMM for m > 8), so every
- * GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
+ * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; so have Q5_K, Q2_K and Q3_K of the
+ * rest of QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182; Q2_K / Q3_K where k is a multiple of 1024 /
+ * 2048), Q8_K has the streaming GEMV, and every shape these kernels do not take runs through the
+ * general kernel, so every GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
  * are container types the reference only decodes to f32 when a file is loaded (GgufFile::tensor_f32,
  * rlx-gguf/src/lib.rs:323-353, decoders :635-729) and no QuantScheme names; here they dequantise bit-exactly
  * and multiply through the general kernel, so such a tensor can stay packed on the device as well. */
@@ -217,7 +217,7 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  2 = whenever a workspace is given
  *   "gemm_pair": the tcgen05 GEMM with two CTAs per MMA (a cluster of two SMs on 256 weight rows x 256 activation
  *                  rows, each CTA loading half of the activation tile): 0 = automatic (n a multiple of 256, at
- *                  least one tile pair per resident cluster, not Q6_K, no k split chosen), 1 = never, 2 = wherever
+ *                  least one tile pair per resident cluster, not Q6_K or Q3_K, no k split chosen), 1 = never, 2 = wherever
  *                  n is a multiple of 256.  Same bits as the single-CTA kernel.  "gemm_pair_clusters" (read only):
  *                  clusters the device keeps resident, 0 until the paired kernel has run
  *   "gemm_tile_x": 0 = automatic, 128 or 256 = activation rows per tile of the tcgen05 GEMM

@@ -64,8 +64,14 @@ template <> struct GemmRaw<RLXQ_Q5_K> { static constexpr uint32_t ROW = 176, STA
 // The box starts at the 16-byte boundary below it and is 240 bytes wide (15 chunks: conflict-free, and
 // 14 + 210 <= 240); the decoder is compiled for each of the eight possible offsets 2 (g mod 8).
 template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STAGES = 4, GROUPS = 3; };
+// Q2_K super-blocks are 84 bytes (group g starts 4 (g mod 4) bytes past a 16-byte boundary: a 112-byte box covers
+// 12 + 84), Q3_K's 110 bytes (2-byte aligned only, like Q6_K: a 144-byte box covers 14 + 110).
+template <> struct GemmRaw<RLXQ_Q2_K> { static constexpr uint32_t ROW = 112, STAGES = 5, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q3_K> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 3; };
 template <uint32_t SCHEME> __device__ __forceinline__ uint32_t gemm_raw_x(uint32_t g) {   // box start, 8-byte elements
     if (SCHEME == RLXQ_Q6_K) return ((210u * g) & ~15u) / 8u;
+    if (SCHEME == RLXQ_Q2_K) return ((84u * g) & ~15u) / 8u;
+    if (SCHEME == RLXQ_Q3_K) return ((110u * g) & ~15u) / 8u;
     return g * (GemmRaw<SCHEME>::ROW / 8u);
 }
 
@@ -334,6 +340,115 @@ template <int S, int O> struct Decode64Q6 {
     }
 };
 
+// Q2_K as the reference reads it (rlx-gguf/src/lib.rs:857-886): d, dmin (f16) | 16 scale bytes (low nibble scale,
+// high nibble min) | 64 quant bytes.  Weights [64 S, 64 S + 64) are two 2-bit planes (shift 4 (S % 2), + 2) of the
+// 32 quant bytes of half S / 2, sixteen weights per scale byte: w = (d * sc) * q - dmin * mn, product and
+// difference rounded separately.  O = byte offset of the super-block in the row buffer (a multiple of 4).
+template <int S, int O> struct Decode64Q2 {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        constexpr int h = S / 2;
+        Span<O, 4> hd;
+        Span<O + 4 + 8 * h + 4 * (S % 2), 4> sc;
+        Span<O + 20 + 32 * h, 32> qs;
+        hd.load(row); sc.load(row); qs.load(row);
+        const uint32_t hw = hd.template word<O>();
+        const float d = f16_bits_to_f32(hw & 0xFFFFu), dmin = f16_bits_to_f32(hw >> 16);
+        const uint32_t scw = sc.template word<O + 4 + 8 * h + 4 * (S % 2)>();    // scale bytes of (plane, sixteen) = (0,0) (0,1) (1,0) (1,1)
+        const uint64_t off = f32x2_splat(-8388608.0f);
+#pragma unroll
+        for (int pl = 0; pl < 2; ++pl) {
+            const int shift = 4 * (S % 2) + 2 * pl;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t sb = (scw >> (16 * pl + 8 * (i >> 2))) & 0xFFu;
+                const uint64_t dl2 = f32x2_splat(d * (float)(sb & 0xFu)), ml2 = f32x2_splat(-(dmin * (float)(sb >> 4)));
+                const uint32_t q = (word_at(qs, i) >> shift) & 0x03030303u;
+                v[16 * pl + 2 * i] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<0>(q), off)), ml2));
+                v[16 * pl + 2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(dl2, add_f32x2(magic_pair<1>(q), off)), ml2));
+            }
+        }
+    }
+    __device__ static __forceinline__ uint32_t word_at(const Span<O + 20 + 32 * (S / 2), 32>& qs, int i) {
+        constexpr int base = O + 20 + 32 * (S / 2);
+        switch (i) {
+            case 0: return qs.template word<base>();      case 1: return qs.template word<base + 4>();
+            case 2: return qs.template word<base + 8>();  case 3: return qs.template word<base + 12>();
+            case 4: return qs.template word<base + 16>(); case 5: return qs.template word<base + 20>();
+            case 6: return qs.template word<base + 24>(); default: return qs.template word<base + 28>();
+        }
+    }
+};
+template <int S>
+__device__ __forceinline__ void decode64_q2(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
+    switch (g & 3u) {      // 84 g mod 16 = 4 (g mod 4)
+        case 0: Decode64Q2<S, 0>::run(row, v); break;   case 1: Decode64Q2<S, 4>::run(row, v); break;
+        case 2: Decode64Q2<S, 8>::run(row, v); break;   default: Decode64Q2<S, 12>::run(row, v); break;
+    }
+}
+
+// Q3_K as the reference reads it (rlx-gguf/src/lib.rs:889-930): d (f16) | 12 scale bytes (sixteen 6-bit scales) |
+// 32 high-mask bytes | 64 quant bytes.  Weights [64 S, 64 S + 64): planes 2 (S % 2), + 1 of the 32 quant bytes of
+// half S / 2; weight = (d * (scale - 32)) * (q - (mask bit ? 0 : 4)), mask bit 4 (S / 2) + plane of the weight's
+// mask byte.  The four scales of the group are the bytes of word S of the unpacked scale words.
+template <int S, int O> struct Decode64Q3 {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        constexpr int h = S / 2;
+        Span<O, 14> hd;
+        Span<O + 14, 32> hm;
+        Span<O + 46 + 32 * h, 32> qs;
+        hd.load(row); hm.load(row); qs.load(row);
+        const float d = f16_bits_to_f32(hd.template word<O>() & 0xFFFFu);
+        const uint32_t a0 = hd.template word<O + 2>(), a1 = hd.template word<O + 6>(), tmp = hd.template word<O + 10>();
+        uint32_t scw;
+        if (S == 0) scw = (a0 & 0x0F0F0F0Fu) | ((tmp & 0x03030303u) << 4);
+        else if (S == 1) scw = (a1 & 0x0F0F0F0Fu) | (((tmp >> 2) & 0x03030303u) << 4);
+        else if (S == 2) scw = ((a0 >> 4) & 0x0F0F0F0Fu) | (((tmp >> 4) & 0x03030303u) << 4);
+        else scw = ((a1 >> 4) & 0x0F0F0F0Fu) | (((tmp >> 6) & 0x03030303u) << 4);
+        const uint64_t off = f32x2_splat(-(8388608.0f + 4.0f));
+#pragma unroll
+        for (int pl = 0; pl < 2; ++pl) {
+            const int plane = 2 * (S % 2) + pl;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int sb = (int)((scw >> (16 * pl + 8 * (i >> 2))) & 0xFFu) - 32;
+                const uint64_t dl2 = f32x2_splat(d * (float)sb);
+                const uint32_t q = (word_q(qs, i) >> (2 * plane)) & 0x03030303u;
+                const uint32_t hb = (word_h(hm, i) >> (4 * h + plane)) & 0x01010101u;
+                const uint32_t u = q | (hb << 2);                 // q + 4 where the mask bit is set: weight = u - 4
+                v[16 * pl + 2 * i] = scaled_pair<0>(u, off, dl2);
+                v[16 * pl + 2 * i + 1] = scaled_pair<1>(u, off, dl2);
+            }
+        }
+    }
+    __device__ static __forceinline__ uint32_t word_q(const Span<O + 46 + 32 * (S / 2), 32>& qs, int i) {
+        constexpr int base = O + 46 + 32 * (S / 2);
+        switch (i) {
+            case 0: return qs.template word<base>();      case 1: return qs.template word<base + 4>();
+            case 2: return qs.template word<base + 8>();  case 3: return qs.template word<base + 12>();
+            case 4: return qs.template word<base + 16>(); case 5: return qs.template word<base + 20>();
+            case 6: return qs.template word<base + 24>(); default: return qs.template word<base + 28>();
+        }
+    }
+    __device__ static __forceinline__ uint32_t word_h(const Span<O + 14, 32>& hm, int i) {
+        constexpr int base = O + 14;
+        switch (i) {
+            case 0: return hm.template word<base>();      case 1: return hm.template word<base + 4>();
+            case 2: return hm.template word<base + 8>();  case 3: return hm.template word<base + 12>();
+            case 4: return hm.template word<base + 16>(); case 5: return hm.template word<base + 20>();
+            case 6: return hm.template word<base + 24>(); default: return hm.template word<base + 28>();
+        }
+    }
+};
+template <int S>
+__device__ __forceinline__ void decode64_q3(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
+    switch (g & 7u) {      // 110 g mod 16 = (16 - 2 (g mod 8)) mod 16
+        case 0: Decode64Q3<S, 0>::run(row, v); break;   case 1: Decode64Q3<S, 14>::run(row, v); break;
+        case 2: Decode64Q3<S, 12>::run(row, v); break;  case 3: Decode64Q3<S, 10>::run(row, v); break;
+        case 4: Decode64Q3<S, 8>::run(row, v); break;   case 5: Decode64Q3<S, 6>::run(row, v); break;
+        case 6: Decode64Q3<S, 4>::run(row, v); break;   default: Decode64Q3<S, 2>::run(row, v); break;
+    }
+}
+
 // Dispatch on the (warp-uniform) offset of group g inside its row buffer.
 template <int S>
 __device__ __forceinline__ void decode64_q6(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
@@ -348,6 +463,8 @@ __device__ __forceinline__ void decode64_q6(const uint8_t* row, uint32_t g, uint
 template <uint32_t SCHEME, int S>
 __device__ __forceinline__ void decode64(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
     if constexpr (SCHEME == RLXQ_Q6_K) decode64_q6<S>(row, g, v);
+    else if constexpr (SCHEME == RLXQ_Q2_K) decode64_q2<S>(row, g, v);
+    else if constexpr (SCHEME == RLXQ_Q3_K) decode64_q3<S>(row, g, v);
     else Decode64<SCHEME, S>::run(row, v);
 }
 
@@ -844,10 +961,11 @@ struct PairBars {
 
 // How a decode warp waits.  Where the decoders keep pace with the MMA they spend their time waiting, and one polling
 // lane per warp keeps the barrier word free (every lane polling serialises on it).  Q6_K's decoders are the pacing
-// part and hardly ever find a barrier closed: there the single instruction of an all-lane poll is the cheaper form.
+// part (Q3_K's too) and hardly ever find a barrier closed: there the single instruction of an all-lane poll is the
+// cheaper form.
 template <uint32_t SCHEME>
 __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, uint32_t lane) {
-    if constexpr (SCHEME == RLXQ_Q6_K) return mbar_wait(bar, parity);
+    if constexpr (SCHEME == RLXQ_Q6_K || SCHEME == RLXQ_Q3_K) return mbar_wait(bar, parity);
     else return mbar_wait_warp(bar, parity, lane);
 }
 
@@ -1070,8 +1188,10 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
 // ---- host side --------------------------------------------------------------------------------
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
-    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K && scheme != RLXQ_Q5_K) return false;
-    if (scheme == RLXQ_Q6_K && k % 2048) return false;   // rows must stay 16-byte aligned
+    if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K && scheme != RLXQ_Q5_K &&
+        scheme != RLXQ_Q2_K && scheme != RLXQ_Q3_K) return false;
+    if ((scheme == RLXQ_Q6_K || scheme == RLXQ_Q3_K) && k % 2048) return false;   // rows must stay 16-byte aligned
+    if (scheme == RLXQ_Q2_K && k % 1024) return false;
     if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
     return true;
 }
@@ -1161,13 +1281,14 @@ static bool gemm_pair_fits(uint32_t m, uint32_t k, uint32_t n) {
     return n % 256 == 0 && m >= 1 && k % 256 == 0;
 }
 // Chosen by itself where it measured faster: at least one 256 x 256 tile pair per resident cluster, and a format
-// whose decoder keeps pace with two groups of decode warps (Q6_K's three groups lose 12 % in the paired form).
+// whose decoder keeps pace with two groups of decode warps (Q6_K and Q3_K, with three groups, lose 5-12 % in the
+// paired form on large shapes).
 template <uint32_t SCHEME>
 static bool gemm_wants_pair(uint32_t m, uint32_t k, uint32_t n) {
     const int64_t opt = options().gemm_pair.load();
     if (opt == 1 || !gemm_pair_fits(m, k, n)) return false;
     if (opt == 2) return true;
-    if (SCHEME == RLXQ_Q6_K) return false;
+    if (SCHEME == RLXQ_Q6_K || SCHEME == RLXQ_Q3_K) return false;
     return (uint64_t)(n / 256) * ((m + 255) / 256) >= (uint64_t)sm_count() / 2;
 }
 template <uint32_t SCHEME>
@@ -1264,6 +1385,8 @@ int launch_gemm_grouped(cudaStream_t stream, uint32_t scheme, const void* x, uin
         case RLXQ_Q8_0: return launch_gemm_grouped_s<RLXQ_Q8_0>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q4_K: return launch_gemm_grouped_s<RLXQ_Q4_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q5_K: return launch_gemm_grouped_s<RLXQ_Q5_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q2_K: return launch_gemm_grouped_s<RLXQ_Q2_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q3_K: return launch_gemm_grouped_s<RLXQ_Q3_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q6_K: return launch_gemm_grouped_s<RLXQ_Q6_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }
@@ -1276,6 +1399,8 @@ int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const ui
         case RLXQ_Q8_0: return launch_gemm_s<RLXQ_Q8_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q5_K: return launch_gemm_s<RLXQ_Q5_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q2_K: return launch_gemm_s<RLXQ_Q2_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q3_K: return launch_gemm_s<RLXQ_Q3_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
     }
