@@ -55,9 +55,9 @@ enum rlxq_status {
 
 /* Scheme ids.  0..5 keep the values of gguf_scheme_id (rlx-cuda/src/gguf_host.rs:24-34);
  * Q4_0 and Q8_0 have no id there (that function panics on them) and get 6 and 7.  Q4_K, Q6_K,
- * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; so have Q5_K, Q2_K and Q3_K of the
- * rest of QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182; Q2_K / Q3_K where k is a multiple of 1024 /
- * 2048), Q8_K has the streaming GEMV, and every shape these kernels do not take runs through the
+ * Q4_0 and Q8_0 have the streaming GEMV and the tensor-core GEMM; so has the rest of
+ * QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182): Q5_K, and Q2_K, Q8_K / Q3_K where k is a multiple
+ * of 1024 / 2048; every shape these kernels do not take runs through the
  * general kernel, so every GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
  * are container types the reference only decodes to f32 when a file is loaded (GgufFile::tensor_f32,
  * rlx-gguf/src/lib.rs:323-353, decoders :635-729) and no QuantScheme names; here they dequantise bit-exactly

@@ -67,10 +67,14 @@ template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STA
 // Q2_K super-blocks are 84 bytes (group g starts 4 (g mod 4) bytes past a 16-byte boundary: a 112-byte box covers
 // 12 + 84), Q3_K's 110 bytes (2-byte aligned only, like Q6_K: a 144-byte box covers 14 + 110).
 template <> struct GemmRaw<RLXQ_Q2_K> { static constexpr uint32_t ROW = 112, STAGES = 5, GROUPS = 2; };
+// Q8_K: 292 bytes (f32 d, 256 int8, 16 int16 block sums that the decoder does not read); 4 (g mod 4) bytes past a
+// boundary, a 304-byte box (19 chunks) covers 12 + 292.
+template <> struct GemmRaw<RLXQ_Q8_K> { static constexpr uint32_t ROW = 304, STAGES = 4, GROUPS = 2; };
 template <> struct GemmRaw<RLXQ_Q3_K> { static constexpr uint32_t ROW = 144, STAGES = 5, GROUPS = 3; };
 template <uint32_t SCHEME> __device__ __forceinline__ uint32_t gemm_raw_x(uint32_t g) {   // box start, 8-byte elements
     if (SCHEME == RLXQ_Q6_K) return ((210u * g) & ~15u) / 8u;
     if (SCHEME == RLXQ_Q2_K) return ((84u * g) & ~15u) / 8u;
+    if (SCHEME == RLXQ_Q8_K) return ((292u * g) & ~15u) / 8u;
     if (SCHEME == RLXQ_Q3_K) return ((110u * g) & ~15u) / 8u;
     return g * (GemmRaw<SCHEME>::ROW / 8u);
 }
@@ -386,6 +390,29 @@ __device__ __forceinline__ void decode64_q2(const uint8_t* row, uint32_t g, uint
     }
 }
 
+// Q8_K (rlx-gguf/src/lib.rs:848-854, 1121-1140): w = d * q with an f32 d.
+template <int S, int O> struct Decode64Q8K {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        Span<O, 4> hd;
+        Span<O + 4 + 64 * S, 64> qs;
+        hd.load(row); qs.load(row);
+        const uint64_t d2 = f32x2_splat(__uint_as_float(hd.template word<O>())), off = f32x2_splat(-(8388608.0f + 128.0f));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t u = qs.w[(O + 4 + 64 * S) / 4 - 4 * Span<O + 4 + 64 * S, 64>::C0 + i] ^ 0x80808080u;   // int8 -> q + 128
+            v[2 * i] = scaled_pair<0>(u, off, d2);
+            v[2 * i + 1] = scaled_pair<1>(u, off, d2);
+        }
+    }
+};
+template <int S>
+__device__ __forceinline__ void decode64_q8k(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
+    switch (g & 3u) {      // 292 g mod 16 = 4 (g mod 4)
+        case 0: Decode64Q8K<S, 0>::run(row, v); break;   case 1: Decode64Q8K<S, 4>::run(row, v); break;
+        case 2: Decode64Q8K<S, 8>::run(row, v); break;   default: Decode64Q8K<S, 12>::run(row, v); break;
+    }
+}
+
 // Q3_K as the reference reads it (rlx-gguf/src/lib.rs:889-930): d (f16) | 12 scale bytes (sixteen 6-bit scales) |
 // 32 high-mask bytes | 64 quant bytes.  Weights [64 S, 64 S + 64): planes 2 (S % 2), + 1 of the 32 quant bytes of
 // half S / 2; weight = (d * (scale - 32)) * (q - (mask bit ? 0 : 4)), mask bit 4 (S / 2) + plane of the weight's
@@ -464,6 +491,7 @@ template <uint32_t SCHEME, int S>
 __device__ __forceinline__ void decode64(const uint8_t* row, uint32_t g, uint32_t (&v)[32]) {
     if constexpr (SCHEME == RLXQ_Q6_K) decode64_q6<S>(row, g, v);
     else if constexpr (SCHEME == RLXQ_Q2_K) decode64_q2<S>(row, g, v);
+    else if constexpr (SCHEME == RLXQ_Q8_K) decode64_q8k<S>(row, g, v);
     else if constexpr (SCHEME == RLXQ_Q3_K) decode64_q3<S>(row, g, v);
     else Decode64<SCHEME, S>::run(row, v);
 }
@@ -1189,9 +1217,9 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
     if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K && scheme != RLXQ_Q5_K &&
-        scheme != RLXQ_Q2_K && scheme != RLXQ_Q3_K) return false;
+        scheme != RLXQ_Q2_K && scheme != RLXQ_Q3_K && scheme != RLXQ_Q8_K) return false;
     if ((scheme == RLXQ_Q6_K || scheme == RLXQ_Q3_K) && k % 2048) return false;   // rows must stay 16-byte aligned
-    if (scheme == RLXQ_Q2_K && k % 1024) return false;
+    if ((scheme == RLXQ_Q2_K || scheme == RLXQ_Q8_K) && k % 1024) return false;
     if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
     return true;
 }
@@ -1386,6 +1414,7 @@ int launch_gemm_grouped(cudaStream_t stream, uint32_t scheme, const void* x, uin
         case RLXQ_Q4_K: return launch_gemm_grouped_s<RLXQ_Q4_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q5_K: return launch_gemm_grouped_s<RLXQ_Q5_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q2_K: return launch_gemm_grouped_s<RLXQ_Q2_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q8_K: return launch_gemm_grouped_s<RLXQ_Q8_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q3_K: return launch_gemm_grouped_s<RLXQ_Q3_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q6_K: return launch_gemm_grouped_s<RLXQ_Q6_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
@@ -1400,6 +1429,7 @@ int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const ui
         case RLXQ_Q4_K: return launch_gemm_s<RLXQ_Q4_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q5_K: return launch_gemm_s<RLXQ_Q5_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q2_K: return launch_gemm_s<RLXQ_Q2_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q8_K: return launch_gemm_s<RLXQ_Q8_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q3_K: return launch_gemm_s<RLXQ_Q3_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");

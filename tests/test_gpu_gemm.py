@@ -51,7 +51,8 @@ SHAPES = [("q4_0", 256, 256, 128), ("q4_0", 9, 512, 130), ("q8_0", 300, 512, 200
           ("q6_k", 256, 2048, 128), ("q6_k", 300, 4096, 200), ("q6_k", 64, 6144, 131),
           ("q5_k", 256, 512, 128), ("q5_k", 300, 2048, 200), ("q5_k", 70, 4096, 77),
           ("q2_k", 256, 1024, 128), ("q2_k", 300, 3072, 200), ("q2_k", 70, 4096, 77),
-          ("q3_k", 256, 2048, 128), ("q3_k", 300, 4096, 200), ("q3_k", 64, 6144, 131)]
+          ("q3_k", 256, 2048, 128), ("q3_k", 300, 4096, 200), ("q3_k", 64, 6144, 131),
+          ("q8_k", 256, 1024, 128), ("q8_k", 300, 4096, 200), ("q8_k", 70, 3072, 77)]
 
 
 @pytest.mark.parametrize("sch,m,k,n", SHAPES)
@@ -109,7 +110,7 @@ def test_stream_k_split_matches_oracle_and_is_deterministic(sch, m, k, n, y_bf16
 PAIR_SHAPES = [("q8_0", 256, 256, 256, False), ("q4_0", 300, 512, 512, True), ("q4_k", 1000, 2048, 1024, False),
                ("q5_k", 777, 1024, 2560, True), ("q6_k", 512, 2048, 768, False), ("q8_0", 9, 768, 256, False),
                ("q4_k", 2048, 1024, 5120, True), ("q4_0", 129, 4096, 1280, False),
-               ("q2_k", 300, 2048, 512, False), ("q3_k", 520, 2048, 256, True)]
+               ("q2_k", 300, 2048, 512, False), ("q3_k", 520, 2048, 256, True), ("q8_k", 260, 2048, 512, True)]
 
 
 @pytest.mark.parametrize("sch,m,k,n,y_bf16", PAIR_SHAPES)

@@ -6,7 +6,7 @@ They complete QuantScheme::is_gguf (rlx-ir/src/quant.rs:170-182): with them ever
 dequantise-everything kernel).  Dequantisation is bit-exact against the oracle; the matmul goes through the integer-MMA units where the shape allows (Q5_K, Q8_K, Q2_K, Q3_K), else the
 general kernel (f32 accumulation in a different order from the CPU's) and is held to 2e-5 * |x| * |w_row|.
 Q5_K also has the integer streaming GEMV (batch 1-2); Q5_K, Q2_K and Q3_K the tensor-core GEMM (batch > 8, k a multiple of
-256 / 1024 / 2048; f32 activations as two bf16 halves).
+256 / 1024 / 2048, Q8_K 1024; f32 activations as two bf16 halves).
 """
 import json
 import os
@@ -107,7 +107,7 @@ def test_matmul_matches_oracle(sch, m, k, n, x_bf16):
     w, x = make_case(s, m, k, n, seed=2000 + m + n, x_bf16=x_bf16)
     y = _gpu_matmul(s, w, x, n, x_bf16=x_bf16)
     tol = 2e-5
-    gemm_k = {"q5_k": 256, "q2_k": 1024, "q3_k": 2048}.get(sch)
+    gemm_k = {"q5_k": 256, "q2_k": 1024, "q3_k": 2048, "q8_k": 1024}.get(sch)
     if gemm_k and m > 8 and k % gemm_k == 0:    # tensor-core GEMM (f32 activations as two bf16 halves): weights rounded once to bf16
         tol = min(1e-3, (24e-3 if sch in ("q2_k", "q3_k") else 12e-3) / np.sqrt(k))   # few distinct values per sub-block: rounding errors repeat
     assert_within_tolerance(y, reference(s, w, x, n), bound(s, w, x, n), tol=tol, what=f"{sch} {m}x{k}x{n}")
