@@ -61,7 +61,8 @@ enum rlxq_status {
  * general kernel, so every GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
  * are container types the reference only decodes to f32 when a file is loaded (GgufFile::tensor_f32,
  * rlx-gguf/src/lib.rs:323-353, decoders :635-729) and no QuantScheme names; here they dequantise bit-exactly
- * and multiply through the general kernel, so such a tensor can stay packed on the device as well. */
+ * and multiply through the general kernel (m <= 8) and the tensor-core GEMM (m > 8), so such a tensor can
+ * stay packed on the device as well. */
 enum rlxq_scheme {
     RLXQ_Q4_K = 0, RLXQ_Q5_K = 1, RLXQ_Q6_K = 2, RLXQ_Q8_K = 3, RLXQ_Q2_K = 4, RLXQ_Q3_K = 5,
     RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7, RLXQ_Q4_1 = 8, RLXQ_Q5_0 = 9, RLXQ_Q5_1 = 10

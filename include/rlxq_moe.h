@@ -10,7 +10,7 @@
  * counting sort (grouped_moe_sort_plan, gguf_matmul.rs:178-205) runs on the device and one kernel
  * walks every expert's rows, so nothing crosses PCIe and nothing synchronises.  Up to 8 rows (decode)
  * go row by row through the streaming GEMV, the expert picked on the device.  From 32 rows on, for the
- * formats and shapes the tensor-core GEMM takes (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, Q2_K, Q3_K, Q8_K; k a multiple of 256, 1024 for Q2_K and Q8_K, 2048 for Q3_K and
+ * formats and shapes the tensor-core GEMM takes (every format; k a multiple of 256, 1024 for Q2_K and Q8_K, 2048 for Q3_K and
  * Q6_K; 16-byte aligned stack), every expert's rows are gathered next to each other as bf16 (f32 activations
  * as hi + lo halves) and one launch of the GEMM in its grouped form multiplies each 128- or 256-row tile by its
  * expert's slab; the weight operand is bf16(d * q) there, as in rlxq_matmul for m > 8.

@@ -67,6 +67,11 @@ template <> struct GemmRaw<RLXQ_Q6_K> { static constexpr uint32_t ROW = 240, STA
 // Q2_K super-blocks are 84 bytes (group g starts 4 (g mod 4) bytes past a 16-byte boundary: a 112-byte box covers
 // 12 + 84), Q3_K's 110 bytes (2-byte aligned only, like Q6_K: a 144-byte box covers 14 + 110).
 template <> struct GemmRaw<RLXQ_Q2_K> { static constexpr uint32_t ROW = 112, STAGES = 5, GROUPS = 2; };
+// The 32-weight container types: Q4_1 (20-byte blocks: 160 bytes per 256 weights, fetched as 176 so that a row of the
+// box is an odd number of 16-byte chunks), Q5_0 (22: 176), Q5_1 (24: 192, fetched as 208).
+template <> struct GemmRaw<RLXQ_Q4_1> { static constexpr uint32_t ROW = 176, STAGES = 5, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q5_0> { static constexpr uint32_t ROW = 176, STAGES = 4, GROUPS = 2; };
+template <> struct GemmRaw<RLXQ_Q5_1> { static constexpr uint32_t ROW = 208, STAGES = 4, GROUPS = 2; };
 // Q8_K: 292 bytes (f32 d, 256 int8, 16 int16 block sums that the decoder does not read); 4 (g mod 4) bytes past a
 // boundary, a 304-byte box (19 chunks) covers 12 + 292.
 template <> struct GemmRaw<RLXQ_Q8_K> { static constexpr uint32_t ROW = 304, STAGES = 4, GROUPS = 2; };
@@ -75,6 +80,8 @@ template <uint32_t SCHEME> __device__ __forceinline__ uint32_t gemm_raw_x(uint32
     if (SCHEME == RLXQ_Q6_K) return ((210u * g) & ~15u) / 8u;
     if (SCHEME == RLXQ_Q2_K) return ((84u * g) & ~15u) / 8u;
     if (SCHEME == RLXQ_Q8_K) return ((292u * g) & ~15u) / 8u;
+    if (SCHEME == RLXQ_Q4_1) return g * (160u / 8u);
+    if (SCHEME == RLXQ_Q5_1) return g * (192u / 8u);
     if (SCHEME == RLXQ_Q3_K) return ((110u * g) & ~15u) / 8u;
     return g * (GemmRaw<SCHEME>::ROW / 8u);
 }
@@ -389,6 +396,55 @@ __device__ __forceinline__ void decode64_q2(const uint8_t* row, uint32_t g, uint
         case 2: Decode64Q2<S, 8>::run(row, v); break;   default: Decode64Q2<S, 12>::run(row, v); break;
     }
 }
+
+// The 32-bit word at even byte offset `rel` of a word array (offsets are constants once the loops are unrolled).
+__device__ __forceinline__ uint32_t word_of(const uint32_t* w, int rel) {
+    return (rel % 4 == 0) ? w[rel / 4] : __funnelshift_r(w[rel / 4], w[rel / 4 + 1], 16);
+}
+// four bits -> bit 0 of four bytes
+__device__ __forceinline__ uint32_t spread4(uint32_t x) { return ((x & 0xFu) * 0x00204081u) & 0x01010101u; }
+
+// Q4_1 / Q5_0 / Q5_1 (rlx-gguf/src/lib.rs:635-729): blocks of 32 weights, d (f16) [m (f16)] [qh (u32)] 16 nibble
+// bytes; low nibbles are weights 0..15, high nibbles 16..31, bit j (j + 16) of qh the fifth bit of weight j (16 + j).
+// Q4_1, Q5_1: d * q + m (product and sum rounded separately); Q5_0: d * (q - 16).
+template <int S, int BB, bool HAS_M, bool HAS_H> struct Decode64Blk32 {
+    __device__ static __forceinline__ void run(const uint8_t* row, uint32_t (&v)[32]) {
+        constexpr int B0 = 2 * BB * S;
+        Span<B0, 2 * BB> sp;
+        sp.load(row);
+        constexpr int R0 = B0 - 16 * Span<B0, 2 * BB>::C0;
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const int base = R0 + BB * blk;
+            const uint32_t hw = word_of(sp.w, base);
+            const uint64_t d2 = f32x2_splat(f16_bits_to_f32(hw & 0xFFFFu));
+            const uint64_t m2 = HAS_M ? f32x2_splat(f16_bits_to_f32(hw >> 16)) : 0ull;
+            const int oh = HAS_M ? 4 : 2, oq = oh + (HAS_H ? 4 : 0);
+            const uint32_t qh = HAS_H ? word_of(sp.w, base + oh) : 0u;
+            const uint64_t off = f32x2_splat(HAS_M ? -8388608.0f : -(8388608.0f + 16.0f));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t q = word_of(sp.w, base + oq + 4 * i);
+                uint32_t lo = q & 0x0F0F0F0Fu, hi = (q >> 4) & 0x0F0F0F0Fu;
+                if (HAS_H) { lo |= spread4(qh >> (4 * i)) << 4; hi |= spread4(qh >> (16 + 4 * i)) << 4; }
+                if (HAS_M) {
+                    v[16 * blk + 2 * i] = bf16x2_of(add_f32x2(mul_f32x2(d2, add_f32x2(magic_pair<0>(lo), off)), m2));
+                    v[16 * blk + 2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(d2, add_f32x2(magic_pair<1>(lo), off)), m2));
+                    v[16 * blk + 8 + 2 * i] = bf16x2_of(add_f32x2(mul_f32x2(d2, add_f32x2(magic_pair<0>(hi), off)), m2));
+                    v[16 * blk + 8 + 2 * i + 1] = bf16x2_of(add_f32x2(mul_f32x2(d2, add_f32x2(magic_pair<1>(hi), off)), m2));
+                } else {
+                    v[16 * blk + 2 * i] = scaled_pair<0>(lo, off, d2);
+                    v[16 * blk + 2 * i + 1] = scaled_pair<1>(lo, off, d2);
+                    v[16 * blk + 8 + 2 * i] = scaled_pair<0>(hi, off, d2);
+                    v[16 * blk + 8 + 2 * i + 1] = scaled_pair<1>(hi, off, d2);
+                }
+            }
+        }
+    }
+};
+template <int S> struct Decode64<RLXQ_Q4_1, S> : Decode64Blk32<S, 20, true, false> {};
+template <int S> struct Decode64<RLXQ_Q5_0, S> : Decode64Blk32<S, 22, false, true> {};
+template <int S> struct Decode64<RLXQ_Q5_1, S> : Decode64Blk32<S, 24, true, true> {};
 
 // Q8_K (rlx-gguf/src/lib.rs:848-854, 1121-1140): w = d * q with an f32 d.
 template <int S, int O> struct Decode64Q8K {
@@ -1217,7 +1273,8 @@ __global__ void __launch_bounds__(kGemmMaxBlock, 1) gemm_pair_kernel(const __gri
 bool gemm_tc_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, const void* w, const void* x, bool xbf) {
     if (!xbf || m == 0 || n == 0 || k == 0 || k % 256) return false;
     if (scheme != RLXQ_Q4_0 && scheme != RLXQ_Q8_0 && scheme != RLXQ_Q4_K && scheme != RLXQ_Q6_K && scheme != RLXQ_Q5_K &&
-        scheme != RLXQ_Q2_K && scheme != RLXQ_Q3_K && scheme != RLXQ_Q8_K) return false;
+        scheme != RLXQ_Q2_K && scheme != RLXQ_Q3_K && scheme != RLXQ_Q8_K && scheme != RLXQ_Q4_1 && scheme != RLXQ_Q5_0 &&
+        scheme != RLXQ_Q5_1) return false;
     if ((scheme == RLXQ_Q6_K || scheme == RLXQ_Q3_K) && k % 2048) return false;   // rows must stay 16-byte aligned
     if ((scheme == RLXQ_Q2_K || scheme == RLXQ_Q8_K) && k % 1024) return false;
     if (((uintptr_t)w & 15u) || ((uintptr_t)x & 15u)) return false;
@@ -1415,6 +1472,9 @@ int launch_gemm_grouped(cudaStream_t stream, uint32_t scheme, const void* x, uin
         case RLXQ_Q5_K: return launch_gemm_grouped_s<RLXQ_Q5_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q2_K: return launch_gemm_grouped_s<RLXQ_Q2_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q8_K: return launch_gemm_grouped_s<RLXQ_Q8_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q4_1: return launch_gemm_grouped_s<RLXQ_Q4_1>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q5_0: return launch_gemm_grouped_s<RLXQ_Q5_0>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
+        case RLXQ_Q5_1: return launch_gemm_grouped_s<RLXQ_Q5_1>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q3_K: return launch_gemm_grouped_s<RLXQ_Q3_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         case RLXQ_Q6_K: return launch_gemm_grouped_s<RLXQ_Q6_K>(stream, x, x_rows, w, num_slabs, y2, k, n, gt, group_tiles, tile_rows);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");
@@ -1430,6 +1490,9 @@ int launch_gemm_tc(cudaStream_t stream, uint32_t scheme, const void* x, const ui
         case RLXQ_Q5_K: return launch_gemm_s<RLXQ_Q5_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q2_K: return launch_gemm_s<RLXQ_Q2_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q8_K: return launch_gemm_s<RLXQ_Q8_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q4_1: return launch_gemm_s<RLXQ_Q4_1>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q5_0: return launch_gemm_s<RLXQ_Q5_0>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
+        case RLXQ_Q5_1: return launch_gemm_s<RLXQ_Q5_1>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q3_K: return launch_gemm_s<RLXQ_Q3_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         case RLXQ_Q6_K: return launch_gemm_s<RLXQ_Q6_K>(stream, x, w, y, ybf, m, k, n, ws, ws_bytes);
         default: return fail(RLXQ_E_SCHEME, "unknown scheme");

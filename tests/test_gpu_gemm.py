@@ -26,8 +26,9 @@ def _reset_options():
 
 def _tol(k, sch=None):
     # Q2_K / Q3_K: a sub-block of sixteen weights holds at most four / eight distinct values, so the bf16 rounding
-    # errors of its weights repeat instead of averaging out: twice the allowance of the other formats
-    return min(1e-3, (16e-3 if sch in ("q2_k", "q3_k") else 8e-3) / np.sqrt(k))
+    # errors of its weights repeat instead of averaging out: twice the allowance of the other formats.  Likewise
+    # Q4_1 / Q5_1, whose d * q + m keeps every weight of a block at about the same magnitude (one rounding step).
+    return min(1e-3, (16e-3 if sch in ("q2_k", "q3_k", "q4_1", "q5_1") else 8e-3) / np.sqrt(k))
 
 
 def _case(s, m, k, n, seed):
@@ -52,7 +53,9 @@ SHAPES = [("q4_0", 256, 256, 128), ("q4_0", 9, 512, 130), ("q8_0", 300, 512, 200
           ("q5_k", 256, 512, 128), ("q5_k", 300, 2048, 200), ("q5_k", 70, 4096, 77),
           ("q2_k", 256, 1024, 128), ("q2_k", 300, 3072, 200), ("q2_k", 70, 4096, 77),
           ("q3_k", 256, 2048, 128), ("q3_k", 300, 4096, 200), ("q3_k", 64, 6144, 131),
-          ("q8_k", 256, 1024, 128), ("q8_k", 300, 4096, 200), ("q8_k", 70, 3072, 77)]
+          ("q8_k", 256, 1024, 128), ("q8_k", 300, 4096, 200), ("q8_k", 70, 3072, 77),
+          ("q4_1", 256, 256, 128), ("q4_1", 300, 2048, 200), ("q5_0", 256, 512, 128), ("q5_0", 70, 4096, 77),
+          ("q5_1", 256, 256, 128), ("q5_1", 300, 1024, 200)]
 
 
 @pytest.mark.parametrize("sch,m,k,n", SHAPES)
@@ -110,7 +113,8 @@ def test_stream_k_split_matches_oracle_and_is_deterministic(sch, m, k, n, y_bf16
 PAIR_SHAPES = [("q8_0", 256, 256, 256, False), ("q4_0", 300, 512, 512, True), ("q4_k", 1000, 2048, 1024, False),
                ("q5_k", 777, 1024, 2560, True), ("q6_k", 512, 2048, 768, False), ("q8_0", 9, 768, 256, False),
                ("q4_k", 2048, 1024, 5120, True), ("q4_0", 129, 4096, 1280, False),
-               ("q2_k", 300, 2048, 512, False), ("q3_k", 520, 2048, 256, True), ("q8_k", 260, 2048, 512, True)]
+               ("q2_k", 300, 2048, 512, False), ("q3_k", 520, 2048, 256, True), ("q8_k", 260, 2048, 512, True),
+               ("q4_1", 300, 1024, 512, False), ("q5_0", 520, 768, 256, True), ("q5_1", 260, 512, 512, False)]
 
 
 @pytest.mark.parametrize("sch,m,k,n,y_bf16", PAIR_SHAPES)
