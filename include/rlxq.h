@@ -61,8 +61,8 @@ enum rlxq_status {
  * general kernel, so every GGUF scheme the reference lowers runs on the GPU without its host fallback.  Q4_1, Q5_0 and Q5_1 (8, 9, 10)
  * are container types the reference only decodes to f32 when a file is loaded (GgufFile::tensor_f32,
  * rlx-gguf/src/lib.rs:323-353, decoders :635-729) and no QuantScheme names; here they dequantise bit-exactly
- * and multiply through the general kernel (m <= 8) and the tensor-core GEMM (m > 8), so such a tensor can
- * stay packed on the device as well. */
+ * and multiply through the streaming GEMV (m <= 8) and the tensor-core GEMM (m > 8) like the others, so such
+ * a tensor can stay packed on the device as well. */
 enum rlxq_scheme {
     RLXQ_Q4_K = 0, RLXQ_Q5_K = 1, RLXQ_Q6_K = 2, RLXQ_Q8_K = 3, RLXQ_Q2_K = 4, RLXQ_Q3_K = 5,
     RLXQ_Q4_0 = 6, RLXQ_Q8_0 = 7, RLXQ_Q4_1 = 8, RLXQ_Q5_0 = 9, RLXQ_Q5_1 = 10
@@ -202,7 +202,7 @@ RLXQ_API uint64_t rlxq_launch_count(void);
  *                  1 = force the generic warp-per-row kernel, 2 = force the staged tensor-mode
  *                  GEMV, 3 = force the integer GEMV with its dp4a units (m <= 4), 4 = force the tcgen05 GEMV (m <= 8;
  *                  Q4_0, Q8_0, Q4_K; k a multiple of 256), 5 = force the integer GEMV with its integer-MMA units
- *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K with k a multiple of 256, 2048 for Q6_K; Q8_K, Q2_K with k a
+ *                  (m <= 8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, Q4_1, Q5_0, Q5_1 with k a multiple of 256, 2048 for Q6_K; Q8_K, Q2_K with k a
  *                  multiple of 1024, Q3_K of 2048: whole 16-byte groups of super-blocks per row).  2 to 5: error if the shape does not allow it.  The tcgen05 GEMV is
  *                  correct but slower than the others on the shapes measured so far, hence not automatic.
  *   "gemv_tc_ctas": CTAs per SM of the tcgen05 GEMV, 2 (default) or 1

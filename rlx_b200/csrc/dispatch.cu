@@ -83,7 +83,8 @@ int dispatch_matmul(cudaStream_t stream, uint32_t scheme, const void* x, bool xb
             return fail(RLXQ_E_SHAPE, "integer GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
         if (force == 2 && !can_tc)
             return fail(RLXQ_E_SHAPE, "staged GEMV does not support m=%u k=%u n=%u (or 16-byte alignment)", m, k, n);
-        const bool no_dp4a = scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K;   // MMA units only
+        const bool no_dp4a = scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K || scheme == RLXQ_Q4_1 ||
+                             scheme == RLXQ_Q5_0 || scheme == RLXQ_Q5_1;                             // MMA units only
         if (force == 0 && (m >= 2 || no_dp4a) && int_mma_supported(scheme, m, k, n, w, x))
             return launch_gemv_int_mma(stream, scheme, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes);
         if (force == 3 || (force == 0 && can_int && m <= 2))

@@ -565,6 +565,65 @@ template <int MM> struct QUnitMma<RLXQ_Q4_0, MM> {
     __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
 };
 
+// ---- Q4_1 / Q5_0 / Q5_1 (rlx-gguf/src/lib.rs:635-729): blocks of 32 weights, d (f16) [m (f16)] [qh (u32)] and 16
+// nibble bytes laid out as Q4_0's (low nibbles weights 0..15, high nibbles 16..31); bit j (16 + j) of qh is the
+// fifth bit of weight j (16 + j).  Q4_1, Q5_1: w = d q + m, the m term through the activation block sums as Q4_K's
+// min; Q5_0: w = d (q - 16), the offset folded into the integer sum as Q4_0's.  BB = bytes per block.
+__device__ __forceinline__ uint32_t spread4_bits(uint32_t x) { return ((x & 0xFu) * 0x00204081u) & 0x01010101u; }
+template <int MM, int BB, bool HAS_M, bool HAS_H> struct QUnitMmaBlk32 {
+    static_assert(MM == 4 || MM == 8, "groups of four activation rows");
+    static constexpr int NT = 1, NACC = MM, MMG = MM / 4;
+    static constexpr bool HALF_OFFSETS = false;
+    __device__ static __forceinline__ uint32_t first_row(uint32_t lane) { return lane >> 2; }
+    // the 32-bit word at byte offset o (even) behind p
+    __device__ static __forceinline__ uint32_t word(uint32_t p, uint32_t o) {
+        return (o & 2u) ? __funnelshift_r(lds32(p + o - 2), lds32(p + o + 2), 16) : lds32(p + o);
+    }
+    __device__ static __forceinline__ void run(const QLane& L, uint32_t u, uint32_t kb, float (&tot)[MM], uint32_t part) {
+        const uint32_t t = L.lane & 3u;
+        const uint32_t p0 = L.row + u * (8 * BB) + 4 * BB * part, p8 = p0 + 8 * L.row_pitch;
+        const uint32_t fb = L.xh + ((kb >> 5) + 4 * part) * (MMG * 256) + L.lane * 8;
+        const uint32_t sb = L.sb + ((kb >> 5) + 4 * part) * (MMG * 32) + t * 8;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            constexpr int OQ = 2 + (HAS_M ? 2 : 0) + (HAS_H ? 4 : 0);
+            const uint32_t o = BB * b;
+            const uint32_t h0 = word(p0, o), h8 = word(p8, o);                   // d (and m) of rows r and r + 8
+            const float d0 = f16_bits_to_f32(h0 & 0xFFFFu), d8 = f16_bits_to_f32(h8 & 0xFFFFu);
+            const uint32_t q0 = word(p0, o + OQ + 4 * t), q8 = word(p8, o + OQ + 4 * t);
+            uint32_t a0 = q0 & 0x0F0F0F0Fu, a2 = (q0 >> 4) & 0x0F0F0F0Fu;
+            uint32_t a1 = q8 & 0x0F0F0F0Fu, a3 = (q8 >> 4) & 0x0F0F0F0Fu;
+            if (HAS_H) {
+                const uint32_t g0 = word(p0, o + OQ - 4), g8 = word(p8, o + OQ - 4);
+                a0 |= spread4_bits(g0 >> (4 * t)) << 4; a2 |= spread4_bits(g0 >> (16 + 4 * t)) << 4;
+                a1 |= spread4_bits(g8 >> (4 * t)) << 4; a3 |= spread4_bits(g8 >> (16 + 4 * t)) << 4;
+            }
+#pragma unroll
+            for (int gq = 0; gq < MMG; ++gq) {
+                const uint2 bb = lds64(fb + (b * MMG + gq) * 256);
+                const uint2 sc = lds64(sb + (b * MMG + gq) * 32);
+                int c[4];
+                imma_u8s8(c, a0, a1, a2, a3, bb.x, bb.y);
+                const float s = __uint_as_float(sc.x);
+                if (HAS_M) {
+                    const float sxf = __uint_as_float(sc.y);                       // scale * sum(X)
+                    const float m0 = f16_bits_to_f32(h0 >> 16), m8 = f16_bits_to_f32(h8 >> 16);
+                    tot[2 * gq] = fmaf(d0 * s, (float)(c[0] * 128 + c[1]), fmaf(m0, sxf, tot[2 * gq]));
+                    tot[2 * gq + 1] = fmaf(d8 * s, (float)(c[2] * 128 + c[3]), fmaf(m8, sxf, tot[2 * gq + 1]));
+                } else {
+                    const int sx = (int)sc.y;                                      // -16 * sum(X)
+                    tot[2 * gq] = fmaf(d0 * s, (float)(c[0] * 128 + c[1] + sx), tot[2 * gq]);
+                    tot[2 * gq + 1] = fmaf(d8 * s, (float)(c[2] * 128 + c[3] + sx), tot[2 * gq + 1]);
+                }
+            }
+        }
+    }
+    __device__ static __forceinline__ void finalize(float (&tot)[MM], uint32_t lane) { mma_rows_to_lanes<MM>(tot, lane); }
+};
+template <int MM> struct QUnitMma<RLXQ_Q4_1, MM> : QUnitMmaBlk32<MM, 20, true, false> {};
+template <int MM> struct QUnitMma<RLXQ_Q5_0, MM> : QUnitMmaBlk32<MM, 22, false, true> {};
+template <int MM> struct QUnitMma<RLXQ_Q5_1, MM> : QUnitMmaBlk32<MM, 24, true, true> {};
+
 // ---- Q8_0: the quants are the A fragment as they are (s8 x s8).  Blocks are 34 bytes: an even block of
 // the unit starts on a word (d, then the quants from byte 2: two words funnel-shifted per fragment
 // register), an odd one two bytes into a word (quants aligned).
@@ -974,9 +1033,14 @@ template <> struct SumBias<RLXQ_Q6_K> { static constexpr int value = -32; };
 template <> struct SumBias<RLXQ_Q8_K> { static constexpr int value = 0; };
 template <> struct SumBias<RLXQ_Q2_K> { static constexpr int value = 1; };
 template <> struct SumBias<RLXQ_Q3_K> { static constexpr int value = -4; };
+template <> struct SumBias<RLXQ_Q4_1> { static constexpr int value = 1; };
+template <> struct SumBias<RLXQ_Q5_0> { static constexpr int value = -16; };
+template <> struct SumBias<RLXQ_Q5_1> { static constexpr int value = 1; };
 // Whether the fragment-ordered activations carry the block sum as the float s_b * bias * sum(X) (formats
 // with a min term) or as the integer bias * sum(X) (added to the dot product before it is converted).
-constexpr bool frag_sum_is_float(uint32_t scheme) { return scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K; }
+constexpr bool frag_sum_is_float(uint32_t scheme) {
+    return scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q4_1 || scheme == RLXQ_Q5_1;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Kernel 1: activations -> two int8 limbs + per-32 scale + per-SUB integer sums (workspace).
@@ -2051,7 +2115,8 @@ struct IntPlan {
 // Formats that have a integer-MMA unit (QUnitMma).
 constexpr bool int_has_mma(uint32_t scheme) {
     return scheme == RLXQ_Q4_0 || scheme == RLXQ_Q8_0 || scheme == RLXQ_Q4_K || scheme == RLXQ_Q5_K || scheme == RLXQ_Q6_K ||
-           scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K;
+           scheme == RLXQ_Q8_K || scheme == RLXQ_Q2_K || scheme == RLXQ_Q3_K || scheme == RLXQ_Q4_1 || scheme == RLXQ_Q5_0 ||
+           scheme == RLXQ_Q5_1;
 }
 // Formats that have a dp4a unit (QUnit); the others run batch 1 on their integer-MMA unit as well.
 // formats whose down projection also exists as a pushing kernel (tensor-parallel exchange inside the finisher)
@@ -2300,6 +2365,9 @@ bool int_mma_supported(uint32_t scheme, uint32_t m, uint32_t k, uint32_t n, cons
         case RLXQ_Q8_K: return plan_int<RLXQ_Q8_K, true>(m, k, n).ok;
         case RLXQ_Q2_K: return plan_int<RLXQ_Q2_K, true>(m, k, n).ok;
         case RLXQ_Q3_K: return plan_int<RLXQ_Q3_K, true>(m, k, n).ok;
+        case RLXQ_Q4_1: return plan_int<RLXQ_Q4_1, true>(m, k, n).ok;
+        case RLXQ_Q5_0: return plan_int<RLXQ_Q5_0, true>(m, k, n).ok;
+        case RLXQ_Q5_1: return plan_int<RLXQ_Q5_1, true>(m, k, n).ok;
         default: return false;
     }
 }
@@ -2315,6 +2383,9 @@ size_t int_mma_workspace_bytes(uint32_t scheme, uint32_t m, uint32_t k, uint32_t
         case RLXQ_Q8_K: pl = plan_int<RLXQ_Q8_K, true>(m, k, n); break;
         case RLXQ_Q2_K: pl = plan_int<RLXQ_Q2_K, true>(m, k, n); break;
         case RLXQ_Q3_K: pl = plan_int<RLXQ_Q3_K, true>(m, k, n); break;
+        case RLXQ_Q4_1: pl = plan_int<RLXQ_Q4_1, true>(m, k, n); break;
+        case RLXQ_Q5_0: pl = plan_int<RLXQ_Q5_0, true>(m, k, n); break;
+        case RLXQ_Q5_1: pl = plan_int<RLXQ_Q5_1, true>(m, k, n); break;
         default: break;
     }
     return pl.ok ? pl.ws_bytes : 0;
@@ -2332,6 +2403,9 @@ int launch_gemv_int_mma(cudaStream_t stream, uint32_t scheme, const void* x, boo
         case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q4_1: return launch_int_s<RLXQ_Q4_1>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q5_0: return launch_int_s<RLXQ_Q5_0>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
+        case RLXQ_Q5_1: return launch_int_s<RLXQ_Q5_1>(stream, x, xbf, w, y, ybf, m, k, n, ws, ws_bytes, err, false, nullptr, 0, true);
         default: return fail(RLXQ_E_SCHEME, "no integer-MMA GEMV for scheme %u", scheme);
     }
 }
@@ -2383,6 +2457,9 @@ int launch_gemv_int_swiglu(cudaStream_t stream, uint32_t scheme, const float* gu
         case RLXQ_Q8_K: return launch_int_s<RLXQ_Q8_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
         case RLXQ_Q2_K: return launch_int_s<RLXQ_Q2_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
         case RLXQ_Q3_K: return launch_int_s<RLXQ_Q3_K>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        case RLXQ_Q4_1: return launch_int_s<RLXQ_Q4_1>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        case RLXQ_Q5_0: return launch_int_s<RLXQ_Q5_0>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
+        case RLXQ_Q5_1: return launch_int_s<RLXQ_Q5_1>(stream, gu, false, w, y, ybf, m, k, n, ws, ws_bytes, err, true, nullptr, 0, true, tp);
         default: return fail(RLXQ_E_SCHEME, "no integer GEMV for scheme %u", scheme);
     }
 }

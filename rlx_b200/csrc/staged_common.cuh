@@ -45,6 +45,19 @@ template <> struct StagedTraits<RLXQ_Q5_K> {
 
 // Q8_K, Q2_K, Q3_K only run in the integer GEMV with its integer-MMA units, which reads UNIT_B, AG and SUB
 // (rows of 292-, 84- and 110-byte super-blocks are 16-byte aligned every 4, 4 and 8 of them).
+// The 32-weight container types (20-, 22- and 24-byte blocks): integer-MMA units only, like the three below.
+template <> struct StagedTraits<RLXQ_Q4_1> {
+    static constexpr uint32_t UNIT_B = 160, AG = 1, CU = 8, STRIDE = 1296, STAGES = 4, SUB = 32;
+    static constexpr float BIAS = 0.f;
+};
+template <> struct StagedTraits<RLXQ_Q5_0> {
+    static constexpr uint32_t UNIT_B = 176, AG = 1, CU = 8, STRIDE = 1424, STAGES = 4, SUB = 32;
+    static constexpr float BIAS = 0.f;
+};
+template <> struct StagedTraits<RLXQ_Q5_1> {
+    static constexpr uint32_t UNIT_B = 192, AG = 1, CU = 8, STRIDE = 1552, STAGES = 4, SUB = 32;
+    static constexpr float BIAS = 0.f;
+};
 template <> struct StagedTraits<RLXQ_Q8_K> {
     static constexpr uint32_t UNIT_B = 292, AG = 4, CU = 4, STRIDE = 1200, STAGES = 4, SUB = 32;
     static constexpr float BIAS = 0.f;

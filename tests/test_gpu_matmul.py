@@ -398,6 +398,9 @@ IMMA_SHAPES = [("q4_0", 3, 256, 100, False, False), ("q4_0", 4, 4096, 11008, Fal
                ("q2_k", 5, 28672, 300, False, False), ("q2_k", 2, 5120, 777, False, True),
                ("q3_k", 1, 2048, 100, False, False), ("q3_k", 4, 4096, 4096, False, False), ("q3_k", 8, 2048, 1000, True, False),
                ("q3_k", 7, 28672, 300, False, False), ("q3_k", 2, 6144, 777, False, True),
+               ("q4_1", 1, 256, 100, False, False), ("q4_1", 4, 4096, 1000, False, False), ("q4_1", 8, 2048, 300, True, False),
+               ("q5_0", 1, 512, 100, False, False), ("q5_0", 3, 4096, 1000, False, False), ("q5_0", 8, 11008, 256, False, True),
+               ("q5_1", 2, 256, 100, False, False), ("q5_1", 5, 4096, 777, False, False), ("q5_1", 8, 14336, 300, True, False),
                # fragments of all rows do not fit in shared memory: they stream through the ring beside the weights
                ("q4_0", 8, 11008, 4096, False, False), ("q6_k", 8, 8192, 1000, False, False), ("q4_k", 4, 28672, 2048, False, False),
                ("q8_0", 8, 14336, 777, True, True), ("q4_k", 7, 28672, 520, True, False)]
@@ -454,8 +457,8 @@ def test_integer_mma_gemv_refuses_what_it_cannot_run():
     import torch
     R.set_option("gemv_kernel", 5)
     try:
-        s = O.Q4_1                                               # no MMA unit for this format
-        w, x = make_case(s, 4, 2048, 16, seed=3)
+        s = O.Q2_K                                               # rows of 84-byte super-blocks: k a multiple of 1024
+        w, x = make_case(s, 4, 768, 16, seed=3)
         with pytest.raises(R.RlxqError) as e:
             R.matmul(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), s, 16)
         assert e.value.status == -2
@@ -532,11 +535,11 @@ def test_matmul_chain_rejects_layers_that_do_not_fit_together():
 
 
 # ------------------------------------------------------------------ seeded random shapes through the automatic dispatch
-def _random_gemv_cases(count=96, seed=20240611):
+def _random_gemv_cases(count=110, seed=20240611):
     rng = np.random.default_rng(seed)
     cases = []
     while len(cases) < count:
-        sch = ["q4_0", "q8_0", "q4_k", "q5_k", "q6_k", "q8_k", "q2_k", "q3_k"][int(rng.integers(0, 8))]
+        sch = ["q4_0", "q8_0", "q4_k", "q5_k", "q6_k", "q8_k", "q2_k", "q3_k", "q4_1", "q5_0", "q5_1"][int(rng.integers(0, 11))]
         unit = {"q6_k": 2048, "q3_k": 2048, "q8_k": 1024, "q2_k": 1024}.get(sch, 256)
         k = unit * int(rng.integers(1, 32768 // unit + 1))
         m = int(rng.integers(1, 9))
