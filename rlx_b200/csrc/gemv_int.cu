@@ -7,8 +7,9 @@
 // conversion and one FMA per 32-weight block apply d_block * s_block (f32 from there on).
 // Two kinds of unit do the multiplying:
 //  * dp4a units (batch 1-2, on request 3-4): one dp4a per four weights, limb and activation row;
-//  * integer-MMA units (batch 2-8; Q4_0, Q8_0, Q4_K, Q5_K, Q6_K): one m16n8k32 MMA per 32-weight block of all
-//    16 tile rows against four activation rows x two limbs (m16n8k16 per 16-weight sub-block for Q6_K).  mma.sync with 8-bit integers runs at
+//  * integer-MMA units (batch 2-8 for Q4_0, Q8_0, Q4_K, Q5_K, Q6_K; batch 1-8 for Q8_K, Q2_K, Q3_K, Q4_1, Q5_0,
+//    Q5_1, which have no dp4a unit): one m16n8k32 MMA per 32-weight block of all 16 tile rows against four
+//    activation rows x two limbs (m16n8k16 per 16-weight sub-block for Q6_K, Q2_K, Q3_K).  mma.sync with 8-bit integers runs at
 //    one m16n8k32 per 8 cycles per sub-core here, far more than the stream needs; what the units
 //    save is instruction issue, which is what bounds the dp4a units from batch 3 on.
 //
