@@ -1289,7 +1289,7 @@ static __device__ __noinline__ void tp_wait_and_sum(const TpPush& tp, unsigned l
         if (!ok) atomicExch(err, 40 + (int)lane);
     }
     if (!__all_sync(0xFFFFFFFFu, ok)) return;
-    const float* slots = reinterpret_cast<const float*>(tp.buf[tp.rank] + kCommHeader) + tp_parity;
+    const float* slots = reinterpret_cast<const float*>(tp.buf[tp.rank] + comm_push_offset(tp.max_elems)) + tp_parity;
     for (uint32_t c0 = e0; c0 < e1; c0 += 256u) {
         float part[8][kCommMaxWorld];
 #pragma unroll
@@ -1566,7 +1566,7 @@ __global__ void __launch_bounds__(int_threads(MMA), (MMA || MM > 2) ? 1 : 2) gem
 #pragma unroll
                             for (uint32_t pr = 0; pr < kCommMaxWorld; ++pr)
                                 if (pr < P.tp.world)
-                                    asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(P.tp.buf[pr] + kCommHeader) + tp_slot + o),
+                                    asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(P.tp.buf[pr] + comm_push_offset(P.tp.max_elems)) + tp_slot + o),
                                                  "f"(v[cp]) : "memory");
                         } else if (P.y_bf16) reinterpret_cast<uint16_t*>(P.y)[o] = (uint16_t)f32_to_bf16_bits(v[cp]);
                         else reinterpret_cast<float*>(P.y)[o] = v[cp];

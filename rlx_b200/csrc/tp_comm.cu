@@ -3,23 +3,27 @@
 // The decode step of the tensor-parallel FFN ends with a sum of world partial rows [m, d_model] (32 KiB
 // at m = 1).  For that size a library all-reduce is all latency (10-20 us).  Here every rank writes its
 // partial straight into every peer's buffer (posted stores over NVLink: nobody waits for a read to come
-// back), raises a flag in every peer's header behind them, waits for the peers' flags in its own header,
-// and then adds the world partials that now sit in its own memory, in rank order -- the order of the
-// reference's host collective (rlx-driver/src/collective.rs:107-127: put, barrier, fold from the identity),
-// so the result is the same on every rank and from run to run.  Plain peer stores; no multimem, no TMA.
-// (The first version pulled: publish locally, flag, then read every peer's partial.  Its sum loop over the
-// ranks was not unrolled, so each thread paid one NVLink round trip per peer, one after the other: 33 us
-// of a 53 us step on eight GPUs.)
+// back) as 8-byte words {value, step tag}: a word is stored and loaded whole, so a reader that finds the tag
+// of the current step in a word has the value that belongs to it.  No flag follows the data and no fence
+// orders the two: a rank polls the words in its own memory (bounded) and adds the world partials in rank order
+// -- the order of the reference's host collective (rlx-driver/src/collective.rs:107-127: put, barrier, fold
+// from the identity), so the result is the same on every rank and from run to run.  Plain peer stores; no
+// multimem, no TMA.
+// (Earlier forms, per step on eight GPUs: pulling the peers' partials with a sum loop that was not unrolled,
+// 33 us of a 53 us step; pushing floats and raising a flag behind them with st.release.sys, whose fence waits
+// for every posted store to be acknowledged, 8.4 us of 27.8.)
 //
-// The vector is cut into kCommParts parts, one CTA each, every part with its own epoch and flags, so the
-// parts never wait for one another: eight SMs push and add instead of one.
+// The vector is cut into kCommParts parts, one CTA each, every part with its own step counter, so the parts
+// never wait for one another: eight SMs push and add instead of one.
 //
-// Buffer of a rank: [header 1 KiB: epoch[part], flags[part][8]] [parity 0: world slots] [parity 1: world
-// slots], a slot max_elems floats.  The epochs live on the device and are advanced by the kernel, so a
-// captured launch works on every replay; the two parities alternate with them, which is what lets a fast
+// Buffer of a rank: [header 1 KiB: step counter per part, the words of the pushing down projection]
+// [parity 0: a slot of max_elems tagged words per possible rank] [parity 1: the same] [the float slots of the
+// pushing down projection, two parities].  The step counters live on the device and are advanced by the kernel,
+// so a captured launch works on every replay; the two parities alternate with them, which is what lets a fast
 // rank push the next step while a slow one still adds the previous one (a rank cannot be two steps ahead:
-// finishing a step takes every peer's flag of that step).  Every wait is bounded: a rank whose peer never
-// arrives records an error word and returns without touching (that part of) dst.
+// finishing a step takes every peer's words of that step, which a peer sends only after it finished the step
+// before).  Every wait is bounded: a rank whose peer never arrives records an error word and returns without
+// touching (that part of) dst.
 #include "common.cuh"
 #include "rlxq_tp.h"
 #include "staged_common.cuh"
@@ -38,21 +42,14 @@ struct CommParams {
     uint32_t spin_limit;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+// a tagged word: stored and loaded as one 8-byte access
+__device__ __forceinline__ void st_word_sys(void* p, float v, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float4 ld_sys_f4(const float4* p) {        // no caching: another GPU wrote it
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_sys_f4(float4* p, float4 v) {
-    asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+__device__ __forceinline__ uint2 ld_word_sys(const void* p) {        // no caching: another GPU wrote it
+    uint2 w;
+    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(p) : "memory");
+    return w;
 }
 
 __global__ void __launch_bounds__(512) tp_allreduce_kernel(const CommParams P) {
@@ -62,7 +59,6 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const CommParams P) {
     griddep_wait();                  // src comes from the kernel in front
     const uint32_t part = blockIdx.x;
     unsigned long long* hdr = reinterpret_cast<unsigned long long*>(P.buf[P.rank]);
-    unsigned long long* my_flags = hdr + kCommParts + part * kCommMaxWorld;           // written by the peers
     if (threadIdx.x == 0) {
         s_epoch = hdr[part] + 1ull;
         hdr[part] = s_epoch;
@@ -70,43 +66,52 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const CommParams P) {
     }
     __syncthreads();
     const unsigned long long epoch = s_epoch;
-    const size_t parity = (size_t)(epoch & 1ull) * kCommMaxWorld * P.max_elems;      // floats
-    // this CTA's share of the float4s
-    const uint32_t n4 = P.elems / 4, per = (n4 + kCommParts - 1) / kCommParts;
-    const uint32_t i0 = min(n4, part * per), i1 = min(n4, i0 + per);
-    // 1. this rank's partial into its slot of every rank's buffer (its own included)
+    const uint32_t tag = (uint32_t)(epoch & 0x7FFFFFFFull) | 0x80000000u;        // never the zero of a fresh buffer
+    const size_t parity = (size_t)(epoch & 1ull) * kCommMaxWorld * P.max_elems;   // words
+    // this CTA's share of the elements
+    const uint32_t per = (P.elems + kCommParts - 1) / kCommParts;
+    const uint32_t i0 = min(P.elems, part * per), i1 = min(P.elems, i0 + per);
+    // 1. this rank's partial, tagged, into its slot of every peer's buffer
     for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-        const float4 v = reinterpret_cast<const float4*>(P.src)[i];
+        const float v = P.src[i];
 #pragma unroll
         for (uint32_t r = 0; r < kCommMaxWorld; ++r)
-            if (r < P.world)
-                st_sys_f4(reinterpret_cast<float4*>(P.buf[r] + kCommHeader) + (parity + (size_t)P.rank * P.max_elems) / 4 + i, v);
+            if (r < P.world && r != P.rank)
+                st_word_sys(reinterpret_cast<uint2*>(P.buf[r] + kCommHeader) + parity + (size_t)P.rank * P.max_elems + i, v, tag);
     }
-    __syncthreads();                 // the release stores below, after this barrier, cover every thread's writes
-    // 2. tell every peer, 3. wait for every peer (one thread per peer)
-    if (threadIdx.x < P.world && threadIdx.x != P.rank) {
-        const uint32_t p = threadIdx.x;
-        st_release_sys(reinterpret_cast<unsigned long long*>(P.buf[p]) + kCommParts + part * kCommMaxWorld + P.rank, epoch);
-        bool ok = false;
+    // 2. wait, bounded, until every peer's word of every element of this thread carries the tag: the words of all
+    //    peers are loaded together (one trip through the memory system per attempt, not one per peer)
+    const uint2* mine = reinterpret_cast<const uint2*>(P.buf[P.rank] + kCommHeader) + parity;
+    bool ok = true;
+    for (uint32_t i = i0 + threadIdx.x; i < i1 && ok; i += blockDim.x) {
+        uint32_t late = 0;
         for (uint32_t it = 0; it < P.spin_limit; ++it) {
-            if (ld_acquire_sys(my_flags + p) >= epoch) { ok = true; break; }
+            uint32_t t[kCommMaxWorld];
+#pragma unroll
+            for (uint32_t r = 0; r < kCommMaxWorld; ++r)
+                t[r] = (r < P.world && r != P.rank) ? ld_word_sys(mine + (size_t)r * P.max_elems + i).y : tag;
+            late = 0;
+#pragma unroll
+            for (uint32_t r = 0; r < kCommMaxWorld; ++r)
+                if (t[r] != tag) late |= 1u << r;
+            if (late == 0) break;
         }
-        if (!ok) { s_fail = 1; atomicExch(P.err, 40 + (int)p); }
+        if (late) { ok = false; s_fail = 1; atomicExch(P.err, 40 + (int)(__ffs(late) - 1)); }
     }
     __syncthreads();
     if (s_fail) return;
-    // 4. sum in rank order, out of this rank's own memory; all loads of an element are issued before the first add
-    const float4* mine = reinterpret_cast<const float4*>(P.buf[P.rank] + kCommHeader) + parity / 4;
+    // 3. sum in rank order (this rank's own partial straight from src); all loads of an element are issued
+    //    before the first add
     for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-        float4 v[kCommMaxWorld];
+        float v[kCommMaxWorld];
 #pragma unroll
         for (uint32_t r = 0; r < kCommMaxWorld; ++r)
-            if (r < P.world) v[r] = ld_sys_f4(mine + (size_t)r * (P.max_elems / 4) + i);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < P.world) v[r] = (r == P.rank) ? P.src[i] : __uint_as_float(ld_word_sys(mine + (size_t)r * P.max_elems + i).x);
+        float acc = 0.f;
 #pragma unroll
         for (uint32_t r = 0; r < kCommMaxWorld; ++r)
-            if (r < P.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
-        reinterpret_cast<float4*>(P.dst)[i] = acc;
+            if (r < P.world) acc += v[r];
+        P.dst[i] = acc;
     }
 }
 
@@ -117,7 +122,8 @@ using namespace rlxq;
 extern "C" int rlxq_tp_comm_bytes(uint32_t max_elems, size_t* bytes) {
     if (!bytes) return fail(RLXQ_E_NULL, "bytes is null");
     if (max_elems == 0 || max_elems % 4) return fail(RLXQ_E_SHAPE, "max_elems=%u must be a positive multiple of 4", max_elems);
-    *bytes = kCommHeader + 2 * (size_t)kCommMaxWorld * max_elems * 4;      // two parities of one slot per possible rank
+    // two parities of one slot of tagged words per possible rank, then the float slots of the pushing down projection
+    *bytes = comm_push_offset(max_elems) + 2 * (size_t)kCommMaxWorld * max_elems * 4;
     return RLXQ_OK;
 }
 

@@ -245,11 +245,10 @@ def test_peer_memory_all_reduce_two_gpus(tmp_path):
 # ------------------------------------------------------------------ a bounded wait that runs out (one GPU)
 @pytest.mark.gpu
 def test_peer_all_reduce_wait_runs_out_and_the_context_stays_usable():
-    """rlxq_tp_allreduce_sum with world = 2 where the "peer" is a second buffer on the same GPU whose flag nobody
-    raises: with a short poll limit the kernel gives up, leaves dst alone and records 40 + peer rank;
-    rlxq_device_status turns that into RLXQ_E_TIMEOUT, and the next call (the peer's flag and data now written
-    by the host, as a live peer would) completes normally.  Nothing faults and nothing hangs: the wait is a
-    counted loop of plain loads."""
+    """rlxq_tp_allreduce_sum with world = 2 where the "peer" is a second buffer on the same GPU that nobody writes:
+    with a short poll limit the kernel gives up, leaves dst alone and records 40 + peer rank; rlxq_device_status turns
+    that into RLXQ_E_TIMEOUT, and the next call (the peer's tagged words now written by the host, as a live peer would
+    push them) completes normally.  Nothing faults and nothing hangs: the wait is a counted loop of plain loads."""
     import ctypes as C
     import torch
     from rlx_b200._lib import lib
@@ -273,14 +272,14 @@ def test_peer_all_reduce_wait_runs_out_and_the_context_stays_usable():
         assert st == -8 and code.value == 41, (st, code.value)  # RLXQ_E_TIMEOUT, waiting for rank 1
         assert torch.all(dst == 7.0)                             # the sum never ran
         assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0   # reported once, then clear
-        # now play the peer from the host, as a live peer would push: its partial into rank 1's slot of rank 0's
-        # buffer (both parities: [header][parity][rank slot of n floats, 8 of them]), its flags far ahead of any epoch
+        # now play the peer from the host, as a live peer would push: rank 1's partial as 8-byte words {value, step tag}
+        # into rank 1's slot of rank 0's buffer ([header][parity][rank slot of n words, 8 of them]).  The call above
+        # was step 1 of every part, the next is step 2: parity 0, tag 0x80000002.
         peer = O.fill_normal(2, n)
-        hdr, parts = 1024, 8            # header: epoch[parts], flags[parts][8]
-        for parity in (0, 1):
-            copy_to_device(bufs[0] + hdr + (parity * 8 + 1) * n * 4, peer)
-        for part in range(parts):
-            copy_to_device(bufs[0] + 8 * (parts + part * 8 + 1), np.array([1 << 40], np.int64))
+        words = np.empty((n, 2), np.uint32)
+        words[:, 0] = peer.view(np.uint32)
+        words[:, 1] = 0x80000002
+        copy_to_device(bufs[0] + 1024 + (0 * 8 + 1) * n * 8, words.ravel())
         assert lib.rlxq_tp_allreduce_sum(stream, 0, 2, arr, n, src.data_ptr(), dst.data_ptr(), n) == 0
         assert lib.rlxq_device_status(C.byref(code)) == 0 and code.value == 0
         want = O.allreduce_sum(np.stack([src.cpu().numpy(), peer]))
