@@ -67,9 +67,11 @@ RLXQ_API int rlxq_tp_ffn_partial(rlxq_stream_t stream, uint32_t scheme_gate_up, 
  * every rank allocates a buffer with rlxq_tp_comm_alloc, exports its handle, the ranks exchange the
  * handles through whatever channel they share (torch.distributed, MPI, a file) and open each other's
  * with rlxq_tp_ipc_open.  Per step: rlxq_tp_allreduce_sum on every rank.  world <= 8.
- * A buffer holds a 1 KiB header and, twice, one slot of max_elems floats per possible rank (64 * max_elems
- * + 1024 bytes): every rank stores its partial into its slot of every peer's buffer, raises flags there, and
- * adds the slots of its own buffer once all flags are in (eight CTAs, an eighth of the vector each). */
+ * A buffer holds a 1 KiB header, twice one slot of max_elems 8-byte words {value, step tag} per possible rank,
+ * and twice one slot of max_elems floats per possible rank for rlxq_tp_ffn_step's pushing form (192 * max_elems
+ * + 1024 bytes; rlxq_tp_comm_bytes says): every rank stores its partial, tagged with the step, into its slot of
+ * every peer's buffer and adds the slots of its own buffer once every word carries the tag of the step (eight
+ * CTAs, an eighth of the vector each; no flag and no fence between data and flag: a word arrives whole). */
 RLXQ_API int rlxq_tp_comm_bytes(uint32_t max_elems, size_t* bytes);
 RLXQ_API int rlxq_tp_comm_alloc(uint32_t max_elems, void** buf);       /* cudaMalloc + zero; not capture-safe */
 RLXQ_API int rlxq_tp_comm_free(void* buf);
